@@ -1,0 +1,155 @@
+"""The C oracle must reproduce, bit for bit, the fixtures written by the independent
+numpy restatement in tests/golden/make_golden.py, and the literal expectations the
+reference's own tests hold."""
+import glob
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+
+DT = {"f32": oracle.F32, "f16": oracle.F16, "bf16": oracle.BF16}
+
+
+def _load(path):
+    return dict(np.load(path))
+
+
+def _bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+QX = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "test_q*.npz")) +
+            glob.glob(os.path.join(os.path.dirname(__file__), "golden", "family_qmv_*.npz")))
+
+
+@pytest.mark.parametrize("path", QX, ids=[os.path.basename(p)[:-4] for p in QX])
+def test_qmm_oracle_matches_fixture(path):
+    fx = _load(path)
+    dt = DT[os.path.basename(path)[:-4].rsplit("_", 1)[1]]
+    m, n, k, bits, gs = (int(v) for v in fx["meta"])
+    # bit-exact integer codes
+    assert np.array_equal(oracle.unpack_matrix(fx["w"], k, bits), fx["codes"])
+    assert np.array_equal(oracle.pack_matrix(fx["codes"], bits), fx["w"].reshape(n, -1))
+    s = oracle.round_through(fx["scales"], dt)
+    b = oracle.round_through(fx["biases"], dt)
+    x = oracle.round_through(fx["x"], dt)
+    acc = oracle.qmm(fx["w"], s, b, x, m, n, k, bits, gs)
+    assert np.array_equal(_bits(acc), _bits(fx["acc"]))
+    assert np.array_equal(_bits(oracle.round_through(acc, dt)), _bits(fx["expected"]))
+    # M = 1 of qmm is qmv (tests/qmm_gpu_correctness.rs:341-393): row 0 alone gives the same numbers
+    acc0 = oracle.qmm(fx["w"], s, b, x[:1], 1, n, k, bits, gs)
+    assert np.array_equal(_bits(acc0[0]), _bits(acc[0]))
+    # a row slice equals the same rows of the full result
+    part = oracle.qmm(fx["w"], s, b, x, m, n, k, bits, gs, rows=(n // 4, n // 2))
+    assert np.array_equal(_bits(part[:, n // 4:n // 2]), _bits(acc[:, n // 4:n // 2]))
+    # dequant view agrees with code*scale+bias
+    deq = oracle.dequant(fx["w"], s, b, n, k, bits, gs)
+    ref = fx["codes"].astype(np.float32) * np.repeat(s.reshape(n, -1), gs, axis=1) \
+        + np.repeat(b.reshape(n, -1), gs, axis=1)
+    assert np.array_equal(_bits(deq), _bits(ref.astype(np.float32)))
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+def test_gather_oracle_matches_fixture(golden_dir, dt):
+    fx = _load(os.path.join(golden_dir, f"test_moe_gather_qmm_int4_{dt}.npz"))
+    t_rows, k_in, m_out, ne, bits, gs = (int(v) for v in fx["meta"])
+    s = oracle.round_through(fx["scales"], DT[dt])
+    b = oracle.round_through(fx["biases"], DT[dt])
+    x = oracle.round_through(fx["x"], DT[dt])
+    acc = oracle.gather_qmm(x, fx["w"], s, b, t_rows, k_in, m_out, ne, bits, gs,
+                            expert_offsets=fx["expert_offsets"])
+    assert np.array_equal(_bits(acc), _bits(fx["acc"]))
+    # per-row index form gives the same result as the CSR form
+    idx = np.array([0, 0, 1, 1, 1, 2], dtype=np.uint32)
+    acc2 = oracle.gather_qmm(x, fx["w"], s, b, t_rows, k_in, m_out, ne, bits, gs, indices=idx)
+    assert np.array_equal(_bits(acc2), _bits(acc))
+
+
+@pytest.fixture(scope="module")
+def moe(golden_dir):
+    return _load(os.path.join(golden_dir, "moe_and_layout.npz"))
+
+
+def test_router_topk_fixtures(moe):
+    idx, w = oracle.router_topk(moe["topk_base_logits"], 64, 4)
+    assert np.array_equal(idx, moe["topk_base_idx"])
+    np.testing.assert_allclose(w, moe["topk_base_w"], rtol=0, atol=1e-6)
+    idx, w = oracle.router_topk(moe["topk_k1_logits"], 32, 1)
+    assert np.array_equal(idx, moe["topk_k1_idx"])
+    assert np.all(np.abs(w - 1.0) < 1e-6)            # moe_gpu_correctness.rs:297-300
+    idx, _ = oracle.router_topk(moe["topk_tie_logits"], 8, 2)
+    assert idx.tolist() == [[2, 5]]                  # moe_gpu_correctness.rs:334
+    idx, w = oracle.router_topk(moe["topk_next_logits"], 32, 4, norm_topk_prob=0)
+    assert np.array_equal(idx, moe["topk_next_idx"])
+    np.testing.assert_allclose(w, moe["topk_next_w"], rtol=0, atol=1e-6)
+    assert np.all(w.sum(axis=1) < 1.0)
+
+
+def test_router_topk_nan_inf_invariants(moe):
+    """moe_gpu_correctness.rs:524-597."""
+    idx, _ = oracle.router_topk(moe["topk_naninf_logits"], 16, 4)
+    assert np.array_equal(idx, moe["topk_naninf_idx"])
+    for r in range(4):
+        assert len(set(idx[r].tolist())) == 4
+    assert idx[1, 0] == 7 and idx[3, 0] == 11
+    assert 3 not in idx[2] and 5 not in idx[0] and 2 not in idx[3]
+
+
+def test_unpermute_and_swiglu_fixtures(moe):
+    out = oracle.moe_unpermute(moe["unperm_eo"], moe["unperm_inv"], moe["unperm_w"])
+    assert np.array_equal(_bits(out), _bits(moe["unperm_out"]))
+    sw = oracle.swiglu(moe["swiglu_gate"], moe["swiglu_up"])
+    np.testing.assert_allclose(sw, moe["swiglu_out"], rtol=2e-7, atol=1e-7)  # expf vs numpy exp: 1 ulp
+
+
+def test_worked_bit_layouts(moe):
+    assert np.array_equal(oracle.pack_matrix(moe["layout_b3_codes"], 3), moe["layout_b3_words"])
+    assert np.array_equal(oracle.pack_matrix(moe["layout_b6_codes"], 6), moe["layout_b6_words"])
+    w4 = oracle.pack_matrix(moe["layout_b4_codes"], 4)
+    assert w4.tolist() == [[0x87654321]]             # low nibble first along K
+    # 3-bit period: code 10 straddles words 0/1, code 21 straddles words 1/2
+    c = np.zeros((1, 32), dtype=np.uint32)
+    c[0, 10] = 0b101
+    w = oracle.pack_matrix(c, 3)
+    assert w[0, 0] == (0b01 << 30) and w[0, 1] == 0b1 and w[0, 2] == 0
+    c = np.zeros((1, 32), dtype=np.uint32)
+    c[0, 21] = 0b110
+    w = oracle.pack_matrix(c, 3)
+    assert w[0, 1] == (0b0 << 31) and w[0, 2] == 0b11
+    c[0, 21] = 0b111
+    w = oracle.pack_matrix(c, 3)
+    assert w[0, 1] == (1 << 31) and w[0, 2] == 0b11
+
+
+def test_moe_sort_definition():
+    rng = np.random.default_rng(0)
+    n_tokens, k, ne = 37, 4, 9
+    topk = np.stack([rng.permutation(ne)[:k] for _ in range(n_tokens)]).astype(np.uint32)
+    sti, inv, off, rex = oracle.moe_sort(topk, ne)
+    flat = topk.reshape(-1)
+    order = np.lexsort((np.arange(flat.size), flat))      # stable by (expert, flat slot)
+    assert np.array_equal(sti, (order // k).astype(np.uint32))
+    assert np.array_equal(rex, flat[order])
+    assert np.array_equal(inv.reshape(-1)[order], np.arange(flat.size))
+    assert np.array_equal(off, np.concatenate([[0], np.cumsum(np.bincount(flat, minlength=ne))]))
+    # permute is a bit-exact row copy (moe_gpu_correctness.rs:627-672)
+    tok = rng.standard_normal((n_tokens, 16)).astype(np.float32)
+    assert np.array_equal(oracle.moe_permute(tok, sti), tok[sti])
+
+
+def test_rounding_matches_torch():
+    import torch
+    rng = np.random.default_rng(1)
+    a = np.concatenate([rng.standard_normal(20000).astype(np.float32) * s for s in (1e-8, 1e-4, 1, 300, 7e4)])
+    a = np.concatenate([a, np.array([0.0, -0.0, 65504.0, 65520.0, 65519.9, 6.1e-5, 5.96e-8, 2.98e-8,
+                                     2.9802325e-08, 1.0000001, 3.3895314e38], dtype=np.float32)])
+    t = torch.from_numpy(a)
+    for dt, tdt in ((oracle.BF16, torch.bfloat16), (oracle.F16, torch.float16)):
+        ref = t.to(tdt).to(torch.float32).numpy()
+        got = oracle.round_through(a, dt)
+        assert np.array_equal(_bits(got), _bits(ref))
+        bits = oracle.to_bits16(a, dt)
+        assert np.array_equal(bits.view(np.int16), t.to(tdt).view(torch.int16).numpy())
+        assert np.array_equal(_bits(oracle.from_bits16(bits, dt)), _bits(ref))
