@@ -1,0 +1,381 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-matmul hot path on B200 (one JSON line on stdout).
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--m 1]
+
+Workload (``config.workload``): the Llama-3-8B-shaped decode projection set, 4-bit
+codes, group 64, bf16 activations, M = 1: per layer q 4096->4096, k/v 4096->1024 (x2),
+o 4096->4096, gate/up 4096->14336 (x2), down 14336->4096, over 32 layers of random
+codes (3.9 GB of packed weights, scales and biases: far larger than L2, so every step
+streams from HBM).  One "step" = one pass of qmv over all 224 matrices.  With N > 1
+every matrix is N-split (row blocks of the weight) and the output slices are
+all-gathered over NCCL, one collective per dependent phase of a layer (qkv | o |
+gate,up | down).
+
+metric = qmv HBM GB/s = algorithmic bytes of the whole job / step time, with
+algorithmic bytes per matrix = N*K*bits/8 + 2*N*(K/G)*sz + M*K*sz + M*N*sz
+(the reference's bytes_moved, crates/metaltile-std/src/mlx/quantized.rs:5804).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LAYERS = 32
+# (name, K, N, phase)
+PROJ = [("q", 4096, 4096, 0), ("k", 4096, 1024, 0), ("v", 4096, 1024, 0), ("o", 4096, 4096, 1),
+        ("gate", 4096, 14336, 2), ("up", 4096, 14336, 2), ("down", 14336, 4096, 3)]
+BITS, GROUP = 4, 64
+METRIC = "qmv HBM GB/s (% of peak) and qmm TFLOP/s at 1/2/4/8xB200 vs CPU oracle"
+
+
+def alg_bytes(m, n, k, bits=BITS, g=GROUP, sz=2):
+    return n * k * bits // 8 + 2 * n * (k // g) * sz + m * k * sz + m * n * sz
+
+
+def step_bytes(m, layers=LAYERS):
+    return layers * sum(alg_bytes(m, n, k) for _, k, n, _ in PROJ)
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), d.get("bf16_tflops_sustained", 1400.0), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(vis.split(",")[index]) if vis and vis.split(",")[index].isdigit() else index
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+                 "sw_power_cap": 0x4, "hw_power_brake": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def start(self):
+        if self.nv:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+
+    def stop(self):
+        if self._thr:
+            self._stop.set()
+            self._thr.join()
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------
+def cpu_reference_arm(args):
+    """The reference's own CPU implementation of the path (the scalar dequant-then-dot oracle,
+    restated in C because no Rust toolchain exists here), all host threads, bounded sample."""
+    import numpy as np
+    import oracle
+    from metaltile_b200 import synth
+    threads = oracle.max_threads()
+    layers = 1
+    mats = []
+    for li in range(layers):
+        for pi, (_, k, n, _) in enumerate(PROJ):
+            w, s, b = synth.quantized_matrix(n, k, BITS, GROUP, seed=0, salt=li * 8 + pi)
+            x = synth.activations(args.m, k, seed=0, salt=li * 8 + pi)
+            s, b, x = (oracle.round_through(a, oracle.BF16) for a in (s, b, x))
+            mats.append((w, s, b, x, n, k))
+
+    def one_step():
+        for w, s, b, x, n, k in mats:
+            oracle.qmm(w, s, b, x, args.m, n, k, BITS, GROUP, threads=threads)
+
+    for _ in range(max(args.warmup, 1)):
+        one_step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        one_step()
+    dt = (time.perf_counter() - t0) / args.steps
+    nbytes = step_bytes(args.m, layers)
+    return nbytes / dt / 1e9, dt * 1e3, threads, f"{layers} of {LAYERS} layers ({len(mats)} matrices) per step"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=1, help="activation rows per projection (1 or 8)")
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary single-kernel measurements")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    config = {"workload": f"llama3_8b_decode_projections_4bit_g64_bf16_m{args.m}", "layers": args.layers,
+              "matrices_per_step": 7 * args.layers, "bits": BITS, "group_size": GROUP, "M": args.m,
+              "sharding": f"n_split_{world}" if world > 1 else "none",
+              "l2": "working set 3.9 GB per step >> 126 MB L2"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        val, ms, threads, sample = cpu_reference_arm(args)
+        print(json.dumps({
+            "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+            "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}))
+        return
+
+    import torch
+    import torch.distributed as dist
+    from metaltile_b200 import ops
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ctx = ops.context(dev)
+    M = args.m
+
+    # ---- synthetic weights, N-split across ranks ------------------------------------------
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234 + rank)
+    layers = []
+    for _ in range(args.layers):
+        mats = []
+        for name, k, n, phase in PROJ:
+            nl = n // world
+            w = torch.randint(-2 ** 31, 2 ** 31 - 1, (nl, k * BITS // 32), dtype=torch.int32, device=dev, generator=gen)
+            sc = (0.002 + 0.018 * torch.rand((nl, k // GROUP), device=dev, generator=gen))
+            bi = -8.0 * sc + 1e-3 * torch.randn((nl, k // GROUP), device=dev, generator=gen)
+            mats.append((w, sc.to(torch.bfloat16), bi.to(torch.bfloat16), k, nl, phase))
+        layers.append(mats)
+    # activations: one x per distinct K (every projection of the step reads its x from HBM/L2)
+    xs_host = {k: torch.randn((M, k), generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).pin_memory()
+               for k in (4096, 14336)}
+    xs = {k: v.to(dev) for k, v in xs_host.items()}
+    # per layer, per phase: local output slab [M, sum(nl)] and the gathered buffer [world, M, sum(nl)]
+    phase_cols = [sum(n // world for _, _, n, p in PROJ if p == ph) for ph in range(4)]
+    out_local = [[torch.empty((M, c), dtype=torch.bfloat16, device=dev) for c in phase_cols] for _ in range(args.layers)]
+    out_full = [[torch.empty((world, M, c), dtype=torch.bfloat16, device=dev) for c in phase_cols]
+                for _ in range(args.layers)] if world > 1 else None
+    # each projection writes its own contiguous [M, nl] tile, then tiles are packed per phase
+    tiles = [[torch.empty((M, nl), dtype=torch.bfloat16, device=dev) for (_, _, _, _, nl, _) in mats] for mats in layers]
+
+    def step():
+        for li, mats in enumerate(layers):
+            for ph in range(4):
+                col = 0
+                for pi, (w, sc, bi, k, nl, phase) in enumerate(mats):
+                    if phase != ph:
+                        continue
+                    if M == 1:   # a [1, nl] slice of the phase slab is contiguous: write in place
+                        ops.qmv(w, sc, bi, xs[k], BITS, GROUP, out=out_local[li][ph][:, col:col + nl], ctx=ctx)
+                    else:
+                        ops.qmv(w, sc, bi, xs[k], BITS, GROUP, out=tiles[li][pi], ctx=ctx)
+                        out_local[li][ph][:, col:col + nl].copy_(tiles[li][pi])
+                    col += nl
+                if world > 1:
+                    dist.all_gather_into_tensor(out_full[li][ph], out_local[li][ph])
+
+    launches_per_step = 7 * args.layers
+
+    # capture the step in a CUDA graph: 224 launches of ~1-5 us each are otherwise host-bound
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(args.warmup):
+        graph.replay()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms = timed(graph.replay, args.steps)
+    clocks = sampler.stop()
+    total_bytes = step_bytes(M, args.layers)       # whole job (all ranks together)
+    value = total_bytes / (ms * 1e-3) / 1e9
+
+    # ---- end to end: pinned host activations in, host results out, through the C ABI ---------
+    out_host = [[torch.empty((world if world > 1 else 1, M, c), dtype=torch.bfloat16).pin_memory() for c in phase_cols]
+                for _ in range(args.layers)]
+    h2d = sum(v.numel() * 2 for v in xs_host.values())
+    d2h = sum(t.numel() * 2 for l in out_host for t in l)
+    stream = torch.cuda.current_stream().cuda_stream
+    lib, h = ctx._lib, ctx._h
+
+    def e2e_step():
+        for k, v in xs_host.items():
+            lib.mtc_upload(h, stream, xs[k].data_ptr(), v.data_ptr(), v.numel() * 2)
+        graph.replay()
+        for li in range(args.layers):
+            for ph in range(4):
+                src = out_full[li][ph] if world > 1 else out_local[li][ph]
+                lib.mtc_download(h, stream, out_host[li][ph].data_ptr(), src.data_ptr(), src.numel() * 2)
+        lib.mtc_sync(h, stream)
+
+    for _ in range(3):
+        e2e_step()
+    e2e_steps = max(3, min(args.steps, 50))
+    e2e_ms = timed(e2e_step, e2e_steps)
+    e2e_value = total_bytes / (e2e_ms * 1e-3) / 1e9
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    hbm_peak, tf_burst, tf_sus, peak_kind = measured_peaks()
+    per_launch_bytes = total_bytes / world / launches_per_step
+    us_per_launch = ms * 1e3 / launches_per_step
+    roofline = {"bound": "hbm", "achieved": value / world, "peak": hbm_peak, "unit": "GB/s",
+                "frac": value / world / hbm_peak, "traffic": None, "peak_kind": peak_kind,
+                "kernel": "qmv_kernel<4,1,4>", "alg_bytes_per_launch": per_launch_bytes,
+                "avg_us_per_launch": us_per_launch,
+                "note": "per-GPU; launch-averaged over the 4 matrix shapes of the step (graph replay, events)"}
+    line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config, "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": launches_per_step * args.steps, "roofline": roofline}
+
+    if not args.no_extra:
+        try:
+            line["extra"] = extra_measurements(ctx, dev, hbm_peak, tf_burst)
+        except Exception as e:  # secondary numbers must never sink the headline line
+            line["extra"] = {"error": repr(e)}
+    if not args.no_cpu and world == 1:
+        try:
+            ns = argparse.Namespace(m=M, steps=3, warmup=1)
+            val, cms, threads, sample = cpu_reference_arm(ns)
+            line["cpu_baseline"] = {"value": val, "unit": "GB/s", "cores": threads, "kind": "port",
+                                    "sample": sample, "ms_per_sample": cms}
+        except Exception as e:
+            line["cpu_baseline"] = {"error": repr(e)}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def extra_measurements(ctx, dev, hbm_peak, tf_peak):
+    """Single-kernel numbers for the other configurations (cold L2: buffers rotate through > 126 MB)."""
+    import torch
+    from metaltile_b200 import ops
+    out = {}
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(99)
+
+    def make(n, k, m, copies):
+        sets = []
+        for _ in range(copies):
+            w = torch.randint(-2 ** 31, 2 ** 31 - 1, (n, k * BITS // 32), dtype=torch.int32, device=dev, generator=gen)
+            sc = (0.002 + 0.018 * torch.rand((n, k // GROUP), device=dev, generator=gen)).to(torch.bfloat16)
+            bi = (-8.0 * sc.float()).to(torch.bfloat16)
+            sets.append((w, sc, bi))
+        x = torch.randn((m, k), device=dev, generator=gen).to(torch.bfloat16)
+        o = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        return sets, x, o
+
+    def time_rot(fn_list, reps):
+        g = torch.cuda.CUDAGraph()
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for f in fn_list:
+                f()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g):
+            for f in fn_list:
+                f()
+        for _ in range(3):
+            g.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (reps * len(fn_list))  # us per launch
+
+    for name, (m, n, k) in {"c0_qmv_m1_4096x4096": (1, 4096, 4096), "qmv_m1_8192x8192": (1, 8192, 8192),
+                            "qmv_m8_4096x4096": (8, 4096, 4096), "qmv_m16_4096x4096": (16, 4096, 4096)}.items():
+        copies = max(2, int(300e6 // alg_bytes(m, n, k)) + 1)   # > 2x L2 in rotation
+        sets, x, o = make(n, k, m, copies)
+        fns = [(lambda w=w, sc=sc, bi=bi: ops.qmv(w, sc, bi, x, BITS, GROUP, out=o, ctx=ctx)) for (w, sc, bi) in sets]
+        us = time_rot(fns, 20)
+        gbs = alg_bytes(m, n, k) / us / 1e3
+        out[name] = {"us": us, "GB/s": gbs, "frac_of_hbm_peak": gbs / hbm_peak, "cold_l2_copies": copies}
+        del sets, fns
+    return out
+
+
+if __name__ == "__main__":
+    main()

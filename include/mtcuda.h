@@ -1,0 +1,128 @@
+/*
+ * mtcuda.h — C ABI of the B200 (sm_100a) back end for metaltile's affine
+ * group-quantized matmul family: qmv (decode), qmm (prefill), the MoE
+ * gather_qmm and the routing kernels around it.
+ *
+ * This is the boundary a `metaltile-runtime` CUDA backend binds through FFI.
+ * Each entry names the reference interface it stands in for (paths relative to
+ * the metaltile repository).  Conventions:
+ *   - every call returns an `mtc_status` (0 = ok, negative = error); the
+ *     message of the last error of a context is read with mtc_last_error();
+ *   - one mtc_ctx per device, not thread-safe (the reference's Context is
+ *     !Send and its tests serialise GPU access: crates/metaltile-std/tests/common/mod.rs:11-27);
+ *   - pointers named d_* / w / scales / biases / x / out of the typed ops are
+ *     DEVICE pointers (16-byte aligned); `stream` is a cudaStream_t passed as
+ *     void* (NULL = default stream); typed ops are asynchronous and never block;
+ *   - layouts are exactly the reference's: w u32[N, K*bits/32] (row = LSB-first
+ *     bit-stream, low field first along K), scales/biases T[N, K/group_size],
+ *     x T[M, K], out T[M, N] row-major; T in {f32, f16, bf16};
+ *   - there is no CPU fallback: without a CUDA device mtc_init fails with
+ *     MTC_ERR_NO_DEVICE and nothing else can be called.
+ */
+#ifndef MTCUDA_H
+#define MTCUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct mtc_ctx mtc_ctx;
+
+/* Activation dtype T (metaltile-core DType::{F32,F16,BF16},
+ * crates/metaltile-core/src/dsl/dtype.rs:11-33). */
+typedef enum { MTC_F32 = 0, MTC_F16 = 1, MTC_BF16 = 2 } mtc_dtype;
+
+/* Mirrors the variants of MetalTileError (crates/metaltile-runtime/src/error.rs:7-56). */
+typedef enum {
+    MTC_OK = 0,
+    MTC_ERR_NO_DEVICE = -1,          /* NoDevice */
+    MTC_ERR_BUFFER = -2,             /* Buffer: allocation / copy failed, bad pointer or alignment */
+    MTC_ERR_BUFFER_SIZE = -3,        /* BufferSize: a named buffer is smaller than the kernel needs */
+    MTC_ERR_DISPATCH = -4,           /* Dispatch: launch or execution error */
+    MTC_ERR_FUNCTION_NOT_FOUND = -5, /* FunctionNotFound: unknown kernel name */
+    MTC_ERR_UNSUPPORTED = -6,        /* Unsupported: shape / bits / dtype outside the kernel's contract */
+    MTC_ERR_TIMEOUT = -7,            /* a bounded device-side wait expired (see mtc_status_word) */
+    MTC_ERR_INVALID = -8             /* null / inconsistent argument */
+} mtc_status;
+
+/* ---- lifecycle: Context::new (crates/metaltile-runtime/src/context.rs:160-240) ---- */
+int mtc_init(int device, mtc_ctx **out_ctx);
+int mtc_destroy(mtc_ctx *ctx);
+const char *mtc_last_error(mtc_ctx *ctx); /* valid until the next call on ctx; ctx may be NULL */
+/* `tile device --json` keys (crates/metaltile-cli/src/cmd/device.rs:55-66) plus
+ * sm_count, cc, hbm_bytes, l2_bytes, driver, runtime. */
+int mtc_device_info(mtc_ctx *ctx, char *json, size_t cap);
+
+/* ---- memory: Context::upload_resident / ResidentBuffer (context.rs:330-350,104-117),
+ *      GpuRunner::buffer_bytes / buffer_zeros / read_bytes
+ *      (crates/metaltile-std/src/runner.rs:317-360) ---- */
+int mtc_alloc(mtc_ctx *ctx, size_t bytes, void **d_ptr);
+int mtc_free(mtc_ctx *ctx, void *d_ptr);
+int mtc_upload(mtc_ctx *ctx, void *stream, void *d_dst, const void *h_src, size_t bytes);
+int mtc_download(mtc_ctx *ctx, void *stream, void *h_dst, const void *d_src, size_t bytes);
+int mtc_memset(mtc_ctx *ctx, void *stream, void *d_ptr, int value, size_t bytes);
+int mtc_sync(mtc_ctx *ctx, void *stream); /* commit + waitUntilCompleted (single_dispatch.rs:95-98) */
+/* 0 when no kernel has reported a bounded-wait expiry or a rejected index since
+ * the context was created; otherwise a kernel-specific code. */
+int mtc_status_word(mtc_ctx *ctx, uint32_t *word);
+
+/* ---- typed ops (device pointers, asynchronous on `stream`) ---- */
+
+/* mt_qmv and the generic mt_qmv_b{3,4,5,6,8} / mt_qmm_b* / mt_qmm{,_bm2,_bm4} and
+ * dequant_gemv_int2 family: out[m,n] = sum_k (q*scale + bias) * x[m,k], f32
+ * accumulate (crates/metaltile-std/src/mlx/quantized.rs:7-308,343-1441,4273-4392;
+ * crates/metaltile-std/src/ffai/dequant_gemv.rs:52-105).  CUDA-core path, any M
+ * (tuned for M <= 16), bits in {2,3,4,5,6,8}, K*bits % 32 == 0, group_size | K. */
+int mtc_qmv(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases,
+            const void *x, void *out, int M, int N, int K, int bits, int group_size, int dtype);
+
+/* mt_qmm_for + mt_qmm_mma* (quantized.rs:5040-5065,2106-2362): picks the kernel
+ * from M like the reference's selector: M <= 16 -> the qmv path above; larger M
+ * with f16/bf16 activations -> the tensor-core (tcgen05) prefill kernel, which
+ * like mt_qmm_mma dequantises the weight tile to T before the MMA
+ * (quantized.rs:2245-2252); f32 activations always take the CUDA-core path.
+ * Ragged M needs no padding (the reference pads to 32: quantized_mma_dynamic_m.rs:46-112). */
+int mtc_qmm(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases,
+            const void *x, void *out, int M, int N, int K, int bits, int group_size, int dtype);
+/* Name of the kernel family mtc_qmm would run for these arguments
+ * ("qmv_cuda_core", "qmm_tcgen05"); the analogue of asserting on
+ * mt_qmm_for's routing (quantized.rs:5127-5199). */
+const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dtype);
+
+/* Integer codes of a packed matrix, one byte per code, for bit-exact checks of
+ * the unpacker against the oracle (no reference counterpart as a kernel; the
+ * layout is quantized.rs:4296-4314 and :4354-4379). */
+int mtc_unpack_codes(mtc_ctx *ctx, void *stream, const void *w, void *codes_u8, int N, int K,
+                     int bits);
+
+/* ---- name-keyed dispatch with HOST buffers: Context::dispatch_with_grid
+ *      (crates/metaltile-runtime/src/context.rs:269-284) ----
+ * `bufs` binds host byte buffers and 4-byte little-endian constexprs BY NAME
+ * (run_kernel.rs:56-65,100-107).  Inputs are uploaded, the kernel selected by the
+ * reference's kernel name (e.g. "mt_qmv", "mt_qmm_mma", "mt_qmv_b3",
+ * "mt_moe_gather_qmm_int4") runs, and every buffer flagged is_output is copied back
+ * into its host storage before the call returns (single_dispatch.rs:100-117).
+ * grid / tpg are accepted for signature parity and ignored: launch geometry
+ * belongs to the back end.  elapsed_us (may be NULL) receives the device time
+ * of the kernel alone, like DispatchResult::elapsed_us (single_dispatch.rs:119). */
+typedef struct {
+    const char *name;
+    void *data;      /* host pointer */
+    size_t bytes;
+    int is_output;   /* 1: copied back after the kernel */
+} mtc_named_buf;
+
+int mtc_dispatch(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_buf *bufs, int n_bufs,
+                 const uint32_t grid[3], const uint32_t tpg[3], float *elapsed_us);
+/* Number of kernel names mtc_dispatch knows, and the i-th name (registry walk:
+ * all_kernels(), crates/metaltile-core/src/toolchain/registry.rs:56-78). */
+int mtc_kernel_count(void);
+const char *mtc_kernel_name(int i);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MTCUDA_H */

@@ -1,0 +1,73 @@
+"""ctypes loader for ``libmtcuda.so`` (the C ABI declared in ``include/mtcuda.h``).
+
+There is no fallback: if the shared library is missing or a symbol is absent the
+import of the op raises, and without a CUDA device ``mtc_init`` reports
+``NoDevice``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libmtcuda.so")
+
+F32, F16, BF16 = 0, 1, 2
+
+STATUS_NAMES = {
+    0: "Ok", -1: "NoDevice", -2: "Buffer", -3: "BufferSize", -4: "Dispatch",
+    -5: "FunctionNotFound", -6: "Unsupported", -7: "Timeout", -8: "Invalid",
+}
+
+
+class NamedBuf(ctypes.Structure):
+    _fields_ = [("name", ctypes.c_char_p), ("data", ctypes.c_void_p), ("bytes", ctypes.c_size_t),
+                ("is_output", ctypes.c_int)]
+
+
+_vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+_DENSE = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i]
+
+# name -> (restype, argtypes); every symbol include/mtcuda.h declares
+SIGNATURES = {
+    "mtc_init": (_i, [_i, ctypes.POINTER(_vp)]),
+    "mtc_destroy": (_i, [_vp]),
+    "mtc_last_error": (ctypes.c_char_p, [_vp]),
+    "mtc_device_info": (_i, [_vp, ctypes.c_char_p, _sz]),
+    "mtc_alloc": (_i, [_vp, _sz, ctypes.POINTER(_vp)]),
+    "mtc_free": (_i, [_vp, _vp]),
+    "mtc_upload": (_i, [_vp, _vp, _vp, _vp, _sz]),
+    "mtc_download": (_i, [_vp, _vp, _vp, _vp, _sz]),
+    "mtc_memset": (_i, [_vp, _vp, _vp, _i, _sz]),
+    "mtc_sync": (_i, [_vp, _vp]),
+    "mtc_status_word": (_i, [_vp, ctypes.POINTER(ctypes.c_uint32)]),
+    "mtc_qmv": (_i, _DENSE),
+    "mtc_qmm": (_i, _DENSE),
+    "mtc_qmm_route": (ctypes.c_char_p, [_i, _i, _i, _i, _i, _i]),
+    "mtc_unpack_codes": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i]),
+    "mtc_dispatch": (_i, [_vp, ctypes.c_char_p, _i, ctypes.POINTER(NamedBuf), _i,
+                          ctypes.POINTER(ctypes.c_uint32), ctypes.POINTER(ctypes.c_uint32),
+                          ctypes.POINTER(ctypes.c_float)]),
+    "mtc_kernel_count": (_i, []),
+    "mtc_kernel_name": (ctypes.c_char_p, [_i]),
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the library and bind every declared symbol; raises if anything is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} not found: build it with `python -m metaltile_b200.build` "
+            "(there is no CPU or PyTorch fallback for these ops)")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the export is missing
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib

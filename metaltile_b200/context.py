@@ -1,0 +1,141 @@
+"""Host-side mirror of the reference's runtime interface, over the C ABI.
+
+``Context`` follows ``metaltile_runtime::Context``
+(crates/metaltile-runtime/src/context.rs:160-399): ``dispatch_with_grid`` binds
+host byte buffers and constexprs BY NAME, runs the kernel selected by its
+reference name and returns the output buffers plus the kernel's device time.
+``MetalTileError`` carries the same variants as crates/metaltile-runtime/src/error.rs:7-56.
+The typed methods (``qmv``, ``qmm`` ...) take device pointers and are asynchronous;
+they are what a resident-buffer caller (GpuRunner, crates/metaltile-std/src/runner.rs:413)
+uses.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+from dataclasses import dataclass, field
+from typing import Dict, Mapping, Optional, Sequence
+
+from . import _lib
+from ._lib import BF16, F16, F32, NamedBuf
+
+DTYPES = {"f32": F32, "f16": F16, "bf16": BF16}
+
+
+class MetalTileError(RuntimeError):
+    """Error of a back-end call; ``variant`` is the reference's enum variant name."""
+
+    def __init__(self, code: int, message: str):
+        self.code = code
+        self.variant = _lib.STATUS_NAMES.get(code, f"Unknown({code})")
+        super().__init__(f"{self.variant}: {message}")
+
+
+@dataclass
+class DispatchResult:
+    """crates/metaltile-runtime/src/context.rs:49-56."""
+    outputs: Dict[str, bytes] = field(default_factory=dict)
+    elapsed_us: float = 0.0
+
+
+def _dt(dtype) -> int:
+    if isinstance(dtype, int):
+        return dtype
+    return DTYPES[str(dtype).replace("torch.", "").replace("bfloat16", "bf16").replace("float16", "f16")
+                  .replace("float32", "f32")]
+
+
+class Context:
+    """One per device; not thread-safe (the caller serialises, as the reference's tests do)."""
+
+    def __init__(self, device: int = 0):
+        self._lib = _lib.load()
+        h = ctypes.c_void_p()
+        rc = self._lib.mtc_init(int(device), ctypes.byref(h))
+        if rc != 0:
+            raise MetalTileError(rc, (self._lib.mtc_last_error(None) or b"").decode())
+        self._h = h
+        self.device = int(device)
+
+    # ---- lifecycle ------------------------------------------------------------
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.mtc_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int):
+        if rc != 0:
+            raise MetalTileError(rc, (self._lib.mtc_last_error(self._h) or b"").decode())
+
+    def device_info(self) -> dict:
+        buf = ctypes.create_string_buffer(1024)
+        self._check(self._lib.mtc_device_info(self._h, buf, len(buf)))
+        return json.loads(buf.value.decode())
+
+    def status_word(self) -> int:
+        w = ctypes.c_uint32()
+        self._check(self._lib.mtc_status_word(self._h, ctypes.byref(w)))
+        return int(w.value)
+
+    def sync(self, stream: int = 0):
+        self._check(self._lib.mtc_sync(self._h, ctypes.c_void_p(stream)))
+
+    # ---- name-keyed host-buffer dispatch ----------------------------------------
+    def dispatch_with_grid(self, kernel: str, buffers: Mapping[str, bytes],
+                           fn_consts: Optional[Mapping[str, int]] = None,
+                           grid_groups: Sequence[int] = (1, 1, 1),
+                           threads_per_group: Sequence[int] = (1, 1, 1),
+                           dtype="f32", outputs: Sequence[str] = ("out",)) -> DispatchResult:
+        """``Context::dispatch_with_grid`` (context.rs:269-284).
+
+        ``buffers`` maps parameter names to host bytes; constexprs may be given either
+        as 4-byte little-endian entries of ``buffers`` (as the reference's test runner
+        does, run_kernel.rs:56-65) or through ``fn_consts``.  ``grid_groups`` /
+        ``threads_per_group`` are accepted and ignored.
+        """
+        items = dict(buffers)
+        for k, v in (fn_consts or {}).items():
+            items[k] = int(v).to_bytes(4, "little")
+        keep = []
+        arr = (NamedBuf * len(items))()
+        for i, (name, data) in enumerate(items.items()):
+            raw = ctypes.create_string_buffer(bytes(data), len(data))
+            keep.append(raw)
+            arr[i].name = name.encode()
+            arr[i].data = ctypes.cast(raw, ctypes.c_void_p)
+            arr[i].bytes = len(data)
+            arr[i].is_output = 1 if name in outputs else 0
+        g = (ctypes.c_uint32 * 3)(*[int(v) for v in grid_groups])
+        t = (ctypes.c_uint32 * 3)(*[int(v) for v in threads_per_group])
+        us = ctypes.c_float(0.0)
+        self._check(self._lib.mtc_dispatch(self._h, kernel.encode(), _dt(dtype), arr, len(items), g, t,
+                                           ctypes.byref(us)))
+        res = DispatchResult(elapsed_us=float(us.value))
+        for i, name in enumerate(items):
+            if arr[i].is_output:
+                res.outputs[name] = keep[i].raw
+        return res
+
+    def kernel_names(self):
+        return [self._lib.mtc_kernel_name(i).decode() for i in range(self._lib.mtc_kernel_count())]
+
+    # ---- typed, device-pointer ops (asynchronous on `stream`) ---------------------
+    def qmv(self, w, scales, biases, x, out, M, N, K, bits, group_size, dtype, stream: int = 0):
+        self._check(self._lib.mtc_qmv(self._h, stream, w, scales, biases, x, out, M, N, K, bits, group_size,
+                                      _dt(dtype)))
+
+    def qmm(self, w, scales, biases, x, out, M, N, K, bits, group_size, dtype, stream: int = 0):
+        self._check(self._lib.mtc_qmm(self._h, stream, w, scales, biases, x, out, M, N, K, bits, group_size,
+                                      _dt(dtype)))
+
+    def qmm_route(self, M, N, K, bits, group_size, dtype) -> str:
+        return self._lib.mtc_qmm_route(M, N, K, bits, group_size, _dt(dtype)).decode()
+
+    def unpack_codes(self, w, codes, N, K, bits, stream: int = 0):
+        self._check(self._lib.mtc_unpack_codes(self._h, stream, w, codes, N, K, bits))

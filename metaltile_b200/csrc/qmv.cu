@@ -1,0 +1,439 @@
+// qmv — affine group-quantized matrix-vector / small-M matmul on CUDA cores (sm_100a).
+//
+//   out[m, n] = sum_k (q(n,k) * scale[n, k/G] + bias[n, k/G]) * x[m, k]      (f32 accumulate)
+//
+// Stands in for mt_qmv, mt_qmm{,_bm2,_bm4}, the generic mt_qmv_b*/mt_qmm_b* family
+// (crates/metaltile-std/src/mlx/quantized.rs:7-308,343-1441,4273-4392) and the
+// 2-bit dequant_gemv (crates/metaltile-std/src/ffai/dequant_gemv.rs:52-105).
+//
+// Design (HBM-bound, no tensor cores):
+//   * a warp owns R = 4 weight rows at a time; lane l owns "chunks" l, l+32, ... of
+//     the row, a chunk being 16 or 32 consecutive codes loaded with one vector load
+//     (128-bit for 4/8-bit, 64-bit for 2-bit, 3 or 5 words for the 3/5/6-bit
+//     streams, whose period is exactly one chunk so no code straddles a lane);
+//   * codes are never converted with I2F: `word & (mask << p)` reinterpreted as
+//     f32 is the subnormal-or-tiny number q * 2^(p-149) exactly (bits 0..23 of an
+//     f32 are linear in the integer they hold), and x is staged once per CTA in
+//     shared memory as f32 pre-multiplied by 2^(64-p).  One LOP3 + one FFMA per
+//     (code, m); a funnel shift every 24 bits brings later codes below bit 24;
+//   * the reference's algebraic split (quantized.rs:29-32):
+//     acc += scale * sum(q*x) + bias * sum(x) per chunk; sum(x) comes from the same
+//     staging pass;
+//   * x tiles live in shared memory in a lane-interleaved layout so every
+//     LDS.128 of a warp is conflict-free;
+//   * rows are dealt round-robin over CTAs so all 148 SMs stream at once; small N
+//     splits K over the warps of a CTA (intra-CTA split-K, reduced in shared
+//     memory, no global scratch).
+// Domain note: the 2^64 pre-scale keeps every product exact for |x| < 2^63; beyond
+// that the staged value overflows to inf where the reference would stay finite.
+#include "common.cuh"
+
+namespace mtc {
+namespace {
+
+template <int BITS>
+struct Pack {
+    static constexpr int WORDS = BITS == 2 ? 2 : (BITS == 4 || BITS == 8) ? 4 : (BITS == 6 ? 3 : BITS);
+    static constexpr int CODES = WORDS * 32 / BITS;  // 2,3,4,5-bit: 32; 6,8-bit: 16
+    static constexpr int CPW = 24 / BITS;            // codes per 24-bit window
+    static constexpr int NWIN = (CODES + CPW - 1) / CPW;
+    static constexpr uint32_t MASK = (1u << BITS) - 1u;
+};
+
+constexpr int kPreExp = 64;  // x is staged as x * 2^(kPreExp - p)
+
+struct QmvArgs {
+    const uint32_t *w;
+    const void *scales, *biases, *x;
+    void *out;
+    int M, N, K, gs, dt;
+    int wpr, gpr;      // words per weight row, groups per row
+    int nchunks, njb;  // chunks per row, ceil(nchunks / 32)
+    int kb_jb, nkb;    // chunk-iterations per staged K block, number of K blocks
+    int ksplit;        // warps sharing one row group
+    int groups, iters; // row groups (ceil(N/R)), row-group iterations per CTA slot
+};
+
+template <int WORDS>
+__device__ __forceinline__ void load_words(const uint32_t *p, uint32_t (&w)[WORDS]) {
+    if constexpr (WORDS == 4) {
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "l"(p));
+    } else if constexpr (WORDS == 2) {
+        asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];"
+                     : "=r"(w[0]), "=r"(w[1]) : "l"(p));
+    } else {
+#pragma unroll
+        for (int i = 0; i < WORDS; ++i) w[i] = __ldg(p + i);  // neighbours share sectors: keep in L1
+    }
+}
+
+__device__ __forceinline__ float comp(const float4 &v, int i) {
+    return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
+}
+
+// Stage one K block of x (all MT rows) into shared memory:
+//   xs   : f32, element (chunk c, code i, row m) at float4 index
+//          ((c>>5) * (CODES*MT/4) + (i*MT+m)/4) * 32 + (c&31), component (i*MT+m)%4,
+//          value x[m, k] * 2^(kPreExp - (i % CPW) * BITS);
+//   xsum : plain sum of the chunk's x values, at ((c>>5)*32 + (c&31)) * MT + m.
+template <int BITS, int MT>
+__device__ __forceinline__ void stage_x(const QmvArgs &a, float *xs, float *xsum, int chunk0, int nch) {
+    using P = Pack<BITS>;
+    constexpr int E4 = P::CODES * MT / 4;
+    for (int c = threadIdx.x; c < nch; c += blockDim.x) {
+        const int jb = c >> 5, ln = c & 31;
+        const size_t k0 = static_cast<size_t>(chunk0 + c) * P::CODES;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            float v[P::CODES];
+            if (m < a.M) {
+                const size_t base = static_cast<size_t>(m) * a.K + k0;
+                if (a.dt == MTC_F32) {
+                    const float4 *p = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(a.x) + base);
+#pragma unroll
+                    for (int q = 0; q < P::CODES / 4; ++q) {
+                        float4 t = __ldg(p + q);
+                        v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
+                    }
+                } else {
+                    const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(a.x) + base);
+#pragma unroll
+                    for (int q = 0; q < P::CODES / 8; ++q) {
+                        uint4 t = __ldg(p + q);
+                        uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                        for (int h = 0; h < 4; ++h) {
+                            if (a.dt == MTC_BF16) {
+                                v[8 * q + 2 * h] = __uint_as_float(u[h] << 16);
+                                v[8 * q + 2 * h + 1] = __uint_as_float(u[h] & 0xFFFF0000u);
+                            } else {
+                                float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&u[h]));
+                                v[8 * q + 2 * h] = f.x;
+                                v[8 * q + 2 * h + 1] = f.y;
+                            }
+                        }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < P::CODES; ++i) v[i] = 0.0f;
+            }
+            float s = 0.0f;
+#pragma unroll
+            for (int i = 0; i < P::CODES; ++i) s += v[i];
+            xsum[(jb * 32 + ln) * MT + m] = s;
+#pragma unroll
+            for (int i = 0; i < P::CODES; ++i) {
+                const int p = (i % P::CPW) * BITS;
+                v[i] *= __uint_as_float(static_cast<uint32_t>(kPreExp - p + 127) << 23);
+            }
+            if constexpr (MT == 1) {
+                float4 *dst = reinterpret_cast<float4 *>(xs) + static_cast<size_t>(jb) * E4 * 32 + ln;
+#pragma unroll
+                for (int q = 0; q < P::CODES / 4; ++q)
+                    dst[q * 32] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < P::CODES; ++i) {
+                    const int lin = i * MT + m;
+                    xs[((static_cast<size_t>(jb) * E4 + lin / 4) * 32 + ln) * 4 + (lin & 3)] = v[i];
+                }
+            }
+        }
+    }
+}
+
+template <int BITS, int MT, int R>
+__global__ void __launch_bounds__(256) qmv_kernel(const QmvArgs a) {
+    using P = Pack<BITS>;
+    constexpr int E4 = P::CODES * MT / 4;
+    extern __shared__ __align__(16) float smem[];
+    float *xs = smem;
+    float *xsum = xs + static_cast<size_t>(a.kb_jb) * 32 * P::CODES * MT;
+    float *red = xsum + static_cast<size_t>(a.kb_jb) * 32 * MT;
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int KS = a.ksplit, slots = nwarps / KS, slot = warp / KS, ks = warp % KS;
+    const float kPost = __uint_as_float(static_cast<uint32_t>(149 - kPreExp + 127) << 23);
+
+    for (int it = 0; it < a.iters; ++it) {
+        const int g = (it * slots + slot) * gridDim.x + blockIdx.x;
+        const bool active = g < a.groups;
+        const int n0 = g * R;
+        float acc[R][MT];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int m = 0; m < MT; ++m) acc[r][m] = 0.0f;
+
+        for (int kb = 0; kb < a.nkb; ++kb) {
+            const int jb_lo = kb * a.kb_jb;
+            const int jb_hi = min(jb_lo + a.kb_jb, a.njb);
+            if (a.nkb > 1 || it == 0) {
+                __syncthreads();
+                stage_x<BITS, MT>(a, xs, xsum, jb_lo * 32, min(jb_hi * 32, a.nchunks) - jb_lo * 32);
+                __syncthreads();
+            }
+            if (!active) continue;
+            for (int jb = jb_lo + ks; jb < jb_hi; jb += KS) {
+                const int j = jb * 32 + lane;
+                if (j >= a.nchunks) continue;
+                uint32_t wreg[R][P::WORDS];
+                float sc[R], bi[R];
+                const int grp = (j * P::CODES) / a.gs;
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const int row = min(n0 + r, a.N - 1);
+                    load_words<P::WORDS>(a.w + static_cast<size_t>(row) * a.wpr + static_cast<size_t>(j) * P::WORDS,
+                                         wreg[r]);
+                    sc[r] = ld_as_f32(a.scales, static_cast<size_t>(row) * a.gpr + grp, a.dt) * kPost;
+                    bi[r] = ld_as_f32(a.biases, static_cast<size_t>(row) * a.gpr + grp, a.dt);
+                }
+                const int jbl = jb - jb_lo;
+                const float4 *xv = reinterpret_cast<const float4 *>(xs) + static_cast<size_t>(jbl) * E4 * 32 + lane;
+                float dot[R][MT];
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) dot[r][m] = 0.0f;
+                float4 xq = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int wi = 0; wi < P::NWIN; ++wi) {
+                    constexpr int kWinBits = P::CPW * BITS;
+                    const int word = (wi * kWinBits) / 32, sh = (wi * kWinBits) % 32;
+                    uint32_t v[R];
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        if (sh == 0) v[r] = wreg[r][word];
+                        else if (word + 1 < P::WORDS) v[r] = __funnelshift_r(wreg[r][word], wreg[r][word + 1], sh);
+                        else v[r] = wreg[r][word] >> sh;
+                    }
+#pragma unroll
+                    for (int c = 0; c < P::CPW; ++c) {
+                        const int i = wi * P::CPW + c;
+                        if (i < P::CODES) {
+                            float f[R];
+#pragma unroll
+                            for (int r = 0; r < R; ++r) f[r] = __uint_as_float(v[r] & (P::MASK << (c * BITS)));
+#pragma unroll
+                            for (int m = 0; m < MT; ++m) {
+                                const int lin = i * MT + m;
+                                if ((lin & 3) == 0) xq = xv[(lin >> 2) * 32];
+                                const float xval = comp(xq, lin & 3);
+#pragma unroll
+                                for (int r = 0; r < R; ++r) dot[r][m] = fmaf(f[r], xval, dot[r][m]);
+                            }
+                        }
+                    }
+                }
+                const float *xsp = xsum + (jbl * 32 + lane) * MT;
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    const float sx = xsp[m];
+#pragma unroll
+                    for (int r = 0; r < R; ++r) acc[r][m] = fmaf(sc[r], dot[r][m], fmaf(bi[r], sx, acc[r][m]));
+                }
+            }
+        }
+
+        // K reduction: lanes of the warp, then (split-K) the warps sharing the row group.
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                float v = acc[r][m];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                acc[r][m] = v;
+            }
+        if (KS > 1) {
+            if (lane == 0) {
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) red[(warp * R + r) * MT + m] = acc[r][m];
+            }
+            __syncthreads();
+            if (ks == 0 && lane == 0) {
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+#pragma unroll
+                    for (int m = 0; m < MT; ++m)
+                        for (int q = 1; q < KS; ++q) acc[r][m] += red[((warp + q) * R + r) * MT + m];
+            }
+            __syncthreads();
+        }
+        if (active && ks == 0 && lane == 0) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                if (n0 + r < a.N) {
+#pragma unroll
+                    for (int m = 0; m < MT; ++m)
+                        if (m < a.M) st_from_f32(a.out, static_cast<size_t>(m) * a.N + n0 + r, acc[r][m], a.dt);
+                }
+            }
+        }
+    }
+}
+
+// Any-shape fallback (unaligned pointers, group sizes that are not a multiple of the
+// chunk, K not a multiple of the chunk): one warp per weight row, lanes stride over k,
+// scalar two-word extraction like the reference's generic kernels
+// (crates/metaltile-std/src/mlx/quantized.rs:4300-4325,4357-4390).
+__global__ void __launch_bounds__(256)
+qmv_generic_kernel(const uint32_t *w, const void *scales, const void *biases, const void *x, void *out,
+                   int M, int N, int K, int bits, int gs, int dt) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= N) return;
+    const size_t wpr = static_cast<size_t>(K) * bits / 32, gpr = K / gs;
+    const uint32_t *wr = w + row * wpr;
+    for (int m = 0; m < M; ++m) {
+        float acc = 0.0f;
+        for (int k = lane; k < K; k += 32) {
+            const float s = ld_as_f32(scales, row * gpr + k / gs, dt);
+            const float b = ld_as_f32(biases, row * gpr + k / gs, dt);
+            const float q = static_cast<float>(code_at(wr, k, bits));
+            acc = fmaf(fmaf(q, s, b), ld_as_f32(x, static_cast<size_t>(m) * K + k, dt), acc);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) st_from_f32(out, static_cast<size_t>(m) * N + row, acc, dt);
+    }
+}
+
+__global__ void unpack_codes_kernel(const uint32_t *w, uint8_t *codes, int N, int K, int bits) {
+    const size_t wpr = static_cast<size_t>(K) * bits / 32;
+    const size_t total = static_cast<size_t>(N) * K;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t r = i / K;
+        codes[i] = static_cast<uint8_t>(code_at(w + r * wpr, static_cast<uint32_t>(i - r * K), bits));
+    }
+}
+
+constexpr int kRows = 4;
+constexpr int kWarps = 8;
+constexpr size_t kSmemBudget = 80 * 1024;
+
+template <int BITS, int MT>
+cudaError_t launch_tile(Ctx *ctx, cudaStream_t st, QmvArgs a) {
+    using P = Pack<BITS>;
+    a.nchunks = a.K / P::CODES;
+    a.njb = (a.nchunks + 31) / 32;
+    const size_t per_jb = (static_cast<size_t>(32) * P::CODES * MT + 32 * MT) * sizeof(float);
+    const size_t red_bytes = static_cast<size_t>(kWarps) * kRows * MT * sizeof(float);
+    int max_jb = static_cast<int>((kSmemBudget - red_bytes) / per_jb);
+    if (max_jb < 1) max_jb = 1;
+    a.nkb = (a.njb + max_jb - 1) / max_jb;
+    a.kb_jb = (a.njb + a.nkb - 1) / a.nkb;
+    a.groups = (a.N + kRows - 1) / kRows;
+    const int sms = ctx->sm_count;
+    int ks = 1;
+    while (ks < kWarps && a.groups * ks * 2 <= sms * kWarps && a.kb_jb >= 2 * ks) ks *= 2;  // each warp keeps >= 1 chunk-iteration
+    a.ksplit = ks;
+    const int slots = kWarps / ks;
+    const size_t smem = per_jb * a.kb_jb + red_bytes;
+    int ctas_per_sm = static_cast<int>((200 * 1024) / (smem + 1024));
+    ctas_per_sm = ctas_per_sm < 1 ? 1 : (ctas_per_sm > 2 ? 2 : ctas_per_sm);
+    int grid = (a.groups + slots - 1) / slots;
+    if (grid > sms * ctas_per_sm) grid = sms * ctas_per_sm;
+    a.iters = (a.groups + slots * grid - 1) / (slots * grid);
+    auto kern = qmv_kernel<BITS, MT, kRows>;
+    kern<<<grid, kWarps * 32, smem, st>>>(a);
+    return cudaGetLastError();
+}
+
+template <int BITS>
+cudaError_t launch_bits(Ctx *ctx, cudaStream_t st, const QmvArgs &a) {
+    if (a.M == 1) return launch_tile<BITS, 1>(ctx, st, a);
+    if (a.M == 2) return launch_tile<BITS, 2>(ctx, st, a);
+    if (a.M <= 4) return launch_tile<BITS, 4>(ctx, st, a);
+    if (a.M <= 8) return launch_tile<BITS, 8>(ctx, st, a);
+    return launch_tile<BITS, 16>(ctx, st, a);
+}
+
+template <int BITS>
+cudaError_t set_attrs_bits() {
+    const int bytes = static_cast<int>(kSmemBudget + 4096);
+    cudaError_t e;
+#define MTC_SET(MT_)                                                                                     \
+    e = cudaFuncSetAttribute(qmv_kernel<BITS, MT_, kRows>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); \
+    if (e != cudaSuccess) return e;
+    MTC_SET(1) MTC_SET(2) MTC_SET(4) MTC_SET(8) MTC_SET(16)
+#undef MTC_SET
+    return cudaSuccess;
+}
+
+}  // namespace
+
+// Opt every instantiation into > 48 KB of dynamic shared memory (once per device, from mtc_init).
+cudaError_t qmv_init_device() {
+    cudaError_t e;
+    if ((e = set_attrs_bits<2>()) != cudaSuccess) return e;
+    if ((e = set_attrs_bits<3>()) != cudaSuccess) return e;
+    if ((e = set_attrs_bits<4>()) != cudaSuccess) return e;
+    if ((e = set_attrs_bits<5>()) != cudaSuccess) return e;
+    if ((e = set_attrs_bits<6>()) != cudaSuccess) return e;
+    return set_attrs_bits<8>();
+}
+
+cudaError_t launch_qmv(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases,
+                       const void *x, void *out, int M, int N, int K, int bits, int group_size, int dt,
+                       std::string *why) {
+    const bool bits_ok = bits == 2 || bits == 3 || bits == 4 || bits == 5 || bits == 6 || bits == 8;
+    if (!bits_ok || M < 0 || N < 0 || K <= 0 || group_size <= 0 || K % group_size != 0 ||
+        (static_cast<long long>(K) * bits) % 32 != 0) {
+        if (why) *why = "qmv: need bits in {2,3,4,5,6,8}, group_size | K, K*bits % 32 == 0";
+        return cudaErrorInvalidValue;
+    }
+    if (M == 0 || N == 0) return cudaSuccess;
+    const int codes = (bits == 6 || bits == 8) ? 16 : 32;
+    const size_t esz = dtype_size(dt);
+    const auto aligned = [](const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; };
+    const bool fast = K % codes == 0 && group_size % codes == 0 && aligned(w, 16) && aligned(x, 16) &&
+                      (static_cast<size_t>(K) * esz) % 16 == 0 && aligned(scales, esz) && aligned(biases, esz) &&
+                      (static_cast<size_t>(K) * bits / 8) % (bits == 2 ? 8 : (bits == 4 || bits == 8) ? 16 : 4) == 0;
+    if (!fast) {
+        const int wpb = 8;
+        qmv_generic_kernel<<<(N + wpb - 1) / wpb, wpb * 32, 0, st>>>(
+            static_cast<const uint32_t *>(w), scales, biases, x, out, M, N, K, bits, group_size, dt);
+        return cudaGetLastError();
+    }
+    for (int m0 = 0; m0 < M; m0 += 16) {
+        QmvArgs a{};
+        a.w = static_cast<const uint32_t *>(w);
+        a.scales = scales;
+        a.biases = biases;
+        a.x = static_cast<const char *>(x) + static_cast<size_t>(m0) * K * esz;
+        a.out = static_cast<char *>(out) + static_cast<size_t>(m0) * N * esz;
+        a.M = M - m0 < 16 ? M - m0 : 16;
+        a.N = N;
+        a.K = K;
+        a.gs = group_size;
+        a.dt = dt;
+        a.wpr = K * bits / 32;
+        a.gpr = K / group_size;
+        cudaError_t e;
+        switch (bits) {
+            case 2: e = launch_bits<2>(ctx, st, a); break;
+            case 3: e = launch_bits<3>(ctx, st, a); break;
+            case 4: e = launch_bits<4>(ctx, st, a); break;
+            case 5: e = launch_bits<5>(ctx, st, a); break;
+            case 6: e = launch_bits<6>(ctx, st, a); break;
+            default: e = launch_bits<8>(ctx, st, a); break;
+        }
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
+cudaError_t launch_unpack_codes(cudaStream_t st, const void *w, void *codes, int N, int K, int bits) {
+    if (N <= 0 || K <= 0) return cudaSuccess;
+    unpack_codes_kernel<<<kNumSMsB200 * 4, 256, 0, st>>>(static_cast<const uint32_t *>(w),
+                                                          static_cast<uint8_t *>(codes), N, K, bits);
+    return cudaGetLastError();
+}
+
+}  // namespace mtc

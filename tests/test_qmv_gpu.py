@@ -1,0 +1,206 @@
+"""Parity of the CUDA qmv path with the CPU oracle (all calls go through the C ABI)."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from helpers import DT_NAMES, ODT, TOL, bytes_to_f32, dense_case, dt_bytes, rel_err, to_dev
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    from metaltile_b200 import ops
+    return ops.context(0)
+
+
+def run_qmv(w, s, b, x, bits, gs, dt, fn="qmv"):
+    import torch
+    from metaltile_b200 import ops
+    out = getattr(ops, fn)(to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt), bits, gs)
+    torch.cuda.synchronize()
+    return out.float().cpu().numpy()
+
+
+# ---- the reference's registered #[test_kernel] cases, by kernel name, host buffers ----
+REGISTERED = {
+    "test_qmv": ("mt_qmv", "gs_per_row", False),
+    "test_qmv_int8_fast": ("mt_qmv_int8_fast", "gs_per_row", False),
+    "test_qmm": ("mt_qmm", "gs_per_row", True),
+    "test_qmm_int8_fast": ("mt_qmm_int8_fast", "gs_per_row", True),
+    "test_qmm_mma": ("mt_qmm_mma", "gs_per_row", True),
+    "test_qmm_mma_m16": ("mt_qmm_mma_m16", "gs_per_row", True),
+    "test_qmm_mma_int8": ("mt_qmm_mma_int8", "gs_per_row", True),
+    "test_qmm_mma_int2": ("mt_qmm_mma_int2", "gs_per_row", True),
+}
+
+
+@pytest.mark.parametrize("dt", DT_NAMES)
+@pytest.mark.parametrize("case", sorted(REGISTERED))
+def test_registered_cases_via_dispatch(ctx, case, dt):
+    fx = dict(np.load(os.path.join(GOLDEN, f"{case}_{dt}.npz")))
+    kernel, gs_const, has_n = REGISTERED[case]
+    m, n, k, bits, gs = (int(v) for v in fx["meta"])
+    bufs = {"w": fx["w"].tobytes(), "scales": dt_bytes(fx["scales"], dt), "biases": dt_bytes(fx["biases"], dt),
+            "x": dt_bytes(fx["x"], dt), "out": bytes(m * n * (4 if dt == "f32" else 2)),
+            "k": k.to_bytes(4, "little"), gs_const: (k // gs).to_bytes(4, "little")}
+    if has_n:
+        bufs["n"] = n.to_bytes(4, "little")
+    res = ctx.dispatch_with_grid(kernel, bufs, {}, (max(n // 8, 1), 1, 1), (64, 1, 1), dtype=dt)
+    got = bytes_to_f32(res.outputs["out"], dt).reshape(m, n)
+    assert np.any(got != 0.0)
+    assert rel_err(got, fx["expected"]) <= TOL[dt]
+    assert res.elapsed_us > 0.0
+
+
+@pytest.mark.parametrize("dt", ["f32", "bf16"])
+@pytest.mark.parametrize("bits", [3, 4, 5, 6, 8])
+def test_family_cases_via_dispatch(ctx, bits, dt):
+    """mt_qmv_b* with quantised real weights (tests/quantized_family_gpu_correctness.rs:200-233)."""
+    fx = dict(np.load(os.path.join(GOLDEN, f"family_qmv_b{bits}_{dt}.npz")))
+    m, n, k, _, gs = (int(v) for v in fx["meta"])
+    bufs = {"w": fx["w"].tobytes(), "scales": dt_bytes(fx["scales"], dt), "biases": dt_bytes(fx["biases"], dt),
+            "x": dt_bytes(fx["x"], dt), "out": bytes(m * n * (4 if dt == "f32" else 2))}
+    res = ctx.dispatch_with_grid(f"mt_qmv_b{bits}", bufs, {"k": k, "n": n, "group_size": gs}, (n, 1, 1),
+                                 (32, 1, 1), dtype=dt)
+    got = bytes_to_f32(res.outputs["out"], dt).reshape(m, n)
+    assert np.any(got != 0.0)
+    assert rel_err(got, fx["expected"]) <= TOL[dt]
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 5, 6, 8])
+def test_unpacked_codes_bit_exact(bits):
+    import torch
+    from metaltile_b200 import ops, synth
+    n, k = 257, 4096
+    w = synth.words(n * k * bits // 32, seed=3).reshape(n, -1)
+    got = ops.unpack_codes(to_dev(w), k, bits)
+    torch.cuda.synchronize()
+    assert np.array_equal(got.cpu().numpy(), oracle.unpack_matrix(w, k, bits))
+
+
+def test_config0_qmv_4bit_g64_4096(ctx):
+    """The headline case: bf16 x[1,4096], W 4096x4096 4-bit g64, seed 0."""
+    w, s, b, x = dense_case(1, 4096, 4096, 4, 64, "bf16", seed=0)
+    ref = oracle.qmm(w, s, b, x, 1, 4096, 4096, 4, 64)
+    got = run_qmv(w, s, b, x, 4, 64, "bf16")
+    assert rel_err(got, ref) <= TOL["bf16"]
+    # tighter diagnosis: before the final bf16 rounding the kernel is within f32 round-off of the
+    # oracle, so got must equal round_bf16(ref) except for values on a rounding boundary
+    exp = oracle.round_through(ref, oracle.BF16)
+    assert np.mean(got == exp) > 0.99
+
+
+SWEEP = [(bits, gs, m, kn, dt)
+         for bits in (2, 3, 4, 6, 8) for gs in (32, 64, 128) for m in (1, 4, 8, 16)
+         for kn in (2048,) for dt in DT_NAMES]
+
+
+@pytest.mark.parametrize("bits,gs,m,kn,dt", SWEEP)
+def test_sweep_2048(bits, gs, m, kn, dt):
+    w, s, b, x = dense_case(m, kn, kn, bits, gs, dt, seed=0, salt=bits)
+    ref = oracle.qmm(w, s, b, x, m, kn, kn, bits, gs)
+    got = run_qmv(w, s, b, x, bits, gs, dt)
+    assert rel_err(got, ref) <= TOL[dt]
+
+
+@pytest.mark.parametrize("bits,gs,m,kn,dt", [
+    (4, 64, 1, 8192, "bf16"), (4, 64, 16, 4096, "bf16"), (3, 32, 8, 4096, "f16"), (6, 128, 4, 8192, "f32"),
+    (2, 64, 1, 8192, "f32"), (8, 32, 16, 4096, "f32"), (5, 64, 3, 4096, "bf16"),
+])
+def test_sweep_large(bits, gs, m, kn, dt):
+    w, s, b, x = dense_case(m, kn, kn, bits, gs, dt, seed=0, salt=7)
+    ref = oracle.qmm(w, s, b, x, m, kn, kn, bits, gs)
+    got = run_qmv(w, s, b, x, bits, gs, dt)
+    assert rel_err(got, ref) <= TOL[dt]
+
+
+@pytest.mark.parametrize("m,n,k,bits,gs,dt", [
+    (1, 1024, 4096, 4, 64, "bf16"),     # Llama kv projection: split-K path
+    (8, 1024, 4096, 4, 64, "bf16"),
+    (1, 14336, 4096, 4, 64, "bf16"),    # gate/up
+    (1, 4096, 14336, 4, 64, "bf16"),    # down: K = 14336
+    (8, 4096, 14336, 4, 64, "bf16"),
+    (1, 128, 4096, 4, 64, "bf16"),      # an 8-way shard of kv
+    (1, 2048, 768, 4, 64, "bf16"),      # MoE down shape
+    (5, 37, 96, 4, 32, "f32"),          # ragged N, tiny K
+    (3, 7, 32, 8, 32, "f16"),
+    (17, 64, 256, 4, 64, "bf16"),       # M > 16: two M tiles
+    (33, 40, 512, 3, 64, "f32"),
+    (2, 9, 1536, 6, 128, "bf16"),
+])
+def test_shapes_and_edges(m, n, k, bits, gs, dt):
+    w, s, b, x = dense_case(m, n, k, bits, gs, dt, seed=1, salt=m + n)
+    ref = oracle.qmm(w, s, b, x, m, n, k, bits, gs)
+    got = run_qmv(w, s, b, x, bits, gs, dt)
+    assert got.shape == (m, n)
+    assert rel_err(got, ref) <= TOL[dt]
+
+
+def test_generic_fallback_paths(ctx):
+    """Group sizes below the chunk and unaligned pointers take the any-shape kernel."""
+    import torch
+    from metaltile_b200 import ops
+    # group_size 16 with 4-bit codes (chunk = 32 codes)
+    w, s, b, x = dense_case(2, 33, 128, 4, 16, "f32", seed=2)
+    ref = oracle.qmm(w, s, b, x, 2, 33, 128, 4, 16)
+    assert rel_err(run_qmv(w, s, b, x, 4, 16, "f32"), ref) <= TOL["f32"]
+    # weights at a 4-byte (not 16-byte) aligned address
+    w, s, b, x = dense_case(1, 64, 256, 4, 64, "bf16", seed=2)
+    ref = oracle.qmm(w, s, b, x, 1, 64, 256, 4, 64)
+    flat = torch.zeros(w.size + 1, dtype=torch.int32, device="cuda")
+    flat[1:] = to_dev(w).reshape(-1)
+    wv = flat[1:].view(64, -1)
+    assert wv.data_ptr() % 16 != 0
+    out = ops.qmv(wv, to_dev(s, "bf16"), to_dev(b, "bf16"), to_dev(x, "bf16"), 4, 64)
+    torch.cuda.synchronize()
+    assert rel_err(out.float().cpu().numpy(), ref) <= TOL["bf16"]
+
+
+def test_m1_equals_row_of_batched(ctx):
+    """M = 1 of qmm is qmv (tests/qmm_gpu_correctness.rs:341-393)."""
+    w, s, b, x = dense_case(8, 512, 1024, 4, 64, "f32", seed=4)
+    full = run_qmv(w, s, b, x, 4, 64, "f32", fn="qmm")
+    for r in (0, 5):
+        one = run_qmv(w, s, b, x[r:r + 1], 4, 64, "f32")
+        assert rel_err(one[0], full[r]) <= 1e-5
+
+
+def test_linearity_at_full_size(ctx):
+    """qmv(x1 + x2) = qmv(x1) + qmv(x2) up to round-off, at K = N = 8192 (size-independent property)."""
+    w, s, b, x = dense_case(2, 8192, 8192, 4, 64, "f32", seed=5)
+    xs = np.stack([x[0], x[1], x[0] + x[1]])
+    got = run_qmv(w, s, b, xs, 4, 64, "f32")
+    assert rel_err(got[2], got[0] + got[1]) <= 1e-4
+
+
+def test_empty_inputs(ctx):
+    import torch
+    from metaltile_b200 import ops
+    w, s, b, x = dense_case(1, 8, 64, 4, 64, "f32")
+    out = ops.qmv(to_dev(w), to_dev(s), to_dev(b), to_dev(x[:0]), 4, 64)
+    torch.cuda.synchronize()
+    assert out.shape == (0, 8)
+
+
+def test_error_behaviour(ctx):
+    from metaltile_b200 import MetalTileError
+    w, s, b, x = dense_case(1, 8, 64, 4, 64, "f32")
+    good = {"w": w.tobytes(), "scales": s.tobytes(), "biases": b.tobytes(), "x": x.tobytes(), "out": bytes(32)}
+    with pytest.raises(MetalTileError) as ei:
+        ctx.dispatch_with_grid("mt_not_a_kernel", good, {"k": 64, "gs_per_row": 1})
+    assert ei.value.variant == "FunctionNotFound"
+    with pytest.raises(MetalTileError) as ei:       # undersized buffer (buffer_plan.rs:68-76)
+        ctx.dispatch_with_grid("mt_qmm", dict(good, w=w.tobytes()[:-4]), {"k": 64, "n": 8, "gs_per_row": 1})
+    assert ei.value.variant == "BufferSize"
+    with pytest.raises(MetalTileError) as ei:       # missing constexpr
+        ctx.dispatch_with_grid("mt_qmm", good, {"k": 64, "gs_per_row": 1})
+    assert ei.value.variant == "Buffer"
+    with pytest.raises(MetalTileError) as ei:       # unsupported width
+        ctx.qmv(1, 1, 1, 1, 1, 1, 8, 64, 7, 64, "f32")
+    assert ei.value.variant == "Unsupported"
+    assert ctx.status_word() == 0
