@@ -92,6 +92,49 @@ int mtc_qmm(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
  * mt_qmm_for's routing (quantized.rs:5127-5199). */
 const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dtype);
 
+/* Tuning knobs of the back end, the counterpart of the reference's per-kernel MslConfig /
+ * TileConfig switches (crates/metaltile-codegen/src/msl/config.rs:27-96,
+ * crates/metaltile-core/src/toolchain/config.rs:11-96).  Options:
+ *   "qmm_tile_tokens"  token rows per tensor-core work item (0 = chosen per shape; else a multiple
+ *                      of 16 in [16, 256]) */
+int mtc_set_option(mtc_ctx *ctx, const char *name, int value);
+
+/* mt_moe_gather_qmm_int4 / _b{3,5,6,8} / _m8 / _m16 / _m32 (CSR form: expert_offsets u32[E+1],
+ * crates/metaltile-std/src/ffai/moe.rs:358-433,461-605,634,900,1363) and mt_moe_gather_qmm_mma_*
+ * (per-row form: indices u32[m_total], moe.rs:2256-2533,2552-2835): out[t, n] = sum_k x[t,k] * w(E(t), n, k).
+ * x rows are sorted by expert; w is stacked u32[E, n_out, k_in*bits/32], scales/biases T[E, n_out, k_in/group].
+ * Exactly one of expert_offsets / indices is non-NULL.  f16/bf16 activations with k_in % 64 == 0 and a
+ * power-of-two group >= 32 run on the tensor cores, everything else on CUDA cores. */
+int mtc_gather_qmm(mtc_ctx *ctx, void *stream, const void *x, const void *w, const void *scales,
+                   const void *biases, const void *expert_offsets, const void *indices, void *out,
+                   int m_total, int n_out, int k_in, int n_experts, int bits, int group_size, int dtype);
+const char *mtc_gather_qmm_route(int m_total, int n_out, int k_in, int bits, int group_size, int dtype);
+
+/* mt_moe_router_topk (moe.rs:65-192): indices_out u32[n_rows, k], weights_out T[n_rows, k]; ties go to
+ * the lower expert index, NaN never wins; norm_topk_prob 1 = softmax over the chosen k, 0 = chosen
+ * probabilities of the softmax over all experts. */
+int mtc_moe_router_topk(mtc_ctx *ctx, void *stream, const void *router_logits, void *indices_out,
+                        void *weights_out, int n_rows, int n_experts, int k, int norm_topk_prob, int dtype);
+
+/* The expert sort the reference leaves to its caller (contract: moe.rs:253-271,200-207,311-314).
+ * Stable sort of flat slots f = token*k + slot by (expert[f], f): sort_token_idx u32[n_tokens*k]
+ * (source token of permuted row p), inv_perm u32[n_tokens, k] (row of (token, slot)), expert_offsets
+ * u32[n_experts+1] (CSR), row_expert u32[n_tokens*k] (expert of permuted row p; may be NULL). */
+int mtc_moe_sort(mtc_ctx *ctx, void *stream, const void *topk_idx, int n_tokens, int k, int n_experts,
+                 void *sort_token_idx, void *inv_perm, void *expert_offsets, void *row_expert);
+
+/* mt_moe_permute (moe.rs:283-302): permuted[p, :] = tokens[sort_token_idx[p], :], bit-exact copy. */
+int mtc_moe_permute(mtc_ctx *ctx, void *stream, const void *tokens, const void *sort_token_idx,
+                    void *permuted, int n_rows, int hidden, int dtype);
+
+/* mt_moe_unpermute (moe.rs:222-249): out[t, h] = sum_j top_k_weights[t, j] * expert_outputs[inv_perm[t, j], h],
+ * f32 accumulate, j ascending. */
+int mtc_moe_unpermute(mtc_ctx *ctx, void *stream, const void *expert_outputs, const void *inv_perm,
+                      const void *top_k_weights, void *out, int n_tokens, int hidden, int k, int dtype);
+
+/* mt_swiglu (crates/metaltile-std/src/mlx/swiglu.rs:45-57): out = silu(gate) * up, computed in f32. */
+int mtc_swiglu(mtc_ctx *ctx, void *stream, const void *gate, const void *up, void *out, size_t n, int dtype);
+
 /* Integer codes of a packed matrix, one byte per code, for bit-exact checks of
  * the unpacker against the oracle (no reference counterpart as a kernel; the
  * layout is quantized.rs:4296-4314 and :4354-4379). */

@@ -44,6 +44,14 @@ SIGNATURES = {
     "mtc_qmv": (_i, _DENSE),
     "mtc_qmm": (_i, _DENSE),
     "mtc_qmm_route": (ctypes.c_char_p, [_i, _i, _i, _i, _i, _i]),
+    "mtc_gather_qmm": (_i, [_vp] * 9 + [_i] * 7),
+    "mtc_gather_qmm_route": (ctypes.c_char_p, [_i] * 6),
+    "mtc_moe_router_topk": (_i, [_vp] * 5 + [_i] * 5),
+    "mtc_moe_sort": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "mtc_moe_permute": (_i, [_vp] * 5 + [_i] * 3),
+    "mtc_moe_unpermute": (_i, [_vp] * 6 + [_i] * 4),
+    "mtc_swiglu": (_i, [_vp] * 5 + [_sz, _i]),
+    "mtc_set_option": (_i, [_vp, ctypes.c_char_p, _i]),
     "mtc_unpack_codes": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i]),
     "mtc_dispatch": (_i, [_vp, ctypes.c_char_p, _i, ctypes.POINTER(NamedBuf), _i,
                           ctypes.POINTER(ctypes.c_uint32), ctypes.POINTER(ctypes.c_uint32),

@@ -137,5 +137,37 @@ class Context:
     def qmm_route(self, M, N, K, bits, group_size, dtype) -> str:
         return self._lib.mtc_qmm_route(M, N, K, bits, group_size, _dt(dtype)).decode()
 
+    def gather_qmm(self, x, w, scales, biases, out, m_total, n_out, k_in, n_experts, bits, group_size, dtype,
+                   expert_offsets=None, indices=None, stream: int = 0):
+        self._check(self._lib.mtc_gather_qmm(self._h, stream, x, w, scales, biases, expert_offsets, indices, out,
+                                             m_total, n_out, k_in, n_experts, bits, group_size, _dt(dtype)))
+
+    def gather_qmm_route(self, m_total, n_out, k_in, bits, group_size, dtype) -> str:
+        return self._lib.mtc_gather_qmm_route(m_total, n_out, k_in, bits, group_size, _dt(dtype)).decode()
+
+    def moe_router_topk(self, logits, indices_out, weights_out, n_rows, n_experts, k, norm_topk_prob, dtype,
+                        stream: int = 0):
+        self._check(self._lib.mtc_moe_router_topk(self._h, stream, logits, indices_out, weights_out, n_rows,
+                                                  n_experts, k, norm_topk_prob, _dt(dtype)))
+
+    def moe_sort(self, topk_idx, n_tokens, k, n_experts, sort_token_idx, inv_perm, expert_offsets, row_expert=None,
+                 stream: int = 0):
+        self._check(self._lib.mtc_moe_sort(self._h, stream, topk_idx, n_tokens, k, n_experts, sort_token_idx,
+                                           inv_perm, expert_offsets, row_expert))
+
+    def moe_permute(self, tokens, sort_token_idx, permuted, n_rows, hidden, dtype, stream: int = 0):
+        self._check(self._lib.mtc_moe_permute(self._h, stream, tokens, sort_token_idx, permuted, n_rows, hidden,
+                                              _dt(dtype)))
+
+    def moe_unpermute(self, expert_outputs, inv_perm, weights, out, n_tokens, hidden, k, dtype, stream: int = 0):
+        self._check(self._lib.mtc_moe_unpermute(self._h, stream, expert_outputs, inv_perm, weights, out, n_tokens,
+                                                hidden, k, _dt(dtype)))
+
+    def swiglu(self, gate, up, out, n, dtype, stream: int = 0):
+        self._check(self._lib.mtc_swiglu(self._h, stream, gate, up, out, n, _dt(dtype)))
+
+    def set_option(self, name: str, value: int):
+        self._check(self._lib.mtc_set_option(self._h, name.encode(), int(value)))
+
     def unpack_codes(self, w, codes, N, K, bits, stream: int = 0):
         self._check(self._lib.mtc_unpack_codes(self._h, stream, w, codes, N, K, bits))

@@ -22,6 +22,9 @@ struct Ctx {
     uint32_t *d_status = nullptr;  // device status word (bounded waits / rejected indices)
     void *d_scratch = nullptr;     // grow-only scratch owned by the context
     size_t scratch_bytes = 0;
+    int qmm_force_tn = 0;          // option "qmm_tile_tokens": 0 = choose per shape
+    void *d_worklist = nullptr;    // gather_qmm work list (grow-only, owned by the context)
+    size_t worklist_bytes = 0;
 };
 
 inline int fail(Ctx *ctx, int code, const std::string &msg) {
@@ -67,6 +70,28 @@ cudaError_t launch_qmv(Ctx *ctx, cudaStream_t st, const void *w, const void *sca
                        const void *x, void *out, int M, int N, int K, int bits, int group_size, int dt,
                        std::string *why);
 cudaError_t qmv_init_device();
+bool qmm_tcgen05_supported(int M, int N, int K, int bits, int group_size, int dt, const void *w, const void *x,
+                           const void *out);
+cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases,
+                               const void *x, void *out, int M, int N, int K, int bits, int group_size, int dt,
+                               std::string *why);
+size_t gather_items_bytes(int total_rows, int n_experts, int N, int TN_hint);
+cudaError_t launch_gather_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *x, const void *w, const void *scales,
+                                      const void *biases, const uint32_t *expert_offsets, const uint32_t *indices,
+                                      void *out, int total_rows, int N, int K, int n_experts, int bits, int group_size,
+                                      int dt, void *scratch, size_t scratch_bytes, std::string *why);
+cudaError_t launch_router_topk(cudaStream_t st, const void *logits, uint32_t *idx, void *wts, int n_rows, int n_experts,
+                               int k, int norm, int dt);
+cudaError_t launch_moe_sort(cudaStream_t st, const uint32_t *topk_idx, int n_tokens, int k, int n_experts, uint32_t *sti,
+                            uint32_t *inv, uint32_t *offsets, uint32_t *row_expert, uint32_t *status);
+cudaError_t launch_permute(cudaStream_t st, const void *tokens, const uint32_t *sti, void *permuted, int n_rows, int hidden,
+                           int dt);
+cudaError_t launch_unpermute(cudaStream_t st, const void *eo, const uint32_t *inv, const void *wts, void *out, int n_tokens,
+                             int hidden, int k, int dt);
+cudaError_t launch_swiglu(cudaStream_t st, const void *gate, const void *up, void *out, size_t n, int dt);
+cudaError_t launch_gather_generic(cudaStream_t st, const void *x, const void *w, const void *scales, const void *biases,
+                                  const uint32_t *offsets, const uint32_t *indices, void *out, int t_rows, int k_in, int n_out,
+                                  int n_experts, int bits, int gs, int dt);
 cudaError_t launch_unpack_codes(cudaStream_t st, const void *w, void *codes, int N, int K, int bits);
 
 }  // namespace mtc

@@ -1,0 +1,620 @@
+// qmm / gather_qmm — prefill and MoE matmuls on the sm_100a tensor cores.
+//
+//   dense : out[m, n]  = sum_k x[m, k] * w(n, k)                      (mt_qmm_mma family)
+//   gather: out[t, n]  = sum_k x[t, k] * w(E(t), n, k), rows sorted by expert (mt_moe_gather_qmm_*)
+//
+// Stands in for mt_qmm_mma and its int8/int2/bit-stream variants
+// (crates/metaltile-std/src/mlx/quantized.rs:2106-2362,2731,3330,4720-5012) and for the MoE gather
+// kernels (crates/metaltile-std/src/ffai/moe.rs:358-605,2256-2835).  Like the reference's MMA kernels
+// the weight tile is dequantised to the activation type on chip and fed to the matrix unit with f32
+// accumulation (quantized.rs:2245-2252); unlike them neither M nor the rows of an expert need padding.
+//
+// The product is computed transposed: D^T[n, t] = W_tile[128 x K] * X_chunk[TN x K]^T, so the
+// dequantised weights are the A operand (always a full 128-row MMA, however few tokens there are) and
+// the activations are the B operand (TN = 16..256 token rows, straight from TMA).
+//
+// One persistent CTA per SM, 512 threads, warp-specialised:
+//   warp 0      producer   one lane issues TMA (cp.async.bulk.tensor, 128B swizzle) loads of the X
+//                          chunk [TN x 64] into a 4-stage shared-memory ring
+//   warp 1      MMA        one lane issues tcgen05.mma (M=128, N=TN, K=16, kind::f16), accumulators in
+//                          TMEM, double buffered (2 x 256 columns)
+//   warp 2      TMEM allocation / deallocation
+//   warps 4-7   epilogue   tcgen05.ld of the finished accumulator, f32 -> T, transposed stores to out
+//   warps 8-15  dequant    256 threads = 128 weight rows x 2 halves of a 64-wide k block: packed words
+//                          come straight from global memory into registers one k block ahead, every
+//                          code is extracted with one LOP3 ((win & mask<<p) | 1.0f, minus 1.0f =
+//                          q * 2^(p-23)), w = q*scale + bias in f32, rounded to T, written as the
+//                          K-major 128B-swizzled A operand tile the MMA reads
+// Stage hand-off uses mbarriers; tcgen05.commit releases a stage when its MMAs have read it.  Every
+// wait is bounded: on expiry the kernel records a code in the context's status word, all roles leave
+// their loops, TMEM is released and the kernel returns.
+//
+// Work items (weight-row tile, expert, first token row, token count) are enumerated arithmetically
+// for the dense case and read from a list in scratch memory for the gather case; that list is built
+// on the device from expert_offsets by build_items_kernel.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace mtc {
+namespace {
+
+constexpr int BMW = 128;         // weight rows per tile (TMEM lanes, MMA M)
+constexpr int BK = 64;           // k per stage: 64 x 16-bit = one 128B swizzle row
+constexpr int TN_MAX = 256;      // token rows per tile (TMEM columns of one accumulator, MMA N)
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BMW * BK * 2;       // 16 KB, dequantised weights
+constexpr int B_BYTES = TN_MAX * BK * 2;    // 32 KB, activations
+constexpr int NUM_THREADS = 512;
+constexpr int DEQ_WARP0 = 8, DEQ_THREADS = 256;
+constexpr int EPI_WARP0 = 4;
+constexpr uint32_t kSpinLimit = 1u << 22;   // bounded waits: ~seconds, then give up
+
+struct QmmParams {
+    const uint32_t *w;
+    const void *scales, *biases;
+    void *out;
+    uint32_t *status;
+    const int4 *items;           // gather: {n_tile, expert, row_start, row_count}; dense: nullptr
+    const int *item_count;       // gather: device counter; dense: nullptr
+    int dense_items;             // dense: number of items = n_tiles * m_chunks
+    int m_chunks;                // dense: token chunks per weight-row tile
+    int M;                       // dense: rows of x; gather: total rows of x
+    int N, K, gs_shift, dt;      // N: weight rows per expert (output columns)
+    int wpr, gpr;                // words / groups per weight row
+    int TN;                      // token rows per item (TMA box rows, MMA N)
+    uint32_t idesc;
+};
+
+struct __align__(8) SmemCtrl {
+    uint64_t full_x[STAGES];     // TMA bytes of the X stage have landed
+    uint64_t full_w[STAGES];     // dequant warps finished the W stage
+    uint64_t empty[STAGES];      // MMAs that read the stage have completed
+    uint64_t acc_full[2];        // accumulator buffer complete
+    uint64_t acc_empty[2];       // epilogue drained the accumulator buffer
+    uint32_t tmem_base;
+    volatile uint32_t abort;
+};
+
+// ---- PTX wrappers -------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and raises the CTA's abort flag + the global status word) when the
+// barrier did not complete within kSpinLimit polls or another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, SmemCtrl *ctl, uint32_t *status, uint32_t code) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if ((i & 63u) == 63u && ctl->abort) return false;
+    }
+    ctl->abort = 1;
+    atomicCAS(status, 0u, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row atoms 1024 B apart.
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);   // start address  [0,14)
+    d |= static_cast<uint64_t>(1) << 16;                   // leading byte offset (unused with 128B swizzle)
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;           // stride byte offset [32,46)
+    d |= static_cast<uint64_t>(1) << 46;                   // descriptor version (sm_100)
+    d |= static_cast<uint64_t>(2) << 61;                   // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, int f16) {
+    if (f16) {
+        __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<uint32_t *>(&h);
+    }
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+
+// ---- dequantisation of half a W row segment (32 codes = BITS words) into 4 swizzled 16-byte chunks --
+template <int BITS>
+struct QPack {
+    static constexpr int WPH = BITS;            // u32 words per 32 codes
+    static constexpr int CPW = 23 / BITS;       // codes per window: a window must fit the 23 mantissa bits
+    static constexpr uint32_t MASK = (1u << BITS) - 1u;
+};
+
+template <int BITS>
+__device__ __forceinline__ void load_half_words(const uint32_t *p, uint32_t (&w)[BITS], bool valid) {
+    if (!valid) {
+#pragma unroll
+        for (int i = 0; i < BITS; ++i) w[i] = 0u;
+        return;
+    }
+    if constexpr (BITS % 4 == 0) {          // 4-, 8-bit: 16-byte pieces
+#pragma unroll
+        for (int i = 0; i < BITS / 4; ++i) {
+            uint4 v = __ldg(reinterpret_cast<const uint4 *>(p) + i);
+            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+        }
+    } else if constexpr (BITS % 2 == 0) {   // 2-, 6-bit: 8-byte pieces
+#pragma unroll
+        for (int i = 0; i < BITS / 2; ++i) {
+            uint2 v = __ldg(reinterpret_cast<const uint2 *>(p) + i);
+            w[2 * i] = v.x; w[2 * i + 1] = v.y;
+        }
+    } else {                                // 3-, 5-bit: single words
+#pragma unroll
+        for (int i = 0; i < BITS; ++i) w[i] = __ldg(p + i);
+    }
+}
+
+template <int BITS>
+__device__ __forceinline__ void dequant_half(const uint32_t (&w)[BITS], float s, float b, uint8_t *row_base, int chunk0,
+                                             int r7, int f16) {
+    using Q = QPack<BITS>;
+    // a code at bit p of a window becomes q * 2^(p-23) after the magic subtract: fold 2^(23-p) into the scale
+    float sp[Q::CPW];
+#pragma unroll
+    for (int c = 0; c < Q::CPW; ++c) sp[c] = s * __uint_as_float(static_cast<uint32_t>(23 - c * BITS + 127) << 23);
+    float vals[8];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const int wi = i / Q::CPW, c = i % Q::CPW;
+        const int sbit = wi * Q::CPW * BITS, word = sbit / 32, sh = sbit % 32;
+        uint32_t win;
+        if (sh == 0) win = w[word];
+        else if (word + 1 < BITS) win = __funnelshift_r(w[word], w[word + 1], sh);
+        else win = w[word] >> sh;
+        const float f = __uint_as_float((win & (Q::MASK << (c * BITS))) | 0x3F800000u) - 1.0f;
+        vals[i & 7] = fmaf(f, sp[c], b);
+        if ((i & 7) == 7) {
+            const int chunk = chunk0 + (i >> 3);
+            uint4 o;
+            o.x = pack2(vals[0], vals[1], f16);
+            o.y = pack2(vals[2], vals[3], f16);
+            o.z = pack2(vals[4], vals[5], f16);
+            o.w = pack2(vals[6], vals[7], f16);
+            *reinterpret_cast<uint4 *>(row_base + ((chunk ^ r7) << 4)) = o;
+        }
+    }
+}
+
+struct Item {
+    int n_tile, expert, row0, rows;
+};
+
+__device__ __forceinline__ Item get_item(const QmmParams &p, int i) {
+    Item it;
+    if (p.items) {
+        const int4 v = __ldg(p.items + i);
+        it.n_tile = v.x; it.expert = v.y; it.row0 = v.z; it.rows = v.w;
+    } else {   // dense: token chunks of one weight-row tile are adjacent, so concurrent CTAs share the W tile in L2
+        it.n_tile = i / p.m_chunks;
+        it.expert = 0;
+        it.row0 = (i - it.n_tile * p.m_chunks) * p.TN;
+        it.rows = min(p.TN, p.M - it.row0);
+    }
+    return it;
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t *sW = smem;                                  // STAGES x 16 KB: dequantised weights (A operand)
+    uint8_t *sX = smem + STAGES * A_BYTES;               // STAGES x 32 KB: activations (B operand)
+    SmemCtrl *ctl = reinterpret_cast<SmemCtrl *>(smem + STAGES * (A_BYTES + B_BYTES));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_kb = p.K / BK;
+    const int num_items = p.items ? __ldg(p.item_count) : p.dense_items;
+    const uint32_t x_bytes = static_cast<uint32_t>(p.TN) * BK * 2;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&ctl->full_x[s], 1);
+            mbar_init(&ctl->full_w[s], DEQ_THREADS / 32);
+            mbar_init(&ctl->empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&ctl->acc_full[b], 1);
+            mbar_init(&ctl->acc_empty[b], 4);
+        }
+        ctl->abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- producer: TMA loads of the X chunk ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x) {
+                const Item item = get_item(p, i);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!(ok = mbar_wait(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x101))) break;
+                    mbar_expect_tx(&ctl->full_x[s], x_bytes);
+                    tma_load_2d(sX + s * B_BYTES, &tmap_x, kb * BK, item.row0, &ctl->full_x[s]);
+                }
+            }
+            if (!ok) {   // let copies already in flight land before the CTA tears down
+                for (int s = 0; s < STAGES; ++s)
+                    for (uint32_t j = 0; j < 4096 && !mbar_try(&ctl->full_x[s], 0) && !mbar_try(&ctl->full_x[s], 1); ++j) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t it = 0, tile_i = 0;
+            bool ok = true;
+            for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x, ++tile_i) {
+                const int buf = tile_i & 1;
+                const uint32_t acc_ph = (tile_i >> 1) & 1;
+                if (!(ok = mbar_wait(&ctl->acc_empty[buf], acc_ph ^ 1, ctl, p.status, 0x201))) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + buf * TN_MAX;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!(ok = mbar_wait(&ctl->full_x[s], ph, ctl, p.status, 0x202))) break;
+                    if (!(ok = mbar_wait(&ctl->full_w[s], ph, ctl, p.status, 0x203))) break;
+                    tc_fence_after();
+                    const uint64_t adesc = make_desc_sw128(smem_u32(sW + s * A_BYTES));
+                    const uint64_t bdesc = make_desc_sw128(smem_u32(sX + s * B_BYTES));
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)   // 16 elements = 32 bytes further along the swizzled row
+                        umma_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, p.idesc, (kb | k) ? 1u : 0u);
+                    umma_commit(&ctl->empty[s]);         // frees the stage when these MMAs have read it
+                }
+                if (ok) umma_commit(&ctl->acc_full[buf]);
+            }
+        }
+    } else if (warp >= EPI_WARP0 && warp < EPI_WARP0 + 4) {
+        // ---------------- epilogue: TMEM -> registers -> out (transposed) ----------------
+        const int q = warp - EPI_WARP0;          // == warp % 4: the TMEM lane quarter this warp may read
+        uint32_t tile_i = 0;
+        bool ok = true;
+        for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x, ++tile_i) {
+            const int buf = tile_i & 1;
+            const uint32_t acc_ph = (tile_i >> 1) & 1;
+            const Item item = get_item(p, i);
+            if (!(ok = mbar_wait(&ctl->acc_full[buf], acc_ph, ctl, p.status, 0x301))) break;
+            tc_fence_after();
+            const int n = item.n_tile * BMW + q * 32 + lane;     // output column owned by this thread
+            const bool n_ok = n < p.N;
+            const int cols = (item.rows + 15) & ~15;
+            for (int c0 = 0; c0 < cols; c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * TN_MAX + c0, v);
+                if (n_ok) {
+                    // lanes of a warp hold 32 consecutive columns of the same output row: 64-byte segments
+                    if (p.dt == MTC_F16) {
+                        __half *o = static_cast<__half *>(p.out) + static_cast<size_t>(item.row0 + c0) * p.N + n;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (c0 + j < item.rows) o[static_cast<size_t>(j) * p.N] = __float2half_rn(__uint_as_float(v[j]));
+                    } else {
+                        __nv_bfloat16 *o = static_cast<__nv_bfloat16 *>(p.out) + static_cast<size_t>(item.row0 + c0) * p.N + n;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (c0 + j < item.rows) o[static_cast<size_t>(j) * p.N] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
+        }
+    } else if (warp >= DEQ_WARP0) {
+        // ---------------- dequant: packed W rows -> swizzled A operand tile ----------------
+        const int t = threadIdx.x - DEQ_WARP0 * 32;
+        const int r = t & (BMW - 1);                       // row of the W tile
+        const int h = t >> 7;                              // which 32-code half of the 64-wide k block
+        const int r7 = r & 7;
+        const int f16 = p.dt == MTC_F16;
+        uint8_t *row_smem = sW + (r >> 3) * 1024 + r7 * 128;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x) {
+            const Item item = get_item(p, i);
+            const int n = item.n_tile * BMW + r;
+            const bool valid = n < p.N;
+            const size_t grow = static_cast<size_t>(item.expert) * p.N + (valid ? n : 0);
+            const uint32_t *wrow = p.w + grow * p.wpr + h * BITS;
+            const unsigned short *sc16 = static_cast<const unsigned short *>(p.scales) + grow * p.gpr;
+            const unsigned short *bi16 = static_cast<const unsigned short *>(p.biases) + grow * p.gpr;
+            uint32_t wnext[BITS];
+            uint32_t sn = 0, bn = 0;                       // raw 16-bit scale / bias, converted when used
+            load_half_words<BITS>(wrow, wnext, valid);
+            if (valid) {
+                const int g = (h * 32) >> p.gs_shift;
+                sn = __ldg(sc16 + g);
+                bn = __ldg(bi16 + g);
+            }
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                uint32_t wcur[BITS];
+#pragma unroll
+                for (int j = 0; j < BITS; ++j) wcur[j] = wnext[j];
+                const uint32_t sr = sn, br = bn;
+                if (kb + 1 < num_kb) {                     // request the next k block before converting this one
+                    load_half_words<BITS>(wrow + static_cast<size_t>(kb + 1) * (2 * BITS), wnext, valid);
+                    if (valid) {
+                        const int g = ((kb + 1) * BK + h * 32) >> p.gs_shift;
+                        sn = __ldg(sc16 + g);
+                        bn = __ldg(bi16 + g);
+                    }
+                }
+                // the stage is free once empty[s] has completed (the producer waits on the same barrier)
+                if (!(ok = mbar_wait(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x401))) break;
+                float sc, bi;
+                if (f16) {
+                    sc = __half2float(__ushort_as_half(static_cast<unsigned short>(sr)));
+                    bi = __half2float(__ushort_as_half(static_cast<unsigned short>(br)));
+                } else {
+                    sc = __uint_as_float(sr << 16);
+                    bi = __uint_as_float(br << 16);
+                }
+                dequant_half<BITS>(wcur, sc, bi, row_smem + s * A_BYTES, h * 4, r7, f16);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> async proxy (MMA)
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&ctl->full_w[s]);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
+    }
+}
+
+// Work list of the gather case, built on the device from the CSR expert_offsets (or, when only the
+// per-row expert ids are given, from those: rows are sorted by expert, so offsets[e] is the first
+// row whose id is >= e).  Layout of the scratch block: int count; int pad[3]; int4 items[].
+// Expert-major order: the token chunks and weight-row tiles of one expert are adjacent, so the
+// CTAs working at the same time share that expert's X rows in L2.
+__global__ void build_items_kernel(const uint32_t *expert_offsets, const uint32_t *indices, int total_rows, int n_experts,
+                                   int n_tiles, int TN, int *count_out, int4 *items, int max_items) {
+    extern __shared__ int sh[];          // [n_experts + 1] offsets, then [n_experts + 1] item bases
+    int *off = sh, *base = sh + n_experts + 1;
+    for (int e = threadIdx.x; e <= n_experts; e += blockDim.x) {
+        if (expert_offsets) {
+            off[e] = static_cast<int>(expert_offsets[e]);
+        } else {                          // lower bound of e in the sorted per-row ids
+            int lo = 0, hi = total_rows;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (indices[mid] < static_cast<uint32_t>(e)) lo = mid + 1; else hi = mid;
+            }
+            off[e] = lo;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            base[e] = acc;
+            const int rows = max(off[e + 1] - off[e], 0);
+            acc += ((rows + TN - 1) / TN) * n_tiles;
+        }
+        base[n_experts] = acc;
+        *count_out = acc < max_items ? acc : max_items;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+        const int rows = max(off[e + 1] - off[e], 0);
+        const int chunks = (rows + TN - 1) / TN;
+        int idx = base[e];
+        for (int c = 0; c < chunks; ++c)
+            for (int nt = 0; nt < n_tiles; ++nt, ++idx)
+                if (idx < max_items) items[idx] = make_int4(nt, e, off[e] + c * TN, min(TN, rows - c * TN));
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+constexpr size_t kQmmSmem = STAGES * (A_BYTES + B_BYTES) + sizeof(SmemCtrl) + 1024;
+
+template <int BITS>
+cudaError_t launch_bits(cudaStream_t st, const CUtensorMap &tmap, const QmmParams &p, int grid) {
+    auto kern = qmm_tcgen05_kernel<BITS>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kQmmSmem));
+    if (e != cudaSuccess) return e;
+    kern<<<grid, NUM_THREADS, kQmmSmem, st>>>(tmap, p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_any(int bits, cudaStream_t st, const CUtensorMap &tmap, const QmmParams &p, int grid) {
+    switch (bits) {
+        case 2: return launch_bits<2>(st, tmap, p, grid);
+        case 3: return launch_bits<3>(st, tmap, p, grid);
+        case 4: return launch_bits<4>(st, tmap, p, grid);
+        case 5: return launch_bits<5>(st, tmap, p, grid);
+        case 6: return launch_bits<6>(st, tmap, p, grid);
+        default: return launch_bits<8>(st, tmap, p, grid);
+    }
+}
+
+// X as a 2-D tensor [rows, K] of 16-bit elements, box 64 x TN, 128-byte swizzle; rows past the end read as zero.
+cudaError_t make_x_map(CUtensorMap *tmap, const void *x, int rows, int K, int TN, int dt, std::string *why) {
+    EncodeTiledFn encode = get_encode_fn();
+    if (!encode) {
+        if (why) *why = "cuTensorMapEncodeTiled is not available from the driver";
+        return cudaErrorNotSupported;
+    }
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
+    const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(TN)};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(tmap, dt == MTC_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                        const_cast<void *>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        if (why) *why = "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r));
+        return cudaErrorInvalidValue;
+    }
+    return cudaSuccess;
+}
+
+void fill_common(QmmParams &p, Ctx *ctx, const void *w, const void *scales, const void *biases, void *out, int N, int K,
+                 int bits, int group_size, int dt, int TN) {
+    p.w = static_cast<const uint32_t *>(w);
+    p.scales = scales;
+    p.biases = biases;
+    p.out = out;
+    p.status = ctx->d_status;
+    p.N = N; p.K = K; p.dt = dt;
+    p.gs_shift = 0;
+    while ((1 << p.gs_shift) < group_size) ++p.gs_shift;
+    p.wpr = K * bits / 32;
+    p.gpr = K / group_size;
+    p.TN = TN;
+    const uint32_t fmt = dt == MTC_F16 ? 0u : 1u;      // both operands carry the activation type
+    p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(TN >> 3) << 17) |
+              (static_cast<uint32_t>(BMW >> 4) << 24);
+}
+
+}  // namespace
+
+bool qmm_tcgen05_supported(int M, int N, int K, int bits, int group_size, int dt, const void *w, const void *x,
+                           const void *out) {
+    const bool bits_ok = bits == 2 || bits == 3 || bits == 4 || bits == 5 || bits == 6 || bits == 8;
+    const bool gs_ok = group_size >= 32 && (group_size & (group_size - 1)) == 0 && K % group_size == 0;
+    const auto al = [](const void *ptr, size_t a) { return reinterpret_cast<uintptr_t>(ptr) % a == 0; };
+    return bits_ok && gs_ok && (dt == MTC_F16 || dt == MTC_BF16) && M > 0 && N > 0 && K % BK == 0 && al(w, 16) &&
+           al(x, 16) && al(out, 2);
+}
+
+cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases,
+                               const void *x, void *out, int M, int N, int K, int bits, int group_size, int dt,
+                               std::string *why) {
+    int TN = ctx->qmm_force_tn > 0 ? ctx->qmm_force_tn : (M >= TN_MAX ? TN_MAX : ((M + 15) / 16) * 16);
+    CUtensorMap tmap;
+    cudaError_t e = make_x_map(&tmap, x, M, K, TN, dt, why);
+    if (e != cudaSuccess) return e;
+    QmmParams p{};
+    fill_common(p, ctx, w, scales, biases, out, N, K, bits, group_size, dt, TN);
+    p.M = M;
+    p.m_chunks = (M + TN - 1) / TN;
+    p.dense_items = ((N + BMW - 1) / BMW) * p.m_chunks;
+    const int grid = p.dense_items < ctx->sm_count ? p.dense_items : ctx->sm_count;
+    return launch_any(bits, st, tmap, p, grid);
+}
+
+// scratch bytes the gather work list needs for these sizes
+size_t gather_items_bytes(int total_rows, int n_experts, int N, int TN) {
+    const size_t n_tiles = (N + BMW - 1) / BMW;
+    const size_t max_items = n_tiles * (static_cast<size_t>(total_rows) / TN + n_experts + 1);
+    return 16 + max_items * sizeof(int4);
+}
+
+cudaError_t launch_gather_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *x, const void *w, const void *scales,
+                                      const void *biases, const uint32_t *expert_offsets, const uint32_t *indices,
+                                      void *out, int total_rows, int N, int K, int n_experts, int bits, int group_size,
+                                      int dt, void *scratch, size_t scratch_bytes, std::string *why) {
+    // token rows per item: about twice the mean rows per expert, so most experts are one chunk
+    int TN = ctx->qmm_force_tn;
+    if (TN <= 0) {
+        const int mean = (total_rows + n_experts - 1) / n_experts;
+        TN = ((2 * mean + 15) / 16) * 16;
+        if (TN < 32) TN = 32;
+        if (TN > TN_MAX) TN = TN_MAX;
+    }
+    const size_t need = gather_items_bytes(total_rows, n_experts, N, TN);
+    if (!scratch || scratch_bytes < need) {
+        if (why) *why = "gather_qmm: work-list scratch too small";
+        return cudaErrorInvalidValue;
+    }
+    const int n_tiles = (N + BMW - 1) / BMW;
+    const int max_items = static_cast<int>((scratch_bytes - 16) / sizeof(int4));
+    int *count = static_cast<int *>(scratch);
+    int4 *items = reinterpret_cast<int4 *>(static_cast<char *>(scratch) + 16);
+    build_items_kernel<<<1, 256, 2 * (n_experts + 1) * sizeof(int), st>>>(expert_offsets, indices, total_rows, n_experts,
+                                                                         n_tiles, TN, count, items, max_items);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    CUtensorMap tmap;
+    e = make_x_map(&tmap, x, total_rows, K, TN, dt, why);
+    if (e != cudaSuccess) return e;
+    QmmParams p{};
+    fill_common(p, ctx, w, scales, biases, out, N, K, bits, group_size, dt, TN);
+    p.M = total_rows;
+    p.items = items;
+    p.item_count = count;
+    return launch_any(bits, st, tmap, p, ctx->sm_count);
+}
+
+}  // namespace mtc

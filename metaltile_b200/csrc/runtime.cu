@@ -33,7 +33,7 @@ bool dtype_ok(int dt) { return dt == MTC_F32 || dt == MTC_F16 || dt == MTC_BF16;
 // "gs_per_row" (hand-tuned int4/int8/mma kernels: group_size = k / gs_per_row) or
 // "group_size" (generic _b* family).  has_n: whether an `n` constexpr is bound
 // (mt_qmv / mt_qmv_int8_fast take N from the size of `out`).
-enum Family { DENSE_QMV, DENSE_QMM };
+enum Family { DENSE_QMV, DENSE_QMM, GATHER_CSR, GATHER_IDX, ROUTER_TOPK, MOE_PERMUTE, MOE_UNPERMUTE, SWIGLU };
 struct KernelRow {
     const char *name;
     Family family;
@@ -71,6 +71,27 @@ const KernelRow kKernels[] = {
     {"mt_qmm_b5", DENSE_QMV, 5, "group_size", true},
     {"mt_qmm_b6", DENSE_QMV, 6, "group_size", true},
     {"mt_qmm_b8", DENSE_QMV, 8, "group_size", true},
+    // MoE: crates/metaltile-std/src/ffai/moe.rs:65,222,283 (routing), :358,602-605,634,900,1363 (CSR gather),
+    // :2256,2832-2835,2857,3231 (per-row-index gather); crates/metaltile-std/src/mlx/swiglu.rs:45
+    {"mt_moe_router_topk", ROUTER_TOPK, -1, "", false},
+    {"mt_moe_permute", MOE_PERMUTE, -1, "", false},
+    {"mt_moe_unpermute", MOE_UNPERMUTE, -1, "", false},
+    {"mt_swiglu", SWIGLU, -1, "", false},
+    {"mt_moe_gather_qmm_int4", GATHER_CSR, 4, "group_size", false},
+    {"mt_moe_gather_qmm_int4_m8", GATHER_CSR, 4, "group_size", false},
+    {"mt_moe_gather_qmm_int4_m16", GATHER_CSR, 4, "group_size", false},
+    {"mt_moe_gather_qmm_int4_m32", GATHER_CSR, 4, "group_size", false},
+    {"mt_moe_gather_qmm_b3", GATHER_CSR, 3, "group_size", false},
+    {"mt_moe_gather_qmm_b5", GATHER_CSR, 5, "group_size", false},
+    {"mt_moe_gather_qmm_b6", GATHER_CSR, 6, "group_size", false},
+    {"mt_moe_gather_qmm_b8", GATHER_CSR, 8, "group_size", false},
+    {"mt_moe_gather_qmm_mma_int4", GATHER_IDX, 4, "group_size", false},
+    {"mt_moe_gather_qmm_mma_int4_bm16", GATHER_IDX, 4, "group_size", false},
+    {"mt_moe_gather_qmm_mma_int8", GATHER_IDX, 8, "group_size", false},
+    {"mt_moe_gather_qmm_mma_b3", GATHER_IDX, 3, "group_size", false},
+    {"mt_moe_gather_qmm_mma_b5", GATHER_IDX, 5, "group_size", false},
+    {"mt_moe_gather_qmm_mma_b6", GATHER_IDX, 6, "group_size", false},
+    {"mt_moe_gather_qmm_mma_b8", GATHER_IDX, 8, "group_size", false},
 };
 constexpr int kNumKernels = sizeof(kKernels) / sizeof(kKernels[0]);
 
@@ -106,6 +127,25 @@ int ensure_scratch(Ctx *ctx, size_t bytes) {
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+int ensure_worklist(Ctx *ctx, size_t bytes) {
+    if (bytes <= ctx->worklist_bytes) return MTC_OK;
+    if (ctx->d_worklist) cudaFree(ctx->d_worklist);
+    ctx->d_worklist = nullptr;
+    ctx->worklist_bytes = 0;
+    const size_t want = bytes * 2 + (1u << 20);
+    MTC_CUDA(ctx, cudaMalloc(&ctx->d_worklist, want), MTC_ERR_BUFFER);
+    ctx->worklist_bytes = want;
+    return MTC_OK;
+}
+
+// One named host buffer staged in the context's scratch block for mtc_dispatch.
+struct Staged {
+    mtc_named_buf *buf;
+    size_t need;       // bytes the kernel touches (checked against buf->bytes)
+    size_t offset;     // offset in scratch
+    char *dev;
+};
+
 }  // namespace
 
 extern "C" {
@@ -140,11 +180,13 @@ int mtc_init(int device, mtc_ctx **out_ctx) {
     ctx->l2_bytes = static_cast<size_t>(prop.l2CacheSize);
     if ((e = cudaMalloc(&ctx->d_status, sizeof(uint32_t))) != cudaSuccess ||
         (e = cudaMemset(ctx->d_status, 0, sizeof(uint32_t))) != cudaSuccess ||
-        (e = mtc::qmv_init_device()) != cudaSuccess) {
+        (e = mtc::qmv_init_device()) != cudaSuccess ||
+        (e = cudaMalloc(&ctx->d_worklist, 4u << 20)) != cudaSuccess) {
         g_no_ctx_error = std::string("context set-up: ") + cudaGetErrorString(e);
         delete ctx;
         return MTC_ERR_DISPATCH;
     }
+    ctx->worklist_bytes = 4u << 20;
     *out_ctx = ctx;
     return MTC_OK;
 }
@@ -154,6 +196,7 @@ int mtc_destroy(mtc_ctx *ctx) {
     cudaSetDevice(ctx->device);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->d_scratch) cudaFree(ctx->d_scratch);
+    if (ctx->d_worklist) cudaFree(ctx->d_worklist);
     delete ctx;
     return MTC_OK;
 }
@@ -238,15 +281,136 @@ int mtc_qmv(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
     return MTC_OK;
 }
 
+// mt_qmm_for (crates/metaltile-std/src/mlx/quantized.rs:5040-5065) picks by M alone; here M <= 16 or
+// f32 activations stay on the CUDA-core kernels, everything else goes to the tensor cores when the
+// shape meets that kernel's contract (K % 64 == 0, power-of-two group >= 32).
 const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dtype) {
-    (void)N; (void)K; (void)bits; (void)group_size;
-    if (M <= 16 || dtype == MTC_F32) return "qmv_cuda_core";
+    if (M > 16 && mtc::qmm_tcgen05_supported(M, N, K, bits, group_size, dtype, nullptr, nullptr, nullptr))
+        return "qmm_tcgen05";
     return "qmv_cuda_core";
 }
 
 int mtc_qmm(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x,
             void *out, int M, int N, int K, int bits, int group_size, int dtype) {
+    if (!ctx) return MTC_ERR_INVALID;
+    if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "qmm: dtype must be f32, f16 or bf16");
+    if (M > 16 && mtc::qmm_tcgen05_supported(M, N, K, bits, group_size, dtype, w, x, out)) {
+        if (!w || !scales || !biases || !x || !out) return fail(ctx, MTC_ERR_INVALID, "qmm: null pointer");
+        std::string why;
+        cudaError_t e = mtc::launch_qmm_tcgen05(ctx, static_cast<cudaStream_t>(stream), w, scales, biases, x, out, M,
+                                                N, K, bits, group_size, dtype, &why);
+        if (e != cudaSuccess)
+            return fail(ctx, MTC_ERR_DISPATCH, "qmm launch: " + (why.empty() ? std::string(cudaGetErrorString(e)) : why));
+        return MTC_OK;
+    }
     return mtc_qmv(ctx, stream, w, scales, biases, x, out, M, N, K, bits, group_size, dtype);
+}
+
+int mtc_set_option(mtc_ctx *ctx, const char *name, int value) {
+    if (!ctx || !name) return MTC_ERR_INVALID;
+    if (std::strcmp(name, "qmm_tile_tokens") == 0) {
+        if (value != 0 && (value < 16 || value > 256 || value % 16 != 0))
+            return fail(ctx, MTC_ERR_UNSUPPORTED, "qmm_tile_tokens must be 0 or a multiple of 16 in [16, 256]");
+        ctx->qmm_force_tn = value;
+        return MTC_OK;
+    }
+    return fail(ctx, MTC_ERR_UNSUPPORTED, std::string("unknown option: ") + name);
+}
+
+int mtc_gather_qmm(mtc_ctx *ctx, void *stream, const void *x, const void *w, const void *scales, const void *biases,
+                   const void *expert_offsets, const void *indices, void *out, int m_total, int n_out, int k_in,
+                   int n_experts, int bits, int group_size, int dtype) {
+    if (!ctx) return MTC_ERR_INVALID;
+    if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "gather_qmm: dtype must be f32, f16 or bf16");
+    if ((expert_offsets == nullptr) == (indices == nullptr))
+        return fail(ctx, MTC_ERR_INVALID, "gather_qmm: give exactly one of expert_offsets and indices");
+    const bool bits_ok = bits == 2 || bits == 3 || bits == 4 || bits == 5 || bits == 6 || bits == 8;
+    if (!bits_ok || m_total < 0 || n_out < 0 || k_in <= 0 || n_experts <= 0 || group_size <= 0 || k_in % group_size != 0 ||
+        (static_cast<long long>(k_in) * bits) % 32 != 0)
+        return fail(ctx, MTC_ERR_UNSUPPORTED,
+                    "gather_qmm: need bits in {2,3,4,5,6,8}, group_size | k_in, k_in*bits % 32 == 0, n_experts > 0");
+    if (m_total == 0 || n_out == 0) return MTC_OK;
+    if (!x || !w || !scales || !biases || !out) return fail(ctx, MTC_ERR_INVALID, "gather_qmm: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (mtc::qmm_tcgen05_supported(m_total, n_out, k_in, bits, group_size, dtype, w, x, out) && n_experts <= 4096) {
+        int rc = ensure_worklist(ctx, mtc::gather_items_bytes(m_total, n_experts, n_out, 16));
+        if (rc != MTC_OK) return rc;
+        std::string why;
+        cudaError_t e = mtc::launch_gather_qmm_tcgen05(ctx, st, x, w, scales, biases,
+                                                       static_cast<const uint32_t *>(expert_offsets),
+                                                       static_cast<const uint32_t *>(indices), out, m_total, n_out, k_in,
+                                                       n_experts, bits, group_size, dtype, ctx->d_worklist,
+                                                       ctx->worklist_bytes, &why);
+        if (e != cudaSuccess)
+            return fail(ctx, MTC_ERR_DISPATCH, "gather_qmm launch: " + (why.empty() ? std::string(cudaGetErrorString(e)) : why));
+        return MTC_OK;
+    }
+    MTC_CUDA(ctx, mtc::launch_gather_generic(st, x, w, scales, biases, static_cast<const uint32_t *>(expert_offsets),
+                                             static_cast<const uint32_t *>(indices), out, m_total, k_in, n_out, n_experts,
+                                             bits, group_size, dtype), MTC_ERR_DISPATCH);
+    return MTC_OK;
+}
+
+const char *mtc_gather_qmm_route(int m_total, int n_out, int k_in, int bits, int group_size, int dtype) {
+    return mtc::qmm_tcgen05_supported(m_total, n_out, k_in, bits, group_size, dtype, nullptr, nullptr, nullptr)
+               ? "gather_qmm_tcgen05" : "gather_qmm_cuda_core";
+}
+
+int mtc_moe_router_topk(mtc_ctx *ctx, void *stream, const void *router_logits, void *indices_out, void *weights_out,
+                        int n_rows, int n_experts, int k, int norm_topk_prob, int dtype) {
+    if (!ctx) return MTC_ERR_INVALID;
+    if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "router_topk: dtype must be f32, f16 or bf16");
+    // k <= 32 is the reference's hard cap (crates/metaltile-std/src/ffai/moe.rs:88-91); n_experts <= 32 * 32
+    if (n_rows < 0 || n_experts <= 0 || n_experts > 1024 || k <= 0 || k > 32 || k > n_experts)
+        return fail(ctx, MTC_ERR_UNSUPPORTED, "router_topk: need 0 < k <= min(32, n_experts), n_experts <= 1024");
+    if (n_rows > 0 && (!router_logits || !indices_out || !weights_out)) return fail(ctx, MTC_ERR_INVALID, "router_topk: null pointer");
+    MTC_CUDA(ctx, mtc::launch_router_topk(static_cast<cudaStream_t>(stream), router_logits, static_cast<uint32_t *>(indices_out),
+                                          weights_out, n_rows, n_experts, k, norm_topk_prob, dtype), MTC_ERR_DISPATCH);
+    return MTC_OK;
+}
+
+int mtc_moe_sort(mtc_ctx *ctx, void *stream, const void *topk_idx, int n_tokens, int k, int n_experts, void *sort_token_idx,
+                 void *inv_perm, void *expert_offsets, void *row_expert) {
+    if (!ctx) return MTC_ERR_INVALID;
+    if (n_tokens < 0 || k <= 0 || n_experts <= 0 || n_experts > 1024)
+        return fail(ctx, MTC_ERR_UNSUPPORTED, "moe_sort: need k > 0 and 0 < n_experts <= 1024");
+    if (!expert_offsets || (n_tokens > 0 && (!topk_idx || !sort_token_idx || !inv_perm)))
+        return fail(ctx, MTC_ERR_INVALID, "moe_sort: null pointer");
+    MTC_CUDA(ctx, mtc::launch_moe_sort(static_cast<cudaStream_t>(stream), static_cast<const uint32_t *>(topk_idx), n_tokens, k,
+                                       n_experts, static_cast<uint32_t *>(sort_token_idx), static_cast<uint32_t *>(inv_perm),
+                                       static_cast<uint32_t *>(expert_offsets), static_cast<uint32_t *>(row_expert),
+                                       ctx->d_status), MTC_ERR_DISPATCH);
+    return MTC_OK;
+}
+
+int mtc_moe_permute(mtc_ctx *ctx, void *stream, const void *tokens, const void *sort_token_idx, void *permuted, int n_rows,
+                    int hidden, int dtype) {
+    if (!ctx) return MTC_ERR_INVALID;
+    if (!dtype_ok(dtype) || n_rows < 0 || hidden <= 0) return fail(ctx, MTC_ERR_UNSUPPORTED, "moe_permute: bad dtype or shape");
+    if (n_rows > 0 && (!tokens || !sort_token_idx || !permuted)) return fail(ctx, MTC_ERR_INVALID, "moe_permute: null pointer");
+    MTC_CUDA(ctx, mtc::launch_permute(static_cast<cudaStream_t>(stream), tokens, static_cast<const uint32_t *>(sort_token_idx),
+                                      permuted, n_rows, hidden, dtype), MTC_ERR_DISPATCH);
+    return MTC_OK;
+}
+
+int mtc_moe_unpermute(mtc_ctx *ctx, void *stream, const void *expert_outputs, const void *inv_perm, const void *top_k_weights,
+                      void *out, int n_tokens, int hidden, int k, int dtype) {
+    if (!ctx) return MTC_ERR_INVALID;
+    if (!dtype_ok(dtype) || n_tokens < 0 || hidden <= 0 || k <= 0)
+        return fail(ctx, MTC_ERR_UNSUPPORTED, "moe_unpermute: bad dtype or shape");
+    if (n_tokens > 0 && (!expert_outputs || !inv_perm || !top_k_weights || !out))
+        return fail(ctx, MTC_ERR_INVALID, "moe_unpermute: null pointer");
+    MTC_CUDA(ctx, mtc::launch_unpermute(static_cast<cudaStream_t>(stream), expert_outputs, static_cast<const uint32_t *>(inv_perm),
+                                        top_k_weights, out, n_tokens, hidden, k, dtype), MTC_ERR_DISPATCH);
+    return MTC_OK;
+}
+
+int mtc_swiglu(mtc_ctx *ctx, void *stream, const void *gate, const void *up, void *out, size_t n, int dtype) {
+    if (!ctx) return MTC_ERR_INVALID;
+    if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "swiglu: dtype must be f32, f16 or bf16");
+    if (n > 0 && (!gate || !up || !out)) return fail(ctx, MTC_ERR_INVALID, "swiglu: null pointer");
+    MTC_CUDA(ctx, mtc::launch_swiglu(static_cast<cudaStream_t>(stream), gate, up, out, n, dtype), MTC_ERR_DISPATCH);
+    return MTC_OK;
 }
 
 int mtc_unpack_codes(mtc_ctx *ctx, void *stream, const void *w, void *codes_u8, int N, int K, int bits) {
@@ -268,68 +432,189 @@ int mtc_dispatch(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_buf
     const KernelRow *row = find_kernel(kernel_name);
     if (!row) return fail(ctx, MTC_ERR_FUNCTION_NOT_FOUND, std::string("unknown kernel: ") + kernel_name);
     const size_t esz = mtc::dtype_size(dtype);
+    const std::string kn(kernel_name);
 
-    mtc_named_buf *bw = find_buf(bufs, n_bufs, "w"), *bs = find_buf(bufs, n_bufs, "scales"),
-                  *bb = find_buf(bufs, n_bufs, "biases"), *bx = find_buf(bufs, n_bufs, "x"),
-                  *bo = find_buf(bufs, n_bufs, "out");
-    if (!bw || !bs || !bb || !bx || !bo)
-        return fail(ctx, MTC_ERR_BUFFER, std::string(kernel_name) + ": buffers w, scales, biases, x, out must be bound");
-    uint32_t k = 0, n = 0, gsc = 0;
-    if (!read_const(bufs, n_bufs, "k", &k) || k == 0)
-        return fail(ctx, MTC_ERR_BUFFER, std::string(kernel_name) + ": constexpr k missing");
-    if (!read_const(bufs, n_bufs, row->gs_const, &gsc) || gsc == 0)
-        return fail(ctx, MTC_ERR_BUFFER, std::string(kernel_name) + ": constexpr " + row->gs_const + " missing");
-    const uint32_t group_size = std::strcmp(row->gs_const, "gs_per_row") == 0 ? k / gsc : gsc;
-    if (group_size == 0 || k % group_size != 0)
-        return fail(ctx, MTC_ERR_UNSUPPORTED, std::string(kernel_name) + ": group size must divide k");
-    if (row->has_n) {
-        if (!read_const(bufs, n_bufs, "n", &n) || n == 0)
-            return fail(ctx, MTC_ERR_BUFFER, std::string(kernel_name) + ": constexpr n missing");
-    } else {
-        n = static_cast<uint32_t>(bo->bytes / esz);  // mt_qmv: M = 1, N = len(out)
+    // ---- bind buffers and constexprs by name, derive the shape, compute the bytes each buffer must hold
+    std::vector<Staged> st_bufs;
+    std::string err;
+    auto need_buf = [&](const char *name, size_t need) -> Staged * {
+        mtc_named_buf *b = find_buf(bufs, n_bufs, name);
+        if (!b || !b->data) { if (err.empty()) err = kn + ": buffer '" + name + "' must be bound"; return nullptr; }
+        st_bufs.push_back(Staged{b, need, 0, nullptr});
+        return &st_bufs.back();
+    };
+    auto need_const = [&](const char *name, uint32_t *v) {
+        if (!read_const(bufs, n_bufs, name, v) && err.empty()) err = kn + ": constexpr " + name + " missing";
+    };
+    st_bufs.reserve(8);
+    uint32_t k = 0, n = 0, gsc = 0, k_in = 0, m_out = 0, n_exp = 0, gs = 0, hidden = 0, topk = 0, norm = 1, m_total = 0;
+    size_t m = 0, rows = 0;
+    switch (row->family) {
+        case DENSE_QMV:
+        case DENSE_QMM: {
+            need_const("k", &k);
+            need_const(row->gs_const, &gsc);
+            if (row->has_n) need_const("n", &n);
+            if (!err.empty()) break;
+            mtc_named_buf *bx = find_buf(bufs, n_bufs, "x"), *bo = find_buf(bufs, n_bufs, "out");
+            if (!bx || !bo) { err = kn + ": buffers w, scales, biases, x, out must be bound"; break; }
+            if (k == 0 || gsc == 0) { err = kn + ": k and the group constexpr must be positive"; break; }
+            gs = std::strcmp(row->gs_const, "gs_per_row") == 0 ? k / gsc : gsc;
+            if (gs == 0 || k % gs != 0) return fail(ctx, MTC_ERR_UNSUPPORTED, kn + ": group size must divide k");
+            if (!row->has_n) n = static_cast<uint32_t>(bo->bytes / esz);  // mt_qmv: M = 1, N = len(out)
+            m = bx->bytes / (static_cast<size_t>(k) * esz);
+            if (m == 0) return fail(ctx, MTC_ERR_BUFFER_SIZE, kn + ": x holds less than one row of k");
+            if ((static_cast<unsigned long long>(k) * row->bits) % 32 != 0)
+                return fail(ctx, MTC_ERR_UNSUPPORTED, kn + ": k*bits must be a multiple of 32");
+            need_buf("w", static_cast<size_t>(n) * k * row->bits / 8);
+            need_buf("scales", static_cast<size_t>(n) * (k / gs) * esz);
+            need_buf("biases", static_cast<size_t>(n) * (k / gs) * esz);
+            need_buf("x", m * k * esz);
+            need_buf("out", m * n * esz);
+            break;
+        }
+        case GATHER_CSR:
+        case GATHER_IDX: {
+            const bool csr = row->family == GATHER_CSR;
+            need_const("k_in", &k_in);
+            need_const("group_size", &gs);
+            if (csr) { need_const("m_out", &m_out); need_const("n_experts", &n_exp); }
+            else { need_const("n_out", &m_out); need_const("m_total", &m_total); }
+            if (!err.empty()) break;
+            mtc_named_buf *bx = find_buf(bufs, n_bufs, "x");
+            mtc_named_buf *bw = find_buf(bufs, n_bufs, csr ? "weight_packed" : "w");
+            if (!bx || !bw) { err = kn + ": buffers x and " + (csr ? "weight_packed" : "w") + " must be bound"; break; }
+            if (k_in == 0 || gs == 0 || m_out == 0 || k_in % gs != 0 || (static_cast<unsigned long long>(k_in) * row->bits) % 32 != 0)
+                return fail(ctx, MTC_ERR_UNSUPPORTED, kn + ": need k_in*bits % 32 == 0 and group_size | k_in");
+            rows = csr ? bx->bytes / (static_cast<size_t>(k_in) * esz) : m_total;
+            const size_t w_per_expert = static_cast<size_t>(m_out) * k_in * row->bits / 8;
+            if (!csr) n_exp = static_cast<uint32_t>(bw->bytes / w_per_expert);   // stacked [E, n_out, k_in*bits/32]
+            if (n_exp == 0) return fail(ctx, MTC_ERR_BUFFER_SIZE, kn + ": weights hold less than one expert");
+            need_buf("x", rows * k_in * esz);
+            need_buf(csr ? "weight_packed" : "w", static_cast<size_t>(n_exp) * w_per_expert);
+            need_buf("scales", static_cast<size_t>(n_exp) * m_out * (k_in / gs) * esz);
+            need_buf("biases", static_cast<size_t>(n_exp) * m_out * (k_in / gs) * esz);
+            need_buf(csr ? "expert_offsets" : "indices", csr ? (static_cast<size_t>(n_exp) + 1) * 4 : rows * 4);
+            need_buf("out", rows * m_out * esz);
+            break;
+        }
+        case ROUTER_TOPK: {
+            need_const("n_experts", &n_exp);
+            need_const("k", &topk);
+            if (!read_const(bufs, n_bufs, "norm_topk_prob", &norm)) norm = 1;
+            if (!err.empty()) break;
+            mtc_named_buf *bl = find_buf(bufs, n_bufs, "router_logits");
+            if (!bl) { err = kn + ": buffer 'router_logits' must be bound"; break; }
+            if (n_exp == 0) { err = kn + ": n_experts must be positive"; break; }
+            rows = bl->bytes / (static_cast<size_t>(n_exp) * esz);
+            need_buf("router_logits", rows * n_exp * esz);
+            need_buf("indices_out", rows * topk * 4);
+            need_buf("weights_out", rows * topk * esz);
+            break;
+        }
+        case MOE_PERMUTE: {
+            need_const("hidden", &hidden);
+            if (!err.empty()) break;
+            mtc_named_buf *bi = find_buf(bufs, n_bufs, "sort_token_idx"), *bt = find_buf(bufs, n_bufs, "tokens");
+            if (!bi || !bt) { err = kn + ": buffers tokens, sort_token_idx, permuted must be bound"; break; }
+            rows = bi->bytes / 4;
+            need_buf("tokens", bt->bytes);   // row indices are data: the kernel reads the rows they name
+            need_buf("sort_token_idx", rows * 4);
+            need_buf("permuted", rows * hidden * esz);
+            break;
+        }
+        case MOE_UNPERMUTE: {
+            need_const("hidden", &hidden);
+            need_const("k", &topk);
+            if (!err.empty()) break;
+            mtc_named_buf *bi = find_buf(bufs, n_bufs, "inv_perm");
+            if (!bi || topk == 0) { err = kn + ": buffer 'inv_perm' must be bound and k positive"; break; }
+            rows = bi->bytes / (4 * static_cast<size_t>(topk));
+            need_buf("expert_outputs", rows * topk * hidden * esz);
+            need_buf("inv_perm", rows * topk * 4);
+            need_buf("top_k_weights", rows * topk * esz);
+            need_buf("out", rows * hidden * esz);
+            break;
+        }
+        case SWIGLU: {
+            mtc_named_buf *bg = find_buf(bufs, n_bufs, "gate");
+            if (!bg) { err = kn + ": buffer 'gate' must be bound"; break; }
+            rows = bg->bytes / esz;
+            need_buf("gate", rows * esz);
+            need_buf("up", rows * esz);
+            need_buf("out", rows * esz);
+            break;
+        }
     }
-    const size_t m = bx->bytes / (static_cast<size_t>(k) * esz);
-    if (m == 0) return fail(ctx, MTC_ERR_BUFFER_SIZE, std::string(kernel_name) + ": x holds less than one row of k");
-    if ((static_cast<unsigned long long>(k) * row->bits) % 32 != 0)
-        return fail(ctx, MTC_ERR_UNSUPPORTED, std::string(kernel_name) + ": k*bits must be a multiple of 32");
-    const size_t need_w = static_cast<size_t>(n) * k * row->bits / 8;
-    const size_t need_sb = static_cast<size_t>(n) * (k / group_size) * esz;
-    const size_t need_x = m * k * esz, need_o = m * n * esz;
+    if (!err.empty()) return fail(ctx, MTC_ERR_BUFFER, err);
     // An undersized buffer is an error (crates/metaltile-runtime/src/dispatch/buffer_plan.rs:68-76).
-    if (bw->bytes < need_w) return fail(ctx, MTC_ERR_BUFFER_SIZE, "buffer 'w' smaller than n*k*bits/8 bytes");
-    if (bs->bytes < need_sb) return fail(ctx, MTC_ERR_BUFFER_SIZE, "buffer 'scales' smaller than n*(k/group) elements");
-    if (bb->bytes < need_sb) return fail(ctx, MTC_ERR_BUFFER_SIZE, "buffer 'biases' smaller than n*(k/group) elements");
-    if (bo->bytes < need_o) return fail(ctx, MTC_ERR_BUFFER_SIZE, "buffer 'out' smaller than m*n elements");
-
+    size_t total = 0;
+    for (Staged &sb : st_bufs) {
+        if (sb.buf->bytes < sb.need)
+            return fail(ctx, MTC_ERR_BUFFER_SIZE, kn + ": buffer '" + sb.buf->name + "' holds " + std::to_string(sb.buf->bytes) +
+                                                     " bytes, the kernel needs " + std::to_string(sb.need));
+        sb.offset = total;
+        total += align_up(sb.need ? sb.need : 1, 256);
+    }
     MTC_CUDA(ctx, cudaSetDevice(ctx->device), MTC_ERR_NO_DEVICE);
-    const size_t o_w = 0, o_s = align_up(need_w, 256), o_b = o_s + align_up(need_sb, 256),
-                 o_x = o_b + align_up(need_sb, 256), o_o = o_x + align_up(need_x, 256);
-    int rc = ensure_scratch(ctx, o_o + align_up(need_o, 256));
+    int rc = ensure_scratch(ctx, total);
     if (rc != MTC_OK) return rc;
-    char *base = static_cast<char *>(ctx->d_scratch);
     cudaStream_t st = nullptr;
-    MTC_CUDA(ctx, cudaMemcpyAsync(base + o_w, bw->data, need_w, cudaMemcpyHostToDevice, st), MTC_ERR_BUFFER);
-    MTC_CUDA(ctx, cudaMemcpyAsync(base + o_s, bs->data, need_sb, cudaMemcpyHostToDevice, st), MTC_ERR_BUFFER);
-    MTC_CUDA(ctx, cudaMemcpyAsync(base + o_b, bb->data, need_sb, cudaMemcpyHostToDevice, st), MTC_ERR_BUFFER);
-    MTC_CUDA(ctx, cudaMemcpyAsync(base + o_x, bx->data, need_x, cudaMemcpyHostToDevice, st), MTC_ERR_BUFFER);
-    MTC_CUDA(ctx, cudaMemcpyAsync(base + o_o, bo->data, need_o, cudaMemcpyHostToDevice, st), MTC_ERR_BUFFER);
+    for (Staged &sb : st_bufs) {
+        sb.dev = static_cast<char *>(ctx->d_scratch) + sb.offset;
+        if (sb.need) MTC_CUDA(ctx, cudaMemcpyAsync(sb.dev, sb.buf->data, sb.need, cudaMemcpyHostToDevice, st), MTC_ERR_BUFFER);
+    }
+    auto dev = [&](const char *name) -> char * {
+        for (Staged &sb : st_bufs)
+            if (std::strcmp(sb.buf->name, name) == 0) return sb.dev;
+        return nullptr;
+    };
     cudaEvent_t e0 = nullptr, e1 = nullptr;
     if (elapsed_us) {
         MTC_CUDA(ctx, cudaEventCreate(&e0), MTC_ERR_DISPATCH);
         MTC_CUDA(ctx, cudaEventCreate(&e1), MTC_ERR_DISPATCH);
         cudaEventRecord(e0, st);
     }
-    if (row->family == DENSE_QMM)
-        rc = mtc_qmm(ctx, st, base + o_w, base + o_s, base + o_b, base + o_x, base + o_o, static_cast<int>(m),
-                     static_cast<int>(n), static_cast<int>(k), row->bits, static_cast<int>(group_size), dtype);
-    else
-        rc = mtc_qmv(ctx, st, base + o_w, base + o_s, base + o_b, base + o_x, base + o_o, static_cast<int>(m),
-                     static_cast<int>(n), static_cast<int>(k), row->bits, static_cast<int>(group_size), dtype);
+    switch (row->family) {
+        case DENSE_QMM:
+            rc = mtc_qmm(ctx, st, dev("w"), dev("scales"), dev("biases"), dev("x"), dev("out"), static_cast<int>(m),
+                         static_cast<int>(n), static_cast<int>(k), row->bits, static_cast<int>(gs), dtype);
+            break;
+        case DENSE_QMV:
+            rc = mtc_qmv(ctx, st, dev("w"), dev("scales"), dev("biases"), dev("x"), dev("out"), static_cast<int>(m),
+                         static_cast<int>(n), static_cast<int>(k), row->bits, static_cast<int>(gs), dtype);
+            break;
+        case GATHER_CSR:
+            rc = mtc_gather_qmm(ctx, st, dev("x"), dev("weight_packed"), dev("scales"), dev("biases"), dev("expert_offsets"),
+                                nullptr, dev("out"), static_cast<int>(rows), static_cast<int>(m_out), static_cast<int>(k_in),
+                                static_cast<int>(n_exp), row->bits, static_cast<int>(gs), dtype);
+            break;
+        case GATHER_IDX:
+            rc = mtc_gather_qmm(ctx, st, dev("x"), dev("w"), dev("scales"), dev("biases"), nullptr, dev("indices"), dev("out"),
+                                static_cast<int>(rows), static_cast<int>(m_out), static_cast<int>(k_in), static_cast<int>(n_exp),
+                                row->bits, static_cast<int>(gs), dtype);
+            break;
+        case ROUTER_TOPK:
+            rc = mtc_moe_router_topk(ctx, st, dev("router_logits"), dev("indices_out"), dev("weights_out"), static_cast<int>(rows),
+                                     static_cast<int>(n_exp), static_cast<int>(topk), static_cast<int>(norm), dtype);
+            break;
+        case MOE_PERMUTE:
+            rc = mtc_moe_permute(ctx, st, dev("tokens"), dev("sort_token_idx"), dev("permuted"), static_cast<int>(rows),
+                                 static_cast<int>(hidden), dtype);
+            break;
+        case MOE_UNPERMUTE:
+            rc = mtc_moe_unpermute(ctx, st, dev("expert_outputs"), dev("inv_perm"), dev("top_k_weights"), dev("out"),
+                                   static_cast<int>(rows), static_cast<int>(hidden), static_cast<int>(topk), dtype);
+            break;
+        case SWIGLU:
+            rc = mtc_swiglu(ctx, st, dev("gate"), dev("up"), dev("out"), rows, dtype);
+            break;
+    }
     if (elapsed_us) cudaEventRecord(e1, st);
     if (rc == MTC_OK) {
-        for (int i = 0; i < n_bufs; ++i)
-            if (bufs[i].is_output && &bufs[i] == bo)
-                cudaMemcpyAsync(bo->data, base + o_o, need_o, cudaMemcpyDeviceToHost, st);
+        // every is_output parameter is read back (crates/metaltile-runtime/src/dispatch/single_dispatch.rs:100-117)
+        for (Staged &sb : st_bufs)
+            if (sb.buf->is_output && sb.need) cudaMemcpyAsync(sb.buf->data, sb.dev, sb.need, cudaMemcpyDeviceToHost, st);
         cudaError_t e = cudaStreamSynchronize(st);
         if (e != cudaSuccess) rc = fail(ctx, MTC_ERR_DISPATCH, std::string("dispatch: ") + cudaGetErrorString(e));
     }

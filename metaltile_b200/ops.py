@@ -76,3 +76,82 @@ def unpack_codes(w, K: int, bits: int, ctx: Context = None):
     ctx = ctx or context(w.device)
     ctx.unpack_codes(w.data_ptr(), codes.data_ptr(), N, K, bits, _stream())
     return codes
+
+
+# ---- MoE -----------------------------------------------------------------------------------------
+def moe_router_topk(logits, k: int, norm_topk_prob: int = 1, ctx: Context = None):
+    """(indices int32[rows, k], weights T[rows, k]) of ``mt_moe_router_topk``."""
+    rows, n_experts = logits.shape
+    idx = torch.empty((rows, k), dtype=torch.int32, device=logits.device)
+    wts = torch.empty((rows, k), dtype=logits.dtype, device=logits.device)
+    ctx = ctx or context(logits.device)
+    ctx.moe_router_topk(logits.data_ptr(), idx.data_ptr(), wts.data_ptr(), rows, n_experts, k, norm_topk_prob,
+                        _TORCH_DT[logits.dtype], _stream())
+    return idx, wts
+
+
+def moe_sort(topk_idx, n_experts: int, ctx: Context = None):
+    """Stable expert sort: (sort_token_idx[T*k], inv_perm[T, k], expert_offsets[E+1], row_expert[T*k]), int32."""
+    n_tokens, k = topk_idx.shape
+    dev = topk_idx.device
+    sti = torch.empty(n_tokens * k, dtype=torch.int32, device=dev)
+    inv = torch.empty((n_tokens, k), dtype=torch.int32, device=dev)
+    off = torch.empty(n_experts + 1, dtype=torch.int32, device=dev)
+    rex = torch.empty(n_tokens * k, dtype=torch.int32, device=dev)
+    ctx = ctx or context(dev)
+    ctx.moe_sort(topk_idx.data_ptr(), n_tokens, k, n_experts, sti.data_ptr(), inv.data_ptr(), off.data_ptr(),
+                 rex.data_ptr(), _stream())
+    return sti, inv, off, rex
+
+
+def moe_permute(tokens, sort_token_idx, out=None, ctx: Context = None):
+    rows, hidden = sort_token_idx.numel(), tokens.shape[1]
+    if out is None:
+        out = torch.empty((rows, hidden), dtype=tokens.dtype, device=tokens.device)
+    ctx = ctx or context(tokens.device)
+    ctx.moe_permute(tokens.data_ptr(), sort_token_idx.data_ptr(), out.data_ptr(), rows, hidden,
+                    _TORCH_DT[tokens.dtype], _stream())
+    return out
+
+
+def moe_unpermute(expert_outputs, inv_perm, weights, out=None, ctx: Context = None):
+    n_tokens, k = inv_perm.shape
+    hidden = expert_outputs.shape[1]
+    if out is None:
+        out = torch.empty((n_tokens, hidden), dtype=expert_outputs.dtype, device=expert_outputs.device)
+    ctx = ctx or context(expert_outputs.device)
+    ctx.moe_unpermute(expert_outputs.data_ptr(), inv_perm.data_ptr(), weights.data_ptr(), out.data_ptr(), n_tokens,
+                      hidden, k, _TORCH_DT[expert_outputs.dtype], _stream())
+    return out
+
+
+def swiglu(gate, up, out=None, ctx: Context = None):
+    if out is None:
+        out = torch.empty_like(gate)
+    ctx = ctx or context(gate.device)
+    ctx.swiglu(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(), _TORCH_DT[gate.dtype], _stream())
+    return out
+
+
+def gather_qmm(x, w, scales, biases, bits: int, group_size: int, expert_offsets=None, indices=None, out=None,
+               ctx: Context = None):
+    """out[t, n] = sum_k x[t, k] * dequant(w[E(t)])[n, k]; x rows sorted by expert; w [E, n_out, k*bits/32]."""
+    if (expert_offsets is None) == (indices is None):
+        raise ValueError("give exactly one of expert_offsets and indices")
+    m_total, k_in = x.shape
+    n_experts, n_out = w.shape[0], w.shape[1]
+    if w.shape[2] * 32 != k_in * bits:
+        raise ValueError("w must be [E, n_out, k_in*bits/32]")
+    if scales.shape != (n_experts, n_out, k_in // group_size) or biases.shape != scales.shape:
+        raise ValueError("scales/biases must be [E, n_out, k_in/group_size]")
+    for t in (x, w, scales, biases):
+        if not t.is_contiguous():
+            raise ValueError("operands must be contiguous")
+    if out is None:
+        out = torch.empty((m_total, n_out), dtype=x.dtype, device=x.device)
+    ctx = ctx or context(x.device)
+    ctx.gather_qmm(x.data_ptr(), w.data_ptr(), scales.data_ptr(), biases.data_ptr(), out.data_ptr(), m_total, n_out,
+                   k_in, n_experts, bits, group_size, _TORCH_DT[x.dtype],
+                   expert_offsets=None if expert_offsets is None else expert_offsets.data_ptr(),
+                   indices=None if indices is None else indices.data_ptr(), stream=_stream())
+    return out

@@ -1,0 +1,103 @@
+"""Parity of the tensor-core (tcgen05) prefill qmm with the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+import oracle
+from helpers import TOL, dense_case, rel_err, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    from metaltile_b200 import ops
+    return ops.context(0)
+
+
+def run_qmm(w, s, b, x, bits, gs, dt):
+    import torch
+    from metaltile_b200 import ops
+    out = ops.qmm(to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt), bits, gs)
+    torch.cuda.synchronize()
+    return out.float().cpu().numpy()
+
+
+def test_routing_follows_m_and_dtype(ctx):
+    """The selector (mt_qmm_for, crates/metaltile-std/src/mlx/quantized.rs:5040-5065,5127-5199) in this back end."""
+    assert ctx.qmm_route(1, 4096, 4096, 4, 64, "bf16") == "qmv_cuda_core"
+    assert ctx.qmm_route(16, 4096, 4096, 4, 64, "bf16") == "qmv_cuda_core"
+    assert ctx.qmm_route(17, 4096, 4096, 4, 64, "bf16") == "qmm_tcgen05"
+    assert ctx.qmm_route(2048, 14336, 4096, 4, 64, "f16") == "qmm_tcgen05"
+    assert ctx.qmm_route(2048, 14336, 4096, 4, 64, "f32") == "qmv_cuda_core"      # no f32 MMA: stays exact
+    assert ctx.qmm_route(64, 256, 96, 4, 32, "bf16") == "qmv_cuda_core"           # K % 64 != 0
+    assert ctx.qmm_route(64, 256, 512, 7, 64, "bf16") == "qmv_cuda_core"
+
+
+@pytest.mark.parametrize("m,n,k,bits,gs,dt", [
+    (32, 64, 512, 4, 64, "bf16"), (32, 64, 512, 4, 64, "f16"),      # registered mma shape
+    (17, 8, 64, 4, 64, "bf16"),                                    # smallest: one k block, N < 128
+    (128, 256, 512, 4, 64, "bf16"),
+    (200, 304, 1024, 4, 64, "bf16"),                               # ragged M and N
+    (257, 129, 256, 4, 32, "f16"),                                 # two token chunks, group 32
+    (300, 512, 2048, 4, 128, "bf16"),                              # group 128
+    (64, 96, 256, 8, 32, "f16"),
+    (130, 288, 512, 2, 64, "bf16"), (130, 288, 512, 3, 64, "bf16"), (130, 288, 512, 5, 64, "f16"),
+    (130, 288, 512, 6, 128, "bf16"), (130, 288, 512, 8, 64, "bf16"),
+    (1000, 200, 4096, 4, 64, "bf16"),                              # long K: many ring wraps
+])
+def test_qmm_matches_oracle(ctx, m, n, k, bits, gs, dt):
+    assert ctx.qmm_route(m, n, k, bits, gs, dt) == "qmm_tcgen05"
+    w, s, b, x = dense_case(m, n, k, bits, gs, dt, seed=0, salt=m + n)
+    ref = oracle.qmm(w, s, b, x, m, n, k, bits, gs)
+    got = run_qmm(w, s, b, x, bits, gs, dt)
+    assert got.shape == (m, n)
+    assert rel_err(got, ref) <= TOL[dt]
+    assert ctx.status_word() == 0
+
+
+def test_exact_integer_case(ctx):
+    """Scales 1, biases 0, one-hot activations: every output is one integer code, so the result is exact."""
+    import torch
+    from metaltile_b200 import ops, synth
+    m, n, k, bits = 256, 384, 256, 4
+    w = synth.words(n * k * bits // 32, seed=11).reshape(n, -1)
+    codes = oracle.unpack_matrix(w, k, bits)
+    x = np.zeros((m, k), np.float32)
+    x[np.arange(m), (np.arange(m) * 7) % k] = 1.0
+    ones, zeros = np.ones((n, k // 64), np.float32), np.zeros((n, k // 64), np.float32)
+    out = ops.qmm(to_dev(w), to_dev(ones, "bf16"), to_dev(zeros, "bf16"), to_dev(x, "bf16"), bits, 64)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.float().cpu().numpy(), codes[:, (np.arange(m) * 7) % k].T.astype(np.float32))
+
+
+@pytest.mark.parametrize("n,k", [(14336, 4096), (4096, 14336)])
+def test_prefill_2048_on_a_slice(ctx, n, k):
+    """The prefill benchmark shapes; the oracle checks a slice of the weight rows (the CPU needs
+    ~1 s per 64 rows at M = 2048), the rest is covered by the linearity property below."""
+    m, bits, gs, dt = 2048, 4, 64, "bf16"
+    w, s, b, x = dense_case(m, n, k, bits, gs, dt, seed=0, salt=3)
+    got = run_qmm(w, s, b, x, bits, gs, dt)
+    rows = (n // 2 - 64, n // 2 + 64)
+    ref = oracle.qmm(w, s, b, x, m, n, k, bits, gs, rows=rows)
+    assert rel_err(got[:, rows[0]:rows[1]], ref[:, rows[0]:rows[1]]) <= TOL[dt]
+    assert np.all(np.isfinite(got))
+    assert ctx.status_word() == 0
+
+
+def test_linearity_and_row_independence_at_full_size(ctx):
+    """Size-independent properties at M = 2048, N = 14336, K = 4096: rows of x do not interact, and the
+    same row gives the same result wherever it sits in the batch (bit for bit)."""
+    import torch
+    from metaltile_b200 import ops
+    m, n, k, bits, gs, dt = 2048, 14336, 4096, 4, 64, "bf16"
+    w, s, b, x = dense_case(m, n, k, bits, gs, dt, seed=0, salt=5)
+    wd, sd, bd = to_dev(w), to_dev(s, dt), to_dev(b, dt)
+    full = ops.qmm(wd, sd, bd, to_dev(x, dt), bits, gs)
+    perm = np.random.default_rng(0).permutation(m)
+    shuf = ops.qmm(wd, sd, bd, to_dev(x[perm], dt), bits, gs)
+    torch.cuda.synchronize()
+    assert torch.equal(shuf, full[torch.from_numpy(perm).cuda()])
+    # and the decode kernel agrees with the prefill kernel on a few rows
+    few = ops.qmv(wd, sd, bd, to_dev(x[:4], dt), bits, gs)
+    torch.cuda.synchronize()
+    assert rel_err(full[:4].float().cpu().numpy(), few.float().cpu().numpy()) <= TOL[dt]
