@@ -25,6 +25,8 @@ struct Ctx {
     int qmm_force_tn = 0;          // option "qmm_tile_tokens": 0 = choose per shape
     void *d_worklist = nullptr;    // gather_qmm work list (grow-only, owned by the context)
     size_t worklist_bytes = 0;
+    void *d_xconv = nullptr;       // scaled-f16 copy of bf16 activations for the tensor-core kernels (grow-only)
+    size_t xconv_bytes = 0;
 };
 
 inline int fail(Ctx *ctx, int code, const std::string &msg) {

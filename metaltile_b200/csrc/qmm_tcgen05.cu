@@ -23,7 +23,7 @@
 //   warps 8-15  dequant    256 threads = 128 weight rows x 2 halves of a 64-wide k block: packed words
 //                          come straight from global memory into registers one k block ahead, every
 //                          code is extracted with one LOP3 ((win & mask<<p) | 1.0f, minus 1.0f =
-//                          q * 2^(p-23)), w = q*scale + bias in f32, rounded to T, written as the
+//                          q * 2^(p-23)), w = q*scale + bias in f32, rounded to f16, written as the
 //                          K-major 128B-swizzled A operand tile the MMA reads
 // Stage hand-off uses mbarriers; tcgen05.commit releases a stage when its MMAs have read it.  Every
 // wait is bounded: on expiry the kernel records a code in the context's status word, all roles leave
@@ -49,7 +49,6 @@ constexpr int NUM_THREADS = 512;
 constexpr int DEQ_WARP0 = 8, DEQ_THREADS = 256;
 constexpr int EPI_WARP0 = 4;
 constexpr uint32_t kSpinLimit = 1u << 22;   // bounded waits: ~seconds, then give up
-
 struct QmmParams {
     const uint32_t *w;
     const void *scales, *biases;
@@ -60,7 +59,11 @@ struct QmmParams {
     int dense_items;             // dense: number of items = n_tiles * m_chunks
     int m_chunks;                // dense: token chunks per weight-row tile
     int M;                       // dense: rows of x; gather: total rows of x
-    int N, K, gs_shift, dt;      // N: weight rows per expert (output columns)
+    int N, K, gs_shift;          // N: weight rows per expert (output columns)
+    int op_f16;                  // MMA operand format: 1 = f16, 0 = bf16 (dequantised W and the X tensor map)
+    int sb_dt;                   // element type of scales / biases (MTC_F16 or MTC_BF16)
+    int out_dt;                  // element type of out
+    const float *tok_scale;      // per-token power-of-two factor applied in the epilogue, or nullptr
     int wpr, gpr;                // words / groups per weight row
     int TN;                      // token rows per item (TMA box rows, MMA N)
     uint32_t idesc;
@@ -98,8 +101,10 @@ __device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false (and raises the CTA's abort flag + the global status word) when the
-// barrier did not complete within kSpinLimit polls or another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, SmemCtrl *ctl, uint32_t *status, uint32_t code) {
+// barrier did not complete within kSpinLimit polls or another role already aborted.  `sleep_ns` > 0
+// backs off between polls so that waiting warps do not take issue slots from the dequant warps.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, SmemCtrl *ctl, uint32_t *status, uint32_t code,
+                                          uint32_t sleep_ns = 0) {
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
         if (mbar_try(bar, parity)) return true;
         if ((i & 63u) == 63u && ctl->abort) return false;
@@ -107,6 +112,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, SmemCt
     ctl->abort = 1;
     atomicCAS(status, 0u, code);
     return false;
+}
+// Whole-warp wait: lane 0 polls, the result is broadcast.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity, SmemCtrl *ctl, uint32_t *status, uint32_t code,
+                                               uint32_t sleep_ns) {
+    uint32_t ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, ctl, status, code, sleep_ns) ? 1u : 0u;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return ok != 0;
 }
 
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int c0, int c1, uint64_t *bar) {
@@ -149,23 +162,29 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ uint32_t pack2(float lo, float hi, int f16) {
-    if (f16) {
-        __half2 h = __floats2half2_rn(lo, hi);
-        return *reinterpret_cast<uint32_t *>(&h);
-    }
-    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&h);
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));   // first source -> upper half
+    return r;
+}
+// (win & mask) | 1.0f in one LOP3: the constant 1.0f sits in a register, the mask is an immediate
+__device__ __forceinline__ float code_plus_one(uint32_t win, uint32_t mask, uint32_t one) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(win), "r"(mask), "r"(one));
+    return __uint_as_float(r);
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t saddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
 // ---- dequantisation of half a W row segment (32 codes = BITS words) into 4 swizzled 16-byte chunks --
 template <int BITS>
 struct QPack {
-    static constexpr int WPH = BITS;            // u32 words per 32 codes
     static constexpr int CPW = 23 / BITS;       // codes per window: a window must fit the 23 mantissa bits
     static constexpr uint32_t MASK = (1u << BITS) - 1u;
 };
 
+// 32 codes (BITS words) of one weight row, straight from global memory
 template <int BITS>
 __device__ __forceinline__ void load_half_words(const uint32_t *p, uint32_t (&w)[BITS], bool valid) {
     if (!valid) {
@@ -176,13 +195,13 @@ __device__ __forceinline__ void load_half_words(const uint32_t *p, uint32_t (&w)
     if constexpr (BITS % 4 == 0) {          // 4-, 8-bit: 16-byte pieces
 #pragma unroll
         for (int i = 0; i < BITS / 4; ++i) {
-            uint4 v = __ldg(reinterpret_cast<const uint4 *>(p) + i);
+            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(p) + i);
             w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
         }
     } else if constexpr (BITS % 2 == 0) {   // 2-, 6-bit: 8-byte pieces
 #pragma unroll
         for (int i = 0; i < BITS / 2; ++i) {
-            uint2 v = __ldg(reinterpret_cast<const uint2 *>(p) + i);
+            const uint2 v = __ldg(reinterpret_cast<const uint2 *>(p) + i);
             w[2 * i] = v.x; w[2 * i + 1] = v.y;
         }
     } else {                                // 3-, 5-bit: single words
@@ -191,14 +210,17 @@ __device__ __forceinline__ void load_half_words(const uint32_t *p, uint32_t (&w)
     }
 }
 
+// dst[c] = shared-memory address of the c-th of this thread's four 16-byte chunks (swizzle applied by the caller)
 template <int BITS>
-__device__ __forceinline__ void dequant_half(const uint32_t (&w)[BITS], float s, float b, uint8_t *row_base, int chunk0,
-                                             int r7, int f16) {
+__device__ __forceinline__ void dequant_half(const uint32_t (&w)[BITS], float s, float b, const uint32_t (&dst)[4],
+                                             uint32_t stage_off) {
     using Q = QPack<BITS>;
     // a code at bit p of a window becomes q * 2^(p-23) after the magic subtract: fold 2^(23-p) into the scale
     float sp[Q::CPW];
 #pragma unroll
     for (int c = 0; c < Q::CPW; ++c) sp[c] = s * __uint_as_float(static_cast<uint32_t>(23 - c * BITS + 127) << 23);
+    uint32_t one = 0x3F800000u;
+    asm volatile("" : "+r"(one));            // keep 1.0f in a register so the extraction is a single LOP3
     float vals[8];
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
@@ -208,17 +230,11 @@ __device__ __forceinline__ void dequant_half(const uint32_t (&w)[BITS], float s,
         if (sh == 0) win = w[word];
         else if (word + 1 < BITS) win = __funnelshift_r(w[word], w[word + 1], sh);
         else win = w[word] >> sh;
-        const float f = __uint_as_float((win & (Q::MASK << (c * BITS))) | 0x3F800000u) - 1.0f;
+        const float f = code_plus_one(win, Q::MASK << (c * BITS), one) - 1.0f;
         vals[i & 7] = fmaf(f, sp[c], b);
-        if ((i & 7) == 7) {
-            const int chunk = chunk0 + (i >> 3);
-            uint4 o;
-            o.x = pack2(vals[0], vals[1], f16);
-            o.y = pack2(vals[2], vals[3], f16);
-            o.z = pack2(vals[4], vals[5], f16);
-            o.w = pack2(vals[6], vals[7], f16);
-            *reinterpret_cast<uint4 *>(row_base + ((chunk ^ r7) << 4)) = o;
-        }
+        if ((i & 7) == 7)
+            st_shared_v4(dst[i >> 3] + stage_off, pack_f16x2(vals[0], vals[1]), pack_f16x2(vals[2], vals[3]),
+                         pack_f16x2(vals[4], vals[5]), pack_f16x2(vals[6], vals[7]));
     }
 }
 
@@ -286,7 +302,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
-                    if (!(ok = mbar_wait(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x101))) break;
+                    if (!(ok = mbar_wait(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x101, 40))) break;
                     mbar_expect_tx(&ctl->full_x[s], x_bytes);
                     tma_load_2d(sX + s * B_BYTES, &tmap_x, kb * BK, item.row0, &ctl->full_x[s]);
                 }
@@ -332,26 +348,30 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
             const int buf = tile_i & 1;
             const uint32_t acc_ph = (tile_i >> 1) & 1;
             const Item item = get_item(p, i);
-            if (!(ok = mbar_wait(&ctl->acc_full[buf], acc_ph, ctl, p.status, 0x301))) break;
+            if (!(ok = mbar_wait_warp(&ctl->acc_full[buf], acc_ph, ctl, p.status, 0x301, 200))) break;
             tc_fence_after();
             const int n = item.n_tile * BMW + q * 32 + lane;     // output column owned by this thread
             const bool n_ok = n < p.N;
             const int cols = (item.rows + 15) & ~15;
             for (int c0 = 0; c0 < cols; c0 += 16) {
+                float ts[16];                      // per-token factors first, so their latency hides behind the TMEM load
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    ts[j] = (p.tok_scale && c0 + j < item.rows) ? __ldg(p.tok_scale + item.row0 + c0 + j) : 1.0f;
                 uint32_t v[16];
                 tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * TN_MAX + c0, v);
                 if (n_ok) {
                     // lanes of a warp hold 32 consecutive columns of the same output row: 64-byte segments
-                    if (p.dt == MTC_F16) {
+                    if (p.out_dt == MTC_F16) {
                         __half *o = static_cast<__half *>(p.out) + static_cast<size_t>(item.row0 + c0) * p.N + n;
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
-                            if (c0 + j < item.rows) o[static_cast<size_t>(j) * p.N] = __float2half_rn(__uint_as_float(v[j]));
+                            if (c0 + j < item.rows) o[static_cast<size_t>(j) * p.N] = __float2half_rn(__uint_as_float(v[j]) * ts[j]);
                     } else {
                         __nv_bfloat16 *o = static_cast<__nv_bfloat16 *>(p.out) + static_cast<size_t>(item.row0 + c0) * p.N + n;
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
-                            if (c0 + j < item.rows) o[static_cast<size_t>(j) * p.N] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                            if (c0 + j < item.rows) o[static_cast<size_t>(j) * p.N] = __float2bfloat16_rn(__uint_as_float(v[j]) * ts[j]);
                     }
                 }
             }
@@ -365,8 +385,10 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
         const int r = t & (BMW - 1);                       // row of the W tile
         const int h = t >> 7;                              // which 32-code half of the 64-wide k block
         const int r7 = r & 7;
-        const int f16 = p.dt == MTC_F16;
-        uint8_t *row_smem = sW + (r >> 3) * 1024 + r7 * 128;
+        uint32_t dst[4];                                   // this thread's four swizzled 16-byte chunks in stage 0
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            dst[c] = smem_u32(sW) + (r >> 3) * 1024 + r7 * 128 + (((h * 4 + c) ^ r7) << 4);
         uint32_t it = 0;
         bool ok = true;
         for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x) {
@@ -401,16 +423,16 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                     }
                 }
                 // the stage is free once empty[s] has completed (the producer waits on the same barrier)
-                if (!(ok = mbar_wait(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x401))) break;
+                if (!(ok = mbar_wait_warp(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x401, 0))) break;
                 float sc, bi;
-                if (f16) {
+                if (p.sb_dt == MTC_F16) {
                     sc = __half2float(__ushort_as_half(static_cast<unsigned short>(sr)));
                     bi = __half2float(__ushort_as_half(static_cast<unsigned short>(br)));
                 } else {
                     sc = __uint_as_float(sr << 16);
                     bi = __uint_as_float(br << 16);
                 }
-                dequant_half<BITS>(wcur, sc, bi, row_smem + s * A_BYTES, h * 4, r7, f16);
+                dequant_half<BITS>(wcur, sc, bi, dst, s * A_BYTES);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> async proxy (MMA)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ctl->full_w[s]);
@@ -423,6 +445,48 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
     if (warp == 2) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
+    }
+}
+
+// bf16 activations -> f16 with one power-of-two factor per row.  bf16 keeps 8 significant bits, so
+// x * 2^-e is exact in f16 (11 bits) once the row maximum is brought to [2^14, 2^15); elements more than
+// 2^38 below the row maximum lose bits, which changes nothing measurable.  The MMA then runs on f16
+// operands, whose 3 extra mantissa bits keep the dequantised weights 8x closer to the f32 oracle than
+// bf16 weights would be; the epilogue multiplies the accumulator by 2^e again.
+__global__ void __launch_bounds__(256) rows_to_f16_kernel(const __nv_bfloat16 *x, __half *y, float *row_scale, int rows, int K) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const uint4 *src = reinterpret_cast<const uint4 *>(x + static_cast<size_t>(row) * K);
+    uint4 *dst = reinterpret_cast<uint4 *>(y + static_cast<size_t>(row) * K);
+    const int nvec = K / 8;
+    uint32_t amax = 0;                       // max of |x| as bf16 bit patterns (monotone for finite values)
+    for (int i = lane; i < nvec; i += 32) {
+        const uint4 v = __ldg(src + i);
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            amax = max(amax, u[j] & 0x7FFFu);
+            amax = max(amax, (u[j] >> 16) & 0x7FFFu);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const int ex = static_cast<int>(amax >> 7);                    // biased exponent of the row maximum
+    int e = (ex == 0 || ex == 0xFF) ? 0 : ex - 127 - 14;           // zero rows and inf/nan rows stay unscaled
+    e = max(e, -126);                                              // 2^-e and 2^e must both be normal f32 numbers
+    const float down = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);
+    if (lane == 0) row_scale[row] = __uint_as_float(static_cast<uint32_t>(127 + e) << 23);
+    for (int i = lane; i < nvec; i += 32) {
+        const uint4 v = __ldg(src + i);
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __half2 h = __floats2half2_rn(__uint_as_float(u[j] << 16) * down, __uint_as_float(u[j] & 0xFFFF0000u) * down);
+            o[j] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+        dst[i] = make_uint4(o[0], o[1], o[2], o[3]);
     }
 }
 
@@ -486,14 +550,23 @@ EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-constexpr size_t kQmmSmem = STAGES * (A_BYTES + B_BYTES) + sizeof(SmemCtrl) + 1024;
+template <int BITS>
+constexpr size_t qmm_smem_bytes() {
+    return STAGES * (A_BYTES + B_BYTES) + sizeof(SmemCtrl) + 1024;
+}
 
 template <int BITS>
 cudaError_t launch_bits(cudaStream_t st, const CUtensorMap &tmap, const QmmParams &p, int grid) {
     auto kern = qmm_tcgen05_kernel<BITS>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kQmmSmem));
-    if (e != cudaSuccess) return e;
-    kern<<<grid, NUM_THREADS, kQmmSmem, st>>>(tmap, p);
+    constexpr size_t smem = qmm_smem_bytes<BITS>();
+    static_assert(smem <= 227 * 1024, "shared memory budget");
+    static bool attr_set = false;   // one process drives one device (one rank per GPU)
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    kern<<<grid, NUM_THREADS, smem, st>>>(tmap, p);
     return cudaGetLastError();
 }
 
@@ -509,7 +582,7 @@ cudaError_t launch_any(int bits, cudaStream_t st, const CUtensorMap &tmap, const
 }
 
 // X as a 2-D tensor [rows, K] of 16-bit elements, box 64 x TN, 128-byte swizzle; rows past the end read as zero.
-cudaError_t make_x_map(CUtensorMap *tmap, const void *x, int rows, int K, int TN, int dt, std::string *why) {
+cudaError_t make_x_map(CUtensorMap *tmap, const void *x, int rows, int K, int TN, int op_f16, std::string *why) {
     EncodeTiledFn encode = get_encode_fn();
     if (!encode) {
         if (why) *why = "cuTensorMapEncodeTiled is not available from the driver";
@@ -519,7 +592,7 @@ cudaError_t make_x_map(CUtensorMap *tmap, const void *x, int rows, int K, int TN
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
     const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(TN)};
     const cuuint32_t estr[2] = {1, 1};
-    CUresult r = encode(tmap, dt == MTC_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+    CUresult r = encode(tmap, op_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                         const_cast<void *>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -536,15 +609,49 @@ void fill_common(QmmParams &p, Ctx *ctx, const void *w, const void *scales, cons
     p.biases = biases;
     p.out = out;
     p.status = ctx->d_status;
-    p.N = N; p.K = K; p.dt = dt;
+    p.N = N; p.K = K;
+    p.sb_dt = dt;
+    p.out_dt = dt;
+    p.op_f16 = 1;   // bf16 activations are converted to scaled f16 first (see rows_to_f16_kernel)
     p.gs_shift = 0;
     while ((1 << p.gs_shift) < group_size) ++p.gs_shift;
     p.wpr = K * bits / 32;
     p.gpr = K / group_size;
     p.TN = TN;
-    const uint32_t fmt = dt == MTC_F16 ? 0u : 1u;      // both operands carry the activation type
+    const uint32_t fmt = p.op_f16 ? 0u : 1u;           // both operands carry the same 16-bit format
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(TN >> 3) << 17) |
               (static_cast<uint32_t>(BMW >> 4) << 24);
+}
+
+// bf16 activations: stage a scaled f16 copy of x in the context's conversion buffer.
+cudaError_t stage_x(Ctx *ctx, cudaStream_t st, const void *x, int rows, int K, int dt, const void **x_op,
+                    const float **tok_scale, std::string *why) {
+    *x_op = x;
+    *tok_scale = nullptr;
+    if (dt == MTC_F16) return cudaSuccess;
+    const size_t need = ((static_cast<size_t>(rows) * K * 2 + 255) & ~static_cast<size_t>(255)) + static_cast<size_t>(rows) * sizeof(float);
+    if (need > ctx->xconv_bytes) {
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(st, &cs);
+        if (cs != cudaStreamCaptureStatusNone) {
+            if (why) *why = "the f16 staging buffer must grow: run this shape once outside stream capture first";
+            return cudaErrorStreamCaptureUnsupported;
+        }
+        if (ctx->d_xconv) cudaFree(ctx->d_xconv);
+        ctx->d_xconv = nullptr;
+        ctx->xconv_bytes = 0;
+        cudaError_t e = cudaMalloc(&ctx->d_xconv, need);
+        if (e != cudaSuccess) return e;
+        ctx->xconv_bytes = need;
+    }
+    __half *y = static_cast<__half *>(ctx->d_xconv);
+    float *scale = reinterpret_cast<float *>(static_cast<char *>(ctx->d_xconv) + ((static_cast<size_t>(rows) * K * 2 + 255) & ~static_cast<size_t>(255)));
+    rows_to_f16_kernel<<<(rows + 7) / 8, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), y, scale, rows, K);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    *x_op = y;
+    *tok_scale = scale;
+    return cudaSuccess;
 }
 
 }  // namespace
@@ -562,11 +669,16 @@ cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const v
                                const void *x, void *out, int M, int N, int K, int bits, int group_size, int dt,
                                std::string *why) {
     int TN = ctx->qmm_force_tn > 0 ? ctx->qmm_force_tn : (M >= TN_MAX ? TN_MAX : ((M + 15) / 16) * 16);
+    const void *x_op = nullptr;
+    const float *tok_scale = nullptr;
+    cudaError_t e = stage_x(ctx, st, x, M, K, dt, &x_op, &tok_scale, why);
+    if (e != cudaSuccess) return e;
     CUtensorMap tmap;
-    cudaError_t e = make_x_map(&tmap, x, M, K, TN, dt, why);
+    e = make_x_map(&tmap, x_op, M, K, TN, 1, why);
     if (e != cudaSuccess) return e;
     QmmParams p{};
     fill_common(p, ctx, w, scales, biases, out, N, K, bits, group_size, dt, TN);
+    p.tok_scale = tok_scale;
     p.M = M;
     p.m_chunks = (M + TN - 1) / TN;
     p.dense_items = ((N + BMW - 1) / BMW) * p.m_chunks;
@@ -606,11 +718,16 @@ cudaError_t launch_gather_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *x, 
                                                                          n_tiles, TN, count, items, max_items);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
+    const void *x_op = nullptr;
+    const float *tok_scale = nullptr;
+    e = stage_x(ctx, st, x, total_rows, K, dt, &x_op, &tok_scale, why);
+    if (e != cudaSuccess) return e;
     CUtensorMap tmap;
-    e = make_x_map(&tmap, x, total_rows, K, TN, dt, why);
+    e = make_x_map(&tmap, x_op, total_rows, K, TN, 1, why);
     if (e != cudaSuccess) return e;
     QmmParams p{};
     fill_common(p, ctx, w, scales, biases, out, N, K, bits, group_size, dt, TN);
+    p.tok_scale = tok_scale;
     p.M = total_rows;
     p.items = items;
     p.item_count = count;

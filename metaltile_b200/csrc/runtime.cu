@@ -197,6 +197,7 @@ int mtc_destroy(mtc_ctx *ctx) {
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->d_scratch) cudaFree(ctx->d_scratch);
     if (ctx->d_worklist) cudaFree(ctx->d_worklist);
+    if (ctx->d_xconv) cudaFree(ctx->d_xconv);
     delete ctx;
     return MTC_OK;
 }

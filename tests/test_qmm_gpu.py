@@ -35,7 +35,7 @@ def test_routing_follows_m_and_dtype(ctx):
 
 @pytest.mark.parametrize("m,n,k,bits,gs,dt", [
     (32, 64, 512, 4, 64, "bf16"), (32, 64, 512, 4, 64, "f16"),      # registered mma shape
-    (17, 8, 64, 4, 64, "bf16"),                                    # smallest: one k block, N < 128
+    (17, 8, 128, 4, 64, "bf16"),                                   # smallest: two k blocks, N < 128
     (128, 256, 512, 4, 64, "bf16"),
     (200, 304, 1024, 4, 64, "bf16"),                               # ragged M and N
     (257, 129, 256, 4, 32, "f16"),                                 # two token chunks, group 32
