@@ -190,15 +190,29 @@ def main():
             bi = -8.0 * sc + 1e-3 * torch.randn((nl, k // GROUP), device=dev, generator=gen)
             mats.append((w, sc.to(torch.bfloat16), bi.to(torch.bfloat16), k, nl, phase))
         layers.append(mats)
-    # activations: one x per distinct K (every projection of the step reads its x from HBM/L2)
+    # activations: one x per distinct K
     xs_host = {k: torch.randn((M, k), generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).pin_memory()
                for k in (4096, 14336)}
     xs = {k: v.to(dev) for k, v in xs_host.items()}
-    # per layer, per phase: local output slab [M, sum(nl)] and the gathered buffer [world, M, sum(nl)]
+    # per layer, per phase: local output slab [M, sum(nl)] and the gathered buffer [world, M, sum(nl)];
+    # all slabs are views of one allocation, so the end-to-end leg reads the step's results back in one copy
     phase_cols = [sum(n // world for _, _, n, p in PROJ if p == ph) for ph in range(4)]
-    out_local = [[torch.empty((M, c), dtype=torch.bfloat16, device=dev) for c in phase_cols] for _ in range(args.layers)]
-    out_full = [[torch.empty((world, M, c), dtype=torch.bfloat16, device=dev) for c in phase_cols]
-                for _ in range(args.layers)] if world > 1 else None
+    cols_per_layer = sum(phase_cols)
+    local_all = torch.empty(args.layers * M * cols_per_layer, dtype=torch.bfloat16, device=dev)
+    full_all = torch.empty(args.layers * world * M * cols_per_layer, dtype=torch.bfloat16, device=dev) if world > 1 else None
+    out_local, out_full = [], ([] if world > 1 else None)
+    lo = fo = 0
+    for _ in range(args.layers):
+        ll, fl = [], []
+        for c in phase_cols:
+            ll.append(local_all[lo:lo + M * c].view(M, c))
+            lo += M * c
+            if world > 1:
+                fl.append(full_all[fo:fo + world * M * c].view(world * M, c))
+                fo += world * M * c
+        out_local.append(ll)
+        if world > 1:
+            out_full.append(fl)
     # each projection writes its own contiguous [M, nl] tile, then tiles are packed per phase
     tiles = [[torch.empty((M, nl), dtype=torch.bfloat16, device=dev) for (_, _, _, _, nl, _) in mats] for mats in layers]
 
@@ -262,10 +276,10 @@ def main():
     value = total_bytes / (ms * 1e-3) / 1e9
 
     # ---- end to end: pinned host activations in, host results out, through the C ABI ---------
-    out_host = [[torch.empty((world if world > 1 else 1, M, c), dtype=torch.bfloat16).pin_memory() for c in phase_cols]
-                for _ in range(args.layers)]
+    result_dev = full_all if world > 1 else local_all
+    out_host = torch.empty(result_dev.numel(), dtype=torch.bfloat16).pin_memory()
     h2d = sum(v.numel() * 2 for v in xs_host.values())
-    d2h = sum(t.numel() * 2 for l in out_host for t in l)
+    d2h = result_dev.numel() * 2
     stream = torch.cuda.current_stream().cuda_stream
     lib, h = ctx._lib, ctx._h
 
@@ -273,10 +287,7 @@ def main():
         for k, v in xs_host.items():
             lib.mtc_upload(h, stream, xs[k].data_ptr(), v.data_ptr(), v.numel() * 2)
         graph.replay()
-        for li in range(args.layers):
-            for ph in range(4):
-                src = out_full[li][ph] if world > 1 else out_local[li][ph]
-                lib.mtc_download(h, stream, out_host[li][ph].data_ptr(), src.data_ptr(), src.numel() * 2)
+        lib.mtc_download(h, stream, out_host.data_ptr(), result_dev.data_ptr(), d2h)
         lib.mtc_sync(h, stream)
 
     for _ in range(3):
@@ -374,6 +385,55 @@ def extra_measurements(ctx, dev, hbm_peak, tf_peak):
         gbs = alg_bytes(m, n, k) / us / 1e3
         out[name] = {"us": us, "GB/s": gbs, "frac_of_hbm_peak": gbs / hbm_peak, "cold_l2_copies": copies}
         del sets, fns
+    # ---- prefill qmm on the tensor cores (M = 2048), TFLOP/s = 2*M*N*K / time
+    def time_calls(fn, reps=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+    for name, (m, n, k) in {"c3_qmm_m2048_4096to14336": (2048, 14336, 4096), "c3_qmm_m2048_14336to4096": (2048, 4096, 14336)}.items():
+        sets, x, o = make(n, k, m, 1)
+        w, sc, bi = sets[0]
+        us = time_calls(lambda: ops.qmm(w, sc, bi, x, BITS, GROUP, out=o, ctx=ctx))
+        tf = 2.0 * m * n * k / us / 1e6
+        out[name] = {"us": us, "TFLOP/s": tf, "frac_of_bf16_peak": tf / tf_peak, "route": ctx.qmm_route(m, n, k, BITS, GROUP, "bf16")}
+        del sets
+
+    # ---- MoE layer: 512 tokens x hidden 2048, 128 experts (gate/up 2048->768, down 768->2048), top-8
+    T, H, I, E, K8 = 512, 2048, 768, 128, 8
+
+    def experts(n, k):
+        w = torch.randint(-2 ** 31, 2 ** 31 - 1, (E, n, k * BITS // 32), dtype=torch.int32, device=dev, generator=gen)
+        sc = (0.002 + 0.018 * torch.rand((E, n, k // GROUP), device=dev, generator=gen)).to(torch.bfloat16)
+        return w, sc, (-8.0 * sc.float()).to(torch.bfloat16)
+
+    gate, up, down = experts(I, H), experts(I, H), experts(H, I)
+    tok = torch.randn((T, H), device=dev, generator=gen).to(torch.bfloat16)
+    logits = torch.randn((T, E), device=dev, generator=gen).to(torch.bfloat16)
+
+    def moe_layer():
+        idx, wts = ops.moe_router_topk(logits, K8, 1, ctx=ctx)
+        sti, inv, off, _ = ops.moe_sort(idx, E, ctx=ctx)
+        xp = ops.moe_permute(tok, sti, ctx=ctx)
+        g = ops.gather_qmm(xp, *gate, BITS, GROUP, expert_offsets=off, ctx=ctx)
+        u = ops.gather_qmm(xp, *up, BITS, GROUP, expert_offsets=off, ctx=ctx)
+        a = ops.swiglu(g, u, ctx=ctx)
+        y = ops.gather_qmm(a, *down, BITS, GROUP, expert_offsets=off, ctx=ctx)
+        return ops.moe_unpermute(y, inv, wts, ctx=ctx)
+
+    us = time_calls(moe_layer)
+    flops = 2.0 * T * K8 * 3 * H * I
+    wbytes = 3 * E * (H * I * BITS // 8 + 2 * (H * I // GROUP) * 2)
+    out["c4_moe_layer_512tok_128e_top8"] = {"us": us, "TFLOP/s": flops / us / 1e6, "weight_GB/s": wbytes / us / 1e3,
+                                            "frac_of_hbm_peak": wbytes / us / 1e3 / hbm_peak,
+                                            "note": "HBM-bound: 340 MB of expert weights per layer (L2-warm repeats)"}
     return out
 
 

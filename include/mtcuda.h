@@ -96,7 +96,9 @@ const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dty
  * TileConfig switches (crates/metaltile-codegen/src/msl/config.rs:27-96,
  * crates/metaltile-core/src/toolchain/config.rs:11-96).  Options:
  *   "qmm_tile_tokens"  token rows per tensor-core work item (0 = chosen per shape; else a multiple
- *                      of 16 in [16, 256]) */
+ *                      of 16 in [16, 256])
+ *   "qmm_pair"         1: a work item covers two adjacent weight-row tiles that share every
+ *                      activation stage (dense qmm only; default 0) */
 int mtc_set_option(mtc_ctx *ctx, const char *name, int value);
 
 /* mt_moe_gather_qmm_int4 / _b{3,5,6,8} / _m8 / _m16 / _m32 (CSR form: expert_offsets u32[E+1],

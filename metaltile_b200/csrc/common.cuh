@@ -23,6 +23,7 @@ struct Ctx {
     void *d_scratch = nullptr;     // grow-only scratch owned by the context
     size_t scratch_bytes = 0;
     int qmm_force_tn = 0;          // option "qmm_tile_tokens": 0 = choose per shape
+    int qmm_pair = 0;              // option "qmm_pair": 1 = give a work item two adjacent weight-row tiles
     void *d_worklist = nullptr;    // gather_qmm work list (grow-only, owned by the context)
     size_t worklist_bytes = 0;
     void *d_xconv = nullptr;       // scaled-f16 copy of bf16 activations for the tensor-core kernels (grow-only)

@@ -42,7 +42,8 @@ namespace {
 constexpr int BMW = 128;         // weight rows per tile (TMEM lanes, MMA M)
 constexpr int BK = 64;           // k per stage: 64 x 16-bit = one 128B swizzle row
 constexpr int TN_MAX = 256;      // token rows per tile (TMEM columns of one accumulator, MMA N)
-constexpr int STAGES = 4;
+constexpr int MAX_STAGES = 8;    // ring depth: as many stages as fit in RING_BYTES, at most this
+constexpr int RING_BYTES = 192 * 1024;
 constexpr int A_BYTES = BMW * BK * 2;       // 16 KB, dequantised weights
 constexpr int B_BYTES = TN_MAX * BK * 2;    // 32 KB, activations
 constexpr int NUM_THREADS = 512;
@@ -66,13 +67,17 @@ struct QmmParams {
     const float *tok_scale;      // per-token power-of-two factor applied in the epilogue, or nullptr
     int wpr, gpr;                // words / groups per weight row
     int TN;                      // token rows per item (TMA box rows, MMA N)
+    int nst;                     // ring depth
+    int pair;                    // 1: an item covers two adjacent weight-row tiles that share every X stage
+    int pair_items;              // dense + pair: items [0, pair_items) are pairs, the rest single tiles
+    int n_tiles;                 // dense: weight-row tiles
     uint32_t idesc;
 };
 
 struct __align__(8) SmemCtrl {
-    uint64_t full_x[STAGES];     // TMA bytes of the X stage have landed
-    uint64_t full_w[STAGES];     // dequant warps finished the W stage
-    uint64_t empty[STAGES];      // MMAs that read the stage have completed
+    uint64_t full_x[MAX_STAGES]; // TMA bytes of the X stage have landed
+    uint64_t full_w[MAX_STAGES]; // dequant warps finished the W stage
+    uint64_t empty[MAX_STAGES];  // MMAs that read the stage have completed
     uint64_t acc_full[2];        // accumulator buffer complete
     uint64_t acc_empty[2];       // epilogue drained the accumulator buffer
     uint32_t tmem_base;
@@ -239,18 +244,31 @@ __device__ __forceinline__ void dequant_half(const uint32_t (&w)[BITS], float s,
 }
 
 struct Item {
-    int n_tile, expert, row0, rows;
+    int n_tile, expert, row0, rows, nt;     // nt: weight-row tiles covered (1 or 2)
 };
 
 __device__ __forceinline__ Item get_item(const QmmParams &p, int i) {
     Item it;
     if (p.items) {
         const int4 v = __ldg(p.items + i);
-        it.n_tile = v.x; it.expert = v.y; it.row0 = v.z; it.rows = v.w;
-    } else {   // dense: token chunks of one weight-row tile are adjacent, so concurrent CTAs share the W tile in L2
-        it.n_tile = i / p.m_chunks;
+        it.n_tile = v.x; it.expert = v.y & 0xFFFFFF; it.nt = 1 + ((v.y >> 24) & 1); it.row0 = v.z; it.rows = v.w;
+    } else {
+        // dense: the token chunks of one weight-row tile (pair) are adjacent, so CTAs running at the same time
+        // share its packed words in L2.  Pairs first; what does not fill a whole wave of pairs runs as single
+        // tiles so that the last wave is short.
+        int unit, chunk;
         it.expert = 0;
-        it.row0 = (i - it.n_tile * p.m_chunks) * p.TN;
+        if (i < p.pair_items) {
+            unit = i / p.m_chunks; chunk = i - unit * p.m_chunks;
+            it.n_tile = unit * (p.pair ? 2 : 1);
+            it.nt = (p.pair && it.n_tile + 1 < p.n_tiles) ? 2 : 1;
+        } else {
+            const int j = i - p.pair_items;
+            unit = j / p.m_chunks; chunk = j - unit * p.m_chunks;
+            it.n_tile = (p.pair_items / p.m_chunks) * 2 + unit;
+            it.nt = 1;
+        }
+        it.row0 = chunk * p.TN;
         it.rows = min(p.TN, p.M - it.row0);
     }
     return it;
@@ -261,9 +279,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint8_t *sW = smem;                                  // STAGES x 16 KB: dequantised weights (A operand)
-    uint8_t *sX = smem + STAGES * A_BYTES;               // STAGES x 32 KB: activations (B operand)
-    SmemCtrl *ctl = reinterpret_cast<SmemCtrl *>(smem + STAGES * (A_BYTES + B_BYTES));
+    const int nst = p.nst;
+    const uint32_t w_stage = (p.pair ? 2 : 1) * A_BYTES;                // one or two dequantised W tiles per stage
+    const uint32_t x_stage = static_cast<uint32_t>(p.TN) * BK * 2;      // multiple of 2 KB
+    uint8_t *sW = smem;                                  // nst x w_stage: dequantised weights (A operand)
+    uint8_t *sX = smem + nst * w_stage;                  // nst x x_stage: activations (B operand)
+    SmemCtrl *ctl = reinterpret_cast<SmemCtrl *>(smem + RING_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = p.K / BK;
@@ -271,7 +292,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
     const uint32_t x_bytes = static_cast<uint32_t>(p.TN) * BK * 2;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < MAX_STAGES; ++s) {
             mbar_init(&ctl->full_x[s], 1);
             mbar_init(&ctl->full_w[s], DEQ_THREADS / 32);
             mbar_init(&ctl->empty[s], 1);
@@ -300,15 +321,15 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
             for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x) {
                 const Item item = get_item(p, i);
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
+                    const int s = it % nst;
+                    const uint32_t ph = (it / nst) & 1;
                     if (!(ok = mbar_wait(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x101, 40))) break;
                     mbar_expect_tx(&ctl->full_x[s], x_bytes);
-                    tma_load_2d(sX + s * B_BYTES, &tmap_x, kb * BK, item.row0, &ctl->full_x[s]);
+                    tma_load_2d(sX + s * x_stage, &tmap_x, kb * BK, item.row0, &ctl->full_x[s]);
                 }
             }
             if (!ok) {   // let copies already in flight land before the CTA tears down
-                for (int s = 0; s < STAGES; ++s)
+                for (int s = 0; s < nst; ++s)
                     for (uint32_t j = 0; j < 4096 && !mbar_try(&ctl->full_x[s], 0) && !mbar_try(&ctl->full_x[s], 1); ++j) {}
             }
         }
@@ -318,22 +339,27 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
             uint32_t it = 0, tile_i = 0;
             bool ok = true;
             for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x, ++tile_i) {
-                const int buf = tile_i & 1;
-                const uint32_t acc_ph = (tile_i >> 1) & 1;
+                const Item item = get_item(p, i);
+                // pairs: both 256-column accumulators belong to one item (no double buffering);
+                // single tiles: the two accumulators alternate so the epilogue overlaps the next item
+                const int buf = p.pair ? 0 : (tile_i & 1);
+                const uint32_t acc_ph = (p.pair ? tile_i : (tile_i >> 1)) & 1;
                 if (!(ok = mbar_wait(&ctl->acc_empty[buf], acc_ph ^ 1, ctl, p.status, 0x201))) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * TN_MAX;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
+                    const int s = it % nst;
+                    const uint32_t ph = (it / nst) & 1;
                     if (!(ok = mbar_wait(&ctl->full_x[s], ph, ctl, p.status, 0x202))) break;
                     if (!(ok = mbar_wait(&ctl->full_w[s], ph, ctl, p.status, 0x203))) break;
                     tc_fence_after();
-                    const uint64_t adesc = make_desc_sw128(smem_u32(sW + s * A_BYTES));
-                    const uint64_t bdesc = make_desc_sw128(smem_u32(sX + s * B_BYTES));
+                    const uint64_t bdesc = make_desc_sw128(smem_u32(sX + s * x_stage));
+                    for (int t = 0; t < item.nt; ++t) {
+                        const uint64_t adesc = make_desc_sw128(smem_u32(sW + s * w_stage + t * A_BYTES));
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)   // 16 elements = 32 bytes further along the swizzled row
-                        umma_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, p.idesc, (kb | k) ? 1u : 0u);
+                        for (int k = 0; k < BK / 16; ++k)   // 16 elements = 32 bytes further along the swizzled row
+                            umma_f16(tmem_d + t * TN_MAX, adesc + 2 * k, bdesc + 2 * k, p.idesc, (kb | k) ? 1u : 0u);
+                    }
                     umma_commit(&ctl->empty[s]);         // frees the stage when these MMAs have read it
                 }
                 if (ok) umma_commit(&ctl->acc_full[buf]);
@@ -345,33 +371,35 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
         uint32_t tile_i = 0;
         bool ok = true;
         for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x, ++tile_i) {
-            const int buf = tile_i & 1;
-            const uint32_t acc_ph = (tile_i >> 1) & 1;
+            const int buf = p.pair ? 0 : (tile_i & 1);
+            const uint32_t acc_ph = (p.pair ? tile_i : (tile_i >> 1)) & 1;
             const Item item = get_item(p, i);
             if (!(ok = mbar_wait_warp(&ctl->acc_full[buf], acc_ph, ctl, p.status, 0x301, 200))) break;
             tc_fence_after();
-            const int n = item.n_tile * BMW + q * 32 + lane;     // output column owned by this thread
-            const bool n_ok = n < p.N;
             const int cols = (item.rows + 15) & ~15;
-            for (int c0 = 0; c0 < cols; c0 += 16) {
-                float ts[16];                      // per-token factors first, so their latency hides behind the TMEM load
+            for (int t = 0; t < item.nt; ++t) {
+                const int n = (item.n_tile + t) * BMW + q * 32 + lane;     // output column owned by this thread
+                const bool n_ok = n < p.N;
+                for (int c0 = 0; c0 < cols; c0 += 16) {
+                    float ts[16];                  // per-token factors first, so their latency hides behind the TMEM load
 #pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    ts[j] = (p.tok_scale && c0 + j < item.rows) ? __ldg(p.tok_scale + item.row0 + c0 + j) : 1.0f;
-                uint32_t v[16];
-                tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * TN_MAX + c0, v);
-                if (n_ok) {
-                    // lanes of a warp hold 32 consecutive columns of the same output row: 64-byte segments
-                    if (p.out_dt == MTC_F16) {
-                        __half *o = static_cast<__half *>(p.out) + static_cast<size_t>(item.row0 + c0) * p.N + n;
+                    for (int j = 0; j < 16; ++j)
+                        ts[j] = (p.tok_scale && c0 + j < item.rows) ? __ldg(p.tok_scale + item.row0 + c0 + j) : 1.0f;
+                    uint32_t v[16];
+                    tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (buf + t) * TN_MAX + c0, v);
+                    if (n_ok) {
+                        // lanes of a warp hold 32 consecutive columns of the same output row: 64-byte segments
+                        if (p.out_dt == MTC_F16) {
+                            __half *o = static_cast<__half *>(p.out) + static_cast<size_t>(item.row0 + c0) * p.N + n;
 #pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (c0 + j < item.rows) o[static_cast<size_t>(j) * p.N] = __float2half_rn(__uint_as_float(v[j]) * ts[j]);
-                    } else {
-                        __nv_bfloat16 *o = static_cast<__nv_bfloat16 *>(p.out) + static_cast<size_t>(item.row0 + c0) * p.N + n;
+                            for (int j = 0; j < 16; ++j)
+                                if (c0 + j < item.rows) o[static_cast<size_t>(j) * p.N] = __float2half_rn(__uint_as_float(v[j]) * ts[j]);
+                        } else {
+                            __nv_bfloat16 *o = static_cast<__nv_bfloat16 *>(p.out) + static_cast<size_t>(item.row0 + c0) * p.N + n;
 #pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (c0 + j < item.rows) o[static_cast<size_t>(j) * p.N] = __float2bfloat16_rn(__uint_as_float(v[j]) * ts[j]);
+                            for (int j = 0; j < 16; ++j)
+                                if (c0 + j < item.rows) o[static_cast<size_t>(j) * p.N] = __float2bfloat16_rn(__uint_as_float(v[j]) * ts[j]);
+                        }
                     }
                 }
             }
@@ -393,46 +421,62 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
         bool ok = true;
         for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x) {
             const Item item = get_item(p, i);
-            const int n = item.n_tile * BMW + r;
-            const bool valid = n < p.N;
-            const size_t grow = static_cast<size_t>(item.expert) * p.N + (valid ? n : 0);
-            const uint32_t *wrow = p.w + grow * p.wpr + h * BITS;
-            const unsigned short *sc16 = static_cast<const unsigned short *>(p.scales) + grow * p.gpr;
-            const unsigned short *bi16 = static_cast<const unsigned short *>(p.biases) + grow * p.gpr;
-            uint32_t wnext[BITS];
-            uint32_t sn = 0, bn = 0;                       // raw 16-bit scale / bias, converted when used
-            load_half_words<BITS>(wrow, wnext, valid);
-            if (valid) {
-                const int g = (h * 32) >> p.gs_shift;
-                sn = __ldg(sc16 + g);
-                bn = __ldg(bi16 + g);
-            }
-            for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                const int s = it % STAGES;
-                const uint32_t ph = (it / STAGES) & 1;
-                uint32_t wcur[BITS];
+            bool valid[2];
+            const uint32_t *wrow[2];
+            const unsigned short *sc16[2], *bi16[2];
 #pragma unroll
-                for (int j = 0; j < BITS; ++j) wcur[j] = wnext[j];
-                const uint32_t sr = sn, br = bn;
-                if (kb + 1 < num_kb) {                     // request the next k block before converting this one
-                    load_half_words<BITS>(wrow + static_cast<size_t>(kb + 1) * (2 * BITS), wnext, valid);
-                    if (valid) {
-                        const int g = ((kb + 1) * BK + h * 32) >> p.gs_shift;
-                        sn = __ldg(sc16 + g);
-                        bn = __ldg(bi16 + g);
+            for (int t = 0; t < 2; ++t) {
+                const int n = (item.n_tile + t) * BMW + r;
+                valid[t] = t < item.nt && n < p.N;
+                const size_t grow = static_cast<size_t>(item.expert) * p.N + (valid[t] ? n : 0);
+                wrow[t] = p.w + grow * p.wpr + h * BITS;
+                sc16[t] = static_cast<const unsigned short *>(p.scales) + grow * p.gpr;
+                bi16[t] = static_cast<const unsigned short *>(p.biases) + grow * p.gpr;
+            }
+            uint32_t wnext[2][BITS];
+            uint32_t sn[2] = {0, 0}, bn[2] = {0, 0};       // raw 16-bit scale / bias, converted when used
+            auto request = [&](int kb) {
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    if (t < item.nt) {
+                        load_half_words<BITS>(wrow[t] + static_cast<size_t>(kb) * (2 * BITS), wnext[t], valid[t]);
+                        if (valid[t]) {
+                            const int g = (kb * BK + h * 32) >> p.gs_shift;
+                            sn[t] = __ldg(sc16[t] + g);
+                            bn[t] = __ldg(bi16[t] + g);
+                        }
                     }
                 }
+            };
+            request(0);
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int s = it % nst;
+                const uint32_t ph = (it / nst) & 1;
+                uint32_t wcur[2][BITS];
+                uint32_t sr[2], br[2];
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+#pragma unroll
+                    for (int j = 0; j < BITS; ++j) wcur[t][j] = wnext[t][j];
+                    sr[t] = sn[t]; br[t] = bn[t];
+                }
+                if (kb + 1 < num_kb) request(kb + 1);      // the next k block is requested before this one is converted
                 // the stage is free once empty[s] has completed (the producer waits on the same barrier)
                 if (!(ok = mbar_wait_warp(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x401, 0))) break;
-                float sc, bi;
-                if (p.sb_dt == MTC_F16) {
-                    sc = __half2float(__ushort_as_half(static_cast<unsigned short>(sr)));
-                    bi = __half2float(__ushort_as_half(static_cast<unsigned short>(br)));
-                } else {
-                    sc = __uint_as_float(sr << 16);
-                    bi = __uint_as_float(br << 16);
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                    if (t < item.nt) {
+                        float sc, bi;
+                        if (p.sb_dt == MTC_F16) {
+                            sc = __half2float(__ushort_as_half(static_cast<unsigned short>(sr[t])));
+                            bi = __half2float(__ushort_as_half(static_cast<unsigned short>(br[t])));
+                        } else {
+                            sc = __uint_as_float(sr[t] << 16);
+                            bi = __uint_as_float(br[t] << 16);
+                        }
+                        dequant_half<BITS>(wcur[t], sc, bi, dst, s * w_stage + t * A_BYTES);
+                    }
                 }
-                dequant_half<BITS>(wcur, sc, bi, dst, s * A_BYTES);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> async proxy (MMA)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ctl->full_w[s]);
@@ -552,7 +596,7 @@ EncodeTiledFn get_encode_fn() {
 
 template <int BITS>
 constexpr size_t qmm_smem_bytes() {
-    return STAGES * (A_BYTES + B_BYTES) + sizeof(SmemCtrl) + 1024;
+    return RING_BYTES + sizeof(SmemCtrl) + 1024;
 }
 
 template <int BITS>
@@ -618,6 +662,9 @@ void fill_common(QmmParams &p, Ctx *ctx, const void *w, const void *scales, cons
     p.wpr = K * bits / 32;
     p.gpr = K / group_size;
     p.TN = TN;
+    p.pair = 0;
+    p.nst = RING_BYTES / (A_BYTES + TN * BK * 2);
+    if (p.nst > MAX_STAGES) p.nst = MAX_STAGES;
     const uint32_t fmt = p.op_f16 ? 0u : 1u;           // both operands carry the same 16-bit format
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(TN >> 3) << 17) |
               (static_cast<uint32_t>(BMW >> 4) << 24);
@@ -681,8 +728,29 @@ cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const v
     p.tok_scale = tok_scale;
     p.M = M;
     p.m_chunks = (M + TN - 1) / TN;
-    p.dense_items = ((N + BMW - 1) / BMW) * p.m_chunks;
-    const int grid = p.dense_items < ctx->sm_count ? p.dense_items : ctx->sm_count;
+    p.n_tiles = (N + BMW - 1) / BMW;
+    const int sms = ctx->sm_count;
+    // Two adjacent weight-row tiles per item halve the activation traffic from L2 (one X stage feeds both) at
+    // the price of a 3-deep ring and no epilogue overlap; measured slower on B200 for the prefill shapes, so it
+    // is off unless asked for.
+    p.pair = (ctx->qmm_pair > 0 && p.n_tiles >= 2) ? 1 : 0;
+    if (p.pair) {
+        p.nst = RING_BYTES / (2 * A_BYTES + TN * BK * 2);
+        if (p.nst > MAX_STAGES) p.nst = MAX_STAGES;
+        const int pairs = (p.n_tiles + 1) / 2;
+        const int pair_units = pairs * p.m_chunks;
+        // whole waves of pairs; the rest as single tiles (whole pair rows of m_chunks items stay together)
+        int full_units = (pair_units / sms) * sms;
+        full_units = (full_units / p.m_chunks) * p.m_chunks;
+        p.pair_items = full_units;
+        const int tiles_done = (full_units / p.m_chunks) * 2;
+        const int tiles_left = p.n_tiles > tiles_done ? p.n_tiles - tiles_done : 0;
+        p.dense_items = full_units + tiles_left * p.m_chunks;
+    } else {
+        p.pair_items = p.n_tiles * p.m_chunks;
+        p.dense_items = p.pair_items;
+    }
+    const int grid = p.dense_items < sms ? p.dense_items : sms;
     return launch_any(bits, st, tmap, p, grid);
 }
 

@@ -1,0 +1,170 @@
+"""Sharding of the quantized matmuls over the GPUs of one node (one process per GPU).
+
+Two natural splits, each with exactly one exchange step:
+
+* dense projections — N-split (column parallel): rank g owns the contiguous weight rows
+  ``[g*N/G, (g+1)*N/G)`` of ``w``, ``scales`` and ``biases`` (all three are row-of-N major, so no
+  repacking), computes ``out[:, slice]`` and the slices are all-gathered;
+* MoE — expert parallel: rank g owns experts ``[g*E/G, (g+1)*E/G)``; tokens are data parallel; routed
+  rows travel to the owner of their expert with an all-to-all, come back with a second one.
+
+The reference is a single-device library (its tests serialise GPU access with one mutex,
+crates/metaltile-std/tests/common/mod.rs:11-27), so none of this has a counterpart there.
+
+``torch.distributed`` carries the collectives (NCCL on GPUs).  The compute steps go through a backend
+object; the default backend calls the CUDA kernels, and the CPU tests of the exchange logic pass their
+own backend (gloo ranks have no GPU).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+def shard_rows(n: int, world: int, rank: int):
+    """Row range of rank ``rank`` in an even N-split; N must divide evenly (every layer shape here does)."""
+    if n % world != 0:
+        raise ValueError(f"N = {n} does not split evenly over {world} ranks")
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+class CudaBackend:
+    """Compute steps on the local GPU through the C ABI."""
+
+    def __init__(self, ctx=None):
+        from . import ops
+        self.ops = ops
+        self.ctx = ctx
+
+    def qmv(self, w, s, b, x, bits, gs, out=None):
+        return self.ops.qmm(w, s, b, x, bits, gs, out=out, ctx=self.ctx)
+
+    def router_topk(self, logits, k, norm):
+        return self.ops.moe_router_topk(logits, k, norm, ctx=self.ctx)
+
+    def moe_sort(self, idx, n_experts):
+        return self.ops.moe_sort(idx, n_experts, ctx=self.ctx)
+
+    def permute(self, tokens, sti):
+        return self.ops.moe_permute(tokens, sti, ctx=self.ctx)
+
+    def unpermute(self, eo, inv, wts):
+        return self.ops.moe_unpermute(eo, inv, wts, ctx=self.ctx)
+
+    def swiglu(self, g, u):
+        return self.ops.swiglu(g, u, ctx=self.ctx)
+
+    def gather_qmm(self, x, w, s, b, bits, gs, offsets):
+        return self.ops.gather_qmm(x, w, s, b, bits, gs, expert_offsets=offsets, ctx=self.ctx)
+
+
+class ColumnParallelLinear:
+    """One N-split quantized projection: local ``w[N/G, K*bits/32]``, ``scales``/``biases[N/G, K/g]``."""
+
+    def __init__(self, w, scales, biases, bits: int, group_size: int, backend=None, group=None):
+        self.w, self.scales, self.biases = w, scales, biases
+        self.bits, self.group_size = bits, group_size
+        self.backend = backend or CudaBackend()
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+
+    def forward(self, x):
+        """x [M, K] replicated on every rank -> out [M, N] replicated."""
+        local = self.backend.qmv(self.w, self.scales, self.biases, x, self.bits, self.group_size)
+        if self.world == 1:
+            return local
+        m, nl = local.shape
+        flat = torch.empty((self.world * m, nl), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(flat, local.contiguous(), group=self.group)
+        gathered = flat.view(self.world, m, nl)
+        # all-gather yields [G][M][N/G]; row-major [M][N] needs the rank axis next to the columns
+        return gathered.permute(1, 0, 2).reshape(m, self.world * nl) if m > 1 else gathered.reshape(1, -1)
+
+
+@dataclass
+class ExpertShard:
+    """The experts a rank owns: gate / up [E_l, I, H*bits/32], down [E_l, H, I*bits/32] (+ scales, biases)."""
+    gate: tuple
+    up: tuple
+    down: tuple
+    bits: int
+    group_size: int
+
+
+class ExpertParallelMoE:
+    """router -> sort -> permute -> all-to-all -> gather_qmm(gate, up) -> SwiGLU -> gather_qmm(down)
+    -> all-to-all -> unpermute, with ``n_experts`` split evenly over the ranks of ``group``."""
+
+    def __init__(self, shard: ExpertShard, n_experts: int, top_k: int, norm_topk_prob: int = 1, backend=None,
+                 group=None):
+        self.shard, self.n_experts, self.top_k, self.norm = shard, n_experts, top_k, norm_topk_prob
+        self.backend = backend or CudaBackend()
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        if n_experts % self.world != 0:
+            raise ValueError("n_experts must split evenly over the ranks")
+        self.e_local = n_experts // self.world
+
+    def _experts(self, x_sorted, offsets):
+        be, sh = self.backend, self.shard
+        g = be.gather_qmm(x_sorted, *sh.gate, sh.bits, sh.group_size, offsets)
+        u = be.gather_qmm(x_sorted, *sh.up, sh.bits, sh.group_size, offsets)
+        a = be.swiglu(g, u)
+        return be.gather_qmm(a, *sh.down, sh.bits, sh.group_size, offsets)
+
+    def forward(self, tokens, logits):
+        """tokens [T_local, H], logits [T_local, E] -> [T_local, H]."""
+        be, world, e_l = self.backend, self.world, self.e_local
+        idx, wts = be.router_topk(logits, self.top_k, self.norm)
+        sti, inv, off, _ = be.moe_sort(idx, self.n_experts)
+        xp = be.permute(tokens, sti)                      # rows sorted by global expert id = by owner rank
+        if world == 1:
+            y = self._experts(xp, off)
+            return be.unpermute(y, inv, wts)
+
+        off64 = off.to(torch.int64)
+        counts = (off64[1:] - off64[:-1]).reshape(world, e_l)          # rows I send, per (owner, its expert)
+        recv_counts = torch.empty_like(counts)
+        dist.all_to_all_single(recv_counts, counts, group=self.group)  # rows I receive, per (source, my expert)
+        send_splits = counts.sum(dim=1).tolist()                       # host sync: split sizes are Python ints
+        recv_splits = recv_counts.sum(dim=1).tolist()
+        n_recv = int(sum(recv_splits))
+        recv = torch.empty((n_recv, tokens.shape[1]), dtype=tokens.dtype, device=tokens.device)
+        dist.all_to_all_single(recv, xp, recv_splits, send_splits, group=self.group)
+
+        # received rows are source-major, expert-minor; the experts want expert-major order
+        order = expert_major_order(recv_counts)
+        x_sorted = recv.index_select(0, order)
+        local_off = torch.zeros(e_l + 1, dtype=torch.int32, device=tokens.device)
+        local_off[1:] = recv_counts.sum(dim=0).cumsum(0).to(torch.int32)
+        y_sorted = self._experts(x_sorted, local_off)
+
+        y_recv = torch.empty_like(y_sorted)
+        y_recv.index_copy_(0, order, y_sorted)            # back to source-major order
+        y = torch.empty((xp.shape[0], y_recv.shape[1]), dtype=y_recv.dtype, device=y_recv.device)
+        dist.all_to_all_single(y, y_recv, send_splits, recv_splits, group=self.group)
+        return be.unpermute(y, inv, wts)
+
+
+def expert_major_order(recv_counts: torch.Tensor) -> torch.Tensor:
+    """Gather index turning a source-major / expert-minor row list into expert-major / source-minor.
+
+    ``recv_counts[s, e]`` = rows received from source ``s`` for local expert ``e``; rows arrive as
+    ``for s: for e: rows``.  The result lists, for e ascending and s ascending, the positions of those rows.
+    """
+    world, e_l = recv_counts.shape
+    flat = recv_counts.reshape(-1).to(torch.int64)                      # index s*e_l + e
+    start = torch.cumsum(flat, 0) - flat                                # first row of block (s, e) on arrival
+    blocks = torch.arange(world * e_l, device=recv_counts.device).reshape(world, e_l).t().reshape(-1)  # (e, s) order
+    lens = flat[blocks]
+    total = int(lens.sum())
+    if total == 0:
+        return torch.zeros(0, dtype=torch.int64, device=recv_counts.device)
+    block_of_row = torch.repeat_interleave(torch.arange(blocks.numel(), device=lens.device), lens)
+    first_out = torch.cumsum(lens, 0) - lens
+    within = torch.arange(total, device=lens.device) - first_out[block_of_row]
+    return start[blocks][block_of_row] + within

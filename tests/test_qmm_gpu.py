@@ -101,3 +101,21 @@ def test_linearity_and_row_independence_at_full_size(ctx):
     few = ops.qmv(wd, sd, bd, to_dev(x[:4], dt), bits, gs)
     torch.cuda.synchronize()
     assert rel_err(full[:4].float().cpu().numpy(), few.float().cpu().numpy()) <= TOL[dt]
+
+
+def test_paired_weight_tiles_option(ctx):
+    """"qmm_pair" = 1: one activation stage feeds two weight-row tiles; same numbers as the default."""
+    import torch
+    from metaltile_b200 import ops
+    m, n, k, bits, gs, dt = 300, 640 + 128, 512, 4, 64, "f16"       # 6 weight-row tiles, the last pair is odd
+    w, s, b, x = dense_case(m, n, k, bits, gs, dt, seed=0, salt=8)
+    wd, sd, bd, xd = to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt)
+    base = ops.qmm(wd, sd, bd, xd, bits, gs)
+    ctx.set_option("qmm_pair", 1)
+    try:
+        paired = ops.qmm(wd, sd, bd, xd, bits, gs)
+        torch.cuda.synchronize()
+    finally:
+        ctx.set_option("qmm_pair", 0)
+    assert torch.equal(base, paired)
+    assert rel_err(base.float().cpu().numpy(), oracle.qmm(w, s, b, x, m, n, k, bits, gs)) <= TOL[dt]
