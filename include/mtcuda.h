@@ -110,6 +110,20 @@ int mtc_set_option(mtc_ctx *ctx, const char *name, int value);
 int mtc_gather_qmm(mtc_ctx *ctx, void *stream, const void *x, const void *w, const void *scales,
                    const void *biases, const void *expert_offsets, const void *indices, void *out,
                    int m_total, int n_out, int k_in, int n_experts, int bits, int group_size, int dtype);
+/* mtc_gather_qmm without any allocation (no counterpart in the reference; added for hosts that may
+ * not allocate device memory where they run a MoE layer: processes whose device memory is handed out
+ * in full by their own allocator at start-up, and latency-critical loops that must not take the
+ * allocator's lock or risk an out-of-memory error mid-step).  Same arguments and results as
+ * mtc_gather_qmm on its tensor-core path; the work list and the f16 copy of bf16 activations live in one
+ * fixed array inside the library image (about 17 MiB per GPU that loads the library, kept until exit).
+ * Limits: at most 16384 work items (n_out/128 x (m_total/chunk + n_experts)); with bf16 activations
+ * m_total * k_in <= 8 Mi elements and m_total <= 65536; f16 or bf16 only, k_in % 64 == 0, power-of-two
+ * group >= 32.  Larger sizes return MTC_ERR_BUFFER_SIZE, other shapes MTC_ERR_UNSUPPORTED.  The first call on
+ * a device looks up the array's device address (make it before any stream capture).  All calls share the
+ * array: two calls that overlap on the GPU (different streams) race; calls on one stream are safe. */
+int mtc_gather_qmm_static(mtc_ctx *ctx, void *stream, const void *x, const void *w, const void *scales,
+                          const void *biases, const void *expert_offsets, const void *indices, void *out,
+                          int m_total, int n_out, int k_in, int n_experts, int bits, int group_size, int dtype);
 const char *mtc_gather_qmm_route(int m_total, int n_out, int k_in, int bits, int group_size, int dtype);
 
 /* mt_moe_router_topk (moe.rs:65-192): indices_out u32[n_rows, k], weights_out T[n_rows, k]; ties go to

@@ -45,6 +45,7 @@ SIGNATURES = {
     "mtc_qmm": (_i, _DENSE),
     "mtc_qmm_route": (ctypes.c_char_p, [_i, _i, _i, _i, _i, _i]),
     "mtc_gather_qmm": (_i, [_vp] * 9 + [_i] * 7),
+    "mtc_gather_qmm_static": (_i, [_vp] * 9 + [_i] * 7),
     "mtc_gather_qmm_route": (ctypes.c_char_p, [_i] * 6),
     "mtc_moe_router_topk": (_i, [_vp] * 5 + [_i] * 5),
     "mtc_moe_sort": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),

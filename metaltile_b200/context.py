@@ -142,6 +142,12 @@ class Context:
         self._check(self._lib.mtc_gather_qmm(self._h, stream, x, w, scales, biases, expert_offsets, indices, out,
                                              m_total, n_out, k_in, n_experts, bits, group_size, _dt(dtype)))
 
+    def gather_qmm_static(self, x, w, scales, biases, out, m_total, n_out, k_in, n_experts, bits, group_size, dtype,
+                          expert_offsets=None, indices=None, stream: int = 0):
+        """``gather_qmm`` with its scratch in a fixed array of the library: allocates nothing (see mtcuda.h)."""
+        self._check(self._lib.mtc_gather_qmm_static(self._h, stream, x, w, scales, biases, expert_offsets, indices,
+                                                    out, m_total, n_out, k_in, n_experts, bits, group_size, _dt(dtype)))
+
     def gather_qmm_route(self, m_total, n_out, k_in, bits, group_size, dtype) -> str:
         return self._lib.mtc_gather_qmm_route(m_total, n_out, k_in, bits, group_size, _dt(dtype)).decode()
 

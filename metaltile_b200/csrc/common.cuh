@@ -83,6 +83,10 @@ cudaError_t launch_gather_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *x, 
                                       const void *biases, const uint32_t *expert_offsets, const uint32_t *indices,
                                       void *out, int total_rows, int N, int K, int n_experts, int bits, int group_size,
                                       int dt, void *scratch, size_t scratch_bytes, std::string *why);
+cudaError_t launch_gather_qmm_static(Ctx *ctx, cudaStream_t st, const void *x, const void *w, const void *scales,
+                                     const void *biases, const uint32_t *expert_offsets, const uint32_t *indices,
+                                     void *out, int total_rows, int N, int K, int n_experts, int bits, int group_size,
+                                     int dt, std::string *why);
 cudaError_t launch_router_topk(cudaStream_t st, const void *logits, uint32_t *idx, void *wts, int n_rows, int n_experts,
                                int k, int norm, int dt);
 cudaError_t launch_moe_sort(cudaStream_t st, const uint32_t *topk_idx, int n_tokens, int k, int n_experts, uint32_t *sti,

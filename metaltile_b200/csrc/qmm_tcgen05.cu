@@ -802,4 +802,91 @@ cudaError_t launch_gather_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *x, 
     return launch_any(bits, st, tmap, p, ctx->sm_count);
 }
 
+// ---- gather_qmm for callers that cannot allocate ---------------------------------------------------
+// Some hosts of this library may not call cudaMalloc at the point where they run a MoE layer:
+// allocator-managed processes where every device byte is accounted for at start-up, and latency-critical
+// loops that must not take the allocator's lock or meet an out-of-memory error in the middle of a step.  mtc_gather_qmm_static does the same
+// work as mtc_gather_qmm on the tensor-core path but takes its scratch (the work list and the scaled-f16
+// copy of bf16 activations) from one fixed array that lives in the library image: every GPU that loads
+// the library holds these bytes until the process exits.  Limits below; sizes beyond them are refused.
+constexpr size_t kStaticItems = 16384;                        // work items (16 bytes each)
+constexpr size_t kStaticXElems = 8u << 20;                    // bf16 activations staged as f16: m_total * k_in elements
+constexpr size_t kStaticRows = 65536;                         // rows of x (one f32 factor each)
+constexpr size_t kStaticListBytes = 16 + kStaticItems * sizeof(int4);
+constexpr size_t kStaticXOff = (kStaticListBytes + 255) & ~static_cast<size_t>(255);
+constexpr size_t kStaticScaleOff = kStaticXOff + kStaticXElems * 2;
+constexpr size_t kStaticBytes = kStaticScaleOff + kStaticRows * sizeof(float);
+
+static __device__ __align__(256) unsigned char g_gather_static[kStaticBytes];
+
+// The array's name is a host-side handle, not a device address: the address each device gave it is
+// looked up once per device (with that device current) and cached.
+cudaError_t gather_static_base(unsigned char **base) {
+    static unsigned char *cache[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!cache[dev]) {
+        void *ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_gather_static);
+        if (e != cudaSuccess) return e;
+        cache[dev] = static_cast<unsigned char *>(ptr);
+    }
+    *base = cache[dev];
+    return cudaSuccess;
+}
+
+cudaError_t launch_gather_qmm_static(Ctx *ctx, cudaStream_t st, const void *x, const void *w, const void *scales,
+                                     const void *biases, const uint32_t *expert_offsets, const uint32_t *indices,
+                                     void *out, int total_rows, int N, int K, int n_experts, int bits, int group_size,
+                                     int dt, std::string *why) {
+    int TN = ctx->qmm_force_tn;
+    if (TN <= 0) {
+        const int mean = (total_rows + n_experts - 1) / n_experts;
+        TN = ((2 * mean + 15) / 16) * 16;
+        if (TN < 32) TN = 32;
+        if (TN > TN_MAX) TN = TN_MAX;
+    }
+    if (gather_items_bytes(total_rows, n_experts, N, TN) > kStaticListBytes) {
+        if (why) *why = "gather_qmm_static: more than " + std::to_string(kStaticItems) + " work items (n_out/128 * (m_total/chunk + n_experts))";
+        return cudaErrorInvalidValue;
+    }
+    if (dt == MTC_BF16 && (static_cast<size_t>(total_rows) * K > kStaticXElems || static_cast<size_t>(total_rows) > kStaticRows)) {
+        if (why) *why = "gather_qmm_static: bf16 activations are limited to m_total * k_in <= " + std::to_string(kStaticXElems) +
+                        " elements and m_total <= " + std::to_string(kStaticRows);
+        return cudaErrorInvalidValue;
+    }
+    unsigned char *base = nullptr;
+    cudaError_t e = gather_static_base(&base);
+    if (e != cudaSuccess) return e;
+    const int n_tiles = (N + BMW - 1) / BMW;
+    int *count = reinterpret_cast<int *>(base);
+    int4 *items = reinterpret_cast<int4 *>(base + 16);
+    // the list and its count are rewritten by every call; nothing in the array has to start at zero
+    build_items_kernel<<<1, 256, 2 * (n_experts + 1) * sizeof(int), st>>>(expert_offsets, indices, total_rows, n_experts,
+                                                                         n_tiles, TN, count, items, static_cast<int>(kStaticItems));
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    const void *x_op = x;
+    const float *tok_scale = nullptr;
+    if (dt == MTC_BF16) {
+        __half *y = reinterpret_cast<__half *>(base + kStaticXOff);
+        float *scale = reinterpret_cast<float *>(base + kStaticScaleOff);
+        rows_to_f16_kernel<<<(total_rows + 7) / 8, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), y, scale, total_rows, K);
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+        x_op = y;
+        tok_scale = scale;
+    }
+    CUtensorMap tmap;
+    e = make_x_map(&tmap, x_op, total_rows, K, TN, 1, why);
+    if (e != cudaSuccess) return e;
+    QmmParams p{};
+    fill_common(p, ctx, w, scales, biases, out, N, K, bits, group_size, dt, TN);
+    p.tok_scale = tok_scale;
+    p.M = total_rows;
+    p.items = items;
+    p.item_count = count;
+    return launch_any(bits, st, tmap, p, ctx->sm_count);
+}
+
 }  // namespace mtc

@@ -356,6 +356,33 @@ int mtc_gather_qmm(mtc_ctx *ctx, void *stream, const void *x, const void *w, con
     return MTC_OK;
 }
 
+int mtc_gather_qmm_static(mtc_ctx *ctx, void *stream, const void *x, const void *w, const void *scales,
+                          const void *biases, const void *expert_offsets, const void *indices, void *out, int m_total,
+                          int n_out, int k_in, int n_experts, int bits, int group_size, int dtype) {
+    if (!ctx) return MTC_ERR_INVALID;
+    if (dtype != MTC_F16 && dtype != MTC_BF16)
+        return fail(ctx, MTC_ERR_UNSUPPORTED, "gather_qmm_static: dtype must be f16 or bf16 (the tensor-core path)");
+    if ((expert_offsets == nullptr) == (indices == nullptr))
+        return fail(ctx, MTC_ERR_INVALID, "gather_qmm_static: give exactly one of expert_offsets and indices");
+    if (m_total < 0 || n_out < 0 || n_experts <= 0 || n_experts > 4096)
+        return fail(ctx, MTC_ERR_UNSUPPORTED, "gather_qmm_static: need 0 < n_experts <= 4096 and non-negative sizes");
+    if (m_total == 0 || n_out == 0) return MTC_OK;
+    if (!x || !w || !scales || !biases || !out) return fail(ctx, MTC_ERR_INVALID, "gather_qmm_static: null pointer");
+    if (!mtc::qmm_tcgen05_supported(m_total, n_out, k_in, bits, group_size, dtype, w, x, out))
+        return fail(ctx, MTC_ERR_UNSUPPORTED,
+                    "gather_qmm_static: needs bits in {2,3,4,5,6,8}, k_in % 64 == 0, a power-of-two group >= 32 and "
+                    "16-byte aligned x and w");
+    std::string why;
+    cudaError_t e = mtc::launch_gather_qmm_static(ctx, static_cast<cudaStream_t>(stream), x, w, scales, biases,
+                                                  static_cast<const uint32_t *>(expert_offsets),
+                                                  static_cast<const uint32_t *>(indices), out, m_total, n_out, k_in,
+                                                  n_experts, bits, group_size, dtype, &why);
+    if (e == cudaErrorInvalidValue && !why.empty()) return fail(ctx, MTC_ERR_BUFFER_SIZE, why);
+    if (e != cudaSuccess)
+        return fail(ctx, MTC_ERR_DISPATCH, "gather_qmm_static launch: " + (why.empty() ? std::string(cudaGetErrorString(e)) : why));
+    return MTC_OK;
+}
+
 const char *mtc_gather_qmm_route(int m_total, int n_out, int k_in, int bits, int group_size, int dtype) {
     return mtc::qmm_tcgen05_supported(m_total, n_out, k_in, bits, group_size, dtype, nullptr, nullptr, nullptr)
                ? "gather_qmm_tcgen05" : "gather_qmm_cuda_core";
