@@ -296,9 +296,15 @@ def main():
     e2e_ms = timed(e2e_step, e2e_steps)
     e2e_value = total_bytes / (e2e_ms * 1e-3) / 1e9
 
-    if rank != 0:
+    def finish():
+        # NCCL communicators captured in a CUDA graph do not tear down reliably: leave without destroying them
+        sys.stdout.flush()
+        sys.stderr.flush()
         if world > 1:
-            dist.destroy_process_group()
+            os._exit(0)
+
+    if rank != 0:
+        finish()
         return
 
     hbm_peak, tf_burst, tf_sus, peak_kind = measured_peaks()
@@ -330,8 +336,7 @@ def main():
         except Exception as e:
             line["cpu_baseline"] = {"error": repr(e)}
     print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    finish()
 
 
 def extra_measurements(ctx, dev, hbm_peak, tf_peak):

@@ -74,8 +74,10 @@ int mtc_status_word(mtc_ctx *ctx, uint32_t *word);
 /* mt_qmv and the generic mt_qmv_b{3,4,5,6,8} / mt_qmm_b* / mt_qmm{,_bm2,_bm4} and
  * dequant_gemv_int2 family: out[m,n] = sum_k (q*scale + bias) * x[m,k], f32
  * accumulate (crates/metaltile-std/src/mlx/quantized.rs:7-308,343-1441,4273-4392;
- * crates/metaltile-std/src/ffai/dequant_gemv.rs:52-105).  CUDA-core path, any M
- * (tuned for M <= 16), bits in {2,3,4,5,6,8}, K*bits % 32 == 0, group_size | K. */
+ * crates/metaltile-std/src/ffai/dequant_gemv.rs:52-105).  Any M (tuned for M <= 16), bits in
+ * {2,3,4,5,6,8}, K*bits % 32 == 0, group_size | K.  M = 1 and every general case run on CUDA cores;
+ * 2 <= M <= 16 with 4-bit codes, f16/bf16 activations, K % 64 == 0 and a power-of-two group >= 64 use
+ * warp-level tensor-core MMAs on the integer codes (f32 accumulate, affine part applied per group). */
 int mtc_qmv(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases,
             const void *x, void *out, int M, int N, int K, int bits, int group_size, int dtype);
 
@@ -88,7 +90,7 @@ int mtc_qmv(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
 int mtc_qmm(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases,
             const void *x, void *out, int M, int N, int K, int bits, int group_size, int dtype);
 /* Name of the kernel family mtc_qmm would run for these arguments
- * ("qmv_cuda_core", "qmm_tcgen05"); the analogue of asserting on
+ * ("qmv_cuda_core", "qmv_mma_sync", "qmm_tcgen05"); the analogue of asserting on
  * mt_qmm_for's routing (quantized.rs:5127-5199). */
 const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dtype);
 
@@ -97,6 +99,8 @@ const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dty
  * crates/metaltile-core/src/toolchain/config.rs:11-96).  Options:
  *   "qmm_tile_tokens"  token rows per tensor-core work item (0 = chosen per shape; else a multiple
  *                      of 16 in [16, 256])
+ *   "qmv_small_m_mma"  0: keep 2 <= M <= 16 on the CUDA-core kernel (default 1: 4-bit codes with f16/bf16
+ *                      activations and a group that is a multiple of 64 use the warp-level tensor cores)
  *   "qmm_pair"         1: a work item covers two adjacent weight-row tiles that share every
  *                      activation stage (dense qmm only; default 0) */
 int mtc_set_option(mtc_ctx *ctx, const char *name, int value);

@@ -23,6 +23,7 @@ struct Ctx {
     void *d_scratch = nullptr;     // grow-only scratch owned by the context
     size_t scratch_bytes = 0;
     int qmm_force_tn = 0;          // option "qmm_tile_tokens": 0 = choose per shape
+    int qmv_small_m_mma = 1;       // option "qmv_small_m_mma": 0 keeps 2 <= M <= 16 on the CUDA-core kernel
     int qmm_pair = 0;              // option "qmm_pair": 1 = give a work item two adjacent weight-row tiles
     void *d_worklist = nullptr;    // gather_qmm work list (grow-only, owned by the context)
     size_t worklist_bytes = 0;
@@ -73,6 +74,9 @@ cudaError_t launch_qmv(Ctx *ctx, cudaStream_t st, const void *w, const void *sca
                        const void *x, void *out, int M, int N, int K, int bits, int group_size, int dt,
                        std::string *why);
 cudaError_t qmv_init_device();
+bool qmv_mma_supported(int M, int N, int K, int bits, int group_size, int dt, const void *w, const void *x);
+cudaError_t launch_qmv_mma(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases, const void *x,
+                           void *out, int M, int N, int K, int group_size, int dt);
 bool qmm_tcgen05_supported(int M, int N, int K, int bits, int group_size, int dt, const void *w, const void *x,
                            const void *out);
 cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases,

@@ -186,6 +186,47 @@ __global__ void __launch_bounds__(256) unpermute_kernel(const void *expert_out, 
     }
 }
 
+// 16-bit activations, hidden % 8 == 0, 16-byte aligned rows: 8 columns per thread, one 128-bit load per expert row
+__global__ void __launch_bounds__(256) unpermute16_kernel(const uint4 *expert_out, const uint32_t *inv_perm, const void *weights,
+                                                          uint4 *out, int n_tokens, int hidden8, int k, int dt) {
+    const int t = blockIdx.x;
+    if (t >= n_tokens) return;
+    for (int h8 = threadIdx.x; h8 < hidden8; h8 += blockDim.x) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j < k; ++j) {
+            const uint32_t pos = __ldg(inv_perm + static_cast<size_t>(t) * k + j);
+            const float w = ld_as_f32(weights, static_cast<size_t>(t) * k + j, dt);
+            const uint4 v = __ldg(expert_out + static_cast<size_t>(pos) * hidden8 + h8);
+            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float lo, hi;
+                if (dt == MTC_BF16) {
+                    lo = __uint_as_float(u[q] << 16);
+                    hi = __uint_as_float(u[q] & 0xFFFF0000u);
+                } else {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&u[q]));
+                    lo = f.x; hi = f.y;
+                }
+                acc[2 * q] = acc[2 * q] + w * lo;
+                acc[2 * q + 1] = acc[2 * q + 1] + w * hi;
+            }
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (dt == MTC_BF16) {
+                const __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+                o[q] = *reinterpret_cast<const uint32_t *>(&p2);
+            } else {
+                const __half2 p2 = __floats2half2_rn(acc[2 * q], acc[2 * q + 1]);
+                o[q] = *reinterpret_cast<const uint32_t *>(&p2);
+            }
+        }
+        out[static_cast<size_t>(t) * hidden8 + h8] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 // ---- mt_swiglu (swiglu.rs:45-57): silu(g) * u in f32 ------------------------------------------------
 __global__ void __launch_bounds__(256) swiglu_kernel(const void *gate, const void *up, void *out, size_t n, int dt) {
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
@@ -193,6 +234,37 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const void *gate, const voi
         const float g = ld_as_f32(gate, i, dt), u = ld_as_f32(up, i, dt);
         const float s = g / (1.0f + expf(-g));
         st_from_f32(out, i, s * u, dt);
+    }
+}
+
+// 16-bit activations, n % 8 == 0, 16-byte aligned: 8 elements per thread
+__global__ void __launch_bounds__(256) swiglu16_kernel(const uint4 *gate, const uint4 *up, uint4 *out, size_t n8, int dt) {
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n8;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const uint4 gv = __ldg(gate + i), uv = __ldg(up + i);
+        const uint32_t g4[4] = {gv.x, gv.y, gv.z, gv.w}, u4[4] = {uv.x, uv.y, uv.z, uv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            float g0, g1, u0, u1;
+            if (dt == MTC_BF16) {
+                g0 = __uint_as_float(g4[q] << 16); g1 = __uint_as_float(g4[q] & 0xFFFF0000u);
+                u0 = __uint_as_float(u4[q] << 16); u1 = __uint_as_float(u4[q] & 0xFFFF0000u);
+            } else {
+                const float2 gf = __half22float2(*reinterpret_cast<const __half2 *>(&g4[q]));
+                const float2 uf = __half22float2(*reinterpret_cast<const __half2 *>(&u4[q]));
+                g0 = gf.x; g1 = gf.y; u0 = uf.x; u1 = uf.y;
+            }
+            const float r0 = (g0 / (1.0f + expf(-g0))) * u0, r1 = (g1 / (1.0f + expf(-g1))) * u1;
+            if (dt == MTC_BF16) {
+                const __nv_bfloat162 p2 = __floats2bfloat162_rn(r0, r1);
+                o[q] = *reinterpret_cast<const uint32_t *>(&p2);
+            } else {
+                const __half2 p2 = __floats2half2_rn(r0, r1);
+                o[q] = *reinterpret_cast<const uint32_t *>(&p2);
+            }
+        }
+        out[i] = make_uint4(o[0], o[1], o[2], o[3]);
     }
 }
 
@@ -268,15 +340,27 @@ cudaError_t launch_permute(cudaStream_t st, const void *tokens, const uint32_t *
 cudaError_t launch_unpermute(cudaStream_t st, const void *eo, const uint32_t *inv, const void *wts, void *out, int n_tokens,
                              int hidden, int k, int dt) {
     if (n_tokens <= 0) return cudaSuccess;
-    unpermute_kernel<<<n_tokens, 256, 0, st>>>(eo, inv, wts, out, n_tokens, hidden, k, dt);
+    const auto al16 = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    if (dt != MTC_F32 && hidden % 8 == 0 && al16(eo) && al16(out))
+        unpermute16_kernel<<<n_tokens, 256, 0, st>>>(static_cast<const uint4 *>(eo), inv, wts, static_cast<uint4 *>(out), n_tokens,
+                                                     hidden / 8, k, dt);
+    else
+        unpermute_kernel<<<n_tokens, 256, 0, st>>>(eo, inv, wts, out, n_tokens, hidden, k, dt);
     return cudaGetLastError();
 }
 
 cudaError_t launch_swiglu(cudaStream_t st, const void *gate, const void *up, void *out, size_t n, int dt) {
     if (n == 0) return cudaSuccess;
-    size_t grid = (n + 255) / 256;
+    const auto al16 = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    const bool vec = dt != MTC_F32 && n % 8 == 0 && al16(gate) && al16(up) && al16(out);
+    const size_t work = vec ? n / 8 : n;
+    size_t grid = (work + 255) / 256;
     if (grid > static_cast<size_t>(kNumSMsB200) * 16) grid = static_cast<size_t>(kNumSMsB200) * 16;
-    swiglu_kernel<<<static_cast<int>(grid), 256, 0, st>>>(gate, up, out, n, dt);
+    if (vec)
+        swiglu16_kernel<<<static_cast<int>(grid), 256, 0, st>>>(static_cast<const uint4 *>(gate), static_cast<const uint4 *>(up),
+                                                               static_cast<uint4 *>(out), n / 8, dt);
+    else
+        swiglu_kernel<<<static_cast<int>(grid), 256, 0, st>>>(gate, up, out, n, dt);
     return cudaGetLastError();
 }
 

@@ -1,0 +1,519 @@
+// qmv for 2 <= M <= 16 token rows with 4-bit codes and 16-bit activations, on the warp-level tensor
+// cores (mma.sync m16n8k16, f32 accumulate).  Same contract as the CUDA-core kernel of qmv.cu:
+//   out[m, n] = sum_k (q(n,k) * scale[n, k/G] + bias[n, k/G]) * x[m, k]
+// (mt_qmm, mt_qmm_bm2, mt_qmm_bm4, mt_qmm_b4: crates/metaltile-std/src/mlx/quantized.rs:343-1441,4519-4523).
+//
+// Why: on CUDA cores every (code, token) pair costs one FFMA, so M = 8..16 is FFMA-bound at 5-10 % of
+// the HBM roofline.  Here a code costs ~0.9 integer ops regardless of M: the integer codes themselves are
+// the A operand (a code q < 16 is exact in bf16 and f16), the activations are the B operand, and the
+// affine part is applied per group on the f32 accumulators,
+//   acc += scale * (sum_k (OFF + q) x  -  OFF * sum_k x) + bias * sum_k x,
+// where OFF (128 for bf16, 1024 for f16) is the exponent trick that turns `(word >> 4j) & 0x000F000F | magic`
+// into two ready-made 16-bit floats OFF + q without any conversion instruction.
+//
+// Mapping.  A warp owns 16 weight rows; lane = 4*g + t holds rows g and g+8.  Per 64-code segment a lane
+// loads 8 bytes of each of its two rows (words 2t, 2t+1 of the segment), i.e. every byte of the packed
+// matrix is loaded exactly once.  MMA j (j = 0..3) of a segment uses nibbles j and j+4 of those words, so
+// its 16 k-slots are the k values {16t + j, 16t + j + 4, 16t + 8 + j, 16t + 8 + j + 4 : t = 0..3} of the
+// segment; the contraction index may be permuted freely as long as the B operand follows, and B (the
+// activations) is staged in shared memory in exactly that order.  No cross-lane reduction is needed.
+// Group sizes that are multiples of 64 only (one scale/bias pair per segment and row).
+#include "common.cuh"
+
+namespace mtc {
+namespace {
+
+constexpr int kMmaWarps = 8;
+constexpr int kStageBytes = 64 * 1024;   // activations staged at a time: 64 segments (4096 k) for M <= 8, 32 for M <= 16
+constexpr int kMmaPF = 8;                // 64-code segments of packed words in flight per lane
+
+struct MmaArgs {
+    const uint32_t *w;
+    const void *scales, *biases, *x;
+    void *out;
+    int M, N, K, gs_shift, dt;
+    int wpr, gpr, nseg;      // words / groups per weight row, 64-code segments per row
+    int tiles, ksplit_shift, iters;
+};
+
+// d = a * b + (kZero ? 0 : d): m16n8k16, 16-bit operands, f32 accumulators
+template <bool BF16, bool kZero>
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    if (kZero) {
+        if (BF16)
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                         : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+                         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
+        else
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                         : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+                         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
+    } else {
+        if (BF16)
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+        else
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    }
+}
+
+// Two codes of a packed word as two 16-bit floats OFF + q: nibbles j and j+4, one shift and one LOP3.
+template <int J>
+__device__ __forceinline__ uint32_t code_pair(uint32_t word, uint32_t magic) {
+    uint32_t r;
+    const uint32_t sh = J == 0 ? word : word >> (4 * J);
+    asm("lop3.b32 %0, %1, 0x000F000F, %2, 0xEA;" : "=r"(r) : "r"(sh), "r"(magic));   // (sh & mask) | magic
+    return r;
+}
+
+// All MMAs of one 64-code segment for the rows and tokens of this lane: d = sum (OFF + q) x, xs = sum x.
+template <int NT, bool BF16>
+__device__ __forceinline__ void segment_mmas(float (&d)[NT][4], float (&xs)[NT][4], const uint2 cl, const uint2 ch,
+                                             const uint4 *frag /* this lane's chunk 0 of the segment */, int lane) {
+    constexpr uint32_t magic = BF16 ? 0x43004300u : 0x64006400u;
+    constexpr uint32_t one2 = BF16 ? 0x3F803F80u : 0x3C003C00u;
+    const uint32_t ones[4] = {one2, one2, one2, one2};
+    const int sw = (lane >> 2) & 1;                      // the XOR of frag_chunk
+    uint4 bf[2][NT];
+#pragma unroll
+    for (int jp = 0; jp < 2; ++jp)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) bf[jp][nt] = frag[nt * 64 + (jp ^ sw)];
+#define MTC_STEP(J, ZERO)                                                                                 \
+    {                                                                                                     \
+        const uint32_t af[4] = {code_pair<J>(cl.x, magic), code_pair<J>(ch.x, magic), code_pair<J>(cl.y, magic), \
+                                code_pair<J>(ch.y, magic)};                                               \
+        _Pragma("unroll") for (int nt = 0; nt < NT; ++nt) {                                               \
+            const uint4 f = bf[(J) >> 1][nt];                                                             \
+            const uint32_t b0 = ((J) & 1) ? f.z : f.x, b1 = ((J) & 1) ? f.w : f.y;                        \
+            mma16816<BF16, ZERO>(d[nt], af, b0, b1);                                                      \
+            mma16816<BF16, ZERO>(xs[nt], ones, b0, b1);                                                   \
+        }                                                                                                 \
+    }
+    MTC_STEP(0, true)
+    MTC_STEP(1, false)
+    MTC_STEP(2, false)
+    MTC_STEP(3, false)
+#undef MTC_STEP
+}
+
+// Shared-memory address (in 16-byte chunks) of the B fragments of (segment s, token tile nt, lane, j pair jp):
+// a lane's four uint2 fragments (j = 0..3) are 32 contiguous bytes, read as two 16-byte loads; the XOR keeps
+// each quarter-warp of such a load on 32 distinct banks.
+template <int NT>
+__device__ __forceinline__ int frag_chunk(int s, int nt, int lane, int jp) {
+    return ((s * NT + nt) * 32 + lane) * 2 + (jp ^ ((lane >> 2) & 1));
+}
+
+// Stage segments [seg0, seg0 + nseg) of x as B fragments in MMA order: a pure 16-bit permutation.
+//   fragment j of lane 4*m' + t, token m = nt*8 + m':
+//     .x = (x[m][64s+16t+j], x[m][64s+16t+j+4]) low half first, .y = the same 8 further on
+template <int NT>
+__device__ __forceinline__ void stage_x_mma(const MmaArgs &a, uint4 *xb, int seg0, int nseg) {
+    const int total = nseg * NT * 32;                          // (segment, token, t) triples
+    constexpr int U = 4;                                       // loads of U triples in flight per thread
+    for (int base = threadIdx.x; base < total; base += blockDim.x * U) {
+        uint4 v0[U], v1[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = base + u * blockDim.x;
+            const int t = i & 3, m = (i >> 2) % (NT * 8), s = i / (NT * 32);
+            v0[u] = v1[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (i < total && m < a.M) {
+                const uint4 *p = reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(a.x) + static_cast<size_t>(m) * a.K +
+                                                                 static_cast<size_t>(seg0 + s) * 64 + 16 * t);
+                v0[u] = __ldg(p);       // x[16t + 0..7]  as halves h0..h7:  word q holds (h[2q], h[2q+1])
+                v1[u] = __ldg(p + 1);   // x[16t + 8..15]
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = base + u * blockDim.x;
+            if (i >= total) break;
+            const int t = i & 3, m = (i >> 2) % (NT * 8), s = i / (NT * 32);
+            // fragment j: .x = (h[j], h[j+4]) of v0, .y = the same of v1
+            const uint4 f01 = make_uint4(__byte_perm(v0[u].x, v0[u].z, 0x5410), __byte_perm(v1[u].x, v1[u].z, 0x5410),      // j = 0
+                                         __byte_perm(v0[u].x, v0[u].z, 0x7632), __byte_perm(v1[u].x, v1[u].z, 0x7632));     // j = 1
+            const uint4 f23 = make_uint4(__byte_perm(v0[u].y, v0[u].w, 0x5410), __byte_perm(v1[u].y, v1[u].w, 0x5410),      // j = 2
+                                         __byte_perm(v0[u].y, v0[u].w, 0x7632), __byte_perm(v1[u].y, v1[u].w, 0x7632));     // j = 3
+            const int nt = m >> 3, lane = (m & 7) * 4 + t;
+            xb[frag_chunk<NT>(s, nt, lane, 0)] = f01;
+            xb[frag_chunk<NT>(s, nt, lane, 1)] = f23;
+        }
+    }
+}
+
+__device__ __forceinline__ float f32_of16(uint32_t h, bool bf16) {
+    return bf16 ? __uint_as_float(h << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
+}
+
+template <int NT, bool BF16>
+__global__ void __launch_bounds__(kMmaWarps * 32, 2) qmv_mma_kernel(const MmaArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_mma[];
+    constexpr int kBlockSegs = kStageBytes / (NT * 1024);
+    constexpr float off = BF16 ? 128.0f : 1024.0f;
+    uint4 *xb = reinterpret_cast<uint4 *>(smem_mma);                               // kStageBytes of B fragments
+    float *red = reinterpret_cast<float *>(smem_mma + kStageBytes);                // [warps][32][NT*4]
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int ksh = a.ksplit_shift, KS = 1 << ksh, slots = kMmaWarps >> ksh, slot = warp >> ksh, ks = warp & (KS - 1);
+    // balanced contiguous partition of the 16-row tiles over the CTAs
+    const int tile_begin = static_cast<int>((static_cast<long long>(blockIdx.x) * a.tiles) / gridDim.x);
+    const int tile_end = static_cast<int>((static_cast<long long>(blockIdx.x + 1) * a.tiles) / gridDim.x);
+    const int seg_step = KS;                            // this warp's segments: ks, ks + KS, ...
+    const int per_block = kBlockSegs >> ksh;            // of which this many per staged block (a multiple of kMmaPF)
+    const int nblocks = (a.nseg + kBlockSegs - 1) / kBlockSegs;
+    const int grp_shift = a.gs_shift - 6;               // segment -> group
+
+    asm volatile("griddepcontrol.launch_dependents;");
+    bool waited = false;
+
+    for (int it = 0; it < a.iters; ++it) {
+        const int tile = tile_begin + it * slots + slot;
+        const bool active = tile < tile_end;
+        const int n_lo = tile * 16 + g, n_hi = n_lo + 8;
+        const int r_lo = max(0, min(n_lo, a.N - 1)), r_hi = max(0, min(n_hi, a.N - 1));   // rows past N re-read the last row
+        const uint2 *w_lo = reinterpret_cast<const uint2 *>(a.w + static_cast<size_t>(r_lo) * a.wpr) + t;   // + 4 uint2 per segment
+        const uint2 *w_hi = reinterpret_cast<const uint2 *>(a.w + static_cast<size_t>(r_hi) * a.wpr) + t;
+        const uint16_t *sc_lo = static_cast<const uint16_t *>(a.scales) + static_cast<size_t>(r_lo) * a.gpr;
+        const uint16_t *sc_hi = static_cast<const uint16_t *>(a.scales) + static_cast<size_t>(r_hi) * a.gpr;
+        const uint16_t *bi_lo = static_cast<const uint16_t *>(a.biases) + static_cast<size_t>(r_lo) * a.gpr;
+        const uint16_t *bi_hi = static_cast<const uint16_t *>(a.biases) + static_cast<size_t>(r_hi) * a.gpr;
+        float acc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[nt][q] = 0.0f;
+
+        // packed words of kMmaPF segments in flight per lane, requested before the activations are staged:
+        // the weights do not depend on the previous kernel of the stream
+        uint2 wl[kMmaPF], wh[kMmaPF];
+        int s_req = ks;                                  // next segment to request
+#pragma unroll
+        for (int p = 0; p < kMmaPF; ++p) {
+            if (active && s_req < a.nseg) {
+                wl[p] = __ldg(w_lo + s_req * 4);
+                wh[p] = __ldg(w_hi + s_req * 4);
+            }
+            s_req += seg_step;
+        }
+        if (!waited) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            waited = true;
+        }
+
+        for (int kb = 0; kb < nblocks; ++kb) {
+            const int seg0 = kb * kBlockSegs;
+            if (it == 0 || nblocks > 1) {                // one block holding all of K is kept across tiles
+                __syncthreads();
+                stage_x_mma<NT>(a, xb, seg0, min(kBlockSegs, a.nseg - seg0));
+                __syncthreads();
+            }
+            if (!active) continue;
+            int s = seg0 + ks;                           // this warp's next segment
+            for (int r = 0; r < per_block; r += kMmaPF) {
+                if (s >= a.nseg) break;
+#pragma unroll
+                for (int p = 0; p < kMmaPF; ++p) {
+                    if (s < a.nseg) {
+                        // scale and bias of this group for rows g and g+8, used after the MMAs
+                        const int grp = s >> grp_shift;
+                        const uint32_t rs_lo = __ldg(sc_lo + grp), rs_hi = __ldg(sc_hi + grp);
+                        const uint32_t rb_lo = __ldg(bi_lo + grp), rb_hi = __ldg(bi_hi + grp);
+                        const int sl = s & (kBlockSegs - 1);
+                        float d[NT][4], xs[NT][4];
+                        segment_mmas<NT, BF16>(d, xs, wl[p], wh[p], xb + (sl * NT * 32 + lane) * 2, lane);
+                        // the slot is free: request the segment kMmaPF rounds ahead
+                        if (s_req < a.nseg) {
+                            wl[p] = __ldg(w_lo + s_req * 4);
+                            wh[p] = __ldg(w_hi + s_req * 4);
+                        }
+                        // affine part on the accumulators this lane holds: rows g / g+8, tokens 2t, 2t+1
+                        const float s_lo = f32_of16(rs_lo, BF16), s_hi = f32_of16(rs_hi, BF16);
+                        const float b_lo = fmaf(-off, s_lo, f32_of16(rb_lo, BF16)), b_hi = fmaf(-off, s_hi, f32_of16(rb_hi, BF16));
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            acc[nt][0] = fmaf(s_lo, d[nt][0], fmaf(b_lo, xs[nt][0], acc[nt][0]));
+                            acc[nt][1] = fmaf(s_lo, d[nt][1], fmaf(b_lo, xs[nt][1], acc[nt][1]));
+                            acc[nt][2] = fmaf(s_hi, d[nt][2], fmaf(b_hi, xs[nt][0], acc[nt][2]));
+                            acc[nt][3] = fmaf(s_hi, d[nt][3], fmaf(b_hi, xs[nt][1], acc[nt][3]));
+                        }
+                    }
+                    s += seg_step;
+                    s_req += seg_step;
+                }
+            }
+        }
+
+        if (KS > 1) {   // split-K: the warps of a slot add up in shared memory
+            float *mine = red + (warp * 32 + lane) * (NT * 4);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) mine[nt * 4 + q] = acc[nt][q];
+            __syncthreads();
+            if (ks == 0) {
+                for (int o = 1; o < KS; ++o) {
+                    const float *other = red + ((warp + o) * 32 + lane) * (NT * 4);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) acc[nt][q] += other[nt * 4 + q];
+                }
+            }
+            __syncthreads();   // the partial sums are rewritten by the next tile
+        }
+        if (active && ks == 0) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int m0 = nt * 8 + 2 * t;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int m = m0 + (q & 1), n = (q & 2) ? n_hi : n_lo;
+                    if (m < a.M && n < a.N) st_from_f32(a.out, static_cast<size_t>(m) * a.N + n, acc[nt][q], BF16 ? MTC_BF16 : MTC_F16);
+                }
+            }
+        }
+    }
+    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Group size 64 with K a multiple of 512: the K split gives each warp runs of 8 consecutive segments, so the
+// scales and biases of a run are 16 consecutive bytes per row.  They live in registers as four 32-bit pairs per
+// row and array and are re-requested, like the packed words, one run ahead as soon as their segments are done:
+// per segment a lane issues 2 loads of packed words and 2 of scale/bias pairs, with addresses that are constant
+// offsets from six pointers computed once per run, and no predicate inside a run.
+template <int NT, bool BF16>
+__global__ void __launch_bounds__(kMmaWarps * 32, 2) qmv_mma_g64_kernel(const MmaArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_mma[];
+    constexpr int kBlockSegs = kStageBytes / (NT * 1024);
+    constexpr float off = BF16 ? 128.0f : 1024.0f;
+    uint4 *xb = reinterpret_cast<uint4 *>(smem_mma);
+    float *red = reinterpret_cast<float *>(smem_mma + kStageBytes);
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int ksh = a.ksplit_shift, KS = 1 << ksh, slots = kMmaWarps >> ksh, slot = warp >> ksh, ks = warp & (KS - 1);
+    const int tile_begin = static_cast<int>((static_cast<long long>(blockIdx.x) * a.tiles) / gridDim.x);
+    const int tile_end = static_cast<int>((static_cast<long long>(blockIdx.x + 1) * a.tiles) / gridDim.x);
+    const int chunk = kBlockSegs >> ksh;                 // consecutive segments of a staged block owned by this warp
+    const int runs = chunk >> 3;                         // runs of 8 segments per block
+    const int nblocks = (a.nseg + kBlockSegs - 1) / kBlockSegs;
+
+    asm volatile("griddepcontrol.launch_dependents;");
+    bool waited = false;
+
+    for (int it = 0; it < a.iters; ++it) {
+        const int tile = tile_begin + it * slots + slot;
+        const bool active = tile < tile_end;
+        const int n_lo = tile * 16 + g, n_hi = n_lo + 8;
+        const int r_lo = max(0, min(n_lo, a.N - 1)), r_hi = max(0, min(n_hi, a.N - 1));
+        const uint2 *w_lo = reinterpret_cast<const uint2 *>(a.w + static_cast<size_t>(r_lo) * a.wpr) + t;   // + 4 uint2 per segment
+        const uint2 *w_hi = reinterpret_cast<const uint2 *>(a.w + static_cast<size_t>(r_hi) * a.wpr) + t;
+        // 32-bit pairs of 16-bit scales / biases: pair index = segment / 2
+        const uint32_t *sc_lo = reinterpret_cast<const uint32_t *>(static_cast<const uint16_t *>(a.scales) + static_cast<size_t>(r_lo) * a.gpr);
+        const uint32_t *sc_hi = reinterpret_cast<const uint32_t *>(static_cast<const uint16_t *>(a.scales) + static_cast<size_t>(r_hi) * a.gpr);
+        const uint32_t *bi_lo = reinterpret_cast<const uint32_t *>(static_cast<const uint16_t *>(a.biases) + static_cast<size_t>(r_lo) * a.gpr);
+        const uint32_t *bi_hi = reinterpret_cast<const uint32_t *>(static_cast<const uint16_t *>(a.biases) + static_cast<size_t>(r_hi) * a.gpr);
+        float acc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) acc[nt][q] = 0.0f;
+
+        uint2 wl[8], wh[8];
+        uint32_t sp[4][4];                               // [s_lo, s_hi, b_lo, b_hi][pair of the run]
+        // the run requested next: block kb_n, run r_n of it
+        int kb_n = 0, r_n = 0;
+        int s_n = ks * chunk;                            // its first segment
+        bool have_n = active && s_n < a.nseg;
+        if (have_n) {
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                wl[p] = __ldg(w_lo + (s_n + p) * 4);
+                wh[p] = __ldg(w_hi + (s_n + p) * 4);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                sp[0][q] = __ldg(sc_lo + (s_n >> 1) + q);
+                sp[1][q] = __ldg(sc_hi + (s_n >> 1) + q);
+                sp[2][q] = __ldg(bi_lo + (s_n >> 1) + q);
+                sp[3][q] = __ldg(bi_hi + (s_n >> 1) + q);
+            }
+        }
+        if (!waited) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            waited = true;
+        }
+
+        for (int kb = 0; kb < nblocks; ++kb) {
+            if (it == 0 || nblocks > 1) {                // one block holding all of K is kept across tiles
+                __syncthreads();
+                stage_x_mma<NT>(a, xb, kb * kBlockSegs, min(kBlockSegs, a.nseg - kb * kBlockSegs));
+                __syncthreads();
+            }
+            if (!active) continue;
+            for (int r = 0; r < runs; ++r) {
+                const int sl0 = ks * chunk + r * 8;                      // first segment of the run within the block
+                if (kb * kBlockSegs + sl0 >= a.nseg) break;
+                // advance the request stream to the run after this one
+                if (++r_n == runs) {
+                    r_n = 0;
+                    ++kb_n;
+                }
+                s_n = kb_n * kBlockSegs + ks * chunk + r_n * 8;
+                have_n = s_n < a.nseg;
+                const uint2 *wn_lo = w_lo + s_n * 4, *wn_hi = w_hi + s_n * 4;
+                const uint32_t *sn0 = sc_lo + (s_n >> 1), *sn1 = sc_hi + (s_n >> 1), *sn2 = bi_lo + (s_n >> 1), *sn3 = bi_hi + (s_n >> 1);
+                const uint4 *frag = xb + (sl0 * NT * 32 + lane) * 2;
+#pragma unroll
+                for (int p = 0; p < 8; ++p) {
+                    float d[NT][4], xs[NT][4];
+                    segment_mmas<NT, BF16>(d, xs, wl[p], wh[p], frag + p * NT * 64, lane);
+                    if (have_n) {
+                        wl[p] = __ldg(wn_lo + p * 4);
+                        wh[p] = __ldg(wn_hi + p * 4);
+                    }
+                    const int q = p >> 1;
+                    float s_lo, s_hi, o_lo, o_hi;
+                    if (BF16) {
+                        s_lo = __uint_as_float((p & 1) ? (sp[0][q] & 0xFFFF0000u) : (sp[0][q] << 16));
+                        s_hi = __uint_as_float((p & 1) ? (sp[1][q] & 0xFFFF0000u) : (sp[1][q] << 16));
+                        o_lo = __uint_as_float((p & 1) ? (sp[2][q] & 0xFFFF0000u) : (sp[2][q] << 16));
+                        o_hi = __uint_as_float((p & 1) ? (sp[3][q] & 0xFFFF0000u) : (sp[3][q] << 16));
+                    } else {
+                        const __half2 h0 = *reinterpret_cast<const __half2 *>(&sp[0][q]), h1 = *reinterpret_cast<const __half2 *>(&sp[1][q]);
+                        const __half2 h2 = *reinterpret_cast<const __half2 *>(&sp[2][q]), h3 = *reinterpret_cast<const __half2 *>(&sp[3][q]);
+                        s_lo = (p & 1) ? __high2float(h0) : __low2float(h0);
+                        s_hi = (p & 1) ? __high2float(h1) : __low2float(h1);
+                        o_lo = (p & 1) ? __high2float(h2) : __low2float(h2);
+                        o_hi = (p & 1) ? __high2float(h3) : __low2float(h3);
+                    }
+                    if ((p & 1) && have_n) {             // both segments of pair q are done: its registers are free
+                        sp[0][q] = __ldg(sn0 + q);
+                        sp[1][q] = __ldg(sn1 + q);
+                        sp[2][q] = __ldg(sn2 + q);
+                        sp[3][q] = __ldg(sn3 + q);
+                    }
+                    const float b_lo = fmaf(-off, s_lo, o_lo), b_hi = fmaf(-off, s_hi, o_hi);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        acc[nt][0] = fmaf(s_lo, d[nt][0], fmaf(b_lo, xs[nt][0], acc[nt][0]));
+                        acc[nt][1] = fmaf(s_lo, d[nt][1], fmaf(b_lo, xs[nt][1], acc[nt][1]));
+                        acc[nt][2] = fmaf(s_hi, d[nt][2], fmaf(b_hi, xs[nt][0], acc[nt][2]));
+                        acc[nt][3] = fmaf(s_hi, d[nt][3], fmaf(b_hi, xs[nt][1], acc[nt][3]));
+                    }
+                }
+            }
+        }
+
+        if (KS > 1) {   // split-K: the warps of a slot add up in shared memory
+            float *mine = red + (warp * 32 + lane) * (NT * 4);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) mine[nt * 4 + q] = acc[nt][q];
+            __syncthreads();
+            if (ks == 0) {
+                for (int o = 1; o < KS; ++o) {
+                    const float *other = red + ((warp + o) * 32 + lane) * (NT * 4);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) acc[nt][q] += other[nt * 4 + q];
+                }
+            }
+            __syncthreads();   // the partial sums are rewritten by the next tile
+        }
+        if (active && ks == 0) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int m0 = nt * 8 + 2 * t;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int m = m0 + (q & 1), n = (q & 2) ? n_hi : n_lo;
+                    if (m < a.M && n < a.N) st_from_f32(a.out, static_cast<size_t>(m) * a.N + n, acc[nt][q], BF16 ? MTC_BF16 : MTC_F16);
+                }
+            }
+        }
+    }
+    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <int NT>
+constexpr size_t mma_smem_bytes() {
+    return static_cast<size_t>(kStageBytes) + static_cast<size_t>(kMmaWarps) * 32 * NT * 4 * sizeof(float);
+}
+
+template <int NT, bool BF16>
+cudaError_t launch_mma(Ctx *ctx, cudaStream_t st, MmaArgs a) {
+    const int sms = ctx->sm_count;
+    constexpr int kBlockSegs = kStageBytes / (NT * 1024);
+    a.tiles = (a.N + 15) / 16;
+    // split K over the warps of a CTA while every warp keeps a full round of segments per staged block and
+    // the grid is short of two CTAs per SM
+    int ksh = 0;
+    while ((2 << ksh) <= kMmaWarps && (a.tiles << ksh) < sms * 2 * kMmaWarps && a.nseg >= (2 << ksh) * kMmaPF &&
+           (kBlockSegs >> (ksh + 1)) >= kMmaPF)
+        ++ksh;
+    a.ksplit_shift = ksh;
+    const int slots = kMmaWarps >> ksh;
+    int grid = (a.tiles + slots - 1) / slots;
+    if (grid > sms * 2) grid = sms * 2;
+    if (grid < 1) grid = 1;
+    const int max_tiles = (a.tiles + grid - 1) / grid;
+    a.iters = (max_tiles + slots - 1) / slots;
+    constexpr size_t smem = mma_smem_bytes<NT>();
+    const auto al16 = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    const bool g64 = a.gs_shift == 6 && a.K % 512 == 0 && al16(a.scales) && al16(a.biases);
+    auto kernel = g64 ? qmv_mma_g64_kernel<NT, BF16> : qmv_mma_kernel<NT, BF16>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(qmv_mma_kernel<NT, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(qmv_mma_g64_kernel<NT, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kMmaWarps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, a);
+}
+
+}  // namespace
+
+bool qmv_mma_supported(int M, int N, int K, int bits, int group_size, int dt, const void *w, const void *x) {
+    const auto al = [](const void *p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a == 0; };
+    return bits == 4 && M >= 2 && M <= 16 && N > 0 && (dt == MTC_BF16 || dt == MTC_F16) && K % 64 == 0 &&
+           group_size >= 64 && (group_size & (group_size - 1)) == 0 && K % group_size == 0 && al(w, 16) && al(x, 16);
+}
+
+cudaError_t launch_qmv_mma(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases, const void *x,
+                           void *out, int M, int N, int K, int group_size, int dt) {
+    MmaArgs a{};
+    a.w = static_cast<const uint32_t *>(w);
+    a.scales = scales;
+    a.biases = biases;
+    a.x = x;
+    a.out = out;
+    a.M = M; a.N = N; a.K = K; a.dt = dt;
+    a.gs_shift = 0;
+    while ((1 << a.gs_shift) < group_size) ++a.gs_shift;
+    a.wpr = K / 8;
+    a.gpr = K / group_size;
+    a.nseg = K / 64;
+    if (dt == MTC_BF16) return M <= 8 ? launch_mma<1, true>(ctx, st, a) : launch_mma<2, true>(ctx, st, a);
+    return M <= 8 ? launch_mma<1, false>(ctx, st, a) : launch_mma<2, false>(ctx, st, a);
+}
+
+}  // namespace mtc

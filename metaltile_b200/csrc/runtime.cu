@@ -275,6 +275,12 @@ int mtc_qmv(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
     if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "qmv: dtype must be f32, f16 or bf16");
     if (M > 0 && N > 0 && (!w || !scales || !biases || !x || !out)) return fail(ctx, MTC_ERR_INVALID, "qmv: null pointer");
     std::string why;
+    if (ctx->qmv_small_m_mma && mtc::qmv_mma_supported(M, N, K, bits, group_size, dtype, w, x)) {
+        cudaError_t e2 = mtc::launch_qmv_mma(ctx, static_cast<cudaStream_t>(stream), w, scales, biases, x, out, M, N, K,
+                                             group_size, dtype);
+        if (e2 != cudaSuccess) return fail(ctx, MTC_ERR_DISPATCH, std::string("qmv (mma) launch: ") + cudaGetErrorString(e2));
+        return MTC_OK;
+    }
     cudaError_t e = mtc::launch_qmv(ctx, static_cast<cudaStream_t>(stream), w, scales, biases, x, out, M, N, K, bits,
                                     group_size, dtype, &why);
     if (e == cudaErrorInvalidValue && !why.empty()) return fail(ctx, MTC_ERR_UNSUPPORTED, why);
@@ -283,11 +289,13 @@ int mtc_qmv(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
 }
 
 // mt_qmm_for (crates/metaltile-std/src/mlx/quantized.rs:5040-5065) picks by M alone; here M <= 16 or
-// f32 activations stay on the CUDA-core kernels, everything else goes to the tensor cores when the
+// f32 activations stay on the qmv kernels (CUDA cores, or warp-level MMAs for 2 <= M <= 16 with 4-bit codes), everything else goes to the tensor cores when the
 // shape meets that kernel's contract (K % 64 == 0, power-of-two group >= 32).
 const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dtype) {
     if (M > 16 && mtc::qmm_tcgen05_supported(M, N, K, bits, group_size, dtype, nullptr, nullptr, nullptr))
         return "qmm_tcgen05";
+    // alignment is a run-time property of the pointers; the route names the kernel an aligned call gets
+    if (mtc::qmv_mma_supported(M, N, K, bits, group_size, dtype, nullptr, nullptr)) return "qmv_mma_sync";
     return "qmv_cuda_core";
 }
 
@@ -313,6 +321,10 @@ int mtc_set_option(mtc_ctx *ctx, const char *name, int value) {
         if (value != 0 && (value < 16 || value > 256 || value % 16 != 0))
             return fail(ctx, MTC_ERR_UNSUPPORTED, "qmm_tile_tokens must be 0 or a multiple of 16 in [16, 256]");
         ctx->qmm_force_tn = value;
+        return MTC_OK;
+    }
+    if (std::strcmp(name, "qmv_small_m_mma") == 0) {
+        ctx->qmv_small_m_mma = value ? 1 : 0;
         return MTC_OK;
     }
     if (std::strcmp(name, "qmm_pair") == 0) {

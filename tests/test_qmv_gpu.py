@@ -141,6 +141,46 @@ def test_shapes_and_edges(m, n, k, bits, gs, dt):
     assert rel_err(got, ref) <= TOL[dt]
 
 
+@pytest.mark.parametrize("m,n,k,gs,dt", [
+    (2, 4096, 4096, 64, "bf16"), (3, 37, 64, 64, "f16"),        # one segment, ragged N
+    (7, 1000, 2112, 64, "bf16"),                                # 33 segments: two staged blocks, the second ragged
+    (8, 16, 4096, 128, "f16"), (9, 1024, 4096, 64, "bf16"),     # 9 tokens: two token tiles
+    (15, 250, 8192, 256, "bf16"), (16, 14336, 4096, 64, "f16"), (16, 4096, 14336, 64, "bf16"),
+    (12, 8, 128, 64, "bf16"),                                   # fewer rows than one 16-row tile
+])
+def test_small_m_tensor_core_path(ctx, m, n, k, gs, dt):
+    """2 <= M <= 16 with 4-bit codes runs on warp-level MMAs; same oracle, and within round-off of the
+    CUDA-core kernel for the same call."""
+    assert ctx.qmm_route(m, n, k, 4, gs, dt) == "qmv_mma_sync"
+    w, s, b, x = dense_case(m, n, k, 4, gs, dt, seed=6, salt=m * 31 + n)
+    ref = oracle.qmm(w, s, b, x, m, n, k, 4, gs)
+    got = run_qmv(w, s, b, x, 4, gs, dt)
+    assert got.shape == (m, n)
+    assert rel_err(got, ref) <= TOL[dt]
+    ctx.set_option("qmv_small_m_mma", 0)
+    try:
+        cores = run_qmv(w, s, b, x, 4, gs, dt)
+    finally:
+        ctx.set_option("qmv_small_m_mma", 1)
+    assert rel_err(cores, ref) <= TOL[dt]
+    assert rel_err(got, cores) <= TOL[dt]
+
+
+def test_small_m_tensor_core_exact_integers(ctx):
+    """Integer-valued scales, biases and activations: every product and sum is exact in f32, so the MMA
+    path must reproduce the oracle bit for bit (checks the code-to-slot permutation of the operands)."""
+    from metaltile_b200 import synth
+    m, n, k, gs = 5, 48, 256, 64
+    w = synth.words(n * k * 4 // 32, seed=9).reshape(n, -1)
+    rng = np.random.default_rng(9)
+    s = rng.integers(1, 4, size=(n, k // gs)).astype(np.float32)
+    b = rng.integers(-3, 4, size=(n, k // gs)).astype(np.float32)
+    x = rng.integers(-2, 3, size=(m, k)).astype(np.float32)
+    ref = oracle.qmm(w, s, b, x, m, n, k, 4, gs)
+    got = run_qmv(w, s, b, x, 4, gs, "f16")
+    assert np.array_equal(got, oracle.round_through(ref, oracle.F16))
+
+
 def test_generic_fallback_paths(ctx):
     """Group sizes below the chunk and unaligned pointers take the any-shape kernel."""
     import torch
