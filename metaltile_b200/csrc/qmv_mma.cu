@@ -280,73 +280,107 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) qmv_mma_kernel(const MmaArg
     if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
-// Group size 64 with K a multiple of 512: the K split gives each warp runs of 8 consecutive segments, so the
-// scales and biases of a run are 16 consecutive bytes per row.  They live in registers as four 32-bit pairs per
-// row and array and are re-requested, like the packed words, one run ahead as soon as their segments are done:
-// per segment a lane issues 2 loads of packed words and 2 of scale/bias pairs, with addresses that are constant
-// offsets from six pointers computed once per run, and no predicate inside a run.
+// ---- group size 64, K a multiple of 512: packed words through a shared-memory ring ----
+// Loading the A fragments straight from global memory costs one 32-byte sector per row and instruction, eight
+// cache lines per warp-load, and the L1 tag stage becomes the limit.  Here a warp copies a run of 8 consecutive
+// segments of its 16 rows (16 x 256 bytes of packed words, plus 16 bytes of scales and of biases per row) with
+// 16-byte asynchronous copies that cover whole lines and bypass L1, into a private two-deep ring, and reads the
+// fragments back with conflict-free 8-byte shared loads.  No register holds data in flight.
+constexpr int kRingWarps = 16;
+constexpr int kRunWBytes = 16 * 256;                 // packed words of a run: 16 rows x 8 segments x 32 bytes
+constexpr int kRunBytes = kRunWBytes + 2 * 256;      // + scales and biases: 16 rows x 8 groups x 2 bytes each
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
 template <int NT, bool BF16>
-__global__ void __launch_bounds__(kMmaWarps * 32, 2) qmv_mma_g64_kernel(const MmaArgs a) {
-    extern __shared__ __align__(16) unsigned char smem_mma[];
+__global__ void __launch_bounds__(kRingWarps * 32, 1) qmv_mma_ring_kernel(const MmaArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_mma[];
     constexpr int kBlockSegs = kStageBytes / (NT * 1024);
     constexpr float off = BF16 ? 128.0f : 1024.0f;
     uint4 *xb = reinterpret_cast<uint4 *>(smem_mma);
-    float *red = reinterpret_cast<float *>(smem_mma + kStageBytes);
+    unsigned char *ring_all = smem_mma + kStageBytes;                                   // [warps][2][kRunBytes]
+    float *red = reinterpret_cast<float *>(ring_all + kRingWarps * 2 * kRunBytes);      // [warps][32][NT*4]
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int ksh = a.ksplit_shift, KS = 1 << ksh, slots = kMmaWarps >> ksh, slot = warp >> ksh, ks = warp & (KS - 1);
+    const int ksh = a.ksplit_shift, KS = 1 << ksh, slots = kRingWarps >> ksh, slot = warp >> ksh, ks = warp & (KS - 1);
     const int tile_begin = static_cast<int>((static_cast<long long>(blockIdx.x) * a.tiles) / gridDim.x);
     const int tile_end = static_cast<int>((static_cast<long long>(blockIdx.x + 1) * a.tiles) / gridDim.x);
     const int chunk = kBlockSegs >> ksh;                 // consecutive segments of a staged block owned by this warp
     const int runs = chunk >> 3;                         // runs of 8 segments per block
     const int nblocks = (a.nseg + kBlockSegs - 1) / kBlockSegs;
+    const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(ring_all + warp * 2 * kRunBytes));
 
     asm volatile("griddepcontrol.launch_dependents;");
-    bool waited = false;
 
+    // ---- copy side: lane l moves chunk (l & 15) of rows 2i + (l >> 4), i = 0..7, and 16 bytes of scales
+    //      (even lanes) or biases (odd lanes) of row l >> 1.  Chunk c of row r lands at c ^ ((r & 3) << 1). ----
+    const int c_row = lane >> 4, c_chunk = lane & 15, c_srow = lane >> 1;
+    const char *c_sb = static_cast<const char *>((lane & 1) ? a.biases : a.scales);
+    const size_t w_pitch = static_cast<size_t>(a.wpr) * 4, sb_pitch = static_cast<size_t>(a.gpr) * 2;
+    auto issue = [&](int tile, int s_run, int buf) {
+        const uint32_t dst = ring + buf * kRunBytes;
+        const int row0 = tile * 16;
+        const char *src0 = reinterpret_cast<const char *>(a.w) + static_cast<size_t>(s_run) * 32 + c_chunk * 16;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int row = 2 * i + c_row;
+            const int gr = min(row0 + row, a.N - 1);                    // rows past N re-read the last row
+            cp_async16(dst + row * 256 + ((c_chunk ^ ((row & 3) << 1)) << 4), src0 + gr * w_pitch);
+        }
+        const int gr = min(row0 + c_srow, a.N - 1);
+        cp_async16(dst + kRunWBytes + (lane & 1) * 256 + c_srow * 16, c_sb + gr * sb_pitch + static_cast<size_t>(s_run) * 2);
+    };
+    // the runs of this warp in the order (tile, block, run); the copies run one run ahead, across tiles
+    int it_n = 0, kb_n = 0, r_n = -1, s_n = 0, tile_n = tile_begin + slot;
+    bool have_n = false;
+    auto advance = [&]() {
+        have_n = false;
+        for (;;) {
+            if (++r_n == runs) {
+                r_n = 0;
+                if (++kb_n == nblocks) {
+                    kb_n = 0;
+                    ++it_n;
+                    tile_n += slots;
+                }
+            }
+            if (it_n >= a.iters || tile_n >= tile_end) break;
+            s_n = kb_n * kBlockSegs + ks * chunk + r_n * 8;
+            if (s_n < a.nseg) {
+                have_n = true;
+                break;
+            }
+        }
+    };
+    advance();
+    if (have_n) issue(tile_n, s_n, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    // the weights do not depend on the previous kernel of the stream; the activations and the stores do
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    const uint32_t lane_w = g * 256 + ((g & 3) << 5) + t * 8;           // fragment address within a run: ^ (p << 5)
+    int buf = 0;
     for (int it = 0; it < a.iters; ++it) {
         const int tile = tile_begin + it * slots + slot;
         const bool active = tile < tile_end;
-        const int n_lo = tile * 16 + g, n_hi = n_lo + 8;
-        const int r_lo = max(0, min(n_lo, a.N - 1)), r_hi = max(0, min(n_hi, a.N - 1));
-        const uint2 *w_lo = reinterpret_cast<const uint2 *>(a.w + static_cast<size_t>(r_lo) * a.wpr) + t;   // + 4 uint2 per segment
-        const uint2 *w_hi = reinterpret_cast<const uint2 *>(a.w + static_cast<size_t>(r_hi) * a.wpr) + t;
-        // 32-bit pairs of 16-bit scales / biases: pair index = segment / 2
-        const uint32_t *sc_lo = reinterpret_cast<const uint32_t *>(static_cast<const uint16_t *>(a.scales) + static_cast<size_t>(r_lo) * a.gpr);
-        const uint32_t *sc_hi = reinterpret_cast<const uint32_t *>(static_cast<const uint16_t *>(a.scales) + static_cast<size_t>(r_hi) * a.gpr);
-        const uint32_t *bi_lo = reinterpret_cast<const uint32_t *>(static_cast<const uint16_t *>(a.biases) + static_cast<size_t>(r_lo) * a.gpr);
-        const uint32_t *bi_hi = reinterpret_cast<const uint32_t *>(static_cast<const uint16_t *>(a.biases) + static_cast<size_t>(r_hi) * a.gpr);
         float acc[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int q = 0; q < 4; ++q) acc[nt][q] = 0.0f;
-
-        uint2 wl[8], wh[8];
-        uint32_t sp[4][4];                               // [s_lo, s_hi, b_lo, b_hi][pair of the run]
-        // the run requested next: block kb_n, run r_n of it
-        int kb_n = 0, r_n = 0;
-        int s_n = ks * chunk;                            // its first segment
-        bool have_n = active && s_n < a.nseg;
-        if (have_n) {
-#pragma unroll
-            for (int p = 0; p < 8; ++p) {
-                wl[p] = __ldg(w_lo + (s_n + p) * 4);
-                wh[p] = __ldg(w_hi + (s_n + p) * 4);
-            }
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                sp[0][q] = __ldg(sc_lo + (s_n >> 1) + q);
-                sp[1][q] = __ldg(sc_hi + (s_n >> 1) + q);
-                sp[2][q] = __ldg(bi_lo + (s_n >> 1) + q);
-                sp[3][q] = __ldg(bi_hi + (s_n >> 1) + q);
-            }
-        }
-        if (!waited) {
-            asm volatile("griddepcontrol.wait;" ::: "memory");
-            waited = true;
-        }
 
         for (int kb = 0; kb < nblocks; ++kb) {
             if (it == 0 || nblocks > 1) {                // one block holding all of K is kept across tiles
@@ -358,24 +392,24 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) qmv_mma_g64_kernel(const Mm
             for (int r = 0; r < runs; ++r) {
                 const int sl0 = ks * chunk + r * 8;                      // first segment of the run within the block
                 if (kb * kBlockSegs + sl0 >= a.nseg) break;
-                // advance the request stream to the run after this one
-                if (++r_n == runs) {
-                    r_n = 0;
-                    ++kb_n;
-                }
-                s_n = kb_n * kBlockSegs + ks * chunk + r_n * 8;
-                have_n = s_n < a.nseg;
-                const uint2 *wn_lo = w_lo + s_n * 4, *wn_hi = w_hi + s_n * 4;
-                const uint32_t *sn0 = sc_lo + (s_n >> 1), *sn1 = sc_hi + (s_n >> 1), *sn2 = bi_lo + (s_n >> 1), *sn3 = bi_hi + (s_n >> 1);
+                __syncwarp();                                            // every lane is done with the other buffer
+                advance();
+                if (have_n) issue(tile_n, s_n, buf ^ 1);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                asm volatile("cp.async.wait_group 1;" ::: "memory");     // this run has landed (this lane's copies)
+                __syncwarp();                                            // ... and every other lane's
+                const uint32_t rb = ring + buf * kRunBytes;
+                const uint4 v0 = lds128(rb + kRunWBytes + g * 16), v1 = lds128(rb + kRunWBytes + (g + 8) * 16);
+                const uint4 v2 = lds128(rb + kRunWBytes + 256 + g * 16), v3 = lds128(rb + kRunWBytes + 256 + (g + 8) * 16);
+                const uint32_t sp[4][4] = {{v0.x, v0.y, v0.z, v0.w}, {v1.x, v1.y, v1.z, v1.w},
+                                           {v2.x, v2.y, v2.z, v2.w}, {v3.x, v3.y, v3.z, v3.w}};   // [s_lo, s_hi, b_lo, b_hi][pair]
                 const uint4 *frag = xb + (sl0 * NT * 32 + lane) * 2;
+                const uint32_t wbase = rb + lane_w;
 #pragma unroll
                 for (int p = 0; p < 8; ++p) {
+                    const uint2 cl = lds64(wbase ^ (p << 5)), ch = lds64((wbase ^ (p << 5)) + 8 * 256);
                     float d[NT][4], xs[NT][4];
-                    segment_mmas<NT, BF16>(d, xs, wl[p], wh[p], frag + p * NT * 64, lane);
-                    if (have_n) {
-                        wl[p] = __ldg(wn_lo + p * 4);
-                        wh[p] = __ldg(wn_hi + p * 4);
-                    }
+                    segment_mmas<NT, BF16>(d, xs, cl, ch, frag + p * NT * 64, lane);
                     const int q = p >> 1;
                     float s_lo, s_hi, o_lo, o_hi;
                     if (BF16) {
@@ -391,12 +425,6 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) qmv_mma_g64_kernel(const Mm
                         o_lo = (p & 1) ? __high2float(h2) : __low2float(h2);
                         o_hi = (p & 1) ? __high2float(h3) : __low2float(h3);
                     }
-                    if ((p & 1) && have_n) {             // both segments of pair q are done: its registers are free
-                        sp[0][q] = __ldg(sn0 + q);
-                        sp[1][q] = __ldg(sn1 + q);
-                        sp[2][q] = __ldg(sn2 + q);
-                        sp[3][q] = __ldg(sn3 + q);
-                    }
                     const float b_lo = fmaf(-off, s_lo, o_lo), b_hi = fmaf(-off, s_hi, o_hi);
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
@@ -406,6 +434,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) qmv_mma_g64_kernel(const Mm
                         acc[nt][3] = fmaf(s_hi, d[nt][3], fmaf(b_hi, xs[nt][1], acc[nt][3]));
                     }
                 }
+                buf ^= 1;
             }
         }
 
@@ -428,6 +457,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) qmv_mma_g64_kernel(const Mm
             __syncthreads();   // the partial sums are rewritten by the next tile
         }
         if (active && ks == 0) {
+            const int n_lo = tile * 16 + g, n_hi = n_lo + 8;
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 const int m0 = nt * 8 + 2 * t;
@@ -439,12 +469,61 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) qmv_mma_g64_kernel(const Mm
             }
         }
     }
-    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+}
+
+template <int NT>
+constexpr size_t ring_smem_bytes() {
+    return static_cast<size_t>(kStageBytes) + static_cast<size_t>(kRingWarps) * 2 * kRunBytes +
+           static_cast<size_t>(kRingWarps) * 32 * NT * 4 * sizeof(float);
+}
+
+template <int NT, bool BF16>
+cudaError_t launch_ring(Ctx *ctx, cudaStream_t st, MmaArgs a) {
+    const int sms = ctx->sm_count;
+    constexpr int kBlockSegs = kStageBytes / (NT * 1024);
+    a.tiles = (a.N + 15) / 16;
+    int grid = a.tiles < sms ? a.tiles : sms;
+    const int max_tiles = (a.tiles + grid - 1) / grid;
+    // K split over the warps of a CTA: the split with the fewest runs on the busiest warp, ties to the smaller
+    const int runs_row = a.nseg / 8;
+    int best_ksh = 0;
+    long best_cost = -1;
+    for (int ksh = 0; (1 << ksh) <= kRingWarps && (kBlockSegs >> ksh) >= 8; ++ksh) {
+        const int slots = kRingWarps >> ksh;
+        const long iters = (max_tiles + slots - 1) / slots;
+        const long cost = iters * ((runs_row + (1 << ksh) - 1) >> ksh) * 16 + iters;      // runs, then barriers
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best_ksh = ksh;
+        }
+    }
+    a.ksplit_shift = best_ksh;
+    const int slots = kRingWarps >> best_ksh;
+    a.iters = (max_tiles + slots - 1) / slots;
+    constexpr size_t smem = ring_smem_bytes<NT>();
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(qmv_mma_ring_kernel<NT, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kRingWarps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, qmv_mma_ring_kernel<NT, BF16>, a);
 }
 
 template <int NT>
 constexpr size_t mma_smem_bytes() {
-    return static_cast<size_t>(kStageBytes) + static_cast<size_t>(kMmaWarps) * 32 * NT * 4 * sizeof(float);
+    return static_cast<size_t>(kStageBytes) + 2 * static_cast<size_t>(kMmaWarps) * 32 * NT * 4 * sizeof(float);
 }
 
 template <int NT, bool BF16>
@@ -466,14 +545,10 @@ cudaError_t launch_mma(Ctx *ctx, cudaStream_t st, MmaArgs a) {
     const int max_tiles = (a.tiles + grid - 1) / grid;
     a.iters = (max_tiles + slots - 1) / slots;
     constexpr size_t smem = mma_smem_bytes<NT>();
-    const auto al16 = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
-    const bool g64 = a.gs_shift == 6 && a.K % 512 == 0 && al16(a.scales) && al16(a.biases);
-    auto kernel = g64 ? qmv_mma_g64_kernel<NT, BF16> : qmv_mma_kernel<NT, BF16>;
+    auto kernel = qmv_mma_kernel<NT, BF16>;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(qmv_mma_kernel<NT, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(qmv_mma_g64_kernel<NT, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
@@ -512,6 +587,11 @@ cudaError_t launch_qmv_mma(Ctx *ctx, cudaStream_t st, const void *w, const void 
     a.wpr = K / 8;
     a.gpr = K / group_size;
     a.nseg = K / 64;
+    const auto al16 = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    if (group_size == 64 && K % 512 == 0 && al16(scales) && al16(biases)) {
+        if (dt == MTC_BF16) return M <= 8 ? launch_ring<1, true>(ctx, st, a) : launch_ring<2, true>(ctx, st, a);
+        return M <= 8 ? launch_ring<1, false>(ctx, st, a) : launch_ring<2, false>(ctx, st, a);
+    }
     if (dt == MTC_BF16) return M <= 8 ? launch_mma<1, true>(ctx, st, a) : launch_mma<2, true>(ctx, st, a);
     return M <= 8 ? launch_mma<1, false>(ctx, st, a) : launch_mma<2, false>(ctx, st, a);
 }
