@@ -34,6 +34,7 @@ struct MmaArgs {
     int M, N, K, gs_shift, dt;
     int wpr, gpr, nseg;      // words / groups per weight row, 64-code segments per row
     int tiles, ksplit_shift, iters;
+    int block_segs;          // ring kernel: segments of x staged at a time (a multiple of 8 << ksplit_shift)
 };
 
 // d = a * b + (kZero ? 0 : d): m16n8k16, 16-bit operands, f32 accumulators
@@ -41,19 +42,19 @@ template <bool BF16, bool kZero>
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     if (kZero) {
         if (BF16)
-            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+            asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                          : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
                          : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
         else
-            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+            asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                          : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
                          : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
     } else {
         if (BF16)
-            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                          : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
         else
-            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                          : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
     }
 }
@@ -68,7 +69,7 @@ __device__ __forceinline__ uint32_t code_pair(uint32_t word, uint32_t magic) {
 }
 
 // All MMAs of one 64-code segment for the rows and tokens of this lane: d = sum (OFF + q) x, xs = sum x.
-template <int NT, bool BF16>
+template <int NT, bool BF16, bool kSum = true>
 __device__ __forceinline__ void segment_mmas(float (&d)[NT][4], float (&xs)[NT][4], const uint2 cl, const uint2 ch,
                                              const uint4 *frag /* this lane's chunk 0 of the segment */, int lane) {
     constexpr uint32_t magic = BF16 ? 0x43004300u : 0x64006400u;
@@ -88,7 +89,7 @@ __device__ __forceinline__ void segment_mmas(float (&d)[NT][4], float (&xs)[NT][
             const uint4 f = bf[(J) >> 1][nt];                                                             \
             const uint32_t b0 = ((J) & 1) ? f.z : f.x, b1 = ((J) & 1) ? f.w : f.y;                        \
             mma16816<BF16, ZERO>(d[nt], af, b0, b1);                                                      \
-            mma16816<BF16, ZERO>(xs[nt], ones, b0, b1);                                                   \
+            if (kSum) mma16816<BF16, ZERO>(xs[nt], ones, b0, b1);                                         \
         }                                                                                                 \
     }
     MTC_STEP(0, true)
@@ -293,35 +294,69 @@ constexpr int kRunBytes = kRunWBytes + 2 * 256;      // + scales and biases: 16 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-__device__ __forceinline__ uint2 lds64(uint32_t addr) {
-    uint2 v;
-    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
+// Activations of the ring kernel: only the M real tokens are staged, so M = 1 keeps 32768 k values resident and
+// every practical K is staged once per CTA.  16-byte unit of (segment s, token m, quad-lane t, half h):
+//   ((s*M + m)*4 + t)*2 + (h ^ (m & 1));  half h holds the fragments j = 2h, 2h+1 of stage_x_mma's order.
+__device__ __forceinline__ void stage_x_ring(const MmaArgs &a, uint4 *xb, int seg0, int nseg) {
+    // thread -> quad-lane t (2 bits), token m (mb bits), segment = pass * s_step + (thread >> (2 + mb)): no division
+    const int mb = a.M <= 1 ? 0 : a.M <= 2 ? 1 : a.M <= 4 ? 2 : a.M <= 8 ? 3 : 4;
+    const int t = threadIdx.x & 3, m = (threadIdx.x >> 2) & ((1 << mb) - 1), s_first = threadIdx.x >> (2 + mb),
+              s_step = blockDim.x >> (2 + mb);
+    if (m >= a.M) return;
+    constexpr int U = 4;
+    const uint16_t *xrow = static_cast<const uint16_t *>(a.x) + static_cast<size_t>(m) * a.K + static_cast<size_t>(seg0) * 64 + 16 * t;
+    for (int s0 = s_first; s0 < nseg; s0 += s_step * U) {
+        uint4 v0[U], v1[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int s = s0 + u * s_step;
+            if (s < nseg) {
+                const uint4 *p = reinterpret_cast<const uint4 *>(xrow + static_cast<size_t>(s) * 64);
+                v0[u] = __ldg(p);
+                v1[u] = __ldg(p + 1);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int s = s0 + u * s_step;
+            if (s >= nseg) break;
+            const uint4 f01 = make_uint4(__byte_perm(v0[u].x, v0[u].z, 0x5410), __byte_perm(v1[u].x, v1[u].z, 0x5410),
+                                         __byte_perm(v0[u].x, v0[u].z, 0x7632), __byte_perm(v1[u].x, v1[u].z, 0x7632));
+            const uint4 f23 = make_uint4(__byte_perm(v0[u].y, v0[u].w, 0x5410), __byte_perm(v1[u].y, v1[u].w, 0x5410),
+                                         __byte_perm(v0[u].y, v0[u].w, 0x7632), __byte_perm(v1[u].y, v1[u].w, 0x7632));
+            const int i = (s * a.M + m) * 4 + t;
+            xb[i * 2 + (m & 1)] = f01;
+            xb[i * 2 + ((m & 1) ^ 1)] = f23;
+        }
+    }
 }
 
-template <int NT, bool BF16>
+template <int NT, bool BF16, bool kFull /* M == 8 * NT: every lane has a token, strides are constants */>
 __global__ void __launch_bounds__(kRingWarps * 32, 1) qmv_mma_ring_kernel(const MmaArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_mma[];
-    constexpr int kBlockSegs = kStageBytes / (NT * 1024);
     constexpr float off = BF16 ? 128.0f : 1024.0f;
+    constexpr uint32_t magic = BF16 ? 0x43004300u : 0x64006400u;
     uint4 *xb = reinterpret_cast<uint4 *>(smem_mma);
     unsigned char *ring_all = smem_mma + kStageBytes;                                   // [warps][2][kRunBytes]
     float *red = reinterpret_cast<float *>(ring_all + kRingWarps * 2 * kRunBytes);      // [warps][32][NT*4]
+    float *xsum = red + kRingWarps * 32 * NT * 4;                // [block_segs][Mp]: sum of x per segment and token
+    unsigned char *zeros = reinterpret_cast<unsigned char *>(xsum) + (NT == 1 ? 4096 : 2048);   // 32 bytes
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int ksh = a.ksplit_shift, KS = 1 << ksh, slots = kRingWarps >> ksh, slot = warp >> ksh, ks = warp & (KS - 1);
     const int tile_begin = static_cast<int>((static_cast<long long>(blockIdx.x) * a.tiles) / gridDim.x);
     const int tile_end = static_cast<int>((static_cast<long long>(blockIdx.x + 1) * a.tiles) / gridDim.x);
-    const int chunk = kBlockSegs >> ksh;                 // consecutive segments of a staged block owned by this warp
+    const int block_segs = a.block_segs;
+    const int chunk = block_segs >> ksh;                 // consecutive segments of a staged block owned by this warp
     const int runs = chunk >> 3;                         // runs of 8 segments per block
-    const int nblocks = (a.nseg + kBlockSegs - 1) / kBlockSegs;
-    const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(ring_all + warp * 2 * kRunBytes));
+    const int nblocks = (a.nseg + block_segs - 1) / block_segs;
+    const int Mtok = kFull ? NT * 8 : a.M;
+    const int Mp = kFull ? NT * 8 : (a.M + 1) & ~1;
+    unsigned char *ring_p = ring_all + warp * 2 * kRunBytes;
+    const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(ring_p));
+    const unsigned char *smem0 = smem_mma;               // shared-memory loads below are plain loads at byte offsets from here
+    const uint32_t xb_s = 0;
 
     asm volatile("griddepcontrol.launch_dependents;");
 
@@ -358,7 +393,7 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) qmv_mma_ring_kernel(const 
                 }
             }
             if (it_n >= a.iters || tile_n >= tile_end) break;
-            s_n = kb_n * kBlockSegs + ks * chunk + r_n * 8;
+            s_n = kb_n * block_segs + ks * chunk + r_n * 8;
             if (s_n < a.nseg) {
                 have_n = true;
                 break;
@@ -372,6 +407,28 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) qmv_mma_ring_kernel(const 
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const uint32_t lane_w = g * 256 + ((g & 3) << 5) + t * 8;           // fragment address within a run: ^ (p << 5)
+    // B fragments of this lane: token nt*8 + g, quad-lane t.  Lanes without a token read 32 bytes of zeros with
+    // stride 0 instead of branching; the same for the sums of tokens 2t, 2t+1.
+    const uint32_t zero_s = static_cast<uint32_t>(zeros - smem_mma);
+    uint32_t lane_x[NT], x_stride[NT], lane_xs[NT], xs_stride[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const bool has = kFull || nt * 8 + g < Mtok;
+        lane_x[nt] = has ? xb_s + ((nt * 8 + g) * 4 + t) * 32 + ((g & 1) << 4) : zero_s;    // + segment * M * 128; halves at ^ 16
+        x_stride[nt] = has ? Mtok * 128 : 0;
+        const bool has_s = kFull || nt * 8 + 2 * t < Mp;
+        lane_xs[nt] = has_s ? static_cast<uint32_t>(reinterpret_cast<unsigned char *>(xsum + nt * 8 + 2 * t) - smem_mma) : zero_s;   // + segment * Mp * 4
+        xs_stride[nt] = has_s ? Mp * 4 : 0;
+    }
+    if (threadIdx.x < 8) reinterpret_cast<uint32_t *>(zeros)[threadIdx.x] = 0u;     // visible after the first barrier below
+    auto load_frags = [&](int sl, uint4 (&bf)[2][NT]) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            const uint32_t addr = lane_x[nt] + sl * x_stride[nt];
+            bf[0][nt] = *reinterpret_cast<const uint4 *>(smem0 + addr);
+            bf[1][nt] = *reinterpret_cast<const uint4 *>(smem0 + (addr ^ 16));
+        }
+    };
     int buf = 0;
     for (int it = 0; it < a.iters; ++it) {
         const int tile = tile_begin + it * slots + slot;
@@ -384,32 +441,73 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) qmv_mma_ring_kernel(const 
 
         for (int kb = 0; kb < nblocks; ++kb) {
             if (it == 0 || nblocks > 1) {                // one block holding all of K is kept across tiles
+                const int nsb = min(block_segs, a.nseg - kb * block_segs);
                 __syncthreads();
-                stage_x_mma<NT>(a, xb, kb * kBlockSegs, min(kBlockSegs, a.nseg - kb * kBlockSegs));
+                stage_x_ring(a, xb, kb * block_segs, nsb);
+                __syncthreads();
+                // per-segment sums of the activations, once per block instead of once per row tile: a product
+                // with an A operand of ones leaves them in the accumulator layout (tokens 2t, 2t+1 in every row)
+                constexpr uint32_t one2 = BF16 ? 0x3F803F80u : 0x3C003C00u;
+                const uint32_t ones[4] = {one2, one2, one2, one2};
+                for (int sl = warp; sl < nsb; sl += kRingWarps) {
+                    uint4 bf[2][NT];
+                    load_frags(sl, bf);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        float sum[4];
+                        mma16816<BF16, true>(sum, ones, bf[0][nt].x, bf[0][nt].y);
+                        mma16816<BF16, false>(sum, ones, bf[0][nt].z, bf[0][nt].w);
+                        mma16816<BF16, false>(sum, ones, bf[1][nt].x, bf[1][nt].y);
+                        mma16816<BF16, false>(sum, ones, bf[1][nt].z, bf[1][nt].w);
+                        if (g == 0 && nt * 8 + 2 * t < Mp)
+                            *reinterpret_cast<float2 *>(xsum + sl * Mp + nt * 8 + 2 * t) = make_float2(sum[0], sum[1]);
+                    }
+                }
                 __syncthreads();
             }
             if (!active) continue;
             for (int r = 0; r < runs; ++r) {
                 const int sl0 = ks * chunk + r * 8;                      // first segment of the run within the block
-                if (kb * kBlockSegs + sl0 >= a.nseg) break;
+                if (kb * block_segs + sl0 >= a.nseg) break;
                 __syncwarp();                                            // every lane is done with the other buffer
                 advance();
                 if (have_n) issue(tile_n, s_n, buf ^ 1);
                 asm volatile("cp.async.commit_group;" ::: "memory");
                 asm volatile("cp.async.wait_group 1;" ::: "memory");     // this run has landed (this lane's copies)
                 __syncwarp();                                            // ... and every other lane's
-                const uint32_t rb = ring + buf * kRunBytes;
-                const uint4 v0 = lds128(rb + kRunWBytes + g * 16), v1 = lds128(rb + kRunWBytes + (g + 8) * 16);
-                const uint4 v2 = lds128(rb + kRunWBytes + 256 + g * 16), v3 = lds128(rb + kRunWBytes + 256 + (g + 8) * 16);
+                const unsigned char *rb = ring_p + buf * kRunBytes;
+                const uint4 v0 = *reinterpret_cast<const uint4 *>(rb + kRunWBytes + g * 16), v1 = *reinterpret_cast<const uint4 *>(rb + kRunWBytes + (g + 8) * 16);
+                const uint4 v2 = *reinterpret_cast<const uint4 *>(rb + kRunWBytes + 256 + g * 16), v3 = *reinterpret_cast<const uint4 *>(rb + kRunWBytes + 256 + (g + 8) * 16);
                 const uint32_t sp[4][4] = {{v0.x, v0.y, v0.z, v0.w}, {v1.x, v1.y, v1.z, v1.w},
                                            {v2.x, v2.y, v2.z, v2.w}, {v3.x, v3.y, v3.z, v3.w}};   // [s_lo, s_hi, b_lo, b_hi][pair]
-                const uint4 *frag = xb + (sl0 * NT * 32 + lane) * 2;
-                const uint32_t wbase = rb + lane_w;
+                const unsigned char *wrun = rb;
 #pragma unroll
                 for (int p = 0; p < 8; ++p) {
-                    const uint2 cl = lds64(wbase ^ (p << 5)), ch = lds64((wbase ^ (p << 5)) + 8 * 256);
-                    float d[NT][4], xs[NT][4];
-                    segment_mmas<NT, BF16>(d, xs, cl, ch, frag + p * NT * 64, lane);
+                    const uint2 cl = *reinterpret_cast<const uint2 *>(wrun + (lane_w ^ (p << 5)));
+                    const uint2 ch = *reinterpret_cast<const uint2 *>(wrun + (lane_w ^ (p << 5)) + 8 * 256);
+                    uint4 bf[2][NT];
+                    load_frags(sl0 + p, bf);
+                    float d[NT][4], xs[NT][2];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const float2 v = *reinterpret_cast<const float2 *>(smem0 + lane_xs[nt] + (sl0 + p) * xs_stride[nt]);
+                        xs[nt][0] = v.x;
+                        xs[nt][1] = v.y;
+                    }
+#define MTC_STEP(J, ZERO)                                                                                 \
+    {                                                                                                     \
+        const uint32_t af[4] = {code_pair<J>(cl.x, magic), code_pair<J>(ch.x, magic), code_pair<J>(cl.y, magic), \
+                                code_pair<J>(ch.y, magic)};                                               \
+        _Pragma("unroll") for (int nt = 0; nt < NT; ++nt) {                                               \
+            const uint4 f = bf[(J) >> 1][nt];                                                             \
+            mma16816<BF16, ZERO>(d[nt], af, ((J) & 1) ? f.z : f.x, ((J) & 1) ? f.w : f.y);                \
+        }                                                                                                 \
+    }
+                    MTC_STEP(0, true)
+                    MTC_STEP(1, false)
+                    MTC_STEP(2, false)
+                    MTC_STEP(3, false)
+#undef MTC_STEP
                     const int q = p >> 1;
                     float s_lo, s_hi, o_lo, o_hi;
                     if (BF16) {
@@ -475,36 +573,45 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) qmv_mma_ring_kernel(const 
 template <int NT>
 constexpr size_t ring_smem_bytes() {
     return static_cast<size_t>(kStageBytes) + static_cast<size_t>(kRingWarps) * 2 * kRunBytes +
-           static_cast<size_t>(kRingWarps) * 32 * NT * 4 * sizeof(float);
+           static_cast<size_t>(kRingWarps) * 32 * NT * 4 * sizeof(float) + (NT == 1 ? 4096 : 2048) + 64;
 }
 
 template <int NT, bool BF16>
 cudaError_t launch_ring(Ctx *ctx, cudaStream_t st, MmaArgs a) {
     const int sms = ctx->sm_count;
-    constexpr int kBlockSegs = kStageBytes / (NT * 1024);
     a.tiles = (a.N + 15) / 16;
     int grid = a.tiles < sms ? a.tiles : sms;
     const int max_tiles = (a.tiles + grid - 1) / grid;
-    // K split over the warps of a CTA: the split with the fewest runs on the busiest warp, ties to the smaller
-    const int runs_row = a.nseg / 8;
-    int best_ksh = 0;
+    // K split over the warps of a CTA: the split with the fewest runs on the busiest warp (then the fewest
+    // barriers), ties to the smaller.  A staged block holds kStageBytes / (M * 128) segments at most and is a
+    // multiple of 8 segments per warp of the split.
+    const int cap = kStageBytes / (a.M * 128);
+    int best_ksh = 0, best_block = 0;
     long best_cost = -1;
-    for (int ksh = 0; (1 << ksh) <= kRingWarps && (kBlockSegs >> ksh) >= 8; ++ksh) {
+    for (int ksh = 0; (1 << ksh) <= kRingWarps && (8 << ksh) <= cap; ++ksh) {
+        const int unit = 8 << ksh;
+        int block = (a.nseg + unit - 1) / unit * unit;
+        if (block > cap) block = cap / unit * unit;
+        const int nblocks = (a.nseg + block - 1) / block;
         const int slots = kRingWarps >> ksh;
         const long iters = (max_tiles + slots - 1) / slots;
-        const long cost = iters * ((runs_row + (1 << ksh) - 1) >> ksh) * 16 + iters;      // runs, then barriers
+        const long cost = iters * nblocks * ((block >> ksh) / 8) * 16 + iters * nblocks;
         if (best_cost < 0 || cost < best_cost) {
             best_cost = cost;
             best_ksh = ksh;
+            best_block = block;
         }
     }
+    a.block_segs = best_block;
     a.ksplit_shift = best_ksh;
     const int slots = kRingWarps >> best_ksh;
     a.iters = (max_tiles + slots - 1) / slots;
     constexpr size_t smem = ring_smem_bytes<NT>();
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(qmv_mma_ring_kernel<NT, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        cudaError_t e = cudaFuncSetAttribute(qmv_mma_ring_kernel<NT, BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(qmv_mma_ring_kernel<NT, BF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
@@ -518,7 +625,8 @@ cudaError_t launch_ring(Ctx *ctx, cudaStream_t st, MmaArgs a) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, qmv_mma_ring_kernel<NT, BF16>, a);
+    if (a.M == NT * 8) return cudaLaunchKernelEx(&cfg, qmv_mma_ring_kernel<NT, BF16, true>, a);
+    return cudaLaunchKernelEx(&cfg, qmv_mma_ring_kernel<NT, BF16, false>, a);
 }
 
 template <int NT>

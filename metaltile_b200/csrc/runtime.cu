@@ -275,7 +275,8 @@ int mtc_qmv(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
     if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "qmv: dtype must be f32, f16 or bf16");
     if (M > 0 && N > 0 && (!w || !scales || !biases || !x || !out)) return fail(ctx, MTC_ERR_INVALID, "qmv: null pointer");
     std::string why;
-    if (ctx->qmv_small_m_mma && mtc::qmv_mma_supported(M, N, K, bits, group_size, dtype, w, x)) {
+    if (ctx->qmv_small_m_mma && (M >= 2 || ctx->qmv_small_m_mma == 2) &&
+        mtc::qmv_mma_supported(M < 2 ? 2 : M, N, K, bits, group_size, dtype, w, x)) {
         cudaError_t e2 = mtc::launch_qmv_mma(ctx, static_cast<cudaStream_t>(stream), w, scales, biases, x, out, M, N, K,
                                              group_size, dtype);
         if (e2 != cudaSuccess) return fail(ctx, MTC_ERR_DISPATCH, std::string("qmv (mma) launch: ") + cudaGetErrorString(e2));
@@ -324,7 +325,7 @@ int mtc_set_option(mtc_ctx *ctx, const char *name, int value) {
         return MTC_OK;
     }
     if (std::strcmp(name, "qmv_small_m_mma") == 0) {
-        ctx->qmv_small_m_mma = value ? 1 : 0;
+        ctx->qmv_small_m_mma = value < 0 ? 0 : (value > 2 ? 2 : value);
         return MTC_OK;
     }
     if (std::strcmp(name, "qmm_pair") == 0) {

@@ -166,6 +166,19 @@ def test_small_m_tensor_core_path(ctx, m, n, k, gs, dt):
     assert rel_err(got, cores) <= TOL[dt]
 
 
+@pytest.mark.parametrize("n,k,dt", [(4096, 4096, "bf16"), (100, 14336, "f16"), (1024, 512, "bf16")])
+def test_single_row_through_tensor_core_path(ctx, n, k, dt):
+    """Option value 2 sends M = 1 down the same path; K = 14336 stays resident as one staged block."""
+    w, s, b, x = dense_case(1, n, k, 4, 64, dt, seed=8, salt=n)
+    ref = oracle.qmm(w, s, b, x, 1, n, k, 4, 64)
+    ctx.set_option("qmv_small_m_mma", 2)
+    try:
+        got = run_qmv(w, s, b, x, 4, 64, dt)
+    finally:
+        ctx.set_option("qmv_small_m_mma", 1)
+    assert rel_err(got, ref) <= TOL[dt]
+
+
 def test_small_m_tensor_core_exact_integers(ctx):
     """Integer-valued scales, biases and activations: every product and sum is exact in f32, so the MMA
     path must reproduce the oracle bit for bit (checks the code-to-slot permutation of the operands)."""
