@@ -138,6 +138,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=1, help="activation rows per projection (1 or 8)")
     ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--streams", type=int, default=1, help="parallel streams for the independent projections of a phase")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary single-kernel measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     args = ap.parse_args()
@@ -216,19 +217,34 @@ def main():
     # each projection writes its own contiguous [M, nl] tile, then tiles are packed per phase
     tiles = [[torch.empty((M, nl), dtype=torch.bfloat16, device=dev) for (_, _, _, _, nl, _) in mats] for mats in layers]
 
+    # the projections of one phase (q/k/v; gate/up) read the same activations and are independent:
+    # with --streams > 1 they are launched on parallel streams, joined before the phase's all-gather
+    branches = [torch.cuda.Stream() for _ in range(max(0, args.streams - 1))]
+
     def step():
+        main = torch.cuda.current_stream()
         for li, mats in enumerate(layers):
             for ph in range(4):
                 col = 0
+                used = []
                 for pi, (w, sc, bi, k, nl, phase) in enumerate(mats):
                     if phase != ph:
                         continue
-                    if M == 1:   # a [1, nl] slice of the phase slab is contiguous: write in place
-                        ops.qmv(w, sc, bi, xs[k], BITS, GROUP, out=out_local[li][ph][:, col:col + nl], ctx=ctx)
-                    else:
-                        ops.qmv(w, sc, bi, xs[k], BITS, GROUP, out=tiles[li][pi], ctx=ctx)
-                        out_local[li][ph][:, col:col + nl].copy_(tiles[li][pi])
+                    lane = len(used) % (len(branches) + 1)
+                    st = main if lane == 0 else branches[lane - 1]
+                    if st is not main and st not in used:
+                        st.wait_stream(main)
+                    used.append(st)
+                    with torch.cuda.stream(st):
+                        if M == 1:   # a [1, nl] slice of the phase slab is contiguous: write in place
+                            ops.qmv(w, sc, bi, xs[k], BITS, GROUP, out=out_local[li][ph][:, col:col + nl], ctx=ctx)
+                        else:
+                            ops.qmv(w, sc, bi, xs[k], BITS, GROUP, out=tiles[li][pi], ctx=ctx)
+                            out_local[li][ph][:, col:col + nl].copy_(tiles[li][pi])
                     col += nl
+                for st in set(used):
+                    if st is not main:
+                        main.wait_stream(st)
                 if world > 1:
                     dist.all_gather_into_tensor(out_full[li][ph], out_local[li][ph])
 
