@@ -24,6 +24,7 @@ struct Ctx {
     size_t scratch_bytes = 0;
     int qmm_force_tn = 0;          // option "qmm_tile_tokens": 0 = choose per shape
     int qmv_small_m_mma = 1;       // option "qmv_small_m_mma": 0 keeps 2 <= M <= 16 on the CUDA-core kernel
+    int qmm_max_stages = 0;        // option "qmm_max_stages": > 0 caps the ring depth (diagnostic: how much the ring hides)
     int qmm_pair = 0;              // option "qmm_pair": 1 = give a work item two adjacent weight-row tiles
     void *d_worklist = nullptr;    // gather_qmm work list (grow-only, owned by the context)
     size_t worklist_bytes = 0;

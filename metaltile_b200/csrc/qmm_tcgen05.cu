@@ -665,6 +665,7 @@ void fill_common(QmmParams &p, Ctx *ctx, const void *w, const void *scales, cons
     p.pair = 0;
     p.nst = RING_BYTES / (A_BYTES + TN * BK * 2);
     if (p.nst > MAX_STAGES) p.nst = MAX_STAGES;
+    if (ctx->qmm_max_stages > 0 && p.nst > ctx->qmm_max_stages) p.nst = ctx->qmm_max_stages;
     const uint32_t fmt = p.op_f16 ? 0u : 1u;           // both operands carry the same 16-bit format
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(TN >> 3) << 17) |
               (static_cast<uint32_t>(BMW >> 4) << 24);
@@ -737,6 +738,7 @@ cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const v
     if (p.pair) {
         p.nst = RING_BYTES / (2 * A_BYTES + TN * BK * 2);
         if (p.nst > MAX_STAGES) p.nst = MAX_STAGES;
+        if (ctx->qmm_max_stages > 0 && p.nst > ctx->qmm_max_stages) p.nst = ctx->qmm_max_stages;
         const int pairs = (p.n_tiles + 1) / 2;
         const int pair_units = pairs * p.m_chunks;
         // whole waves of pairs; the rest as single tiles (whole pair rows of m_chunks items stay together)

@@ -328,6 +328,10 @@ int mtc_set_option(mtc_ctx *ctx, const char *name, int value) {
         ctx->qmv_small_m_mma = value < 0 ? 0 : (value > 2 ? 2 : value);
         return MTC_OK;
     }
+    if (std::strcmp(name, "qmm_max_stages") == 0) {
+        ctx->qmm_max_stages = value < 0 ? 0 : value;
+        return MTC_OK;
+    }
     if (std::strcmp(name, "qmm_pair") == 0) {
         ctx->qmm_pair = value ? 1 : 0;
         return MTC_OK;
