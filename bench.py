@@ -130,6 +130,11 @@ def cpu_reference_arm(args):
     return nbytes / dt / 1e9, dt * 1e3, threads, f"{layers} of {LAYERS} layers ({len(mats)} matrices) per step"
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes for one launch of the step's kernel
+# (profiles/qmv_pipe_m1_14336x4096_4bit_g64_bf16.md: 33.09 MB / 33.07 MB)
+NCU_TRAFFIC_RATIO = 1.001
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -327,8 +332,9 @@ def main():
     per_launch_bytes = total_bytes / world / launches_per_step
     us_per_launch = ms * 1e3 / launches_per_step
     roofline = {"bound": "hbm", "achieved": value / world, "peak": hbm_peak, "unit": "GB/s",
-                "frac": value / world / hbm_peak, "traffic": None, "peak_kind": peak_kind,
-                "kernel": "qmv_kernel<4,1,4>", "alg_bytes_per_launch": per_launch_bytes,
+                "frac": value / world / hbm_peak, "traffic": per_launch_bytes * NCU_TRAFFIC_RATIO, "peak_kind": peak_kind,
+                "traffic_source": "ncu dram bytes / algorithmic bytes = 1.001 on the 14336x4096 launch, scaled to the average launch",
+                "kernel": "qmv_pipe_kernel<4,1,4,2,2>", "alg_bytes_per_launch": per_launch_bytes,
                 "avg_us_per_launch": us_per_launch,
                 "note": "per-GPU; launch-averaged over the 4 matrix shapes of the step (graph replay, events)"}
     line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,

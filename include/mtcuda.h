@@ -103,6 +103,8 @@ const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dty
  *                      activations and a group that is a multiple of 64 use the warp-level tensor cores);
  *                      2: M = 1 takes that path too (same results within round-off; not faster on B200)
  *   "qmm_max_stages"   > 0 caps the depth of the shared-memory ring of the tensor-core kernel (diagnostic)
+ *   "qmm_raw"          0: the dequant warps of the tensor-core kernel load packed words straight from global
+ *                      memory instead of through the shared-memory staging buffers (default 1)
  *   "qmm_pair"         1: a work item covers two adjacent weight-row tiles that share every
  *                      activation stage (dense qmm only; default 0) */
 int mtc_set_option(mtc_ctx *ctx, const char *name, int value);

@@ -43,7 +43,9 @@ constexpr int BMW = 128;         // weight rows per tile (TMEM lanes, MMA M)
 constexpr int BK = 64;           // k per stage: 64 x 16-bit = one 128B swizzle row
 constexpr int TN_MAX = 256;      // token rows per tile (TMEM columns of one accumulator, MMA N)
 constexpr int MAX_STAGES = 8;    // ring depth: as many stages as fit in RING_BYTES, at most this
-constexpr int RING_BYTES = 192 * 1024;
+constexpr int RING_BYTES = 224 * 1024;      // stages of the ring, then the raw staging buffers; SmemCtrl follows
+constexpr int SB_PER_RAW = 4;               // k blocks per raw super-block: 256 codes = 32*BITS bytes per weight row
+constexpr int RAW_SB_BYTES = 2 * BMW * 16;  // scales then biases of a super-block: 16 bytes per row each
 constexpr int A_BYTES = BMW * BK * 2;       // 16 KB, dequantised weights
 constexpr int B_BYTES = TN_MAX * BK * 2;    // 32 KB, activations
 constexpr int NUM_THREADS = 512;
@@ -68,6 +70,8 @@ struct QmmParams {
     int wpr, gpr;                // words / groups per weight row
     int TN;                      // token rows per item (TMA box rows, MMA N)
     int nst;                     // ring depth
+    int raw;                     // 1: packed words reach the dequant warps through shared memory (cp.async, whole lines)
+    uint32_t raw_off, raw_tile;  // byte offset of the raw buffers in shared memory; bytes of one tile of one buffer
     int pair;                    // 1: an item covers two adjacent weight-row tiles that share every X stage
     int pair_items;              // dense + pair: items [0, pair_items) are pairs, the rest single tiles
     int n_tiles;                 // dense: weight-row tiles
@@ -80,6 +84,7 @@ struct __align__(8) SmemCtrl {
     uint64_t empty[MAX_STAGES];  // MMAs that read the stage have completed
     uint64_t acc_full[2];        // accumulator buffer complete
     uint64_t acc_empty[2];       // epilogue drained the accumulator buffer
+    uint64_t raw_full[2];        // every dequant warp's copies of a raw super-block have landed
     uint32_t tmem_base;
     volatile uint32_t abort;
 };
@@ -182,6 +187,30 @@ __device__ __forceinline__ void st_shared_v4(uint32_t saddr, uint32_t a, uint32_
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+template <int BYTES>
+__device__ __forceinline__ void cp_async_small(uint32_t dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(dst), "l"(src), "n"(BYTES) : "memory");
+}
+// BITS consecutive words from shared memory, with the widest loads the 4*BITS-byte pieces are aligned for
+template <int BITS>
+__device__ __forceinline__ void lds_words(uint32_t addr, uint32_t (&w)[BITS]) {
+    if constexpr (BITS % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < BITS / 4; ++i)
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w[4 * i]), "=r"(w[4 * i + 1]), "=r"(w[4 * i + 2]), "=r"(w[4 * i + 3]) : "r"(addr + 16 * i));
+    } else if constexpr (BITS % 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < BITS / 2; ++i)
+            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(w[2 * i]), "=r"(w[2 * i + 1]) : "r"(addr + 8 * i));
+    } else {
+#pragma unroll
+        for (int i = 0; i < BITS; ++i) asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w[i]) : "r"(addr + 4 * i));
+    }
+}
+
 // ---- dequantisation of half a W row segment (32 codes = BITS words) into 4 swizzled 16-byte chunks --
 template <int BITS>
 struct QPack {
@@ -216,10 +245,60 @@ __device__ __forceinline__ void load_half_words(const uint32_t *p, uint32_t (&w)
 }
 
 // dst[c] = shared-memory address of the c-th of this thread's four 16-byte chunks (swizzle applied by the caller)
+// 4- and 8-bit codes in packed-half arithmetic.  `byte-permute | 0x6400` makes two f16 values 1024 + q without a
+// conversion, HSUB2 removes the 1024 exactly, and one HFMA2 per two codes gives round_f16(q*scale + bias) - the
+// value the f32 path rounds to, up to double rounding - already in the operand's type: ~2 instructions per code
+// instead of ~3.5.  The caller uses it only when the scale is a normal f16 number.
+template <int BITS>
+__device__ __forceinline__ void dequant_half_h2(const uint32_t (&w)[BITS], float s, float b, const uint32_t (&dst)[4],
+                                                uint32_t stage_off) {
+    static_assert(BITS == 4 || BITS == 8, "packed-half path: 4- and 8-bit codes");
+    const __half2 s2 = __float2half2_rn(s), b2 = __float2half2_rn(b);
+    const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+    uint32_t magic = 0x64006400u;
+    asm volatile("" : "+r"(magic));          // in a register, so that mask-and-or is a single LOP3
+    auto finish = [&](uint32_t t) {
+        const __half2 q = __hsub2(*reinterpret_cast<const __half2 *>(&t), k1024);
+        const __half2 v = __hfma2(q, s2, b2);
+        return *reinterpret_cast<const uint32_t *>(&v);
+    };
+    if (BITS == 4) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {        // word i = codes 8i..8i+7 = one 16-byte chunk of the tile row
+            const uint32_t lo = w[i], hi = w[i] >> 4;      // byte j of lo / hi has code 2j / 2j+1 in its low nibble
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t t = __byte_perm(lo, hi, ((4 + j) << 8) | j);          // code 2j -> bits 0..3, code 2j+1 -> bits 16..19
+                uint32_t r;
+                asm("lop3.b32 %0, %1, 0x000F000F, %2, 0xEA;" : "=r"(r) : "r"(t), "r"(magic));
+                o[j] = finish(r);
+            }
+            st_shared_v4(dst[i] + stage_off, o[0], o[1], o[2], o[3]);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {        // words 2i, 2i+1 = codes 8i..8i+7
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)      // two bytes of word 2i + j/2 under the 0x64 exponent bytes
+                o[j] = finish(__byte_perm(w[2 * i + (j >> 1)], 0x64646464u, (j & 1) ? 0x4342 : 0x4140));
+            st_shared_v4(dst[i] + stage_off, o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
 template <int BITS>
 __device__ __forceinline__ void dequant_half(const uint32_t (&w)[BITS], float s, float b, const uint32_t (&dst)[4],
                                              uint32_t stage_off) {
     using Q = QPack<BITS>;
+    if constexpr (BITS == 4 || BITS == 8) {
+        // scale a normal f16 number (its exact value survives the conversion), bias within f16 range
+        if (fabsf(s) >= 6.104e-5f && fabsf(s) <= 65504.0f && fabsf(b) <= 65504.0f) {
+            dequant_half_h2<BITS>(w, s, b, dst, stage_off);
+            return;
+        }
+    }
     // a code at bit p of a window becomes q * 2^(p-23) after the magic subtract: fold 2^(23-p) into the scale
     float sp[Q::CPW];
 #pragma unroll
@@ -300,6 +379,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
         for (int b = 0; b < 2; ++b) {
             mbar_init(&ctl->acc_full[b], 1);
             mbar_init(&ctl->acc_empty[b], 4);
+            mbar_init(&ctl->raw_full[b], DEQ_THREADS / 32);
         }
         ctl->abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -419,6 +499,101 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
             dst[c] = smem_u32(sW) + (r >> 3) * 1024 + r7 * 128 + (((h * 4 + c) ^ r7) << 4);
         uint32_t it = 0;
         bool ok = true;
+        if (p.raw) {
+            // Packed words through shared memory.  A thread that loads its own row's 16 bytes per k block makes
+            // every warp-load touch 32 cache lines (plus 64 for the scale and the bias): measured, the L1 tag stage,
+            // not the arithmetic, set the pace of a k block (0.8 us whatever the tile width or the ring depth).  Here
+            // the 256 dequant threads copy a super-block of 4 k blocks of the tile - 32*BITS contiguous bytes per
+            // row, 16 bytes per thread and copy, two rows per warp-copy - with cp.async into one of two raw
+            // buffers, one super-block ahead and across items, and read their pieces back from shared memory.
+            constexpr int ROW_BYTES = 32 * BITS, PITCH = ROW_BYTES + 16, CPR = 2 * BITS;   // padded rows: conflict-free reads
+            const uint32_t raw0 = smem_u32(smem) + p.raw_off;
+            const uint32_t buf_bytes = (p.pair ? 2u : 1u) * p.raw_tile;
+            const int num_sb = num_kb / SB_PER_RAW;
+            const int sb_bytes = (2 * SB_PER_RAW * BK) >> p.gs_shift;       // scale bytes of a row per super-block: 16, 8 or 4
+            const int srow = t & (BMW - 1), sarr = t >> 7;                  // this thread copies scales (0) or biases (1) of a row
+            auto issue = [&](const Item &im, int sbk, int buf) {
+                for (int tt = 0; tt < im.nt; ++tt) {
+                    const uint32_t dstt = raw0 + buf * buf_bytes + tt * p.raw_tile;
+                    const int n0 = (im.n_tile + tt) * BMW;
+                    const size_t erow = static_cast<size_t>(im.expert) * p.N;
+#pragma unroll
+                    for (int c = 0; c < BITS; ++c) {
+                        const int ch = c * DEQ_THREADS + t, row = ch / CPR, col = ch - row * CPR;
+                        const size_t grow = erow + min(n0 + row, p.N - 1);          // rows past N copy the last row; never stored
+                        cp_async_16(dstt + row * PITCH + col * 16,
+                                    reinterpret_cast<const char *>(p.w + grow * p.wpr) + static_cast<size_t>(sbk) * ROW_BYTES + col * 16);
+                    }
+                    const size_t grow = erow + min(n0 + srow, p.N - 1);
+                    const char *src = static_cast<const char *>(sarr ? p.biases : p.scales) + (grow * p.gpr) * 2 +
+                                      static_cast<size_t>(sbk) * sb_bytes;
+                    const uint32_t d = dstt + BMW * PITCH + sarr * (BMW * 16) + srow * 16;
+                    if (sb_bytes == 16) cp_async_16(d, src);
+                    else if (sb_bytes == 8) cp_async_small<8>(d, src);
+                    else cp_async_small<4>(d, src);
+                }
+            };
+            // request stream: (item, super-block) pairs in processing order
+            int i_n = blockIdx.x, sb_n = 0;
+            Item item_n{};
+            if (i_n < num_items) {
+                item_n = get_item(p, i_n);
+                issue(item_n, 0, 0);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            uint32_t q = 0;
+            for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x) {
+                const Item item = get_item(p, i);
+                for (int sbk = 0; sbk < num_sb && ok; ++sbk, ++q) {
+                    const int buf = q & 1;
+                    // this super-block has landed: my copies, then every warp's (which also says that every warp is
+                    // done reading the other buffer)
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&ctl->raw_full[buf]);
+                    if (!(ok = mbar_wait_warp(&ctl->raw_full[buf], (q >> 1) & 1, ctl, p.status, 0x402, 0))) break;
+                    // the next one, into the other buffer
+                    if (++sb_n == num_sb) {
+                        sb_n = 0;
+                        i_n += gridDim.x;
+                        if (i_n < num_items) item_n = get_item(p, i_n);
+                    }
+                    if (i_n < num_items) issue(item_n, sb_n, buf ^ 1);
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < SB_PER_RAW; ++j, ++it) {
+                        const int s = it % nst;
+                        const uint32_t ph = (it / nst) & 1;
+                        if (!(ok = mbar_wait_warp(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x401, 0))) break;
+                        const int g = (j * BK + h * 32) >> p.gs_shift;       // group within the super-block
+#pragma unroll
+                        for (int tt = 0; tt < 2; ++tt) {
+                            if (tt < item.nt) {
+                                const uint32_t base = raw0 + buf * buf_bytes + tt * p.raw_tile;
+                                uint32_t wv[BITS];
+                                lds_words<BITS>(base + r * PITCH + (2 * j + h) * (4 * BITS), wv);
+                                unsigned short sr, br;
+                                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sr) : "r"(base + BMW * PITCH + r * 16 + g * 2));
+                                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(br) : "r"(base + BMW * PITCH + BMW * 16 + r * 16 + g * 2));
+                                float sc, bi;
+                                if (p.sb_dt == MTC_F16) {
+                                    sc = __half2float(__ushort_as_half(sr));
+                                    bi = __half2float(__ushort_as_half(br));
+                                } else {
+                                    sc = __uint_as_float(static_cast<uint32_t>(sr) << 16);
+                                    bi = __uint_as_float(static_cast<uint32_t>(br) << 16);
+                                }
+                                dequant_half<BITS>(wv, sc, bi, dst, s * w_stage + tt * A_BYTES);
+                            }
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> async proxy (MMA)
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&ctl->full_w[s]);
+                    }
+                }
+            }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        } else
         for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x) {
             const Item item = get_item(p, i);
             bool valid[2];
@@ -646,6 +821,23 @@ cudaError_t make_x_map(CUtensorMap *tmap, const void *x, int rows, int K, int TN
     return cudaSuccess;
 }
 
+// Ring depth and raw staging buffers for p.TN / p.pair.  The raw path needs whole super-blocks (K % 256 == 0), 4 to 16
+// bytes of scales per row and super-block (group 32, 64 or 128) and 16-byte aligned scale / bias arrays; it takes
+// two buffers per weight tile out of the ring, which costs nothing: measured, a ring deeper than 2 stages does not
+// change the time of any shape.
+void plan_smem(QmmParams &p, Ctx *ctx, int bits) {
+    const int stage = (p.pair ? 2 : 1) * A_BYTES + p.TN * BK * 2;
+    const auto al16 = [](const void *ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; };
+    p.raw_tile = static_cast<uint32_t>(BMW * (32 * bits + 16) + RAW_SB_BYTES);
+    const int raw_total = 2 * (p.pair ? 2 : 1) * static_cast<int>(p.raw_tile);
+    p.raw = ctx->qmm_raw != 0 && p.K % (SB_PER_RAW * BK) == 0 && p.gs_shift >= 5 && p.gs_shift <= 7 && al16(p.scales) &&
+            al16(p.biases) && (RING_BYTES - raw_total) / stage >= 2;
+    p.nst = (RING_BYTES - (p.raw ? raw_total : 0)) / stage;
+    if (p.nst > MAX_STAGES) p.nst = MAX_STAGES;
+    if (ctx->qmm_max_stages > 0 && p.nst > ctx->qmm_max_stages) p.nst = ctx->qmm_max_stages;
+    p.raw_off = static_cast<uint32_t>(p.nst * stage);
+}
+
 void fill_common(QmmParams &p, Ctx *ctx, const void *w, const void *scales, const void *biases, void *out, int N, int K,
                  int bits, int group_size, int dt, int TN) {
     p.w = static_cast<const uint32_t *>(w);
@@ -663,9 +855,7 @@ void fill_common(QmmParams &p, Ctx *ctx, const void *w, const void *scales, cons
     p.gpr = K / group_size;
     p.TN = TN;
     p.pair = 0;
-    p.nst = RING_BYTES / (A_BYTES + TN * BK * 2);
-    if (p.nst > MAX_STAGES) p.nst = MAX_STAGES;
-    if (ctx->qmm_max_stages > 0 && p.nst > ctx->qmm_max_stages) p.nst = ctx->qmm_max_stages;
+    plan_smem(p, ctx, bits);
     const uint32_t fmt = p.op_f16 ? 0u : 1u;           // both operands carry the same 16-bit format
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(TN >> 3) << 17) |
               (static_cast<uint32_t>(BMW >> 4) << 24);
@@ -736,9 +926,7 @@ cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const v
     // is off unless asked for.
     p.pair = (ctx->qmm_pair > 0 && p.n_tiles >= 2) ? 1 : 0;
     if (p.pair) {
-        p.nst = RING_BYTES / (2 * A_BYTES + TN * BK * 2);
-        if (p.nst > MAX_STAGES) p.nst = MAX_STAGES;
-        if (ctx->qmm_max_stages > 0 && p.nst > ctx->qmm_max_stages) p.nst = ctx->qmm_max_stages;
+        plan_smem(p, ctx, bits);
         const int pairs = (p.n_tiles + 1) / 2;
         const int pair_units = pairs * p.m_chunks;
         // whole waves of pairs; the rest as single tiles (whole pair rows of m_chunks items stay together)
