@@ -70,6 +70,7 @@ struct QmmParams {
     int wpr, gpr;                // words / groups per weight row
     int TN;                      // token rows per item (TMA box rows, MMA N)
     int nst;                     // ring depth
+    uint32_t hint_ns;            // base suspend-time hint of the waits (0: plain polling)
     int raw;                     // 1: packed words reach the dequant warps through shared memory (cp.async, whole lines)
     uint32_t raw_off, raw_tile;  // byte offset of the raw buffers in shared memory; bytes of one tile of one buffer
     int pair;                    // 1: an item covers two adjacent weight-row tiles that share every X stage
@@ -110,13 +111,25 @@ __device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// try_wait with a suspend-time hint: the thread may sleep in hardware for up to `ns` before it reports failure
+__device__ __forceinline__ bool mbar_try_hint(uint64_t *bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
 // Bounded wait.  Returns false (and raises the CTA's abort flag + the global status word) when the
-// barrier did not complete within kSpinLimit polls or another role already aborted.  `sleep_ns` > 0
-// backs off between polls so that waiting warps do not take issue slots from the dequant warps.
+// barrier did not complete within kSpinLimit polls or another role already aborted.  `sleep_ns` > 0 lets
+// the hardware suspend the thread between polls: without it the fourteen waiting threads of a CTA issue
+// more poll instructions than the dequant warps issue useful ones (ncu: SYNCS + BRA + BREAK were 60 % of all
+// instructions executed).
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, SmemCtrl *ctl, uint32_t *status, uint32_t code,
                                           uint32_t sleep_ns = 0) {
     for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        if (mbar_try(bar, parity)) return true;
+        if (sleep_ns ? mbar_try_hint(bar, parity, sleep_ns) : mbar_try(bar, parity)) return true;
         if ((i & 63u) == 63u && ctl->abort) return false;
     }
     ctl->abort = 1;
@@ -403,7 +416,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % nst;
                     const uint32_t ph = (it / nst) & 1;
-                    if (!(ok = mbar_wait(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x101, 40))) break;
+                    if (!(ok = mbar_wait(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x101, (p.hint_ns & 1) ? 0 : p.hint_ns))) break;
                     mbar_expect_tx(&ctl->full_x[s], x_bytes);
                     tma_load_2d(sX + s * x_stage, &tmap_x, kb * BK, item.row0, &ctl->full_x[s]);
                 }
@@ -454,7 +467,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
             const int buf = p.pair ? 0 : (tile_i & 1);
             const uint32_t acc_ph = (p.pair ? tile_i : (tile_i >> 1)) & 1;
             const Item item = get_item(p, i);
-            if (!(ok = mbar_wait_warp(&ctl->acc_full[buf], acc_ph, ctl, p.status, 0x301, 200))) break;
+            if (!(ok = mbar_wait_warp(&ctl->acc_full[buf], acc_ph, ctl, p.status, 0x301, p.hint_ns))) break;
             tc_fence_after();
             const int cols = (item.rows + 15) & ~15;
             for (int t = 0; t < item.nt; ++t) {
@@ -856,6 +869,7 @@ void fill_common(QmmParams &p, Ctx *ctx, const void *w, const void *scales, cons
     p.TN = TN;
     p.pair = 0;
     plan_smem(p, ctx, bits);
+    p.hint_ns = static_cast<uint32_t>(ctx->qmm_wait_hint_ns);
     const uint32_t fmt = p.op_f16 ? 0u : 1u;           // both operands carry the same 16-bit format
     p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(TN >> 3) << 17) |
               (static_cast<uint32_t>(BMW >> 4) << 24);

@@ -332,6 +332,10 @@ int mtc_set_option(mtc_ctx *ctx, const char *name, int value) {
         ctx->qmm_max_stages = value < 0 ? 0 : value;
         return MTC_OK;
     }
+    if (std::strcmp(name, "qmm_wait_hint_ns") == 0) {
+        ctx->qmm_wait_hint_ns = value < 0 ? 0 : value;
+        return MTC_OK;
+    }
     if (std::strcmp(name, "qmm_raw") == 0) {
         ctx->qmm_raw = value ? 1 : 0;
         return MTC_OK;
