@@ -80,8 +80,7 @@ struct QmmParams {
 };
 
 struct __align__(8) SmemCtrl {
-    uint64_t full_x[MAX_STAGES]; // TMA bytes of the X stage have landed
-    uint64_t full_w[MAX_STAGES]; // dequant warps finished the W stage
+    uint64_t full[MAX_STAGES];   // the X stage has landed (TMA transaction bytes) and the dequant warps finished the W stage
     uint64_t empty[MAX_STAGES];  // MMAs that read the stage have completed
     uint64_t acc_full[2];        // accumulator buffer complete
     uint64_t acc_empty[2];       // epilogue drained the accumulator buffer
@@ -168,6 +167,11 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -385,8 +389,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < MAX_STAGES; ++s) {
-            mbar_init(&ctl->full_x[s], 1);
-            mbar_init(&ctl->full_w[s], DEQ_THREADS / 32);
+            mbar_init(&ctl->full[s], 1 + DEQ_THREADS / 32);
             mbar_init(&ctl->empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -409,53 +412,71 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
     if (warp == 0) {
         // ---------------- producer: TMA loads of the X chunk ----------------
         if (lane == 0) {
-            uint32_t it = 0;
+            int s = 0;
+            uint32_t ph = 0;                              // stage and ring-pass parity, advanced without a division
             bool ok = true;
             for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x) {
                 const Item item = get_item(p, i);
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % nst;
-                    const uint32_t ph = (it / nst) & 1;
-                    if (!(ok = mbar_wait(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x101, (p.hint_ns & 1) ? 0 : p.hint_ns))) break;
-                    mbar_expect_tx(&ctl->full_x[s], x_bytes);
-                    tma_load_2d(sX + s * x_stage, &tmap_x, kb * BK, item.row0, &ctl->full_x[s]);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = mbar_wait(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x101, p.hint_ns))) break;
+                    mbar_expect_tx(&ctl->full[s], x_bytes);
+                    tma_load_2d(sX + s * x_stage, &tmap_x, kb * BK, item.row0, &ctl->full[s]);
+                    if (++s == nst) {
+                        s = 0;
+                        ph ^= 1;
+                    }
                 }
             }
             if (!ok) {   // let copies already in flight land before the CTA tears down
                 for (int s = 0; s < nst; ++s)
-                    for (uint32_t j = 0; j < 4096 && !mbar_try(&ctl->full_x[s], 0) && !mbar_try(&ctl->full_x[s], 1); ++j) {}
+                    for (uint32_t j = 0; j < 4096 && !mbar_try(&ctl->full[s], 0) && !mbar_try(&ctl->full[s], 1); ++j) {}
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            uint32_t it = 0, tile_i = 0;
+        // The whole warp runs the loop so that stage counters, descriptors and accumulator addresses are
+        // warp-uniform values; one elected lane issues.  (With the loop under `if (lane == 0)` every operand of
+        // every tcgen05.mma was moved to a uniform register first and two barriers were polled one after the other:
+        // 1100 cycles per k block whatever the tile width, measured - the issuer, not the tensor pipe or the
+        // producers, set the pace of the kernel.)
+        {
+            uint32_t tile_i = 0;
+            int s = 0;
+            uint32_t ph = 0;
             bool ok = true;
+            const bool leader = elect_one();
+            const uint64_t adesc0 = make_desc_sw128(smem_u32(sW)), bdesc0 = make_desc_sw128(smem_u32(sX));
+            const uint32_t a_step = w_stage >> 4, b_step = x_stage >> 4;      // descriptor address units per stage
             for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x, ++tile_i) {
                 const Item item = get_item(p, i);
                 // pairs: both 256-column accumulators belong to one item (no double buffering);
                 // single tiles: the two accumulators alternate so the epilogue overlaps the next item
                 const int buf = p.pair ? 0 : (tile_i & 1);
                 const uint32_t acc_ph = (p.pair ? tile_i : (tile_i >> 1)) & 1;
-                if (!(ok = mbar_wait(&ctl->acc_empty[buf], acc_ph ^ 1, ctl, p.status, 0x201))) break;
+                if (!(ok = mbar_wait_warp(&ctl->acc_empty[buf], acc_ph ^ 1, ctl, p.status, 0x201, 0))) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * TN_MAX;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const int s = it % nst;
-                    const uint32_t ph = (it / nst) & 1;
-                    if (!(ok = mbar_wait(&ctl->full_x[s], ph, ctl, p.status, 0x202))) break;
-                    if (!(ok = mbar_wait(&ctl->full_w[s], ph, ctl, p.status, 0x203))) break;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = mbar_wait_warp(&ctl->full[s], ph, ctl, p.status, 0x202, 0))) break;
                     tc_fence_after();
-                    const uint64_t bdesc = make_desc_sw128(smem_u32(sX + s * x_stage));
-                    for (int t = 0; t < item.nt; ++t) {
-                        const uint64_t adesc = make_desc_sw128(smem_u32(sW + s * w_stage + t * A_BYTES));
+                    if (leader) {
+                        const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * b_step);
+                        for (int t = 0; t < item.nt; ++t) {
+                            const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * a_step + t * (A_BYTES >> 4));
 #pragma unroll
-                        for (int k = 0; k < BK / 16; ++k)   // 16 elements = 32 bytes further along the swizzled row
-                            umma_f16(tmem_d + t * TN_MAX, adesc + 2 * k, bdesc + 2 * k, p.idesc, (kb | k) ? 1u : 0u);
+                            for (int k = 0; k < BK / 16; ++k)   // 16 elements = 32 bytes further along the swizzled row
+                                umma_f16(tmem_d + t * TN_MAX, adesc + 2 * k, bdesc + 2 * k, p.idesc, (kb | k) ? 1u : 0u);
+                        }
+                        umma_commit(&ctl->empty[s]);         // frees the stage when these MMAs have read it
                     }
-                    umma_commit(&ctl->empty[s]);         // frees the stage when these MMAs have read it
+                    __syncwarp();
+                    if (++s == nst) {
+                        s = 0;
+                        ph ^= 1;
+                    }
                 }
-                if (ok) umma_commit(&ctl->acc_full[buf]);
+                if (ok && leader) umma_commit(&ctl->acc_full[buf]);
+                __syncwarp();
             }
         }
     } else if (warp >= EPI_WARP0 && warp < EPI_WARP0 + 4) {
@@ -510,7 +531,8 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
 #pragma unroll
         for (int c = 0; c < 4; ++c)
             dst[c] = smem_u32(sW) + (r >> 3) * 1024 + r7 * 128 + (((h * 4 + c) ^ r7) << 4);
-        uint32_t it = 0;
+        int s = 0;
+        uint32_t ph = 0;                                  // stage and ring-pass parity, advanced without a division
         bool ok = true;
         if (p.raw) {
             // Packed words through shared memory.  A thread that loads its own row's 16 bytes per k block makes
@@ -574,9 +596,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                     if (i_n < num_items) issue(item_n, sb_n, buf ^ 1);
                     asm volatile("cp.async.commit_group;" ::: "memory");
 #pragma unroll
-                    for (int j = 0; j < SB_PER_RAW; ++j, ++it) {
-                        const int s = it % nst;
-                        const uint32_t ph = (it / nst) & 1;
+                    for (int j = 0; j < SB_PER_RAW; ++j) {
                         if (!(ok = mbar_wait_warp(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x401, 0))) break;
                         const int g = (j * BK + h * 32) >> p.gs_shift;       // group within the super-block
 #pragma unroll
@@ -601,7 +621,11 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                         }
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> async proxy (MMA)
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(&ctl->full_w[s]);
+                        if (lane == 0) mbar_arrive(&ctl->full[s]);
+                        if (++s == nst) {
+                            s = 0;
+                            ph ^= 1;
+                        }
                     }
                 }
             }
@@ -637,9 +661,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                 }
             };
             request(0);
-            for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                const int s = it % nst;
-                const uint32_t ph = (it / nst) & 1;
+            for (int kb = 0; kb < num_kb; ++kb) {
                 uint32_t wcur[2][BITS];
                 uint32_t sr[2], br[2];
 #pragma unroll
@@ -667,7 +689,11 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> async proxy (MMA)
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&ctl->full_w[s]);
+                if (lane == 0) mbar_arrive(&ctl->full[s]);
+                if (++s == nst) {
+                    s = 0;
+                    ph ^= 1;
+                }
             }
         }
     }
