@@ -143,6 +143,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=1, help="activation rows per projection (1 or 8)")
     ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--tp", default="megatron", choices=["megatron", "gather"],
+                    help="N > 1: column-parallel q/k/v/gate/up + row-parallel o/down with one all-reduce each "
+                         "(megatron), or every projection N-split with an all-gather per phase (gather)")
     ap.add_argument("--streams", type=int, default=1, help="parallel streams for the independent projections of a phase")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary single-kernel measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
@@ -154,7 +157,8 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     config = {"workload": f"llama3_8b_decode_projections_4bit_g64_bf16_m{args.m}", "layers": args.layers,
               "matrices_per_step": 7 * args.layers, "bits": BITS, "group_size": GROUP, "M": args.m,
-              "sharding": f"n_split_{world}" if world > 1 else "none",
+              "sharding": "none" if world == 1 else (f"tp{world}_column_qkv_gate_up_row_o_down_2_allreduce_per_layer"
+                                                    if args.tp == "megatron" else f"n_split_{world}_allgather_per_phase"),
               "l2": "working set 3.9 GB per step >> 126 MB L2"}
 
     if args.impl == "reference":
@@ -183,41 +187,53 @@ def main():
     ctx = ops.context(dev)
     M = args.m
 
-    # ---- synthetic weights, N-split across ranks ------------------------------------------
+    # ---- synthetic weights, sharded across ranks -------------------------------------------
+    # megatron: phases 0 and 2 (q/k/v, gate/up) are N-split and their outputs stay on the rank that made them (the
+    # attention heads and the SwiGLU that consume them are sharded the same way); phases 1 and 3 (o, down) are
+    # K-split - each rank multiplies its slice of the activations - and summed with one all-reduce each.
+    row_parallel = (lambda phase: world > 1 and args.tp == "megatron" and phase in (1, 3))
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234 + rank)
     layers = []
     for _ in range(args.layers):
         mats = []
         for name, k, n, phase in PROJ:
-            nl = n // world
-            w = torch.randint(-2 ** 31, 2 ** 31 - 1, (nl, k * BITS // 32), dtype=torch.int32, device=dev, generator=gen)
-            sc = (0.002 + 0.018 * torch.rand((nl, k // GROUP), device=dev, generator=gen))
-            bi = -8.0 * sc + 1e-3 * torch.randn((nl, k // GROUP), device=dev, generator=gen)
-            mats.append((w, sc.to(torch.bfloat16), bi.to(torch.bfloat16), k, nl, phase))
+            nl, kl = (n, k // world) if row_parallel(phase) else (n // world, k)
+            w = torch.randint(-2 ** 31, 2 ** 31 - 1, (nl, kl * BITS // 32), dtype=torch.int32, device=dev, generator=gen)
+            sc = (0.002 + 0.018 * torch.rand((nl, kl // GROUP), device=dev, generator=gen))
+            bi = -8.0 * sc + 1e-3 * torch.randn((nl, kl // GROUP), device=dev, generator=gen)
+            mats.append((w, sc.to(torch.bfloat16), bi.to(torch.bfloat16), (k, kl), nl, phase))
         layers.append(mats)
     # activations: one x per distinct K
     xs_host = {k: torch.randn((M, k), generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).pin_memory()
                for k in (4096, 14336)}
-    xs = {k: v.to(dev) for k, v in xs_host.items()}
+    xs_full = {k: v.to(dev) for k, v in xs_host.items()}
+    # (K, local K) -> the activations a projection reads: all of x, or this rank's K slice (a view for M = 1)
+    xs = {}
+    for k in (4096, 14336):
+        xs[(k, k)] = xs_full[k]
+        if world > 1:
+            kl = k // world
+            xs[(k, kl)] = xs_full[k][:, rank * kl:(rank + 1) * kl]
     # per layer, per phase: local output slab [M, sum(nl)] and the gathered buffer [world, M, sum(nl)];
     # all slabs are views of one allocation, so the end-to-end leg reads the step's results back in one copy
-    phase_cols = [sum(n // world for _, _, n, p in PROJ if p == ph) for ph in range(4)]
+    phase_cols = [sum((n if row_parallel(p) else n // world) for _, _, n, p in PROJ if p == ph) for ph in range(4)]
+    gather = world > 1 and args.tp == "gather"
     cols_per_layer = sum(phase_cols)
     local_all = torch.empty(args.layers * M * cols_per_layer, dtype=torch.bfloat16, device=dev)
-    full_all = torch.empty(args.layers * world * M * cols_per_layer, dtype=torch.bfloat16, device=dev) if world > 1 else None
-    out_local, out_full = [], ([] if world > 1 else None)
+    full_all = torch.empty(args.layers * world * M * cols_per_layer, dtype=torch.bfloat16, device=dev) if gather else None
+    out_local, out_full = [], ([] if gather else None)
     lo = fo = 0
     for _ in range(args.layers):
         ll, fl = [], []
         for c in phase_cols:
             ll.append(local_all[lo:lo + M * c].view(M, c))
             lo += M * c
-            if world > 1:
+            if gather:
                 fl.append(full_all[fo:fo + world * M * c].view(world * M, c))
                 fo += world * M * c
         out_local.append(ll)
-        if world > 1:
+        if gather:
             out_full.append(fl)
     # each projection writes its own contiguous [M, nl] tile, then tiles are packed per phase
     tiles = [[torch.empty((M, nl), dtype=torch.bfloat16, device=dev) for (_, _, _, _, nl, _) in mats] for mats in layers]
@@ -244,14 +260,17 @@ def main():
                         if M == 1:   # a [1, nl] slice of the phase slab is contiguous: write in place
                             ops.qmv(w, sc, bi, xs[k], BITS, GROUP, out=out_local[li][ph][:, col:col + nl], ctx=ctx)
                         else:
-                            ops.qmv(w, sc, bi, xs[k], BITS, GROUP, out=tiles[li][pi], ctx=ctx)
+                            xin = xs[k] if xs[k].is_contiguous() else xs[k].contiguous()
+                            ops.qmv(w, sc, bi, xin, BITS, GROUP, out=tiles[li][pi], ctx=ctx)
                             out_local[li][ph][:, col:col + nl].copy_(tiles[li][pi])
                     col += nl
                 for st in set(used):
                     if st is not main:
                         main.wait_stream(st)
-                if world > 1:
+                if gather:
                     dist.all_gather_into_tensor(out_full[li][ph], out_local[li][ph])
+                elif row_parallel(ph):
+                    dist.all_reduce(out_local[li][ph])
 
     launches_per_step = 7 * args.layers
 
@@ -297,7 +316,7 @@ def main():
     value = total_bytes / (ms * 1e-3) / 1e9
 
     # ---- end to end: pinned host activations in, host results out, through the C ABI ---------
-    result_dev = full_all if world > 1 else local_all
+    result_dev = full_all if gather else local_all
     out_host = torch.empty(result_dev.numel(), dtype=torch.bfloat16).pin_memory()
     h2d = sum(v.numel() * 2 for v in xs_host.values())
     d2h = result_dev.numel() * 2
@@ -306,7 +325,7 @@ def main():
 
     def e2e_step():
         for k, v in xs_host.items():
-            lib.mtc_upload(h, stream, xs[k].data_ptr(), v.data_ptr(), v.numel() * 2)
+            lib.mtc_upload(h, stream, xs_full[k].data_ptr(), v.data_ptr(), v.numel() * 2)
         graph.replay()
         lib.mtc_download(h, stream, out_host.data_ptr(), result_dev.data_ptr(), d2h)
         lib.mtc_sync(h, stream)

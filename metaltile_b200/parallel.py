@@ -1,10 +1,15 @@
 """Sharding of the quantized matmuls over the GPUs of one node (one process per GPU).
 
-Two natural splits, each with exactly one exchange step:
+Three natural splits, each with at most one exchange step:
 
 * dense projections — N-split (column parallel): rank g owns the contiguous weight rows
   ``[g*N/G, (g+1)*N/G)`` of ``w``, ``scales`` and ``biases`` (all three are row-of-N major, so no
-  repacking), computes ``out[:, slice]`` and the slices are all-gathered;
+  repacking), computes ``out[:, slice]``; the slices are all-gathered, or stay where they are when the
+  consumer is sharded the same way (attention heads, SwiGLU);
+* dense projections — K-split (row parallel): rank g owns the columns ``[g*K/G, (g+1)*K/G)`` of every row
+  (a contiguous range of packed words and of groups per row, copied out once at load time), multiplies its
+  slice of the activations and the partial outputs are summed with one all-reduce.  A transformer layer then
+  needs two exchanges (after o and after down) instead of one per projection;
 * MoE — expert parallel: rank g owns experts ``[g*E/G, (g+1)*E/G)``; tokens are data parallel; routed
   rows travel to the owner of their expert with an all-to-all, come back with a second one.
 
@@ -83,6 +88,35 @@ class ColumnParallelLinear:
         gathered = flat.view(self.world, m, nl)
         # all-gather yields [G][M][N/G]; row-major [M][N] needs the rank axis next to the columns
         return gathered.permute(1, 0, 2).reshape(m, self.world * nl) if m > 1 else gathered.reshape(1, -1)
+
+
+def shard_cols(w, scales, biases, bits: int, group_size: int, world: int, rank: int):
+    """The K-slice of rank ``rank``: packed words, scales and biases of columns [rank*K/G, (rank+1)*K/G).
+    K/G must be a multiple of the group size and of 32 codes, so that the slice is whole words and groups."""
+    k = w.shape[-1] * 32 // bits
+    if k % world != 0 or (k // world) % group_size != 0 or ((k // world) * bits) % 32 != 0:
+        raise ValueError(f"K = {k} does not split into {world} slices of whole groups and words")
+    kw, kg = (k // world) * bits // 32, (k // world) // group_size
+    return (w[..., rank * kw:(rank + 1) * kw].contiguous(), scales[..., rank * kg:(rank + 1) * kg].contiguous(),
+            biases[..., rank * kg:(rank + 1) * kg].contiguous())
+
+
+class RowParallelLinear:
+    """One K-split quantized projection: local ``w[N, (K/G)*bits/32]``, ``scales``/``biases[N, (K/G)/g]``."""
+
+    def __init__(self, w, scales, biases, bits: int, group_size: int, backend=None, group=None):
+        self.w, self.scales, self.biases = w, scales, biases
+        self.bits, self.group_size = bits, group_size
+        self.backend = backend or CudaBackend()
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+
+    def forward(self, x_local, out=None):
+        """x_local [M, K/G]: this rank's slice of the activations -> out [M, N], summed over the ranks."""
+        y = self.backend.qmv(self.w, self.scales, self.biases, x_local, self.bits, self.group_size, out=out)
+        if self.world > 1:
+            dist.all_reduce(y, group=self.group)
+        return y
 
 
 @dataclass

@@ -78,6 +78,19 @@ def _worker(rank, world, port, q):
         one = lin.forward(torch.from_numpy(x[:1])).numpy()
         assert np.array_equal(one, ref[:1])
 
+        # ---- K-split + all-reduce: each rank multiplies its slice of the columns, partial sums are added
+        n, k, m = 24, 128, 2                       # K / world = 64 = two groups of 32
+        w, s, b = synth.quantized_matrix(n, k, BITS, GS, seed=3)
+        x = synth.activations(m, k, seed=3)
+        wl, sl_, bl = parallel.shard_cols(torch.from_numpy(w.view(np.int32)), torch.from_numpy(s), torch.from_numpy(b),
+                                          BITS, GS, world, rank)
+        row = parallel.RowParallelLinear(wl, sl_, bl, BITS, GS, backend=be)
+        kl = k // world
+        got = row.forward(torch.from_numpy(x[:, rank * kl:(rank + 1) * kl].copy())).numpy()
+        ref = oracle.qmm(w, s, b, x, m, n, k, BITS, GS)
+        # the split changes the order of the f32 additions only: one extra rounding per rank
+        assert got.shape == (m, n) and np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1.0)) <= 1e-5, "row-parallel result differs"
+
         # ---- expert parallel: 8 experts over 2 ranks, 10 tokens per rank, top-2
         E, H, I, T, K2 = 8, 64, 32, 10, 2
         gate, up, down = _moe_weights(E, H, I)
@@ -116,6 +129,21 @@ def test_two_rank_gloo_exchange():
     for p in procs:
         p.join(timeout=30)
     assert sorted(results) == [(0, "ok"), (1, "ok")], results
+
+
+def test_shard_cols():
+    w, s, b = synth.quantized_matrix(6, 256, BITS, GS, seed=4)
+    wt, st, bt = torch.from_numpy(w.view(np.int32)), torch.from_numpy(s), torch.from_numpy(b)
+    parts = [parallel.shard_cols(wt, st, bt, BITS, GS, 4, r) for r in range(4)]
+    assert torch.equal(torch.cat([p_[0] for p_ in parts], dim=1), wt)
+    assert torch.equal(torch.cat([p_[1] for p_ in parts], dim=1), st)
+    assert parts[0][0].shape == (6, 256 // 4 * BITS // 32) and parts[0][1].shape == (6, 2)
+    # the codes of a slice are the slice of the codes
+    full = oracle.unpack_matrix(w, 256, BITS)
+    part = oracle.unpack_matrix(parts[2][0].numpy().view(np.uint32), 64, BITS)
+    assert np.array_equal(part, full[:, 128:192])
+    with pytest.raises(ValueError):
+        parallel.shard_cols(wt, st, bt, BITS, GS, 16, 0)      # 16 columns per rank: less than a group
 
 
 def test_shard_rows_and_order():
