@@ -146,6 +146,7 @@ def main():
     ap.add_argument("--tp", default="megatron", choices=["megatron", "gather"],
                     help="N > 1: column-parallel q/k/v/gate/up + row-parallel o/down with one all-reduce each "
                          "(megatron), or every projection N-split with an all-gather per phase (gather)")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE", help="mtc_set_option before running")
     ap.add_argument("--streams", type=int, default=1, help="parallel streams for the independent projections of a phase")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary single-kernel measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
@@ -185,6 +186,9 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     ctx = ops.context(dev)
+    for item in args.option:
+        name, value = item.split("=")
+        ctx.set_option(name, int(value))
     M = args.m
 
     # ---- synthetic weights, sharded across ranks -------------------------------------------

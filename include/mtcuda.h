@@ -99,6 +99,9 @@ const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dty
  * crates/metaltile-core/src/toolchain/config.rs:11-96).  Options:
  *   "qmm_tile_tokens"  token rows per tensor-core work item (0 = chosen per shape; else a multiple
  *                      of 16 in [16, 256])
+ *   "qmv_max_ctas_per_sm"  > 0 caps the CTAs per SM of the M = 1 kernel's grid (diagnostic; default 0 = 2)
+ *   "qmm_wait_hint_ns" suspend-time hint (ns) of the tensor-core kernel's waits that have slack: the TMA producer and the
+ *                      epilogue warps (default 5000; 0 = plain polling)
  *   "qmv_small_m_mma"  0: keep 2 <= M <= 16 on the CUDA-core kernel (default 1: 4-bit codes with f16/bf16
  *                      activations and a group that is a multiple of 64 use the warp-level tensor cores);
  *                      2: M = 1 takes that path too (same results within round-off; not faster on B200)

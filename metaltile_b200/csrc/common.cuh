@@ -23,6 +23,7 @@ struct Ctx {
     void *d_scratch = nullptr;     // grow-only scratch owned by the context
     size_t scratch_bytes = 0;
     int qmm_force_tn = 0;          // option "qmm_tile_tokens": 0 = choose per shape
+    int qmv_max_occ = 0;           // option "qmv_max_ctas_per_sm": > 0 caps the CTAs per SM of the qmv kernel's grid
     int qmv_small_m_mma = 1;       // option "qmv_small_m_mma": 0 keeps 2 <= M <= 16 on the CUDA-core kernel
     int qmm_max_stages = 0;        // option "qmm_max_stages": > 0 caps the ring depth (diagnostic: how much the ring hides)
     int qmm_wait_hint_ns = 5000;      // option "qmm_wait_hint_ns": base suspend-time hint of the kernel's mbarrier waits

@@ -506,6 +506,7 @@ cudaError_t launch_pipe(Ctx *ctx, cudaStream_t st, QmvArgs a, size_t per_jb, siz
     if (e != cudaSuccess) return e;
     if (occ < 1) occ = 1;
     if (occ > 2) occ = 2;
+    if (ctx->qmv_max_occ > 0 && occ > ctx->qmv_max_occ) occ = ctx->qmv_max_occ;
     // split K over the warps of a CTA until the resident warp slots (occ CTAs of kWarps per SM) are used
     int ks = 1;
     while (ks < kWarps && a.groups * ks * 2 <= sms * occ * kWarps && a.njb % (ks * 2) == 0) ks *= 2;

@@ -324,6 +324,10 @@ int mtc_set_option(mtc_ctx *ctx, const char *name, int value) {
         ctx->qmm_force_tn = value;
         return MTC_OK;
     }
+    if (std::strcmp(name, "qmv_max_ctas_per_sm") == 0) {
+        ctx->qmv_max_occ = value < 0 ? 0 : value;
+        return MTC_OK;
+    }
     if (std::strcmp(name, "qmv_small_m_mma") == 0) {
         ctx->qmv_small_m_mma = value < 0 ? 0 : (value > 2 ? 2 : value);
         return MTC_OK;

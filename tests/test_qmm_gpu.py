@@ -107,6 +107,58 @@ def test_linearity_and_row_independence_at_full_size(ctx):
     assert rel_err(full[:4].float().cpu().numpy(), few.float().cpu().numpy()) <= TOL[dt]
 
 
+@pytest.mark.parametrize("bits,dt", [(4, "f16"), (8, "bf16")])
+def test_tiny_and_mixed_scales(ctx, bits, dt):
+    """4- and 8-bit codes are dequantised in packed-half arithmetic only when the scale is a normal f16 number;
+    groups with scales below 2^-14 (here 1e-7 .. 1e-5, mixed with ordinary ones) take the f32 path."""
+    m, n, k, gs = 96, 160, 512, 64
+    w, s, b, x = dense_case(m, n, k, bits, gs, dt, seed=12, salt=bits)
+    rng = np.random.default_rng(12)
+    tiny = rng.random(s.shape) < 0.5
+    s = np.where(tiny, (10.0 ** rng.uniform(-7, -5, s.shape)), s).astype(np.float32)
+    s = oracle.round_through(s, oracle.BF16 if dt == "bf16" else oracle.F16)
+    ref = oracle.qmm(w, s, b, x, m, n, k, bits, gs)
+    got = run_qmm(w, s, b, x, bits, gs, dt)
+    assert rel_err(got, ref) <= TOL[dt]
+    assert ctx.status_word() == 0
+
+
+@pytest.mark.parametrize("m,n,k,bits,gs", [(300, 304, 1024, 4, 64), (130, 288, 768, 3, 32), (64, 200, 512, 8, 128)])
+def test_loader_and_wait_options_do_not_change_results(ctx, m, n, k, bits, gs):
+    """The packed words reach the dequant warps through shared-memory staging buffers or straight from global
+    memory, and the waits poll with or without a suspend-time hint: same arithmetic, bit-identical output."""
+    import torch
+    from metaltile_b200 import ops
+    dt = "bf16"
+    w, s, b, x = dense_case(m, n, k, bits, gs, dt, seed=13, salt=k)
+    args = (to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt), bits, gs)
+    base = ops.qmm(*args)
+    outs = []
+    try:
+        for name, value in (("qmm_raw", 0), ("qmm_wait_hint_ns", 0), ("qmm_max_stages", 2)):
+            ctx.set_option(name, value)
+            outs.append(ops.qmm(*args))
+            ctx.set_option(name, {"qmm_raw": 1, "qmm_wait_hint_ns": 5000, "qmm_max_stages": 0}[name])
+    finally:
+        ctx.set_option("qmm_raw", 1)
+        ctx.set_option("qmm_wait_hint_ns", 5000)
+        ctx.set_option("qmm_max_stages", 0)
+    torch.cuda.synchronize()
+    for o in outs:
+        assert torch.equal(o, base)
+    ref = oracle.qmm(w, s, b, x, m, n, k, bits, gs)
+    assert rel_err(base.float().cpu().numpy(), ref) <= TOL[dt]
+    assert ctx.status_word() == 0
+
+
+def test_k_not_a_multiple_of_256(ctx):
+    """K = 320: no whole raw super-block, so the dequant warps load straight from global memory."""
+    m, n, k, bits, gs, dt = 100, 136, 320, 4, 64, "f16"
+    w, s, b, x = dense_case(m, n, k, bits, gs, dt, seed=14)
+    ref = oracle.qmm(w, s, b, x, m, n, k, bits, gs)
+    assert rel_err(run_qmm(w, s, b, x, bits, gs, dt), ref) <= TOL[dt]
+
+
 def test_paired_weight_tiles_option(ctx):
     """"qmm_pair" = 1: one activation stage feeds two weight-row tiles; same numbers as the default."""
     import torch
