@@ -143,9 +143,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=1, help="activation rows per projection (1 or 8)")
     ap.add_argument("--layers", type=int, default=LAYERS)
-    ap.add_argument("--tp", default="megatron", choices=["megatron", "gather"],
-                    help="N > 1: column-parallel q/k/v/gate/up + row-parallel o/down with one all-reduce each "
-                         "(megatron), or every projection N-split with an all-gather per phase (gather)")
+    ap.add_argument("--tp", default="gather", choices=["gather", "megatron"],
+                    help="N > 1: every projection N-split with an all-gather of the outputs per dependent phase (gather, "
+                         "the configuration the metric is quoted on), or column-parallel q/k/v/gate/up + row-parallel "
+                         "o/down with one all-reduce each (megatron)")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE", help="mtc_set_option before running")
     ap.add_argument("--streams", type=int, default=1, help="parallel streams for the independent projections of a phase")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary single-kernel measurements")
