@@ -147,6 +147,10 @@ def main():
                     help="N > 1: every projection N-split with an all-gather of the outputs per dependent phase (gather, "
                          "the configuration the metric is quoted on), or column-parallel q/k/v/gate/up + row-parallel "
                          "o/down with one all-reduce each (megatron)")
+    ap.add_argument("--collective", default="nccl", choices=["nccl", "p2p"],
+                    help="N > 1, --tp gather, M = 1: all-gather with NCCL, or by the qmv kernels' own stores into every "
+                         "rank's buffer (cudaIpc peer mappings) and a one-warp barrier kernel per phase")
+    ap.add_argument("--verify", action="store_true", help="N > 1: check the p2p gather against the NCCL all-gather once")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE", help="mtc_set_option before running")
     ap.add_argument("--streams", type=int, default=1, help="parallel streams for the independent projections of a phase")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary single-kernel measurements")
@@ -162,6 +166,8 @@ def main():
               "sharding": "none" if world == 1 else (f"tp{world}_column_qkv_gate_up_row_o_down_2_allreduce_per_layer"
                                                     if args.tp == "megatron" else f"n_split_{world}_allgather_per_phase"),
               "l2": "working set 3.9 GB per step >> 126 MB L2"}
+    if world > 1:
+        config["collective"] = args.collective if (args.tp == "gather" and args.m == 1) else "nccl"
 
     if args.impl == "reference":
         if rank != 0:
@@ -226,8 +232,16 @@ def main():
     gather = world > 1 and args.tp == "gather"
     cols_per_layer = sum(phase_cols)
     local_all = torch.empty(args.layers * M * cols_per_layer, dtype=torch.bfloat16, device=dev)
-    full_all = torch.empty(args.layers * world * M * cols_per_layer, dtype=torch.bfloat16, device=dev) if gather else None
+    p2p = gather and args.collective == "p2p" and M == 1
+    peer = None
+    if p2p:
+        from metaltile_b200.parallel import PeerGather
+        peer = PeerGather(ctx, args.layers * world * M * cols_per_layer * 2)
+        full_all = peer.tensor(torch.bfloat16)
+    else:
+        full_all = torch.empty(args.layers * world * M * cols_per_layer, dtype=torch.bfloat16, device=dev) if gather else None
     out_local, out_full = [], ([] if gather else None)
+    full_off = []                                  # element offset of every (layer, phase) gathered block
     lo = fo = 0
     for _ in range(args.layers):
         ll, fl = [], []
@@ -236,6 +250,7 @@ def main():
             lo += M * c
             if gather:
                 fl.append(full_all[fo:fo + world * M * c].view(world * M, c))
+                full_off.append(fo)
                 fo += world * M * c
         out_local.append(ll)
         if gather:
@@ -262,7 +277,11 @@ def main():
                         st.wait_stream(main)
                     used.append(st)
                     with torch.cuda.stream(st):
-                        if M == 1:   # a [1, nl] slice of the phase slab is contiguous: write in place
+                        if p2p:      # this rank's slot of the gathered block, in every rank's buffer
+                            c = phase_cols[ph]
+                            off = (full_off[li * 4 + ph] + rank * M * c + col) * 2
+                            peer.qmv_into(w, sc, bi, xs[k], BITS, GROUP, off, st.cuda_stream)
+                        elif M == 1:   # a [1, nl] slice of the phase slab is contiguous: write in place
                             ops.qmv(w, sc, bi, xs[k], BITS, GROUP, out=out_local[li][ph][:, col:col + nl], ctx=ctx)
                         else:
                             xin = xs[k] if xs[k].is_contiguous() else xs[k].contiguous()
@@ -272,7 +291,9 @@ def main():
                 for st in set(used):
                     if st is not main:
                         main.wait_stream(st)
-                if gather:
+                if p2p:
+                    peer.barrier(main.cuda_stream)
+                elif gather:
                     dist.all_gather_into_tensor(out_full[li][ph], out_local[li][ph])
                 elif row_parallel(ph):
                     dist.all_reduce(out_local[li][ph])
@@ -287,6 +308,26 @@ def main():
             step()
     torch.cuda.current_stream().wait_stream(side)
     torch.cuda.synchronize()
+    if p2p and args.verify:
+        # the blocks the kernels' own stores assembled must equal an NCCL all-gather of the same projections
+        dist.barrier()
+        bad = 0
+        for li in (0, args.layers - 1):
+            for ph in range(4):
+                c, col = phase_cols[ph], 0
+                loc = torch.empty((M, c), dtype=torch.bfloat16, device=dev)
+                for (w, sc, bi, k, nl, phase) in layers[li]:
+                    if phase == ph:
+                        ops.qmv(w, sc, bi, xs[k], BITS, GROUP, out=loc[:, col:col + nl], ctx=ctx)
+                        col += nl
+                ref = torch.empty((world * M, c), dtype=torch.bfloat16, device=dev)
+                dist.all_gather_into_tensor(ref, loc)
+                bad += int(not torch.equal(ref, out_full[li][ph]))
+        torch.cuda.synchronize()
+        print(f"[rank {rank}] p2p gather vs NCCL all-gather: {'identical' if bad == 0 else str(bad) + ' blocks differ'}; "
+              f"status word {ctx.status_word():#x}", file=sys.stderr, flush=True)
+        if bad or ctx.status_word():
+            raise SystemExit("p2p gather failed verification")
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph):
         step()
@@ -366,7 +407,7 @@ def main():
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config, "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms},
-            "gpu_launches": launches_per_step * args.steps, "roofline": roofline}
+            "gpu_launches": (launches_per_step + (4 * args.layers if p2p else 0)) * args.steps, "roofline": roofline}
 
     if not args.no_extra:
         try:

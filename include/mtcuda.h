@@ -94,6 +94,28 @@ int mtc_qmm(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
  * mt_qmm_for's routing (quantized.rs:5127-5199). */
 const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dtype);
 
+/* ---- sharded decode: the output all-gather done by the kernel's own stores (one process per GPU) ----
+ * None of these has a counterpart in the reference, which is a single-device library; they serve the N-split
+ * (column-parallel) sharding of a projection over the GPUs of one node.
+ *
+ * mtc_qmv_multi: mtc_qmv that writes its [M, N] output tile to outs[0..n_outs) (1 to 8 destinations, same layout
+ * and dtype each).  With outs[i] = rank i's copy of the gathered buffer, offset to this rank's slot, the all-gather
+ * is the store.  Vectorised CUDA-core path only (power-of-two group, aligned pointers), any M.
+ * mtc_ipc_export / mtc_ipc_open / mtc_ipc_close: share a buffer from mtc_alloc with the other rank processes
+ * (cudaIpc handle, 64 bytes; opening enables peer access; plain peer mappings, no multicast object).
+ * mtc_peer_barrier: enqueue a one-warp kernel that tells every peer "my stores so far are done" and waits until
+ * every peer has said the same.  peer_flags[p] = rank p's flag array (8 x uint32, zeroed once, shared with
+ * mtc_ipc_*), local_flags = this rank's own array, epoch = one uint32 of this rank's memory, zeroed once; every rank
+ * must enqueue the same sequence of barriers.  The wait is bounded (a few seconds): on expiry the status word becomes
+ * 0x601 + the rank that never arrived and the kernel returns. */
+int mtc_qmv_multi(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x,
+                  void *const *outs, int n_outs, int M, int N, int K, int bits, int group_size, int dtype);
+int mtc_ipc_export(mtc_ctx *ctx, void *d_ptr, void *handle64);
+int mtc_ipc_open(mtc_ctx *ctx, const void *handle64, void **d_ptr);
+int mtc_ipc_close(mtc_ctx *ctx, void *d_ptr);
+int mtc_peer_barrier(mtc_ctx *ctx, void *stream, void *const *peer_flags, int n_peers, int rank, void *local_flags,
+                     void *epoch);
+
 /* Tuning knobs of the back end, the counterpart of the reference's per-kernel MslConfig /
  * TileConfig switches (crates/metaltile-codegen/src/msl/config.rs:27-96,
  * crates/metaltile-core/src/toolchain/config.rs:11-96).  Options:

@@ -44,6 +44,11 @@ SIGNATURES = {
     "mtc_qmv": (_i, _DENSE),
     "mtc_qmm": (_i, _DENSE),
     "mtc_qmm_route": (ctypes.c_char_p, [_i, _i, _i, _i, _i, _i]),
+    "mtc_qmv_multi": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i]),
+    "mtc_ipc_export": (_i, [_vp, _vp, _vp]),
+    "mtc_ipc_open": (_i, [_vp, _vp, ctypes.POINTER(_vp)]),
+    "mtc_ipc_close": (_i, [_vp, _vp]),
+    "mtc_peer_barrier": (_i, [_vp, _vp, ctypes.POINTER(_vp), _i, _i, _vp, _vp]),
     "mtc_gather_qmm": (_i, [_vp] * 9 + [_i] * 7),
     "mtc_gather_qmm_static": (_i, [_vp] * 9 + [_i] * 7),
     "mtc_gather_qmm_route": (ctypes.c_char_p, [_i] * 6),

@@ -130,6 +130,41 @@ class Context:
         self._check(self._lib.mtc_qmv(self._h, stream, w, scales, biases, x, out, M, N, K, bits, group_size,
                                       _dt(dtype)))
 
+    def qmv_multi(self, w, scales, biases, x, outs, M, N, K, bits, group_size, dtype, stream: int = 0):
+        """qmv whose output tile is stored to every pointer of ``outs`` (1 to 8)."""
+        arr = (ctypes.c_void_p * len(outs))(*[int(o) for o in outs])
+        self._check(self._lib.mtc_qmv_multi(self._h, stream, w, scales, biases, x, arr, len(outs), M, N, K, bits,
+                                            group_size, _dt(dtype)))
+
+    # ---- buffers shared between the rank processes of one node --------------------
+    def alloc(self, nbytes: int) -> int:
+        p = ctypes.c_void_p()
+        self._check(self._lib.mtc_alloc(self._h, nbytes, ctypes.byref(p)))
+        return int(p.value)
+
+    def free(self, ptr: int):
+        self._check(self._lib.mtc_free(self._h, ptr))
+
+    def memset(self, ptr: int, value: int, nbytes: int, stream: int = 0):
+        self._check(self._lib.mtc_memset(self._h, stream, ptr, value, nbytes))
+
+    def ipc_export(self, ptr: int) -> bytes:
+        h = ctypes.create_string_buffer(64)
+        self._check(self._lib.mtc_ipc_export(self._h, ptr, h))
+        return h.raw
+
+    def ipc_open(self, handle: bytes) -> int:
+        p = ctypes.c_void_p()
+        self._check(self._lib.mtc_ipc_open(self._h, ctypes.create_string_buffer(handle, 64), ctypes.byref(p)))
+        return int(p.value)
+
+    def ipc_close(self, ptr: int):
+        self._check(self._lib.mtc_ipc_close(self._h, ptr))
+
+    def peer_barrier(self, peer_flags, rank: int, local_flags: int, epoch: int, stream: int = 0):
+        arr = (ctypes.c_void_p * len(peer_flags))(*[int(p) for p in peer_flags])
+        self._check(self._lib.mtc_peer_barrier(self._h, stream, arr, len(peer_flags), rank, local_flags, epoch))
+
     def qmm(self, w, scales, biases, x, out, M, N, K, bits, group_size, dtype, stream: int = 0):
         self._check(self._lib.mtc_qmm(self._h, stream, w, scales, biases, x, out, M, N, K, bits, group_size,
                                       _dt(dtype)))

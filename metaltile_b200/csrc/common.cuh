@@ -76,7 +76,10 @@ __device__ __forceinline__ uint32_t code_at(const uint32_t *row, uint32_t k, int
 // Launchers implemented per .cu file; all return cudaError_t from the launch.
 cudaError_t launch_qmv(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases,
                        const void *x, void *out, int M, int N, int K, int bits, int group_size, int dt,
-                       std::string *why);
+                       std::string *why, void *const *extra_outs = nullptr, int n_extra = 0);
+// all ranks have stored: one flag per peer, written with system-scope release, awaited with a bounded poll
+cudaError_t launch_peer_barrier(Ctx *ctx, cudaStream_t st, uint32_t *const *peer_flags, int n_peers, int rank,
+                                uint32_t *local_flags, uint32_t *epoch);
 cudaError_t qmv_init_device();
 bool qmv_mma_supported(int M, int N, int K, int bits, int group_size, int dt, const void *w, const void *x);
 cudaError_t launch_qmv_mma(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases, const void *x,

@@ -1,0 +1,66 @@
+// Cross-GPU hand-off for the sharded decode path: the all-gather of an N-split projection is done by the qmv
+// kernel itself (it stores its output tile into every rank's buffer through peer mappings, see QmvArgs::extra),
+// and this barrier tells every rank that all tiles of a phase have landed.  One process per GPU; the buffers and
+// the flag arrays are plain cudaMalloc memory shared with cudaIpc handles (no multicast objects involved).
+// The reference is a single-device library and has no counterpart.
+#include "common.cuh"
+
+namespace mtc {
+namespace {
+
+constexpr int kMaxPeersB = 8;
+constexpr uint32_t kPollLimit = 1u << 22;     // bounded wait: a few seconds, then the status word says so
+
+struct BarrierArgs {
+    uint32_t *peer_flags[kMaxPeersB];   // peer p's flag array (kMaxPeersB words), mapped into this process
+    uint32_t *local_flags;              // this rank's own array: word p is written by rank p
+    uint32_t *epoch;                    // this rank's barrier counter (the same sequence on every rank)
+    uint32_t *status;
+    int n_peers, rank;
+};
+
+// <<<1, 32>>>.  Stream order guarantees that the kernels before this one (the stores into the peers' buffers) have
+// completed; the flag is written with a system-scope release after a system fence and read with an acquire.
+__global__ void peer_barrier_kernel(const BarrierArgs a) {
+    const int p = threadIdx.x;
+    const uint32_t e = *a.epoch + 1u;
+    if (p < a.n_peers) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.peer_flags[p] + a.rank), "r"(e) : "memory");
+        bool seen = false;
+        for (uint32_t i = 0; i < kPollLimit; ++i) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.local_flags + p) : "memory");
+            if (static_cast<int32_t>(v - e) >= 0) {
+                seen = true;
+                break;
+            }
+            __nanosleep(64);
+        }
+        if (!seen) atomicCAS(a.status, 0u, 0x601u + static_cast<uint32_t>(p));     // rank p never arrived
+    }
+    __syncwarp();
+    if (p == 0) *a.epoch = e;
+}
+
+}  // namespace
+
+cudaError_t launch_peer_barrier(Ctx *ctx, cudaStream_t st, uint32_t *const *peer_flags, int n_peers, int rank,
+                                uint32_t *local_flags, uint32_t *epoch) {
+    if (n_peers < 1 || n_peers > kMaxPeersB || rank < 0 || rank >= n_peers || !peer_flags || !local_flags || !epoch)
+        return cudaErrorInvalidValue;
+    BarrierArgs a{};
+    for (int p = 0; p < n_peers; ++p) {
+        if (!peer_flags[p]) return cudaErrorInvalidValue;
+        a.peer_flags[p] = peer_flags[p];
+    }
+    a.local_flags = local_flags;
+    a.epoch = epoch;
+    a.status = ctx->d_status;
+    a.n_peers = n_peers;
+    a.rank = rank;
+    peer_barrier_kernel<<<1, 32, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace mtc

@@ -42,6 +42,8 @@ struct Pack {
 
 constexpr int kPreExp = 64;  // x is staged as x * 2^(kPreExp - p)
 
+constexpr int kMaxPeers = 8;
+
 struct QmvArgs {
     const uint32_t *w;
     const void *scales, *biases, *x;
@@ -54,6 +56,8 @@ struct QmvArgs {
     int ksplit;        // warps sharing one row group
     int groups, iters; // row groups (ceil(N/R)), row-group iterations per CTA slot
     int gpc;           // consecutive row groups owned by one CTA (its weights are one contiguous range)
+    int n_extra;       // further copies of the output tile (peer GPUs' buffers: the all-gather is the store)
+    void *extra[kMaxPeers - 1];
 };
 
 template <int WORDS>
@@ -252,7 +256,11 @@ __device__ __forceinline__ void reduce_store(const QmvArgs &a, float (&acc)[R][M
             if (n0 + r < a.N) {
 #pragma unroll
                 for (int m = 0; m < MT; ++m)
-                    if (m < a.M) st_from_f32(a.out, static_cast<size_t>(m) * a.N + n0 + r, acc[r][m], a.dt);
+                    if (m < a.M) {
+                        st_from_f32(a.out, static_cast<size_t>(m) * a.N + n0 + r, acc[r][m], a.dt);
+                        for (int e = 0; e < a.n_extra; ++e)
+                            st_from_f32(a.extra[e], static_cast<size_t>(m) * a.N + n0 + r, acc[r][m], a.dt);
+                    }
             }
         }
     }
@@ -605,7 +613,11 @@ cudaError_t qmv_init_device() {
 
 cudaError_t launch_qmv(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases,
                        const void *x, void *out, int M, int N, int K, int bits, int group_size, int dt,
-                       std::string *why) {
+                       std::string *why, void *const *extra_outs, int n_extra) {
+    if (n_extra < 0 || n_extra > kMaxPeers - 1 || (n_extra > 0 && !extra_outs)) {
+        if (why) *why = "qmv: at most 8 output copies";
+        return cudaErrorInvalidValue;
+    }
     const bool bits_ok = bits == 2 || bits == 3 || bits == 4 || bits == 5 || bits == 6 || bits == 8;
     if (!bits_ok || M < 0 || N < 0 || K <= 0 || group_size <= 0 || K % group_size != 0 ||
         (static_cast<long long>(K) * bits) % 32 != 0) {
@@ -620,6 +632,10 @@ cudaError_t launch_qmv(Ctx *ctx, cudaStream_t st, const void *w, const void *sca
     const bool fast = pow2 && K % codes == 0 && group_size % codes == 0 && aligned(w, 16) && aligned(x, 16) &&
                       (static_cast<size_t>(K) * esz) % 16 == 0 && aligned(scales, esz) && aligned(biases, esz) &&
                       (static_cast<size_t>(K) * bits / 8) % (bits == 2 ? 8 : (bits == 4 || bits == 8) ? 16 : 4) == 0;
+    if (!fast && n_extra > 0) {
+        if (why) *why = "qmv with several outputs needs the vectorised path (power-of-two group, aligned pointers)";
+        return cudaErrorInvalidValue;
+    }
     if (!fast) {
         const int wpb = 8;
         qmv_generic_kernel<<<(N + wpb - 1) / wpb, wpb * 32, 0, st>>>(
@@ -633,6 +649,8 @@ cudaError_t launch_qmv(Ctx *ctx, cudaStream_t st, const void *w, const void *sca
         a.biases = biases;
         a.x = static_cast<const char *>(x) + static_cast<size_t>(m0) * K * esz;
         a.out = static_cast<char *>(out) + static_cast<size_t>(m0) * N * esz;
+        a.n_extra = n_extra;
+        for (int e = 0; e < n_extra; ++e) a.extra[e] = static_cast<char *>(extra_outs[e]) + static_cast<size_t>(m0) * N * esz;
         a.M = M - m0 < 16 ? M - m0 : 16;
         a.N = N;
         a.K = K;

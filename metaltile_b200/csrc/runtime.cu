@@ -289,6 +289,54 @@ int mtc_qmv(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
     return MTC_OK;
 }
 
+int mtc_qmv_multi(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x,
+                  void *const *outs, int n_outs, int M, int N, int K, int bits, int group_size, int dtype) {
+    if (!ctx) return MTC_ERR_INVALID;
+    if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "qmv_multi: dtype must be f32, f16 or bf16");
+    if (!outs || n_outs < 1 || n_outs > 8) return fail(ctx, MTC_ERR_INVALID, "qmv_multi: 1 to 8 outputs");
+    for (int i = 0; i < n_outs; ++i)
+        if (!outs[i]) return fail(ctx, MTC_ERR_INVALID, "qmv_multi: null output");
+    if (M > 0 && N > 0 && (!w || !scales || !biases || !x)) return fail(ctx, MTC_ERR_INVALID, "qmv_multi: null pointer");
+    std::string why;
+    cudaError_t e = mtc::launch_qmv(ctx, static_cast<cudaStream_t>(stream), w, scales, biases, x, outs[0], M, N, K, bits,
+                                    group_size, dtype, &why, outs + 1, n_outs - 1);
+    if (e == cudaErrorInvalidValue && !why.empty()) return fail(ctx, MTC_ERR_UNSUPPORTED, why);
+    if (e != cudaSuccess) return fail(ctx, MTC_ERR_DISPATCH, std::string("qmv_multi launch: ") + cudaGetErrorString(e));
+    return MTC_OK;
+}
+
+int mtc_ipc_export(mtc_ctx *ctx, void *d_ptr, void *handle64) {
+    if (!ctx || !d_ptr || !handle64) return fail(ctx, MTC_ERR_INVALID, "ipc_export: null pointer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    MTC_CUDA(ctx, cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t *>(handle64), d_ptr), MTC_ERR_BUFFER);
+    return MTC_OK;
+}
+
+int mtc_ipc_open(mtc_ctx *ctx, const void *handle64, void **d_ptr) {
+    if (!ctx || !handle64 || !d_ptr) return fail(ctx, MTC_ERR_INVALID, "ipc_open: null pointer");
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle64, sizeof(h));
+    MTC_CUDA(ctx, cudaIpcOpenMemHandle(d_ptr, h, cudaIpcMemLazyEnablePeerAccess), MTC_ERR_BUFFER);
+    return MTC_OK;
+}
+
+int mtc_ipc_close(mtc_ctx *ctx, void *d_ptr) {
+    if (!ctx || !d_ptr) return fail(ctx, MTC_ERR_INVALID, "ipc_close: null pointer");
+    MTC_CUDA(ctx, cudaIpcCloseMemHandle(d_ptr), MTC_ERR_BUFFER);
+    return MTC_OK;
+}
+
+int mtc_peer_barrier(mtc_ctx *ctx, void *stream, void *const *peer_flags, int n_peers, int rank, void *local_flags,
+                     void *epoch) {
+    if (!ctx) return MTC_ERR_INVALID;
+    cudaError_t e = mtc::launch_peer_barrier(ctx, static_cast<cudaStream_t>(stream),
+                                             reinterpret_cast<uint32_t *const *>(peer_flags), n_peers, rank,
+                                             static_cast<uint32_t *>(local_flags), static_cast<uint32_t *>(epoch));
+    if (e == cudaErrorInvalidValue) return fail(ctx, MTC_ERR_INVALID, "peer_barrier: 1 to 8 peers, rank < peers, no null pointer");
+    if (e != cudaSuccess) return fail(ctx, MTC_ERR_DISPATCH, std::string("peer_barrier launch: ") + cudaGetErrorString(e));
+    return MTC_OK;
+}
+
 // mt_qmm_for (crates/metaltile-std/src/mlx/quantized.rs:5040-5065) picks by M alone; here M <= 16 or
 // f32 activations stay on the qmv kernels (CUDA cores, or warp-level MMAs for 2 <= M <= 16 with 4-bit codes), everything else goes to the tensor cores when the
 // shape meets that kernel's contract (K % 64 == 0, power-of-two group >= 32).

@@ -119,6 +119,67 @@ class RowParallelLinear:
         return y
 
 
+class _RawCuda:
+    """Adapter that lets torch wrap memory the library allocated (``__cuda_array_interface__``)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerGather:
+    """A gathered-output buffer that every rank's kernels store into directly (one process per GPU).
+
+    Each rank allocates ``nbytes`` plus a flag block with the library (plain device memory), the ranks exchange
+    cudaIpc handles over ``torch.distributed`` and map each other's blocks.  ``qmv_into`` then runs a projection whose
+    output tile lands in every rank's buffer at the same byte offset, and ``barrier`` enqueues the one-warp kernel that
+    makes a phase's tiles visible everywhere - the N-split all-gather without a collective launch.  The waits inside
+    are bounded; ``ctx.status_word()`` reports a rank that never arrived (0x601 + rank)."""
+
+    def __init__(self, ctx, nbytes: int, group=None):
+        self.ctx, self.group, self.nbytes = ctx, group, nbytes
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("at most 8 ranks")
+        self.buf = ctx.alloc(nbytes)
+        self.flags = ctx.alloc(256)                       # 8 flag words, then (at +128) the epoch counter
+        ctx.memset(self.buf, 0, nbytes)
+        ctx.memset(self.flags, 0, 256)
+        ctx.sync()
+        mine = (ctx.ipc_export(self.buf), ctx.ipc_export(self.flags))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, mine, group=group)
+        self.peer_bufs, self.peer_flags = [], []
+        for r, (hb, hf) in enumerate(handles):
+            self.peer_bufs.append(self.buf if r == self.rank else ctx.ipc_open(hb))
+            self.peer_flags.append(self.flags if r == self.rank else ctx.ipc_open(hf))
+        dist.barrier(group=group)
+
+    def tensor(self, dtype=torch.bfloat16):
+        """The local buffer as a flat tensor of ``dtype``."""
+        return torch.as_tensor(_RawCuda(self.buf, self.nbytes), device="cuda").view(dtype)
+
+    def qmv_into(self, w, scales, biases, x, bits, group_size, byte_offset: int, stream: int):
+        """out tile [M, N_local] of this rank -> every rank's buffer at ``byte_offset``."""
+        from .ops import _TORCH_DT
+        m, k = x.shape
+        n = w.shape[0]
+        outs = [self.peer_bufs[self.rank] + byte_offset] + [p + byte_offset for r, p in enumerate(self.peer_bufs) if r != self.rank]
+        self.ctx.qmv_multi(w.data_ptr(), scales.data_ptr(), biases.data_ptr(), x.data_ptr(), outs, m, n, k, bits,
+                           group_size, _TORCH_DT[x.dtype], stream=stream)
+
+    def barrier(self, stream: int):
+        self.ctx.peer_barrier(self.peer_flags, self.rank, self.flags, self.flags + 128, stream=stream)
+
+    def close(self):
+        """Unmap the peers' blocks and free the own ones; every rank calls it after a ``dist.barrier``."""
+        for r in range(self.world):
+            if r != self.rank:
+                self.ctx.ipc_close(self.peer_bufs[r])
+                self.ctx.ipc_close(self.peer_flags[r])
+        self.ctx.free(self.buf)
+        self.ctx.free(self.flags)
+
+
 @dataclass
 class ExpertShard:
     """The experts a rank owns: gate / up [E_l, I, H*bits/32], down [E_l, H, I*bits/32] (+ scales, biases)."""

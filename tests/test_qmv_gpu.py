@@ -194,6 +194,33 @@ def test_small_m_tensor_core_exact_integers(ctx):
     assert np.array_equal(got, oracle.round_through(ref, oracle.F16))
 
 
+def test_multi_output_store_and_single_rank_barrier(ctx):
+    """mtc_qmv_multi writes the same tile to every destination (the sharded path's all-gather is these stores);
+    with one rank the barrier kernel only meets its own flag, raises the epoch and leaves the status word clear."""
+    import torch
+    from metaltile_b200.ops import _TORCH_DT
+    for m, n, k, dt in [(1, 1024, 4096, "bf16"), (3, 200, 512, "f32")]:
+        w, s, b, x = dense_case(m, n, k, 4, 64, dt, seed=15, salt=n)
+        wd, sd, bd, xd = to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt)
+        outs = [torch.zeros((m, n), dtype=xd.dtype, device="cuda") for _ in range(3)]
+        ctx.qmv_multi(wd.data_ptr(), sd.data_ptr(), bd.data_ptr(), xd.data_ptr(), [o.data_ptr() for o in outs], m, n, k, 4, 64,
+                      _TORCH_DT[xd.dtype], stream=torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        ref = oracle.qmm(w, s, b, x, m, n, k, 4, 64)
+        assert rel_err(outs[0].float().cpu().numpy(), ref) <= TOL[dt]
+        assert torch.equal(outs[1], outs[0]) and torch.equal(outs[2], outs[0])
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    for _ in range(3):
+        ctx.peer_barrier([flags.data_ptr()], 0, flags.data_ptr(), flags.data_ptr() + 128, stream=st)
+    torch.cuda.synchronize()
+    assert int(flags[0]) == 3 and int(flags[32]) == 3          # own flag word and the epoch counter
+    assert ctx.status_word() == 0
+    from metaltile_b200 import MetalTileError
+    with pytest.raises(MetalTileError):
+        ctx.peer_barrier([flags.data_ptr()] * 9, 0, flags.data_ptr(), flags.data_ptr() + 128, stream=st)
+
+
 def test_generic_fallback_paths(ctx):
     """Group sizes below the chunk and unaligned pointers take the any-shape kernel."""
     import torch
