@@ -130,6 +130,39 @@ def cpu_reference_arm(args):
     return nbytes / dt / 1e9, dt * 1e3, threads, f"{layers} of {LAYERS} layers ({len(mats)} matrices) per step"
 
 
+def p2p_trial(ctx, dev, rank, world):
+    """One small projection gathered through peer stores + barrier, compared with NCCL; every rank must agree."""
+    ok = 1
+    try:
+        from metaltile_b200.parallel import PeerGather
+        nl, k = 256, 512
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(99 + rank)
+        w = torch.randint(-2 ** 31, 2 ** 31 - 1, (nl, k * BITS // 32), dtype=torch.int32, device=dev, generator=gen)
+        sc = (0.002 + 0.018 * torch.rand((nl, k // GROUP), device=dev, generator=gen)).to(torch.bfloat16)
+        bi = (-8.0 * sc.float()).to(torch.bfloat16)
+        x = torch.randn((1, k), generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).to(dev)
+        peer = PeerGather(ctx, world * nl * 2)
+        st = torch.cuda.current_stream().cuda_stream
+        for _ in range(2):
+            peer.qmv_into(w, sc, bi, x, BITS, GROUP, rank * nl * 2, st)
+            peer.barrier(st)
+        loc = ops.qmv(w, sc, bi, x, BITS, GROUP, ctx=ctx)
+        ref = torch.empty((world, nl), dtype=torch.bfloat16, device=dev)
+        dist.all_gather_into_tensor(ref, loc)
+        torch.cuda.synchronize()
+        if not torch.equal(ref.reshape(-1), peer.tensor(torch.bfloat16)) or ctx.status_word() != 0:
+            ok = 0
+        dist.barrier()
+        peer.close()
+    except Exception as e:  # any failure of the peer path means the NCCL path is used
+        print(f"[rank {rank}] p2p trial failed: {e!r}", file=sys.stderr, flush=True)
+        ok = 0
+    t = torch.tensor([ok], device=dev, dtype=torch.int32)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(int(t.item()))
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes for one launch of the step's kernel
 # (profiles/qmv_pipe_m1_14336x4096_4bit_g64_bf16.md: 33.09 MB / 33.07 MB)
 NCU_TRAFFIC_RATIO = 1.001
@@ -147,9 +180,10 @@ def main():
                     help="N > 1: every projection N-split with an all-gather of the outputs per dependent phase (gather, "
                          "the configuration the metric is quoted on), or column-parallel q/k/v/gate/up + row-parallel "
                          "o/down with one all-reduce each (megatron)")
-    ap.add_argument("--collective", default="nccl", choices=["nccl", "p2p"],
+    ap.add_argument("--collective", default="auto", choices=["auto", "nccl", "p2p"],
                     help="N > 1, --tp gather, M = 1: all-gather with NCCL, or by the qmv kernels' own stores into every "
-                         "rank's buffer (cudaIpc peer mappings) and a one-warp barrier kernel per phase")
+                         "rank's buffer (cudaIpc peer mappings) and a one-warp barrier kernel per phase; auto = p2p when "
+                         "a small trial of it on every rank reproduces the NCCL all-gather, else nccl")
     ap.add_argument("--verify", action="store_true", help="N > 1: check the p2p gather against the NCCL all-gather once")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE", help="mtc_set_option before running")
     ap.add_argument("--streams", type=int, default=1, help="parallel streams for the independent projections of a phase")
@@ -166,8 +200,6 @@ def main():
               "sharding": "none" if world == 1 else (f"tp{world}_column_qkv_gate_up_row_o_down_2_allreduce_per_layer"
                                                     if args.tp == "megatron" else f"n_split_{world}_allgather_per_phase"),
               "l2": "working set 3.9 GB per step >> 126 MB L2"}
-    if world > 1:
-        config["collective"] = args.collective if (args.tp == "gather" and args.m == 1) else "nccl"
 
     if args.impl == "reference":
         if rank != 0:
@@ -232,7 +264,10 @@ def main():
     gather = world > 1 and args.tp == "gather"
     cols_per_layer = sum(phase_cols)
     local_all = torch.empty(args.layers * M * cols_per_layer, dtype=torch.bfloat16, device=dev)
-    p2p = gather and args.collective == "p2p" and M == 1
+    p2p = gather and args.collective in ("p2p", "auto") and M == 1
+    if p2p and args.collective == "auto":
+        p2p = p2p_trial(ctx, dev, rank, world)
+    config_collective = "p2p" if p2p else "nccl"
     peer = None
     if p2p:
         from metaltile_b200.parallel import PeerGather
@@ -393,6 +428,8 @@ def main():
         finish()
         return
 
+    if world > 1:
+        config["collective"] = config_collective
     hbm_peak, tf_burst, tf_sus, peak_kind = measured_peaks()
     per_launch_bytes = total_bytes / world / launches_per_step
     us_per_launch = ms * 1e3 / launches_per_step

@@ -19,10 +19,15 @@ struct BarrierArgs {
     int n_peers, rank;
 };
 
-// <<<1, 32>>>.  Stream order guarantees that the kernels before this one (the stores into the peers' buffers) have
+// <<<1, 32>>>.  After griddepcontrol.wait the kernels before this one (the stores into the peers' buffers) have
 // completed; the flag is written with a system-scope release after a system fence and read with an acquire.
 __global__ void peer_barrier_kernel(const BarrierArgs a) {
     const int p = threadIdx.x;
+    // Programmatic dependent launch on both sides: this kernel is resident before the projections of the phase have
+    // finished and waits for them here; the next phase's kernels may start prefetching their weights now and wait
+    // for this kernel before they read activations or store.
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t e = *a.epoch + 1u;
     if (p < a.n_peers) {
         __threadfence_system();
@@ -35,7 +40,7 @@ __global__ void peer_barrier_kernel(const BarrierArgs a) {
                 seen = true;
                 break;
             }
-            __nanosleep(64);
+            __nanosleep(20);
         }
         if (!seen) atomicCAS(a.status, 0u, 0x601u + static_cast<uint32_t>(p));     // rank p never arrived
     }
@@ -59,8 +64,17 @@ cudaError_t launch_peer_barrier(Ctx *ctx, cudaStream_t st, uint32_t *const *peer
     a.status = ctx->d_status;
     a.n_peers = n_peers;
     a.rank = rank;
-    peer_barrier_kernel<<<1, 32, 0, st>>>(a);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, peer_barrier_kernel, a);
 }
 
 }  // namespace mtc

@@ -140,19 +140,49 @@ class PeerGather:
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         if self.world > 8:
             raise ValueError("at most 8 ranks")
-        self.buf = ctx.alloc(nbytes)
-        self.flags = ctx.alloc(256)                       # 8 flag words, then (at +128) the epoch counter
-        ctx.memset(self.buf, 0, nbytes)
-        ctx.memset(self.flags, 0, 256)
-        ctx.sync()
-        mine = (ctx.ipc_export(self.buf), ctx.ipc_export(self.flags))
+        # every step that can fail locally is followed by an exchange of its outcome, so that either all ranks get a
+        # working object or all ranks raise: no rank is left waiting in a collective for one that gave up
+        self.buf = self.flags = None
+        self.peer_bufs, self.peer_flags = [], []
+        mine = None
+        try:
+            self.buf = ctx.alloc(nbytes)
+            self.flags = ctx.alloc(256)                   # 8 flag words, then (at +128) the epoch counter
+            ctx.memset(self.buf, 0, nbytes)
+            ctx.memset(self.flags, 0, 256)
+            ctx.sync()
+            mine = (ctx.ipc_export(self.buf), ctx.ipc_export(self.flags))
+        except Exception as e:  # reported through the exchange below
+            mine = None
+            self._why = repr(e)
         handles = [None] * self.world
         dist.all_gather_object(handles, mine, group=group)
+        opened = all(h is not None for h in handles)
+        if opened:
+            try:
+                for r, (hb, hf) in enumerate(handles):
+                    self.peer_bufs.append(self.buf if r == self.rank else ctx.ipc_open(hb))
+                    self.peer_flags.append(self.flags if r == self.rank else ctx.ipc_open(hf))
+            except Exception as e:
+                opened = False
+                self._why = repr(e)
+        oks = [None] * self.world
+        dist.all_gather_object(oks, bool(opened), group=group)
+        if not all(oks):
+            self._release()
+            raise RuntimeError(f"peer buffers could not be shared between the ranks ({getattr(self, '_why', 'another rank failed')})")
+
+    def _release(self):
+        for r, (pb, pf) in enumerate(zip(self.peer_bufs, self.peer_flags)):
+            if r != self.rank:
+                self.ctx.ipc_close(pb)
+                self.ctx.ipc_close(pf)
         self.peer_bufs, self.peer_flags = [], []
-        for r, (hb, hf) in enumerate(handles):
-            self.peer_bufs.append(self.buf if r == self.rank else ctx.ipc_open(hb))
-            self.peer_flags.append(self.flags if r == self.rank else ctx.ipc_open(hf))
-        dist.barrier(group=group)
+        if self.buf:
+            self.ctx.free(self.buf)
+        if self.flags:
+            self.ctx.free(self.flags)
+        self.buf = self.flags = None
 
     def tensor(self, dtype=torch.bfloat16):
         """The local buffer as a flat tensor of ``dtype``."""
@@ -172,12 +202,7 @@ class PeerGather:
 
     def close(self):
         """Unmap the peers' blocks and free the own ones; every rank calls it after a ``dist.barrier``."""
-        for r in range(self.world):
-            if r != self.rank:
-                self.ctx.ipc_close(self.peer_bufs[r])
-                self.ctx.ipc_close(self.peer_flags[r])
-        self.ctx.free(self.buf)
-        self.ctx.free(self.flags)
+        self._release()
 
 
 @dataclass

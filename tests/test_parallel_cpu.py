@@ -91,6 +91,35 @@ def _worker(rank, world, port, q):
         # the split changes the order of the f32 additions only: one extra rounding per rank
         assert got.shape == (m, n) and np.max(np.abs(got - ref) / np.maximum(np.abs(ref), 1.0)) <= 1e-5, "row-parallel result differs"
 
+        # ---- peer-buffer setup: a rank whose allocation fails must make every rank raise, none may be left waiting
+        class FakeCtx:
+            def __init__(self, fail):
+                self.fail, self.freed, self.closed, self.n = fail, [], [], 0
+            def alloc(self, nbytes):
+                if self.fail:
+                    raise RuntimeError("out of memory (injected)")
+                self.n += 1
+                return 0x1000 * self.n
+            def memset(self, *a): pass
+            def sync(self): pass
+            def ipc_export(self, ptr): return ptr.to_bytes(8, "little") * 8
+            def ipc_open(self, h): return int.from_bytes(h[:8], "little") + 0x100000
+            def ipc_close(self, ptr): self.closed.append(ptr)
+            def free(self, ptr): self.freed.append(ptr)
+        fake = FakeCtx(fail=(rank == 1))
+        try:
+            parallel.PeerGather(fake, 64)
+            raise AssertionError("peer-buffer setup should have failed on every rank")
+        except RuntimeError as e:
+            assert "could not be shared" in str(e)
+        assert fake.closed == [] and (fake.freed == [0x1000, 0x2000] if rank == 0 else fake.freed == [])
+        good = FakeCtx(fail=False)
+        pg = parallel.PeerGather(good, 64)
+        assert pg.peer_bufs[rank] == 0x1000 and pg.peer_bufs[1 - rank] == 0x1000 + 0x100000
+        assert pg.peer_flags[1 - rank] == 0x2000 + 0x100000
+        pg.close()
+        assert sorted(good.closed) == [0x101000, 0x102000] and good.freed == [0x1000, 0x2000]
+
         # ---- expert parallel: 8 experts over 2 ranks, 10 tokens per rank, top-2
         E, H, I, T, K2 = 8, 64, 32, 10, 2
         gate, up, down = _moe_weights(E, H, I)
