@@ -132,6 +132,9 @@ def cpu_reference_arm(args):
 
 def p2p_trial(ctx, dev, rank, world):
     """One small projection gathered through peer stores + barrier, compared with NCCL; every rank must agree."""
+    import torch
+    import torch.distributed as dist
+    from metaltile_b200 import ops
     ok = 1
     try:
         from metaltile_b200.parallel import PeerGather
