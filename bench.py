@@ -295,6 +295,14 @@ def main():
             out_full.append(fl)
     # each projection writes its own contiguous [M, nl] tile, then tiles are packed per phase
     tiles = [[torch.empty((M, nl), dtype=torch.bfloat16, device=dev) for (_, _, _, _, nl, _) in mats] for mats in layers]
+    if world == 1 and M > 1:
+        # nothing is exchanged on one GPU: the tiles themselves are the result, laid out one after the other in the
+        # result allocation (same bytes as the per-phase slabs), and no packing copy is launched
+        to = 0
+        for li, mats in enumerate(layers):
+            for pi, (_, _, _, _, nl, _) in enumerate(mats):
+                tiles[li][pi] = local_all[to:to + M * nl].view(M, nl)
+                to += M * nl
 
     # the projections of one phase (q/k/v; gate/up) read the same activations and are independent:
     # with --streams > 1 they are launched on parallel streams, joined before the phase's all-gather
@@ -324,7 +332,8 @@ def main():
                         else:
                             xin = xs[k] if xs[k].is_contiguous() else xs[k].contiguous()
                             ops.qmv(w, sc, bi, xin, BITS, GROUP, out=tiles[li][pi], ctx=ctx)
-                            out_local[li][ph][:, col:col + nl].copy_(tiles[li][pi])
+                            if world > 1:
+                                out_local[li][ph][:, col:col + nl].copy_(tiles[li][pi])
                     col += nl
                 for st in set(used):
                     if st is not main:
