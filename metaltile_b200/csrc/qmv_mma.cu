@@ -281,16 +281,21 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) qmv_mma_kernel(const MmaArg
     if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
-// ---- group size 64, K a multiple of 512: packed words through a shared-memory ring ----
+// ---- group size 64, 128 or 256, K a multiple of 512: packed words through a shared-memory ring ----
 // Loading the A fragments straight from global memory costs one 32-byte sector per row and instruction, eight
 // cache lines per warp-load, and the L1 tag stage becomes the limit.  Here a warp copies a run of 8 consecutive
-// segments of its 16 rows (16 x 256 bytes of packed words, plus 16 bytes of scales and of biases per row) with
+// segments of its 16 rows (16 x 256 bytes of packed words, plus the 16, 8 or 4 bytes of scales and of biases that
+// 8, 4 or 2 groups per row take) with
 // 16-byte asynchronous copies that cover whole lines and bypass L1, into a private two-deep ring, and reads the
 // fragments back with conflict-free 8-byte shared loads.  No register holds data in flight.
 constexpr int kRingWarps = 16;
 constexpr int kRunWBytes = 16 * 256;                 // packed words of a run: 16 rows x 8 segments x 32 bytes
 constexpr int kRunBytes = kRunWBytes + 2 * 256;      // + scales and biases: 16 rows x 8 groups x 2 bytes each
 
+template <int BYTES>
+__device__ __forceinline__ void cp_async_small(uint32_t dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(dst), "l"(src), "n"(BYTES) : "memory");
+}
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -331,7 +336,8 @@ __device__ __forceinline__ void stage_x_ring(const MmaArgs &a, uint4 *xb, int se
     }
 }
 
-template <int NT, bool BF16, bool kFull /* M == 8 * NT: every lane has a token, strides are constants */>
+template <int NT, bool BF16, bool kFull /* M == 8 * NT: every lane has a token, strides are constants */,
+          int GSH /* log2(group / 64): 0, 1 or 2 - a run of 8 segments holds 8, 4 or 2 groups per row */>
 __global__ void __launch_bounds__(kRingWarps * 32, 1) qmv_mma_ring_kernel(const MmaArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_mma[];
     constexpr float off = BF16 ? 128.0f : 1024.0f;
@@ -376,7 +382,11 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) qmv_mma_ring_kernel(const 
             cp_async16(dst + row * 256 + ((c_chunk ^ ((row & 3) << 1)) << 4), src0 + gr * w_pitch);
         }
         const int gr = min(row0 + c_srow, a.N - 1);
-        cp_async16(dst + kRunWBytes + (lane & 1) * 256 + c_srow * 16, c_sb + gr * sb_pitch + static_cast<size_t>(s_run) * 2);
+        const uint32_t sdst = dst + kRunWBytes + (lane & 1) * 256 + c_srow * 16;
+        const char *ssrc = c_sb + gr * sb_pitch + static_cast<size_t>(s_run >> GSH) * 2;
+        if (GSH == 0) cp_async16(sdst, ssrc);
+        else if (GSH == 1) cp_async_small<8>(sdst, ssrc);
+        else cp_async_small<4>(sdst, ssrc);
     };
     // the runs of this warp in the order (tile, block, run); the copies run one run ahead, across tiles
     int it_n = 0, kb_n = 0, r_n = -1, s_n = 0, tile_n = tile_begin + slot;
@@ -508,20 +518,20 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) qmv_mma_ring_kernel(const 
                     MTC_STEP(2, false)
                     MTC_STEP(3, false)
 #undef MTC_STEP
-                    const int q = p >> 1;
+                    const int gi = p >> GSH, q = gi >> 1;        // group of this segment within the run, its 32-bit pair
                     float s_lo, s_hi, o_lo, o_hi;
                     if (BF16) {
-                        s_lo = __uint_as_float((p & 1) ? (sp[0][q] & 0xFFFF0000u) : (sp[0][q] << 16));
-                        s_hi = __uint_as_float((p & 1) ? (sp[1][q] & 0xFFFF0000u) : (sp[1][q] << 16));
-                        o_lo = __uint_as_float((p & 1) ? (sp[2][q] & 0xFFFF0000u) : (sp[2][q] << 16));
-                        o_hi = __uint_as_float((p & 1) ? (sp[3][q] & 0xFFFF0000u) : (sp[3][q] << 16));
+                        s_lo = __uint_as_float((gi & 1) ? (sp[0][q] & 0xFFFF0000u) : (sp[0][q] << 16));
+                        s_hi = __uint_as_float((gi & 1) ? (sp[1][q] & 0xFFFF0000u) : (sp[1][q] << 16));
+                        o_lo = __uint_as_float((gi & 1) ? (sp[2][q] & 0xFFFF0000u) : (sp[2][q] << 16));
+                        o_hi = __uint_as_float((gi & 1) ? (sp[3][q] & 0xFFFF0000u) : (sp[3][q] << 16));
                     } else {
                         const __half2 h0 = *reinterpret_cast<const __half2 *>(&sp[0][q]), h1 = *reinterpret_cast<const __half2 *>(&sp[1][q]);
                         const __half2 h2 = *reinterpret_cast<const __half2 *>(&sp[2][q]), h3 = *reinterpret_cast<const __half2 *>(&sp[3][q]);
-                        s_lo = (p & 1) ? __high2float(h0) : __low2float(h0);
-                        s_hi = (p & 1) ? __high2float(h1) : __low2float(h1);
-                        o_lo = (p & 1) ? __high2float(h2) : __low2float(h2);
-                        o_hi = (p & 1) ? __high2float(h3) : __low2float(h3);
+                        s_lo = (gi & 1) ? __high2float(h0) : __low2float(h0);
+                        s_hi = (gi & 1) ? __high2float(h1) : __low2float(h1);
+                        o_lo = (gi & 1) ? __high2float(h2) : __low2float(h2);
+                        o_hi = (gi & 1) ? __high2float(h3) : __low2float(h3);
                     }
                     const float b_lo = fmaf(-off, s_lo, o_lo), b_hi = fmaf(-off, s_hi, o_hi);
 #pragma unroll
@@ -576,7 +586,7 @@ constexpr size_t ring_smem_bytes() {
            static_cast<size_t>(kRingWarps) * 32 * NT * 4 * sizeof(float) + (NT == 1 ? 4096 : 2048) + 64;
 }
 
-template <int NT, bool BF16>
+template <int NT, bool BF16, int GSH>
 cudaError_t launch_ring(Ctx *ctx, cudaStream_t st, MmaArgs a) {
     const int sms = ctx->sm_count;
     a.tiles = (a.N + 15) / 16;
@@ -609,9 +619,9 @@ cudaError_t launch_ring(Ctx *ctx, cudaStream_t st, MmaArgs a) {
     constexpr size_t smem = ring_smem_bytes<NT>();
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(qmv_mma_ring_kernel<NT, BF16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        cudaError_t e = cudaFuncSetAttribute(qmv_mma_ring_kernel<NT, BF16, true, GSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(qmv_mma_ring_kernel<NT, BF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+            e = cudaFuncSetAttribute(qmv_mma_ring_kernel<NT, BF16, false, GSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
@@ -625,8 +635,8 @@ cudaError_t launch_ring(Ctx *ctx, cudaStream_t st, MmaArgs a) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (a.M == NT * 8) return cudaLaunchKernelEx(&cfg, qmv_mma_ring_kernel<NT, BF16, true>, a);
-    return cudaLaunchKernelEx(&cfg, qmv_mma_ring_kernel<NT, BF16, false>, a);
+    if (a.M == NT * 8) return cudaLaunchKernelEx(&cfg, qmv_mma_ring_kernel<NT, BF16, true, GSH>, a);
+    return cudaLaunchKernelEx(&cfg, qmv_mma_ring_kernel<NT, BF16, false, GSH>, a);
 }
 
 template <int NT>
@@ -696,9 +706,14 @@ cudaError_t launch_qmv_mma(Ctx *ctx, cudaStream_t st, const void *w, const void 
     a.gpr = K / group_size;
     a.nseg = K / 64;
     const auto al16 = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
-    if (group_size == 64 && K % 512 == 0 && al16(scales) && al16(biases)) {
-        if (dt == MTC_BF16) return M <= 8 ? launch_ring<1, true>(ctx, st, a) : launch_ring<2, true>(ctx, st, a);
-        return M <= 8 ? launch_ring<1, false>(ctx, st, a) : launch_ring<2, false>(ctx, st, a);
+    if (group_size <= 256 && K % 512 == 0 && al16(scales) && al16(biases)) {
+#define MTC_RING(GSH_)                                                                                              \
+    if (dt == MTC_BF16) return M <= 8 ? launch_ring<1, true, GSH_>(ctx, st, a) : launch_ring<2, true, GSH_>(ctx, st, a); \
+    return M <= 8 ? launch_ring<1, false, GSH_>(ctx, st, a) : launch_ring<2, false, GSH_>(ctx, st, a);
+        if (group_size == 64) { MTC_RING(0) }
+        if (group_size == 128) { MTC_RING(1) }
+        { MTC_RING(2) }
+#undef MTC_RING
     }
     if (dt == MTC_BF16) return M <= 8 ? launch_mma<1, true>(ctx, st, a) : launch_mma<2, true>(ctx, st, a);
     return M <= 8 ? launch_mma<1, false>(ctx, st, a) : launch_mma<2, false>(ctx, st, a);
