@@ -128,6 +128,8 @@ int mtc_peer_barrier(mtc_ctx *ctx, void *stream, void *const *peer_flags, int n_
  *                      activations and a group that is a multiple of 64 use the warp-level tensor cores);
  *                      2: M = 1 takes that path too (same results within round-off; not faster on B200)
  *   "qmm_max_stages"   > 0 caps the depth of the shared-memory ring of the tensor-core kernel (diagnostic)
+ *   "qmm_mma_chunks"   0: 17 <= M <= 64 always runs on the tcgen05 kernel (default 1: 4-bit, f16/bf16, group >= 64
+ *                      shapes run as 16-row chunks of the small-M tensor-core qmv when that fills the GPU better)
  *   "qmm_raw"          0: the dequant warps of the tensor-core kernel load packed words straight from global
  *                      memory instead of through the shared-memory staging buffers (default 1)
  *   "qmm_pair"         1: a work item covers two adjacent weight-row tiles that share every

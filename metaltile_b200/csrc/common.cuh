@@ -27,6 +27,7 @@ struct Ctx {
     int qmv_small_m_mma = 1;       // option "qmv_small_m_mma": 0 keeps 2 <= M <= 16 on the CUDA-core kernel
     int qmm_max_stages = 0;        // option "qmm_max_stages": > 0 caps the ring depth (diagnostic: how much the ring hides)
     int qmm_wait_hint_ns = 5000;      // option "qmm_wait_hint_ns": base suspend-time hint of the kernel's mbarrier waits
+    int qmm_mma_chunks = 1;        // option "qmm_mma_chunks": 0 = 17 <= M <= 64 always on the tcgen05 kernel
     int qmm_raw = 1;               // option "qmm_raw": 0 = dequant warps load their packed words straight from global memory
     int qmm_pair = 0;              // option "qmm_pair": 1 = give a work item two adjacent weight-row tiles
     void *d_worklist = nullptr;    // gather_qmm work list (grow-only, owned by the context)

@@ -340,7 +340,20 @@ int mtc_peer_barrier(mtc_ctx *ctx, void *stream, void *const *peer_flags, int n_
 // mt_qmm_for (crates/metaltile-std/src/mlx/quantized.rs:5040-5065) picks by M alone; here M <= 16 or
 // f32 activations stay on the qmv kernels (CUDA cores, or warp-level MMAs for 2 <= M <= 16 with 4-bit codes), everything else goes to the tensor cores when the
 // shape meets that kernel's contract (K % 64 == 0, power-of-two group >= 32).
+// 17 <= M <= 64: the tcgen05 kernel needs (N / 128) x ceil(M / tile) work items to fill 148 SMs and paces at ~0.85 us
+// per 64 of K whatever M is, so few token rows on a matrix of a few thousand rows leave most SMs idle (M = 32,
+// 4096 x 4096: 54 us on 32 SMs).  The small-M tensor-core qmv in 16-row chunks streams the weights once per chunk
+// on every SM instead (2 x 9.3 us for that case).  Taken for M <= 32 always, up to 64 while the tcgen05 grid would
+// cover less than half of the SMs.
+static bool mma_chunks_preferred(int enabled, int sms, int M, int N, int K, int bits, int group_size, int dtype,
+                                 const void *w, const void *x) {
+    if (!enabled || M <= 16 || M > 64) return false;
+    if (!mtc::qmv_mma_supported(16, N, K, bits, group_size, dtype, w, x)) return false;
+    return M <= 32 || ((N + 127) / 128) * 2 <= sms;
+}
+
 const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dtype) {
+    if (mma_chunks_preferred(1, 148, M, N, K, bits, group_size, dtype, nullptr, nullptr)) return "qmv_mma_sync";
     if (M > 16 && mtc::qmm_tcgen05_supported(M, N, K, bits, group_size, dtype, nullptr, nullptr, nullptr))
         return "qmm_tcgen05";
     // alignment is a run-time property of the pointers; the route names the kernel an aligned call gets
@@ -352,6 +365,18 @@ int mtc_qmm(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
             void *out, int M, int N, int K, int bits, int group_size, int dtype) {
     if (!ctx) return MTC_ERR_INVALID;
     if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "qmm: dtype must be f32, f16 or bf16");
+    if (w && scales && biases && x && out &&
+        mma_chunks_preferred(ctx->qmm_mma_chunks && ctx->qmv_small_m_mma, ctx->sm_count, M, N, K, bits, group_size, dtype, w, x)) {
+        const size_t esz = 2;      // f16 / bf16 only on this path
+        for (int m0 = 0; m0 < M; m0 += 16) {
+            const int mc = M - m0 < 16 ? M - m0 : 16;
+            const char *xc = static_cast<const char *>(x) + static_cast<size_t>(m0) * K * esz;
+            char *oc = static_cast<char *>(out) + static_cast<size_t>(m0) * N * esz;
+            int rc = mtc_qmv(ctx, stream, w, scales, biases, xc, oc, mc, N, K, bits, group_size, dtype);
+            if (rc != MTC_OK) return rc;
+        }
+        return MTC_OK;
+    }
     if (M > 16 && mtc::qmm_tcgen05_supported(M, N, K, bits, group_size, dtype, w, x, out)) {
         if (!w || !scales || !biases || !x || !out) return fail(ctx, MTC_ERR_INVALID, "qmm: null pointer");
         std::string why;
@@ -386,6 +411,10 @@ int mtc_set_option(mtc_ctx *ctx, const char *name, int value) {
     }
     if (std::strcmp(name, "qmm_wait_hint_ns") == 0) {
         ctx->qmm_wait_hint_ns = value < 0 ? 0 : value;
+        return MTC_OK;
+    }
+    if (std::strcmp(name, "qmm_mma_chunks") == 0) {
+        ctx->qmm_mma_chunks = value ? 1 : 0;
         return MTC_OK;
     }
     if (std::strcmp(name, "qmm_raw") == 0) {

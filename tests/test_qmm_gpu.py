@@ -30,7 +30,11 @@ def test_routing_follows_m_and_dtype(ctx):
     assert ctx.qmm_route(16, 4096, 4096, 4, 32, "bf16") == "qmv_cuda_core"        # group < 64
     assert ctx.qmm_route(16, 4096, 4096, 8, 64, "bf16") == "qmv_cuda_core"        # 4-bit codes only
     assert ctx.qmm_route(16, 4096, 4096, 4, 64, "f32") == "qmv_cuda_core"
-    assert ctx.qmm_route(17, 4096, 4096, 4, 64, "bf16") == "qmm_tcgen05"
+    assert ctx.qmm_route(17, 4096, 4096, 4, 64, "bf16") == "qmv_mma_sync"      # few rows: 16-row chunks of the small-M kernel
+    assert ctx.qmm_route(64, 4096, 4096, 4, 64, "bf16") == "qmv_mma_sync"      # 32 weight tiles would fill a fifth of the SMs
+    assert ctx.qmm_route(64, 14336, 4096, 4, 64, "bf16") == "qmm_tcgen05"
+    assert ctx.qmm_route(65, 4096, 4096, 4, 64, "bf16") == "qmm_tcgen05"
+    assert ctx.qmm_route(17, 4096, 4096, 8, 64, "bf16") == "qmm_tcgen05"
     assert ctx.qmm_route(2048, 14336, 4096, 4, 64, "f16") == "qmm_tcgen05"
     assert ctx.qmm_route(2048, 14336, 4096, 4, 64, "f32") == "qmv_cuda_core"      # no f32 MMA: stays exact
     assert ctx.qmm_route(64, 256, 96, 4, 32, "bf16") == "qmv_cuda_core"           # K % 64 != 0
@@ -50,13 +54,38 @@ def test_routing_follows_m_and_dtype(ctx):
     (1000, 200, 4096, 4, 64, "bf16"),                              # long K: many ring wraps
 ])
 def test_qmm_matches_oracle(ctx, m, n, k, bits, gs, dt):
-    assert ctx.qmm_route(m, n, k, bits, gs, dt) == "qmm_tcgen05"
+    """Every shape on the tcgen05 kernel (the chunked small-M route of few-row shapes is switched off here and has
+    its own test below)."""
+    assert ctx.qmm_route(m, n, k, bits, gs, dt) in ("qmm_tcgen05", "qmv_mma_sync")
     w, s, b, x = dense_case(m, n, k, bits, gs, dt, seed=0, salt=m + n)
     ref = oracle.qmm(w, s, b, x, m, n, k, bits, gs)
-    got = run_qmm(w, s, b, x, bits, gs, dt)
+    ctx.set_option("qmm_mma_chunks", 0)
+    try:
+        got = run_qmm(w, s, b, x, bits, gs, dt)
+    finally:
+        ctx.set_option("qmm_mma_chunks", 1)
     assert got.shape == (m, n)
     assert rel_err(got, ref) <= TOL[dt]
     assert ctx.status_word() == 0
+
+
+@pytest.mark.parametrize("m,n,k,gs,dt", [(17, 4096, 4096, 64, "bf16"), (32, 1000, 512, 128, "f16"), (50, 2048, 2048, 64, "bf16"),
+                                         (64, 272, 1024, 64, "f16")])
+def test_few_rows_run_as_chunks_of_the_small_m_kernel(ctx, m, n, k, gs, dt):
+    """17 <= M <= 64 on a matrix too small to fill the GPU with 128-row tiles: 16-row chunks of the tensor-core qmv;
+    same oracle, and within round-off of the tcgen05 kernel."""
+    assert ctx.qmm_route(m, n, k, 4, gs, dt) == "qmv_mma_sync"
+    w, s, b, x = dense_case(m, n, k, 4, gs, dt, seed=16, salt=m)
+    ref = oracle.qmm(w, s, b, x, m, n, k, 4, gs)
+    got = run_qmm(w, s, b, x, 4, gs, dt)
+    assert got.shape == (m, n)
+    assert rel_err(got, ref) <= TOL[dt]
+    ctx.set_option("qmm_mma_chunks", 0)
+    try:
+        tc = run_qmm(w, s, b, x, 4, gs, dt)
+    finally:
+        ctx.set_option("qmm_mma_chunks", 1)
+    assert rel_err(got, tc) <= TOL[dt]
 
 
 def test_exact_integer_case(ctx):
