@@ -100,7 +100,8 @@ const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dty
  *
  * mtc_qmv_multi: mtc_qmv that writes its [M, N] output tile to outs[0..n_outs) (1 to 8 destinations, same layout
  * and dtype each).  With outs[i] = rank i's copy of the gathered buffer, offset to this rank's slot, the all-gather
- * is the store.  Vectorised CUDA-core path only (power-of-two group, aligned pointers), any M.
+ * is the store.  M = 1 on the vectorised CUDA-core path (power-of-two group, aligned pointers, K staged whole);
+ * one destination works for every shape mtc_qmv takes on that path.
  * mtc_ipc_export / mtc_ipc_open / mtc_ipc_close: share a buffer from mtc_alloc with the other rank processes
  * (cudaIpc handle, 64 bytes; opening enables peer access; plain peer mappings, no multicast object).
  * mtc_peer_barrier: enqueue a one-warp kernel that tells every peer "my stores so far are done" and waits until

@@ -56,7 +56,16 @@ struct QmvArgs {
     int ksplit;        // warps sharing one row group
     int groups, iters; // row groups (ceil(N/R)), row-group iterations per CTA slot
     int gpc;           // consecutive row groups owned by one CTA (its weights are one contiguous range)
-    int n_extra;       // further copies of the output tile (peer GPUs' buffers: the all-gather is the store)
+};
+
+// Further copies of the output tile (peer GPUs' buffers: the all-gather is the store).  A second kernel parameter of
+// the multi-destination instantiations only: the single-destination kernels keep their parameter block and code
+// (measured: carrying the pointers and the store loop in every instantiation cost the decode set 6.5 %).
+template <bool kMulti>
+struct QmvTail {};
+template <>
+struct QmvTail<true> {
+    int n_extra;
     void *extra[kMaxPeers - 1];
 };
 
@@ -220,9 +229,10 @@ __device__ __forceinline__ void consume_chunk(const uint32_t (&wreg)[R][Pack<BIT
 
 // K reduction over the lanes of a warp, then (split-K) over the warps sharing the row group,
 // then the store.  Contains __syncthreads when KS > 1: callers keep it CTA-uniform.
-template <int MT, int R>
-__device__ __forceinline__ void reduce_store(const QmvArgs &a, float (&acc)[R][MT], float (&accb)[R][MT], float *red,
-                                             int KS, int ks, int warp, int lane, bool active, int n0) {
+template <int MT, int R, bool kMulti>
+__device__ __forceinline__ void reduce_store(const QmvArgs &a, const QmvTail<kMulti> &tail, float (&acc)[R][MT],
+                                             float (&accb)[R][MT], float *red, int KS, int ks, int warp, int lane,
+                                             bool active, int n0) {
     const float kPost = __uint_as_float(static_cast<uint32_t>(149 - kPreExp + 127) << 23);
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -258,8 +268,10 @@ __device__ __forceinline__ void reduce_store(const QmvArgs &a, float (&acc)[R][M
                 for (int m = 0; m < MT; ++m)
                     if (m < a.M) {
                         st_from_f32(a.out, static_cast<size_t>(m) * a.N + n0 + r, acc[r][m], a.dt);
-                        for (int e = 0; e < a.n_extra; ++e)
-                            st_from_f32(a.extra[e], static_cast<size_t>(m) * a.N + n0 + r, acc[r][m], a.dt);
+                        if constexpr (kMulti) {
+                            for (int e = 0; e < tail.n_extra; ++e)
+                                st_from_f32(tail.extra[e], static_cast<size_t>(m) * a.N + n0 + r, acc[r][m], a.dt);
+                        }
                     }
             }
         }
@@ -272,8 +284,8 @@ __device__ __forceinline__ void reduce_store(const QmvArgs &a, float (&acc)[R][M
 // flat sequence and keeps PF units of packed words and raw scale/bias bits in flight in registers;
 // the first PF units are requested before x is staged, so the DRAM latency of the weights overlaps
 // the staging pass.  Prefetched registers are not touched (not even converted) before their turn.
-template <int BITS, int MT, int R, int V, int PF>
-__global__ void __launch_bounds__(256, (MT <= 2 ? 2 : 1)) qmv_pipe_kernel(const QmvArgs a) {
+template <int BITS, int MT, int R, int V, int PF, bool kMulti = false>
+__global__ void __launch_bounds__(256, (MT <= 2 ? 2 : 1)) qmv_pipe_kernel(const QmvArgs a, const QmvTail<kMulti> tail) {
     using P = Pack<BITS>;
     constexpr int E4 = P::CODES * MT / 4;
     extern __shared__ __align__(16) float smem[];
@@ -381,7 +393,7 @@ __global__ void __launch_bounds__(256, (MT <= 2 ? 2 : 1)) qmv_pipe_kernel(const 
                 }
                 issue(wbuf[p], sraw[p], braw[p]);
                 if (c_jbi == njb_w - 1) {
-                    reduce_store<MT, R>(a, acc, accb, red, KS, ks, warp, lane, active, c_g * R);
+                    reduce_store<MT, R, kMulti>(a, tail, acc, accb, red, KS, ks, warp, lane, active, c_g * R);
 #pragma unroll
                     for (int r = 0; r < R; ++r)
 #pragma unroll
@@ -447,7 +459,7 @@ __global__ void __launch_bounds__(256) qmv_kernel(const QmvArgs a) {
                 consume_chunk<BITS, MT, R>(wreg, sc, bi, xv, xsum + (jbl * 32 + lane) * MT, acc, accb);
             }
         }
-        reduce_store<MT, R>(a, acc, accb, red, KS, ks, warp, lane, active, n0);
+        reduce_store<MT, R, false>(a, QmvTail<false>{}, acc, accb, red, KS, ks, warp, lane, active, n0);
     }
 }
 
@@ -500,7 +512,8 @@ struct Shape {
 };
 
 template <int BITS, int MT, int V>
-cudaError_t launch_pipe(Ctx *ctx, cudaStream_t st, QmvArgs a, size_t per_jb, size_t red_bytes) {
+cudaError_t launch_pipe(Ctx *ctx, cudaStream_t st, QmvArgs a, size_t per_jb, size_t red_bytes,
+                        const QmvTail<true> *tail = nullptr) {
     using P = Pack<BITS>;
     constexpr int PF = Shape<BITS, MT>::PF;
     const int sms = ctx->sm_count;
@@ -537,11 +550,23 @@ cudaError_t launch_pipe(Ctx *ctx, cudaStream_t st, QmvArgs a, size_t per_jb, siz
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kern, a);
+    if constexpr (MT == 1) {
+        if (tail) {        // multi-destination instantiation: same configuration, one more parameter
+            auto mk = qmv_pipe_kernel<BITS, MT, kRows, V, PF, true>;
+            static bool attr_set = false;
+            if (!attr_set) {
+                e = cudaFuncSetAttribute(mk, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemPipe + 4096));
+                if (e != cudaSuccess) return e;
+                attr_set = true;
+            }
+            return cudaLaunchKernelEx(&cfg, mk, a, *tail);
+        }
+    }
+    return cudaLaunchKernelEx(&cfg, kern, a, QmvTail<false>{});
 }
 
 template <int BITS, int MT>
-cudaError_t launch_tile(Ctx *ctx, cudaStream_t st, QmvArgs a) {
+cudaError_t launch_tile(Ctx *ctx, cudaStream_t st, QmvArgs a, const QmvTail<true> *tail) {
     using P = Pack<BITS>;
     constexpr int V = Shape<BITS, MT>::V;
     a.nchunks = a.K / P::CODES;
@@ -551,9 +576,10 @@ cudaError_t launch_tile(Ctx *ctx, cudaStream_t st, QmvArgs a) {
     const size_t red_bytes = static_cast<size_t>(kWarps) * kRows * MT * sizeof(float);
     const size_t whole_k = per_jb * ((a.nchunks + 31) / 32 + 1) + red_bytes;
     if (whole_k <= kSmemPipe) {
-        if (V > 1 && a.nchunks % V == 0 && a.gs >= V * P::CODES) return launch_pipe<BITS, MT, V>(ctx, st, a, per_jb, red_bytes);
-        return launch_pipe<BITS, MT, 1>(ctx, st, a, per_jb, red_bytes);
+        if (V > 1 && a.nchunks % V == 0 && a.gs >= V * P::CODES) return launch_pipe<BITS, MT, V>(ctx, st, a, per_jb, red_bytes, tail);
+        return launch_pipe<BITS, MT, 1>(ctx, st, a, per_jb, red_bytes, tail);
     }
+    if (tail) return cudaErrorNotSupported;     // several destinations: whole K staged only
     a.njb = (a.nchunks + 31) / 32;
 
     int max_jb = static_cast<int>((kSmemBlocked - red_bytes) / per_jb);
@@ -572,12 +598,13 @@ cudaError_t launch_tile(Ctx *ctx, cudaStream_t st, QmvArgs a) {
 }
 
 template <int BITS>
-cudaError_t launch_bits(Ctx *ctx, cudaStream_t st, const QmvArgs &a) {
-    if (a.M == 1) return launch_tile<BITS, 1>(ctx, st, a);
-    if (a.M == 2) return launch_tile<BITS, 2>(ctx, st, a);
-    if (a.M <= 4) return launch_tile<BITS, 4>(ctx, st, a);
-    if (a.M <= 8) return launch_tile<BITS, 8>(ctx, st, a);
-    return launch_tile<BITS, 16>(ctx, st, a);
+cudaError_t launch_bits(Ctx *ctx, cudaStream_t st, const QmvArgs &a, const QmvTail<true> *tail) {
+    if (a.M == 1) return launch_tile<BITS, 1>(ctx, st, a, tail);
+    if (tail) return cudaErrorNotSupported;     // several destinations: M = 1 (the sharded decode case)
+    if (a.M == 2) return launch_tile<BITS, 2>(ctx, st, a, nullptr);
+    if (a.M <= 4) return launch_tile<BITS, 4>(ctx, st, a, nullptr);
+    if (a.M <= 8) return launch_tile<BITS, 8>(ctx, st, a, nullptr);
+    return launch_tile<BITS, 16>(ctx, st, a, nullptr);
 }
 
 template <int BITS>
@@ -649,8 +676,10 @@ cudaError_t launch_qmv(Ctx *ctx, cudaStream_t st, const void *w, const void *sca
         a.biases = biases;
         a.x = static_cast<const char *>(x) + static_cast<size_t>(m0) * K * esz;
         a.out = static_cast<char *>(out) + static_cast<size_t>(m0) * N * esz;
-        a.n_extra = n_extra;
-        for (int e = 0; e < n_extra; ++e) a.extra[e] = static_cast<char *>(extra_outs[e]) + static_cast<size_t>(m0) * N * esz;
+        QmvTail<true> tail{};
+        tail.n_extra = n_extra;
+        for (int e = 0; e < n_extra; ++e) tail.extra[e] = static_cast<char *>(extra_outs[e]) + static_cast<size_t>(m0) * N * esz;
+        const QmvTail<true> *tp = n_extra > 0 ? &tail : nullptr;
         a.M = M - m0 < 16 ? M - m0 : 16;
         a.N = N;
         a.K = K;
@@ -662,13 +691,15 @@ cudaError_t launch_qmv(Ctx *ctx, cudaStream_t st, const void *w, const void *sca
         a.gpr = K / group_size;
         cudaError_t e;
         switch (bits) {
-            case 2: e = launch_bits<2>(ctx, st, a); break;
-            case 3: e = launch_bits<3>(ctx, st, a); break;
-            case 4: e = launch_bits<4>(ctx, st, a); break;
-            case 5: e = launch_bits<5>(ctx, st, a); break;
-            case 6: e = launch_bits<6>(ctx, st, a); break;
-            default: e = launch_bits<8>(ctx, st, a); break;
+            case 2: e = launch_bits<2>(ctx, st, a, tp); break;
+            case 3: e = launch_bits<3>(ctx, st, a, tp); break;
+            case 4: e = launch_bits<4>(ctx, st, a, tp); break;
+            case 5: e = launch_bits<5>(ctx, st, a, tp); break;
+            case 6: e = launch_bits<6>(ctx, st, a, tp); break;
+            default: e = launch_bits<8>(ctx, st, a, tp); break;
         }
+        if (e == cudaErrorNotSupported && why) *why = "qmv with several outputs: M = 1 with the whole K staged in shared memory only";
+        if (e == cudaErrorNotSupported) return cudaErrorInvalidValue;
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;

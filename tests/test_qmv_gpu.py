@@ -199,7 +199,7 @@ def test_multi_output_store_and_single_rank_barrier(ctx):
     with one rank the barrier kernel only meets its own flag, raises the epoch and leaves the status word clear."""
     import torch
     from metaltile_b200.ops import _TORCH_DT
-    for m, n, k, dt in [(1, 1024, 4096, "bf16"), (3, 200, 512, "f32")]:
+    for m, n, k, dt in [(1, 1024, 4096, "bf16"), (1, 200, 512, "f32"), (1, 4096, 14336, "f16")]:
         w, s, b, x = dense_case(m, n, k, 4, 64, dt, seed=15, salt=n)
         wd, sd, bd, xd = to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt)
         outs = [torch.zeros((m, n), dtype=xd.dtype, device="cuda") for _ in range(3)]
@@ -219,6 +219,10 @@ def test_multi_output_store_and_single_rank_barrier(ctx):
     from metaltile_b200 import MetalTileError
     with pytest.raises(MetalTileError):
         ctx.peer_barrier([flags.data_ptr()] * 9, 0, flags.data_ptr(), flags.data_ptr() + 128, stream=st)
+    with pytest.raises(MetalTileError) as ei:      # several destinations are the M = 1 decode case only
+        ctx.qmv_multi(wd.data_ptr(), sd.data_ptr(), bd.data_ptr(), xd.data_ptr(), [o.data_ptr() for o in outs], 3, n, k, 4, 64,
+                      _TORCH_DT[xd.dtype], stream=st)
+    assert ei.value.variant == "Unsupported"
 
 
 def test_generic_fallback_paths(ctx):
