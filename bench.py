@@ -189,6 +189,8 @@ def main():
                          "a small trial of it on every rank reproduces the NCCL all-gather, else nccl")
     ap.add_argument("--verify", action="store_true", help="N > 1: check the p2p gather against the NCCL all-gather once")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE", help="mtc_set_option before running")
+    ap.add_argument("--mode", default="chain", choices=["chain", "launches"],
+                    help="one GPU: the whole step as one prepared chain (mtc_chain_run) or as one mtc_qmv launch per projection")
     ap.add_argument("--streams", type=int, default=1, help="parallel streams for the independent projections of a phase")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary single-kernel measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
@@ -346,6 +348,25 @@ def main():
                     dist.all_reduce(out_local[li][ph])
 
     launches_per_step = 7 * args.layers
+    chain = None
+    if world == 1 and args.mode == "chain":
+        # one prepared chain for the whole step: a persistent grid walks the 224 projections, the four dependent
+        # phases of every layer are device-side counters instead of launch boundaries
+        from metaltile_b200.ops import _projection
+        projs = []
+        for li, mats in enumerate(layers):
+            col = [0, 0, 0, 0]
+            for pi, (w, sc, bi, k, nl, phase) in enumerate(mats):
+                o = out_local[li][phase][:, col[phase]:col[phase] + nl] if M == 1 else tiles[li][pi]
+                col[phase] += nl
+                projs.append(_projection(w, sc, bi, xs[k], BITS, GROUP, [o], phase=li * 4 + phase))
+        chain = ctx.chain_create(projs)
+        if chain.fused:
+            launches_per_step = 1
+
+            def step():      # noqa: F811
+                chain.run(torch.cuda.current_stream().cuda_stream)
+        config["dispatch"] = "one chain per step" if chain.fused else "one launch per projection"
 
     # capture the step in a CUDA graph: 224 launches of ~1-5 us each are otherwise host-bound
     side = torch.cuda.Stream()

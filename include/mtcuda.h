@@ -64,10 +64,17 @@ int mtc_free(mtc_ctx *ctx, void *d_ptr);
 int mtc_upload(mtc_ctx *ctx, void *stream, void *d_dst, const void *h_src, size_t bytes);
 int mtc_download(mtc_ctx *ctx, void *stream, void *h_dst, const void *d_src, size_t bytes);
 int mtc_memset(mtc_ctx *ctx, void *stream, void *d_ptr, int value, size_t bytes);
-int mtc_sync(mtc_ctx *ctx, void *stream); /* commit + waitUntilCompleted (single_dispatch.rs:95-98) */
-/* 0 when no kernel has reported a bounded-wait expiry or a rejected index since
- * the context was created; otherwise a kernel-specific code. */
+/* commit + waitUntilCompleted (single_dispatch.rs:95-98).  Returns MTC_ERR_TIMEOUT when a kernel of this context has
+ * given up on a bounded device-side wait since the status word was last cleared (the kernel has returned, the GPU
+ * is usable, the results are not); mtc_sync_deadline also returns MTC_ERR_TIMEOUT when the stream has not finished
+ * after timeout_ms milliseconds of host time (timeout_ms < 0: wait without a deadline). */
+int mtc_sync(mtc_ctx *ctx, void *stream);
+int mtc_sync_deadline(mtc_ctx *ctx, void *stream, int timeout_ms);
+/* 0 when no kernel has reported a bounded-wait expiry or a rejected index since the context was created or the
+ * word was cleared; otherwise the code of the first report: 0x101-0x402 roles of the tensor-core kernel, 0x601 + r
+ * rank r never arrived at a peer barrier, 0x701 / 0x702 phase counter / partial-sum slot of a chained launch. */
 int mtc_status_word(mtc_ctx *ctx, uint32_t *word);
+int mtc_status_clear(mtc_ctx *ctx);
 
 /* ---- typed ops (device pointers, asynchronous on `stream`) ---- */
 
@@ -89,10 +96,44 @@ int mtc_qmv(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
  * Ragged M needs no padding (the reference pads to 32: quantized_mma_dynamic_m.rs:46-112). */
 int mtc_qmm(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases,
             const void *x, void *out, int M, int N, int K, int bits, int group_size, int dtype);
-/* Name of the kernel family mtc_qmm would run for these arguments
- * ("qmv_cuda_core", "qmv_mma_sync", "qmm_tcgen05"); the analogue of asserting on
+/* Name of the kernel family mtc_qmm would run for these arguments with aligned pointers and default options
+ * ("qmv_stream", "qmv_cuda_core", "qmv_mma_sync", "qmm_tcgen05"); the analogue of asserting on
  * mt_qmm_for's routing (quantized.rs:5127-5199). */
 const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dtype);
+
+/* ---- fused and chained decode projections ----
+ * mtc_qmv_desc: one projection, the arguments of mtc_qmv plus up to 8 destinations of the [M, N] result (each gets
+ * the same bytes: local buffer, peer GPUs' buffers) and, in a chain, the phase it belongs to.
+ *
+ * mtc_qmv_batched: 1 to 4 projections that read the SAME activations (same x, M, K, dtype) in one launch, each
+ * writing its own output.  With the outputs laid out one after the other this is ffai_batched_qkv_qgemv(_fast)
+ * (crates/metaltile-std/src/ffai/batched_qkv_qgemv.rs:1-35: q, k, v in one dispatch, one concatenated result) and
+ * ffai_batched_4_qgemv (crates/metaltile-std/src/ffai/batched_4_qgemv.rs:1-45).  Shapes outside the streaming
+ * kernel's contract (4-bit, f16 / bf16, M <= 8, K % 256 == 0, group 64 or 128) run as separate mtc_qmv launches.
+ *
+ * mtc_chain_*: a prepared list of projections walked by ONE persistent grid, the counterpart of
+ * Context::dispatch_chain (crates/metaltile-runtime/src/context.rs:363-395: several passes, one commit, ordering
+ * between passes, no host round trip).  Projections of one phase are independent; a projection of phase p may read
+ * (as x) what phases < p wrote: the grid passes a device-side counter between phases (bounded wait: status word
+ * 0x701 on expiry) instead of a launch boundary, and keeps requesting the weights of later phases meanwhile.
+ * Phases start at 0 and grow by at most one from one projection to the next.  mtc_chain_create copies the
+ * descriptors (the buffers they name must stay valid and in place until mtc_chain_destroy); mtc_chain_run is
+ * asynchronous on `stream` and may be captured in a CUDA graph; runs of one chain must not overlap on the GPU.
+ * Chains outside the streaming kernel's contract run as one mtc_qmv launch per projection, in order. */
+typedef struct {
+    const void *w, *scales, *biases, *x;
+    void *outs[8];
+    int n_outs;
+    int M, N, K, bits, group_size, dtype;
+    int phase;
+} mtc_qmv_desc;
+typedef struct mtc_chain mtc_chain;
+int mtc_qmv_batched(mtc_ctx *ctx, void *stream, const mtc_qmv_desc *descs, int n);
+int mtc_chain_create(mtc_ctx *ctx, const mtc_qmv_desc *descs, int n, mtc_chain **out_chain);
+int mtc_chain_run(mtc_ctx *ctx, void *stream, mtc_chain *chain);
+int mtc_chain_destroy(mtc_ctx *ctx, mtc_chain *chain);
+/* 1 when the chain runs on the persistent streaming kernel, 0 when it falls back to one launch per projection. */
+int mtc_chain_is_fused(const mtc_chain *chain);
 
 /* ---- sharded decode: the output all-gather done by the kernel's own stores (one process per GPU) ----
  * None of these has a counterpart in the reference, which is a single-device library; they serve the N-split

@@ -20,6 +20,14 @@ STATUS_NAMES = {
 }
 
 
+class QmvDesc(ctypes.Structure):
+    """mtc_qmv_desc: one projection of a fused launch or of a chain."""
+    _fields_ = [("w", ctypes.c_void_p), ("scales", ctypes.c_void_p), ("biases", ctypes.c_void_p), ("x", ctypes.c_void_p),
+                ("outs", ctypes.c_void_p * 8), ("n_outs", ctypes.c_int), ("M", ctypes.c_int), ("N", ctypes.c_int),
+                ("K", ctypes.c_int), ("bits", ctypes.c_int), ("group_size", ctypes.c_int), ("dtype", ctypes.c_int),
+                ("phase", ctypes.c_int)]
+
+
 class NamedBuf(ctypes.Structure):
     _fields_ = [("name", ctypes.c_char_p), ("data", ctypes.c_void_p), ("bytes", ctypes.c_size_t),
                 ("is_output", ctypes.c_int)]
@@ -40,11 +48,18 @@ SIGNATURES = {
     "mtc_download": (_i, [_vp, _vp, _vp, _vp, _sz]),
     "mtc_memset": (_i, [_vp, _vp, _vp, _i, _sz]),
     "mtc_sync": (_i, [_vp, _vp]),
+    "mtc_sync_deadline": (_i, [_vp, _vp, _i]),
     "mtc_status_word": (_i, [_vp, ctypes.POINTER(ctypes.c_uint32)]),
+    "mtc_status_clear": (_i, [_vp]),
     "mtc_qmv": (_i, _DENSE),
     "mtc_qmm": (_i, _DENSE),
     "mtc_qmm_route": (ctypes.c_char_p, [_i, _i, _i, _i, _i, _i]),
     "mtc_qmv_multi": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i]),
+    "mtc_qmv_batched": (_i, [_vp, _vp, ctypes.POINTER(QmvDesc), _i]),
+    "mtc_chain_create": (_i, [_vp, ctypes.POINTER(QmvDesc), _i, ctypes.POINTER(_vp)]),
+    "mtc_chain_run": (_i, [_vp, _vp, _vp]),
+    "mtc_chain_destroy": (_i, [_vp, _vp]),
+    "mtc_chain_is_fused": (_i, [_vp]),
     "mtc_ipc_export": (_i, [_vp, _vp, _vp]),
     "mtc_ipc_open": (_i, [_vp, _vp, ctypes.POINTER(_vp)]),
     "mtc_ipc_close": (_i, [_vp, _vp]),

@@ -17,7 +17,7 @@ from dataclasses import dataclass, field
 from typing import Dict, Mapping, Optional, Sequence
 
 from . import _lib
-from ._lib import BF16, F16, F32, NamedBuf
+from ._lib import BF16, F16, F32, NamedBuf, QmvDesc
 
 DTYPES = {"f32": F32, "f16": F16, "bf16": BF16}
 
@@ -83,8 +83,16 @@ class Context:
         self._check(self._lib.mtc_status_word(self._h, ctypes.byref(w)))
         return int(w.value)
 
-    def sync(self, stream: int = 0):
-        self._check(self._lib.mtc_sync(self._h, ctypes.c_void_p(stream)))
+    def status_clear(self):
+        self._check(self._lib.mtc_status_clear(self._h))
+
+    def sync(self, stream: int = 0, timeout_ms: Optional[int] = None):
+        """Wait for ``stream``; raises ``Timeout`` if a kernel gave up on a bounded wait, or (with ``timeout_ms``)
+        if the stream is still running after that many milliseconds."""
+        if timeout_ms is None:
+            self._check(self._lib.mtc_sync(self._h, ctypes.c_void_p(stream)))
+        else:
+            self._check(self._lib.mtc_sync_deadline(self._h, ctypes.c_void_p(stream), int(timeout_ms)))
 
     # ---- name-keyed host-buffer dispatch ----------------------------------------
     def dispatch_with_grid(self, kernel: str, buffers: Mapping[str, bytes],
@@ -135,6 +143,35 @@ class Context:
         arr = (ctypes.c_void_p * len(outs))(*[int(o) for o in outs])
         self._check(self._lib.mtc_qmv_multi(self._h, stream, w, scales, biases, x, arr, len(outs), M, N, K, bits,
                                             group_size, _dt(dtype)))
+
+    # ---- fused and chained decode projections ---------------------------------------
+    @staticmethod
+    def _descs(projections):
+        """``projections``: dicts with w, scales, biases, x, outs (list of device pointers), M, N, K, bits,
+        group_size, dtype and optionally phase -> a ctypes array of ``mtc_qmv_desc``."""
+        arr = (QmvDesc * len(projections))()
+        for d, p in zip(arr, projections):
+            d.w, d.scales, d.biases, d.x = int(p["w"]), int(p["scales"]), int(p["biases"]), int(p["x"])
+            outs = list(p["outs"])
+            for i, o in enumerate(outs):
+                d.outs[i] = int(o)
+            d.n_outs = len(outs)
+            d.M, d.N, d.K = int(p["M"]), int(p["N"]), int(p["K"])
+            d.bits, d.group_size, d.dtype = int(p["bits"]), int(p["group_size"]), _dt(p["dtype"])
+            d.phase = int(p.get("phase", 0))
+        return arr
+
+    def qmv_batched(self, projections, stream: int = 0):
+        """1 to 4 projections that read the same activations, one launch (``mtc_qmv_batched``)."""
+        arr = self._descs(projections)
+        self._check(self._lib.mtc_qmv_batched(self._h, stream, arr, len(projections)))
+
+    def chain_create(self, projections) -> "Chain":
+        """A prepared list of projections walked by one persistent grid (``mtc_chain_create``)."""
+        arr = self._descs(projections)
+        h = ctypes.c_void_p()
+        self._check(self._lib.mtc_chain_create(self._h, arr, len(projections), ctypes.byref(h)))
+        return Chain(self, h)
 
     # ---- buffers shared between the rank processes of one node --------------------
     def alloc(self, nbytes: int) -> int:
@@ -212,3 +249,29 @@ class Context:
 
     def unpack_codes(self, w, codes, N, K, bits, stream: int = 0):
         self._check(self._lib.mtc_unpack_codes(self._h, stream, w, codes, N, K, bits))
+
+
+class Chain:
+    """Handle of ``mtc_chain``: ``run(stream)`` enqueues every projection of the list, ``close()`` frees it.
+    Mirrors the passes handed to ``Context::dispatch_chain`` (crates/metaltile-runtime/src/context.rs:363-395)."""
+
+    def __init__(self, ctx: Context, handle):
+        self._ctx, self._h = ctx, handle
+
+    @property
+    def fused(self) -> bool:
+        return bool(self._ctx._lib.mtc_chain_is_fused(self._h))
+
+    def run(self, stream: int = 0):
+        self._ctx._check(self._ctx._lib.mtc_chain_run(self._ctx._h, stream, self._h))
+
+    def close(self):
+        if self._h:
+            self._ctx._lib.mtc_chain_destroy(self._ctx._h, self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -30,6 +30,9 @@ struct Ctx {
     int qmm_mma_chunks = 1;        // option "qmm_mma_chunks": 0 = 17 <= M <= 64 always on the tcgen05 kernel
     int qmm_raw = 1;               // option "qmm_raw": 0 = dequant warps load their packed words straight from global memory
     int qmm_pair = 0;              // option "qmm_pair": 1 = give a work item two adjacent weight-row tiles
+    uint32_t peer_poll_limit = 1u << 22;   // option "peer_poll_limit": polls of mtc_peer_barrier before it gives up on a peer
+    int qmv_stream = 1;            // option "qmv_stream": 0 = never use the streaming decode kernel (qmv_stream.cu)
+    int pdl_early_weights = 1;     // option "pdl_early_weights": 0 = no load of w / scales / biases before the previous kernel of the stream is complete
     void *d_worklist = nullptr;    // gather_qmm work list (grow-only, owned by the context)
     size_t worklist_bytes = 0;
     void *d_xconv = nullptr;       // scaled-f16 copy of bf16 activations for the tensor-core kernels (grow-only)
@@ -42,6 +45,22 @@ inline int fail(Ctx *ctx, int code, const std::string &msg) {
 }
 
 inline size_t dtype_size(int dt) { return dt == MTC_F32 ? 4 : 2; }
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to (kernel, device): one flag per device, not per process.
+// set(fn) applies `bytes` to the kernel on the current device the first time that device launches it.
+struct PerDeviceAttr {
+    bool done[64] = {};
+    template <typename Fn>
+    cudaError_t set(Fn fn, size_t bytes) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64 && done[dev]) return cudaSuccess;
+        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+        if (e == cudaSuccess && dev >= 0 && dev < 64) done[dev] = true;
+        return e;
+    }
+};
 
 // ---- dtype-generic element access (dtype is a launch-time constant) ----------
 __device__ __forceinline__ float ld_as_f32(const void *p, size_t i, int dt) {
@@ -82,6 +101,15 @@ cudaError_t launch_qmv(Ctx *ctx, cudaStream_t st, const void *w, const void *sca
 cudaError_t launch_peer_barrier(Ctx *ctx, cudaStream_t st, uint32_t *const *peer_flags, int n_peers, int rank,
                                 uint32_t *local_flags, uint32_t *epoch);
 cudaError_t qmv_init_device();
+// streaming decode kernel (qmv_stream.cu): 1-4 projections that share x in one launch, and prepared chains
+bool qmv_stream_supported(int M, int N, int K, int bits, int group_size, int dt, const void *w, const void *scales,
+                          const void *biases, const void *x);
+cudaError_t qmv_stream_init_device();
+cudaError_t launch_qmv_stream(Ctx *ctx, cudaStream_t st, const mtc_qmv_desc *descs, int n);
+struct StreamChain;
+cudaError_t stream_chain_create(Ctx *ctx, const mtc_qmv_desc *descs, int n, StreamChain **out, std::string *why);
+cudaError_t stream_chain_run(Ctx *ctx, cudaStream_t st, StreamChain *c);
+void stream_chain_destroy(StreamChain *c);
 bool qmv_mma_supported(int M, int N, int K, int bits, int group_size, int dt, const void *w, const void *x);
 cudaError_t launch_qmv_mma(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases, const void *x,
                            void *out, int M, int N, int K, int group_size, int dt);

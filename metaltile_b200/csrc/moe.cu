@@ -314,12 +314,9 @@ cudaError_t launch_router_topk(cudaStream_t st, const void *logits, uint32_t *id
 cudaError_t launch_moe_sort(cudaStream_t st, const uint32_t *topk_idx, int n_tokens, int k, int n_experts, uint32_t *sti,
                             uint32_t *inv, uint32_t *offsets, uint32_t *row_expert, uint32_t *status) {
     const size_t smem = (static_cast<size_t>(n_experts) + 1 + 32 * static_cast<size_t>(n_experts)) * sizeof(uint32_t);
-    static bool attr = false;
-    if (!attr) {
-        cudaError_t e = cudaFuncSetAttribute(moe_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e != cudaSuccess) return e;
-        attr = true;
-    }
+    static PerDeviceAttr attr;
+    cudaError_t e = attr.set(moe_sort_kernel, 200 * 1024);
+    if (e != cudaSuccess) return e;
     moe_sort_kernel<<<1, kSortThreads, smem, st>>>(topk_idx, n_tokens * k, k, n_experts, sti, inv, offsets, row_expert, status);
     return cudaGetLastError();
 }

@@ -9,7 +9,6 @@ namespace mtc {
 namespace {
 
 constexpr int kMaxPeersB = 8;
-constexpr uint32_t kPollLimit = 1u << 22;     // bounded wait: a few seconds, then the status word says so
 
 struct BarrierArgs {
     uint32_t *peer_flags[kMaxPeersB];   // peer p's flag array (kMaxPeersB words), mapped into this process
@@ -17,6 +16,7 @@ struct BarrierArgs {
     uint32_t *epoch;                    // this rank's barrier counter (the same sequence on every rank)
     uint32_t *status;
     int n_peers, rank;
+    uint32_t poll_limit;                // bounded wait: 2^22 polls (a few seconds) unless the context says otherwise
 };
 
 // <<<1, 32>>>.  After griddepcontrol.wait the kernels before this one (the stores into the peers' buffers) have
@@ -33,7 +33,7 @@ __global__ void peer_barrier_kernel(const BarrierArgs a) {
         __threadfence_system();
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.peer_flags[p] + a.rank), "r"(e) : "memory");
         bool seen = false;
-        for (uint32_t i = 0; i < kPollLimit; ++i) {
+        for (uint32_t i = 0; i < a.poll_limit; ++i) {
             uint32_t v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.local_flags + p) : "memory");
             if (static_cast<int32_t>(v - e) >= 0) {
@@ -64,6 +64,7 @@ cudaError_t launch_peer_barrier(Ctx *ctx, cudaStream_t st, uint32_t *const *peer
     a.status = ctx->d_status;
     a.n_peers = n_peers;
     a.rank = rank;
+    a.poll_limit = ctx->peer_poll_limit;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(1);
     cfg.blockDim = dim3(32);

@@ -818,12 +818,9 @@ cudaError_t launch_bits(cudaStream_t st, const CUtensorMap &tmap, const QmmParam
     auto kern = qmm_tcgen05_kernel<BITS>;
     constexpr size_t smem = qmm_smem_bytes<BITS>();
     static_assert(smem <= 227 * 1024, "shared memory budget");
-    static bool attr_set = false;   // one process drives one device (one rank per GPU)
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    static PerDeviceAttr attr;
+    cudaError_t e = attr.set(kern, smem);
+    if (e != cudaSuccess) return e;
     kern<<<grid, NUM_THREADS, smem, st>>>(tmap, p);
     return cudaGetLastError();
 }

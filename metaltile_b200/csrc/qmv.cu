@@ -553,12 +553,9 @@ cudaError_t launch_pipe(Ctx *ctx, cudaStream_t st, QmvArgs a, size_t per_jb, siz
     if constexpr (MT == 1) {
         if (tail) {        // multi-destination instantiation: same configuration, one more parameter
             auto mk = qmv_pipe_kernel<BITS, MT, kRows, V, PF, true>;
-            static bool attr_set = false;
-            if (!attr_set) {
-                e = cudaFuncSetAttribute(mk, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemPipe + 4096));
-                if (e != cudaSuccess) return e;
-                attr_set = true;
-            }
+            static PerDeviceAttr attr;
+            e = attr.set(mk, kSmemPipe + 4096);
+            if (e != cudaSuccess) return e;
             return cudaLaunchKernelEx(&cfg, mk, a, *tail);
         }
     }

@@ -617,14 +617,10 @@ cudaError_t launch_ring(Ctx *ctx, cudaStream_t st, MmaArgs a) {
     const int slots = kRingWarps >> best_ksh;
     a.iters = (max_tiles + slots - 1) / slots;
     constexpr size_t smem = ring_smem_bytes<NT>();
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(qmv_mma_ring_kernel<NT, BF16, true, GSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(qmv_mma_ring_kernel<NT, BF16, false, GSH>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    static PerDeviceAttr attr_full, attr_part;
+    cudaError_t e = attr_full.set(qmv_mma_ring_kernel<NT, BF16, true, GSH>, smem);
+    if (e == cudaSuccess) e = attr_part.set(qmv_mma_ring_kernel<NT, BF16, false, GSH>, smem);
+    if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kRingWarps * 32);
@@ -664,12 +660,9 @@ cudaError_t launch_mma(Ctx *ctx, cudaStream_t st, MmaArgs a) {
     a.iters = (max_tiles + slots - 1) / slots;
     constexpr size_t smem = mma_smem_bytes<NT>();
     auto kernel = qmv_mma_kernel<NT, BF16>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(qmv_mma_kernel<NT, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    static PerDeviceAttr smem_attr;
+    cudaError_t e = smem_attr.set(qmv_mma_kernel<NT, BF16>, smem);
+    if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kMmaWarps * 32);

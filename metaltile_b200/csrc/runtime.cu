@@ -1,10 +1,12 @@
 // Runtime behind include/mtcuda.h: context, device memory, the typed entry points and
 // the name-keyed host-buffer dispatch that mirrors Context::dispatch_with_grid
 // (crates/metaltile-runtime/src/context.rs:269-284).
+#include <chrono>
 #include <cstdio>
 #include <cstring>
 #include <map>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "common.cuh"
@@ -23,6 +25,17 @@ thread_local std::string g_no_ctx_error;
         cudaError_t e__ = (expr);                                                              \
         if (e__ != cudaSuccess)                                                                \
             return fail(ctx, code, std::string(#expr) + ": " + cudaGetErrorString(e__));      \
+    } while (0)
+
+// Every entry runs with its context's device current: one host thread may drive contexts on several devices.
+#define MTC_ENTER(ctx)                                                                                  \
+    do {                                                                                                \
+        int cur__ = -1;                                                                                 \
+        if (cudaGetDevice(&cur__) != cudaSuccess || cur__ != (ctx)->device) {                           \
+            cudaError_t e__ = cudaSetDevice((ctx)->device);                                             \
+            if (e__ != cudaSuccess)                                                                     \
+                return fail(ctx, MTC_ERR_NO_DEVICE, std::string("cudaSetDevice: ") + cudaGetErrorString(e__)); \
+        }                                                                                               \
     } while (0)
 
 bool dtype_ok(int dt) { return dt == MTC_F32 || dt == MTC_F16 || dt == MTC_BF16; }
@@ -181,6 +194,7 @@ int mtc_init(int device, mtc_ctx **out_ctx) {
     if ((e = cudaMalloc(&ctx->d_status, sizeof(uint32_t))) != cudaSuccess ||
         (e = cudaMemset(ctx->d_status, 0, sizeof(uint32_t))) != cudaSuccess ||
         (e = mtc::qmv_init_device()) != cudaSuccess ||
+        (e = mtc::qmv_stream_init_device()) != cudaSuccess ||
         (e = cudaMalloc(&ctx->d_worklist, 4u << 20)) != cudaSuccess) {
         g_no_ctx_error = std::string("context set-up: ") + cudaGetErrorString(e);
         delete ctx;
@@ -206,6 +220,7 @@ const char *mtc_last_error(mtc_ctx *ctx) { return ctx ? ctx->last_error.c_str() 
 
 int mtc_device_info(mtc_ctx *ctx, char *json, size_t cap) {
     if (!ctx || !json || cap == 0) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     cudaDeviceProp prop{};
     MTC_CUDA(ctx, cudaGetDeviceProperties(&prop, ctx->device), MTC_ERR_NO_DEVICE);
     int drv = 0, rt = 0;
@@ -223,6 +238,7 @@ int mtc_device_info(mtc_ctx *ctx, char *json, size_t cap) {
 
 int mtc_alloc(mtc_ctx *ctx, size_t bytes, void **d_ptr) {
     if (!ctx || !d_ptr) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     *d_ptr = nullptr;
     if (bytes == 0) return MTC_OK;
     MTC_CUDA(ctx, cudaMalloc(d_ptr, bytes), MTC_ERR_BUFFER);
@@ -231,12 +247,14 @@ int mtc_alloc(mtc_ctx *ctx, size_t bytes, void **d_ptr) {
 
 int mtc_free(mtc_ctx *ctx, void *d_ptr) {
     if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     if (d_ptr) MTC_CUDA(ctx, cudaFree(d_ptr), MTC_ERR_BUFFER);
     return MTC_OK;
 }
 
 int mtc_upload(mtc_ctx *ctx, void *stream, void *d_dst, const void *h_src, size_t bytes) {
     if (!ctx || (bytes && (!d_dst || !h_src))) return fail(ctx, MTC_ERR_INVALID, "upload: null pointer");
+    MTC_ENTER(ctx);
     if (bytes)
         MTC_CUDA(ctx, cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)),
                  MTC_ERR_BUFFER);
@@ -245,6 +263,7 @@ int mtc_upload(mtc_ctx *ctx, void *stream, void *d_dst, const void *h_src, size_
 
 int mtc_download(mtc_ctx *ctx, void *stream, void *h_dst, const void *d_src, size_t bytes) {
     if (!ctx || (bytes && (!h_dst || !d_src))) return fail(ctx, MTC_ERR_INVALID, "download: null pointer");
+    MTC_ENTER(ctx);
     if (bytes)
         MTC_CUDA(ctx, cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)),
                  MTC_ERR_BUFFER);
@@ -253,28 +272,87 @@ int mtc_download(mtc_ctx *ctx, void *stream, void *h_dst, const void *d_src, siz
 
 int mtc_memset(mtc_ctx *ctx, void *stream, void *d_ptr, int value, size_t bytes) {
     if (!ctx || (bytes && !d_ptr)) return fail(ctx, MTC_ERR_INVALID, "memset: null pointer");
+    MTC_ENTER(ctx);
     if (bytes) MTC_CUDA(ctx, cudaMemsetAsync(d_ptr, value, bytes, static_cast<cudaStream_t>(stream)), MTC_ERR_BUFFER);
+    return MTC_OK;
+}
+
+// A kernel that gave up on a bounded wait (or rejected an index) leaves a code in the status word and returns; the
+// host learns of it at the next synchronising call.
+static int check_status(mtc_ctx *ctx, const char *who) {
+    uint32_t word = 0;
+    MTC_CUDA(ctx, cudaMemcpy(&word, ctx->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost), MTC_ERR_DISPATCH);
+    if (word != 0) {
+        char buf[160];
+        std::snprintf(buf, sizeof(buf), "%s: a kernel reported status 0x%x (a bounded device-side wait expired or an index was rejected); "
+                      "results of that stream are not valid", who, word);
+        return fail(ctx, MTC_ERR_TIMEOUT, buf);
+    }
     return MTC_OK;
 }
 
 int mtc_sync(mtc_ctx *ctx, void *stream) {
     if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     MTC_CUDA(ctx, cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), MTC_ERR_DISPATCH);
-    return MTC_OK;
+    return check_status(ctx, "sync");
+}
+
+int mtc_sync_deadline(mtc_ctx *ctx, void *stream, int timeout_ms) {
+    if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    if (timeout_ms < 0) return mtc_sync(ctx, stream);
+    cudaEvent_t ev = nullptr;
+    MTC_CUDA(ctx, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming), MTC_ERR_DISPATCH);
+    cudaError_t e = cudaEventRecord(ev, static_cast<cudaStream_t>(stream));
+    const auto t0 = std::chrono::steady_clock::now();
+    while (e == cudaSuccess) {
+        e = cudaEventQuery(ev);
+        if (e == cudaSuccess) break;
+        if (e != cudaErrorNotReady) break;
+        e = cudaSuccess;
+        const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (ms >= timeout_ms) {
+            cudaEventDestroy(ev);
+            return fail(ctx, MTC_ERR_TIMEOUT, "sync: the stream did not finish within " + std::to_string(timeout_ms) + " ms (it keeps running)");
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+    cudaEventDestroy(ev);
+    if (e != cudaSuccess) return fail(ctx, MTC_ERR_DISPATCH, std::string("sync: ") + cudaGetErrorString(e));
+    return check_status(ctx, "sync");
 }
 
 int mtc_status_word(mtc_ctx *ctx, uint32_t *word) {
     if (!ctx || !word) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     MTC_CUDA(ctx, cudaMemcpy(word, ctx->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost), MTC_ERR_DISPATCH);
+    return MTC_OK;
+}
+
+int mtc_status_clear(mtc_ctx *ctx) {
+    if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    MTC_CUDA(ctx, cudaMemset(ctx->d_status, 0, sizeof(uint32_t)), MTC_ERR_DISPATCH);
     return MTC_OK;
 }
 
 int mtc_qmv(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x,
             void *out, int M, int N, int K, int bits, int group_size, int dtype) {
     if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "qmv: dtype must be f32, f16 or bf16");
     if (M > 0 && N > 0 && (!w || !scales || !biases || !x || !out)) return fail(ctx, MTC_ERR_INVALID, "qmv: null pointer");
     std::string why;
+    if (ctx->qmv_stream && mtc::qmv_stream_supported(M, N, K, bits, group_size, dtype, w, scales, biases, x)) {
+        mtc_qmv_desc d{};
+        d.w = w; d.scales = scales; d.biases = biases; d.x = x;
+        d.outs[0] = out; d.n_outs = 1;
+        d.M = M; d.N = N; d.K = K; d.bits = bits; d.group_size = group_size; d.dtype = dtype;
+        cudaError_t e1 = mtc::launch_qmv_stream(ctx, static_cast<cudaStream_t>(stream), &d, 1);
+        if (e1 != cudaSuccess) return fail(ctx, MTC_ERR_DISPATCH, std::string("qmv (stream) launch: ") + cudaGetErrorString(e1));
+        return MTC_OK;
+    }
     if (ctx->qmv_small_m_mma && (M >= 2 || ctx->qmv_small_m_mma == 2) &&
         mtc::qmv_mma_supported(M < 2 ? 2 : M, N, K, bits, group_size, dtype, w, x)) {
         cudaError_t e2 = mtc::launch_qmv_mma(ctx, static_cast<cudaStream_t>(stream), w, scales, biases, x, out, M, N, K,
@@ -292,12 +370,23 @@ int mtc_qmv(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
 int mtc_qmv_multi(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x,
                   void *const *outs, int n_outs, int M, int N, int K, int bits, int group_size, int dtype) {
     if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "qmv_multi: dtype must be f32, f16 or bf16");
     if (!outs || n_outs < 1 || n_outs > 8) return fail(ctx, MTC_ERR_INVALID, "qmv_multi: 1 to 8 outputs");
     for (int i = 0; i < n_outs; ++i)
         if (!outs[i]) return fail(ctx, MTC_ERR_INVALID, "qmv_multi: null output");
     if (M > 0 && N > 0 && (!w || !scales || !biases || !x)) return fail(ctx, MTC_ERR_INVALID, "qmv_multi: null pointer");
     std::string why;
+    if (ctx->qmv_stream && M > 0 && N > 0 && mtc::qmv_stream_supported(M, N, K, bits, group_size, dtype, w, scales, biases, x)) {
+        mtc_qmv_desc d{};
+        d.w = w; d.scales = scales; d.biases = biases; d.x = x;
+        for (int i = 0; i < n_outs; ++i) d.outs[i] = outs[i];
+        d.n_outs = n_outs;
+        d.M = M; d.N = N; d.K = K; d.bits = bits; d.group_size = group_size; d.dtype = dtype;
+        cudaError_t e1 = mtc::launch_qmv_stream(ctx, static_cast<cudaStream_t>(stream), &d, 1);
+        if (e1 != cudaSuccess) return fail(ctx, MTC_ERR_DISPATCH, std::string("qmv_multi (stream) launch: ") + cudaGetErrorString(e1));
+        return MTC_OK;
+    }
     cudaError_t e = mtc::launch_qmv(ctx, static_cast<cudaStream_t>(stream), w, scales, biases, x, outs[0], M, N, K, bits,
                                     group_size, dtype, &why, outs + 1, n_outs - 1);
     if (e == cudaErrorInvalidValue && !why.empty()) return fail(ctx, MTC_ERR_UNSUPPORTED, why);
@@ -305,8 +394,113 @@ int mtc_qmv_multi(mtc_ctx *ctx, void *stream, const void *w, const void *scales,
     return MTC_OK;
 }
 
+static int check_desc(mtc_ctx *ctx, const mtc_qmv_desc &d, const char *who) {
+    if (!dtype_ok(d.dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, std::string(who) + ": dtype must be f32, f16 or bf16");
+    if (d.n_outs < 1 || d.n_outs > 8) return fail(ctx, MTC_ERR_INVALID, std::string(who) + ": 1 to 8 outputs per projection");
+    for (int i = 0; i < d.n_outs; ++i)
+        if (!d.outs[i]) return fail(ctx, MTC_ERR_INVALID, std::string(who) + ": null output");
+    if (d.M < 0 || d.N < 0 || d.K <= 0) return fail(ctx, MTC_ERR_INVALID, std::string(who) + ": bad shape");
+    if (d.M > 0 && d.N > 0 && (!d.w || !d.scales || !d.biases || !d.x)) return fail(ctx, MTC_ERR_INVALID, std::string(who) + ": null pointer");
+    return MTC_OK;
+}
+
+int mtc_qmv_batched(mtc_ctx *ctx, void *stream, const mtc_qmv_desc *descs, int n) {
+    if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    if (!descs || n < 1 || n > 4) return fail(ctx, MTC_ERR_INVALID, "qmv_batched: 1 to 4 projections");
+    bool fused = ctx->qmv_stream != 0;
+    for (int i = 0; i < n; ++i) {
+        int rc = check_desc(ctx, descs[i], "qmv_batched");
+        if (rc != MTC_OK) return rc;
+        const mtc_qmv_desc &d = descs[i];
+        if (d.x != descs[0].x || d.M != descs[0].M || d.K != descs[0].K || d.dtype != descs[0].dtype)
+            return fail(ctx, MTC_ERR_INVALID, "qmv_batched: the projections must share x, M, K and dtype");
+        fused = fused && d.M > 0 && d.N > 0 &&
+                mtc::qmv_stream_supported(d.M, d.N, d.K, d.bits, d.group_size, d.dtype, d.w, d.scales, d.biases, d.x);
+    }
+    if (fused) {
+        cudaError_t e = mtc::launch_qmv_stream(ctx, static_cast<cudaStream_t>(stream), descs, n);
+        if (e != cudaSuccess) return fail(ctx, MTC_ERR_DISPATCH, std::string("qmv_batched launch: ") + cudaGetErrorString(e));
+        return MTC_OK;
+    }
+    for (int i = 0; i < n; ++i) {
+        const mtc_qmv_desc &d = descs[i];
+        int rc = d.n_outs == 1 ? mtc_qmv(ctx, stream, d.w, d.scales, d.biases, d.x, d.outs[0], d.M, d.N, d.K, d.bits, d.group_size, d.dtype)
+                               : mtc_qmv_multi(ctx, stream, d.w, d.scales, d.biases, d.x, d.outs, d.n_outs, d.M, d.N, d.K, d.bits,
+                                               d.group_size, d.dtype);
+        if (rc != MTC_OK) return rc;
+    }
+    return MTC_OK;
+}
+
+struct mtc_chain {
+    mtc::StreamChain *fused = nullptr;        // the persistent-grid form, or
+    std::vector<mtc_qmv_desc> descs;          // one launch per projection, in order
+};
+
+int mtc_chain_create(mtc_ctx *ctx, const mtc_qmv_desc *descs, int n, mtc_chain **out_chain) {
+    if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    if (!descs || n < 1 || !out_chain) return fail(ctx, MTC_ERR_INVALID, "chain_create: need at least one projection");
+    *out_chain = nullptr;
+    int phase_prev = 0;
+    for (int i = 0; i < n; ++i) {
+        int rc = check_desc(ctx, descs[i], "chain_create");
+        if (rc != MTC_OK) return rc;
+        if (descs[i].phase < phase_prev || descs[i].phase > phase_prev + 1 || (i == 0 && descs[i].phase != 0))
+            return fail(ctx, MTC_ERR_INVALID, "chain_create: phases start at 0 and grow by at most one from one projection to the next");
+        phase_prev = descs[i].phase;
+    }
+    MTC_CUDA(ctx, cudaSetDevice(ctx->device), MTC_ERR_NO_DEVICE);
+    mtc_chain *c = new mtc_chain();
+    c->descs.assign(descs, descs + n);
+    if (ctx->qmv_stream) {
+        std::string why;
+        cudaError_t e = mtc::stream_chain_create(ctx, descs, n, &c->fused, &why);
+        if (e != cudaSuccess && e != cudaErrorInvalidValue) {
+            delete c;
+            return fail(ctx, MTC_ERR_BUFFER, std::string("chain_create: ") + cudaGetErrorString(e));
+        }
+        if (e != cudaSuccess) {
+            c->fused = nullptr;                // outside the streaming kernel's contract: one launch per projection
+            cudaGetLastError();
+        }
+    }
+    *out_chain = c;
+    return MTC_OK;
+}
+
+int mtc_chain_is_fused(const mtc_chain *chain) { return chain && chain->fused ? 1 : 0; }
+
+int mtc_chain_run(mtc_ctx *ctx, void *stream, mtc_chain *chain) {
+    if (!ctx || !chain) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    if (chain->fused) {
+        cudaError_t e = mtc::stream_chain_run(ctx, static_cast<cudaStream_t>(stream), chain->fused);
+        if (e != cudaSuccess) return fail(ctx, MTC_ERR_DISPATCH, std::string("chain_run launch: ") + cudaGetErrorString(e));
+        return MTC_OK;
+    }
+    for (const mtc_qmv_desc &d : chain->descs) {
+        int rc = d.n_outs == 1 ? mtc_qmv(ctx, stream, d.w, d.scales, d.biases, d.x, d.outs[0], d.M, d.N, d.K, d.bits, d.group_size, d.dtype)
+                               : mtc_qmv_multi(ctx, stream, d.w, d.scales, d.biases, d.x, d.outs, d.n_outs, d.M, d.N, d.K, d.bits,
+                                               d.group_size, d.dtype);
+        if (rc != MTC_OK) return rc;
+    }
+    return MTC_OK;
+}
+
+int mtc_chain_destroy(mtc_ctx *ctx, mtc_chain *chain) {
+    if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    if (!chain) return MTC_OK;
+    if (chain->fused) mtc::stream_chain_destroy(chain->fused);
+    delete chain;
+    return MTC_OK;
+}
+
 int mtc_ipc_export(mtc_ctx *ctx, void *d_ptr, void *handle64) {
     if (!ctx || !d_ptr || !handle64) return fail(ctx, MTC_ERR_INVALID, "ipc_export: null pointer");
+    MTC_ENTER(ctx);
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
     MTC_CUDA(ctx, cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t *>(handle64), d_ptr), MTC_ERR_BUFFER);
     return MTC_OK;
@@ -314,6 +508,7 @@ int mtc_ipc_export(mtc_ctx *ctx, void *d_ptr, void *handle64) {
 
 int mtc_ipc_open(mtc_ctx *ctx, const void *handle64, void **d_ptr) {
     if (!ctx || !handle64 || !d_ptr) return fail(ctx, MTC_ERR_INVALID, "ipc_open: null pointer");
+    MTC_ENTER(ctx);
     cudaIpcMemHandle_t h;
     std::memcpy(&h, handle64, sizeof(h));
     MTC_CUDA(ctx, cudaIpcOpenMemHandle(d_ptr, h, cudaIpcMemLazyEnablePeerAccess), MTC_ERR_BUFFER);
@@ -322,6 +517,7 @@ int mtc_ipc_open(mtc_ctx *ctx, const void *handle64, void **d_ptr) {
 
 int mtc_ipc_close(mtc_ctx *ctx, void *d_ptr) {
     if (!ctx || !d_ptr) return fail(ctx, MTC_ERR_INVALID, "ipc_close: null pointer");
+    MTC_ENTER(ctx);
     MTC_CUDA(ctx, cudaIpcCloseMemHandle(d_ptr), MTC_ERR_BUFFER);
     return MTC_OK;
 }
@@ -329,6 +525,7 @@ int mtc_ipc_close(mtc_ctx *ctx, void *d_ptr) {
 int mtc_peer_barrier(mtc_ctx *ctx, void *stream, void *const *peer_flags, int n_peers, int rank, void *local_flags,
                      void *epoch) {
     if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     cudaError_t e = mtc::launch_peer_barrier(ctx, static_cast<cudaStream_t>(stream),
                                              reinterpret_cast<uint32_t *const *>(peer_flags), n_peers, rank,
                                              static_cast<uint32_t *>(local_flags), static_cast<uint32_t *>(epoch));
@@ -353,6 +550,8 @@ static bool mma_chunks_preferred(int enabled, int sms, int M, int N, int K, int 
 }
 
 const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dtype) {
+    if (M >= 1 && M <= 8 && mtc::qmv_stream_supported(M, N, K, bits, group_size, dtype, nullptr, nullptr, nullptr, nullptr))
+        return "qmv_stream";
     if (mma_chunks_preferred(1, 148, M, N, K, bits, group_size, dtype, nullptr, nullptr)) return "qmv_mma_sync";
     if (M > 16 && mtc::qmm_tcgen05_supported(M, N, K, bits, group_size, dtype, nullptr, nullptr, nullptr))
         return "qmm_tcgen05";
@@ -364,6 +563,7 @@ const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dty
 int mtc_qmm(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x,
             void *out, int M, int N, int K, int bits, int group_size, int dtype) {
     if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "qmm: dtype must be f32, f16 or bf16");
     if (w && scales && biases && x && out &&
         mma_chunks_preferred(ctx->qmm_mma_chunks && ctx->qmv_small_m_mma, ctx->sm_count, M, N, K, bits, group_size, dtype, w, x)) {
@@ -421,6 +621,18 @@ int mtc_set_option(mtc_ctx *ctx, const char *name, int value) {
         ctx->qmm_raw = value ? 1 : 0;
         return MTC_OK;
     }
+    if (std::strcmp(name, "peer_poll_limit") == 0) {
+        ctx->peer_poll_limit = value < 1 ? 1u : static_cast<uint32_t>(value);
+        return MTC_OK;
+    }
+    if (std::strcmp(name, "qmv_stream") == 0) {
+        ctx->qmv_stream = value ? 1 : 0;
+        return MTC_OK;
+    }
+    if (std::strcmp(name, "pdl_early_weights") == 0) {
+        ctx->pdl_early_weights = value ? 1 : 0;
+        return MTC_OK;
+    }
     if (std::strcmp(name, "qmm_pair") == 0) {
         ctx->qmm_pair = value ? 1 : 0;
         return MTC_OK;
@@ -432,6 +644,7 @@ int mtc_gather_qmm(mtc_ctx *ctx, void *stream, const void *x, const void *w, con
                    const void *expert_offsets, const void *indices, void *out, int m_total, int n_out, int k_in,
                    int n_experts, int bits, int group_size, int dtype) {
     if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "gather_qmm: dtype must be f32, f16 or bf16");
     if ((expert_offsets == nullptr) == (indices == nullptr))
         return fail(ctx, MTC_ERR_INVALID, "gather_qmm: give exactly one of expert_offsets and indices");
@@ -466,6 +679,7 @@ int mtc_gather_qmm_static(mtc_ctx *ctx, void *stream, const void *x, const void 
                           const void *biases, const void *expert_offsets, const void *indices, void *out, int m_total,
                           int n_out, int k_in, int n_experts, int bits, int group_size, int dtype) {
     if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     if (dtype != MTC_F16 && dtype != MTC_BF16)
         return fail(ctx, MTC_ERR_UNSUPPORTED, "gather_qmm_static: dtype must be f16 or bf16 (the tensor-core path)");
     if ((expert_offsets == nullptr) == (indices == nullptr))
@@ -497,6 +711,7 @@ const char *mtc_gather_qmm_route(int m_total, int n_out, int k_in, int bits, int
 int mtc_moe_router_topk(mtc_ctx *ctx, void *stream, const void *router_logits, void *indices_out, void *weights_out,
                         int n_rows, int n_experts, int k, int norm_topk_prob, int dtype) {
     if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "router_topk: dtype must be f32, f16 or bf16");
     // k <= 32 is the reference's hard cap (crates/metaltile-std/src/ffai/moe.rs:88-91); n_experts <= 32 * 32
     if (n_rows < 0 || n_experts <= 0 || n_experts > 1024 || k <= 0 || k > 32 || k > n_experts)
@@ -510,6 +725,7 @@ int mtc_moe_router_topk(mtc_ctx *ctx, void *stream, const void *router_logits, v
 int mtc_moe_sort(mtc_ctx *ctx, void *stream, const void *topk_idx, int n_tokens, int k, int n_experts, void *sort_token_idx,
                  void *inv_perm, void *expert_offsets, void *row_expert) {
     if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     if (n_tokens < 0 || k <= 0 || n_experts <= 0 || n_experts > 1024)
         return fail(ctx, MTC_ERR_UNSUPPORTED, "moe_sort: need k > 0 and 0 < n_experts <= 1024");
     if (!expert_offsets || (n_tokens > 0 && (!topk_idx || !sort_token_idx || !inv_perm)))
@@ -524,6 +740,7 @@ int mtc_moe_sort(mtc_ctx *ctx, void *stream, const void *topk_idx, int n_tokens,
 int mtc_moe_permute(mtc_ctx *ctx, void *stream, const void *tokens, const void *sort_token_idx, void *permuted, int n_rows,
                     int hidden, int dtype) {
     if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     if (!dtype_ok(dtype) || n_rows < 0 || hidden <= 0) return fail(ctx, MTC_ERR_UNSUPPORTED, "moe_permute: bad dtype or shape");
     if (n_rows > 0 && (!tokens || !sort_token_idx || !permuted)) return fail(ctx, MTC_ERR_INVALID, "moe_permute: null pointer");
     MTC_CUDA(ctx, mtc::launch_permute(static_cast<cudaStream_t>(stream), tokens, static_cast<const uint32_t *>(sort_token_idx),
@@ -534,6 +751,7 @@ int mtc_moe_permute(mtc_ctx *ctx, void *stream, const void *tokens, const void *
 int mtc_moe_unpermute(mtc_ctx *ctx, void *stream, const void *expert_outputs, const void *inv_perm, const void *top_k_weights,
                       void *out, int n_tokens, int hidden, int k, int dtype) {
     if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     if (!dtype_ok(dtype) || n_tokens < 0 || hidden <= 0 || k <= 0)
         return fail(ctx, MTC_ERR_UNSUPPORTED, "moe_unpermute: bad dtype or shape");
     if (n_tokens > 0 && (!expert_outputs || !inv_perm || !top_k_weights || !out))
@@ -545,6 +763,7 @@ int mtc_moe_unpermute(mtc_ctx *ctx, void *stream, const void *expert_outputs, co
 
 int mtc_swiglu(mtc_ctx *ctx, void *stream, const void *gate, const void *up, void *out, size_t n, int dtype) {
     if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "swiglu: dtype must be f32, f16 or bf16");
     if (n > 0 && (!gate || !up || !out)) return fail(ctx, MTC_ERR_INVALID, "swiglu: null pointer");
     MTC_CUDA(ctx, mtc::launch_swiglu(static_cast<cudaStream_t>(stream), gate, up, out, n, dtype), MTC_ERR_DISPATCH);
@@ -553,6 +772,7 @@ int mtc_swiglu(mtc_ctx *ctx, void *stream, const void *gate, const void *up, voi
 
 int mtc_unpack_codes(mtc_ctx *ctx, void *stream, const void *w, void *codes_u8, int N, int K, int bits) {
     if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     if (bits < 1 || bits > 8 || (static_cast<long long>(K) * bits) % 32 != 0)
         return fail(ctx, MTC_ERR_UNSUPPORTED, "unpack_codes: need 1 <= bits <= 8 and K*bits % 32 == 0");
     MTC_CUDA(ctx, mtc::launch_unpack_codes(static_cast<cudaStream_t>(stream), w, codes_u8, N, K, bits), MTC_ERR_DISPATCH);
@@ -566,6 +786,7 @@ int mtc_dispatch(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_buf
                  const uint32_t grid[3], const uint32_t tpg[3], float *elapsed_us) {
     (void)grid; (void)tpg;  // launch geometry belongs to the back end
     if (!ctx || !kernel_name || (!bufs && n_bufs > 0)) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
     if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "dispatch: dtype must be f32, f16 or bf16");
     const KernelRow *row = find_kernel(kernel_name);
     if (!row) return fail(ctx, MTC_ERR_FUNCTION_NOT_FOUND, std::string("unknown kernel: ") + kernel_name);
@@ -755,6 +976,7 @@ int mtc_dispatch(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_buf
             if (sb.buf->is_output && sb.need) cudaMemcpyAsync(sb.buf->data, sb.dev, sb.need, cudaMemcpyDeviceToHost, st);
         cudaError_t e = cudaStreamSynchronize(st);
         if (e != cudaSuccess) rc = fail(ctx, MTC_ERR_DISPATCH, std::string("dispatch: ") + cudaGetErrorString(e));
+        else rc = check_status(ctx, "dispatch");
     }
     if (elapsed_us) {
         float ms = 0.f;

@@ -47,11 +47,22 @@ def _check_dense(w, scales, biases, x, bits, group_size):
     return x2, M, N, K
 
 
+def _check_out(out, M, N, like):
+    """A caller-supplied output must be the dense row-major [M, N] block the kernels write."""
+    if out.device != like.device or out.dtype != like.dtype:
+        raise TypeError("out must live on the same device and have the dtype of x")
+    if out.numel() != M * N or not out.is_contiguous():
+        raise ValueError(f"out must be a contiguous block of M*N = {M * N} elements "
+                         "(a column slice of a wider tensor with M > 1 is not)")
+
+
 def qmv(w, scales, biases, x, bits: int, group_size: int, out=None, ctx: Context = None):
     """out[M, N] = x[M, K] @ dequant(w)[N, K]^T on the CUDA-core path (decode, M <= 16 tuned)."""
     x2, M, N, K = _check_dense(w, scales, biases, x, bits, group_size)
     if out is None:
         out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    else:
+        _check_out(out, M, N, x)
     ctx = ctx or context(x.device)
     ctx.qmv(w.data_ptr(), scales.data_ptr(), biases.data_ptr(), x2.data_ptr(), out.data_ptr(), M, N, K, bits,
             group_size, _TORCH_DT[x.dtype], _stream())
@@ -63,10 +74,45 @@ def qmm(w, scales, biases, x, bits: int, group_size: int, out=None, ctx: Context
     x2, M, N, K = _check_dense(w, scales, biases, x, bits, group_size)
     if out is None:
         out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    else:
+        _check_out(out, M, N, x)
     ctx = ctx or context(x.device)
     ctx.qmm(w.data_ptr(), scales.data_ptr(), biases.data_ptr(), x2.data_ptr(), out.data_ptr(), M, N, K, bits,
             group_size, _TORCH_DT[x.dtype], _stream())
     return out
+
+
+def _projection(w, scales, biases, x, bits, group_size, outs, phase=0):
+    x2, M, N, K = _check_dense(w, scales, biases, x, bits, group_size)
+    for o in outs:
+        _check_out(o, M, N, x)
+    return {"w": w.data_ptr(), "scales": scales.data_ptr(), "biases": biases.data_ptr(), "x": x2.data_ptr(),
+            "outs": [o.data_ptr() for o in outs], "M": M, "N": N, "K": K, "bits": bits, "group_size": group_size,
+            "dtype": _TORCH_DT[x.dtype], "phase": phase}
+
+
+def qmv_batched(mats, x, bits: int, group_size: int, out=None, ctx: Context = None):
+    """Several projections of the same activations in one launch: ``mats`` = [(w, scales, biases), ...] (1 to 4).
+
+    Returns ``out[M, sum(N_i)]`` with the results side by side - for M = 1 the concatenated vector of
+    ``ffai_batched_qkv_qgemv`` (crates/metaltile-std/src/ffai/batched_qkv_qgemv.rs:1-35).  For M > 1 every
+    projection writes its own contiguous [M, N_i] tile and the tiles are returned as a list instead."""
+    x2 = x.reshape(-1, x.shape[-1])
+    M = x2.shape[0]
+    ns = [w.shape[0] for (w, _, _) in mats]
+    ctx = ctx or context(x.device)
+    if M == 1:
+        if out is None:
+            out = torch.empty((1, sum(ns)), dtype=x.dtype, device=x.device)
+        col, tiles = 0, []
+        for n in ns:
+            tiles.append(out[:, col:col + n])
+            col += n
+    else:
+        tiles = [torch.empty((M, n), dtype=x.dtype, device=x.device) for n in ns]
+    projs = [_projection(w, s, b, x2, bits, group_size, [t]) for (w, s, b), t in zip(mats, tiles)]
+    ctx.qmv_batched(projs, _stream())
+    return out if M == 1 else tiles
 
 
 def unpack_codes(w, K: int, bits: int, ctx: Context = None):
@@ -149,6 +195,8 @@ def gather_qmm(x, w, scales, biases, bits: int, group_size: int, expert_offsets=
             raise ValueError("operands must be contiguous")
     if out is None:
         out = torch.empty((m_total, n_out), dtype=x.dtype, device=x.device)
+    else:
+        _check_out(out, m_total, n_out, x)
     ctx = ctx or context(x.device)
     ctx.gather_qmm(x.data_ptr(), w.data_ptr(), scales.data_ptr(), biases.data_ptr(), out.data_ptr(), m_total, n_out,
                    k_in, n_experts, bits, group_size, _TORCH_DT[x.dtype],

@@ -24,9 +24,13 @@ def run_qmm(w, s, b, x, bits, gs, dt):
 
 def test_routing_follows_m_and_dtype(ctx):
     """The selector (mt_qmm_for, crates/metaltile-std/src/mlx/quantized.rs:5040-5065,5127-5199) in this back end."""
-    assert ctx.qmm_route(1, 4096, 4096, 4, 64, "bf16") == "qmv_cuda_core"
+    assert ctx.qmm_route(1, 4096, 4096, 4, 64, "bf16") == "qmv_stream"
+    assert ctx.qmm_route(8, 4096, 4096, 4, 128, "f16") == "qmv_stream"
+    assert ctx.qmm_route(1, 4096, 4096, 4, 64, "f32") == "qmv_cuda_core"
+    assert ctx.qmm_route(1, 4096, 4096, 3, 64, "bf16") == "qmv_cuda_core"
     assert ctx.qmm_route(16, 4096, 4096, 4, 64, "bf16") == "qmv_mma_sync"
-    assert ctx.qmm_route(2, 4096, 4096, 4, 128, "f16") == "qmv_mma_sync"
+    assert ctx.qmm_route(9, 4096, 4096, 4, 128, "f16") == "qmv_mma_sync"
+    assert ctx.qmm_route(2, 4096, 4160, 4, 64, "f16") == "qmv_mma_sync"           # K % 256 != 0: not the streaming kernel
     assert ctx.qmm_route(16, 4096, 4096, 4, 32, "bf16") == "qmv_cuda_core"        # group < 64
     assert ctx.qmm_route(16, 4096, 4096, 8, 64, "bf16") == "qmv_cuda_core"        # 4-bit codes only
     assert ctx.qmm_route(16, 4096, 4096, 4, 64, "f32") == "qmv_cuda_core"

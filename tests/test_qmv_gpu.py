@@ -93,19 +93,49 @@ def test_config0_qmv_4bit_g64_4096(ctx):
     # oracle, so got must equal round_bf16(ref) except for values on a rounding boundary
     exp = oracle.round_through(ref, oracle.BF16)
     assert np.mean(got == exp) > 0.99
+    ctx.set_option("qmv_stream", 0)            # the CUDA-core kernel on the same case
+    try:
+        cores = run_qmv(w, s, b, x, 4, 64, "bf16")
+    finally:
+        ctx.set_option("qmv_stream", 1)
+    assert rel_err(cores, ref) <= TOL["bf16"]
+    assert np.mean(cores == exp) > 0.99
 
 
 SWEEP = [(bits, gs, m, kn, dt)
          for bits in (2, 3, 4, 6, 8) for gs in (32, 64, 128) for m in (1, 4, 8, 16)
-         for kn in (2048,) for dt in DT_NAMES]
+         for kn in (2048, 4096, 8192) for dt in DT_NAMES]
+_CASES = {}
 
 
-@pytest.mark.parametrize("bits,gs,m,kn,dt", SWEEP)
-def test_sweep_2048(bits, gs, m, kn, dt):
-    w, s, b, x = dense_case(m, kn, kn, bits, gs, dt, seed=0, salt=bits)
-    ref = oracle.qmm(w, s, b, x, m, kn, kn, bits, gs)
-    got = run_qmv(w, s, b, x, bits, gs, dt)
-    assert rel_err(got, ref) <= TOL[dt]
+def _sweep_weights(bits, gs, kn):
+    """One weight matrix per (bits, group, size), shared by the M and dtype cells of the sweep (generated once)."""
+    key = (bits, gs, kn)
+    if key not in _CASES:
+        _CASES.clear()                      # the cells are ordered by (bits, gs, ..): keep one matrix at a time
+        from metaltile_b200 import synth
+        w, s, b = synth.quantized_matrix(kn, kn, bits, gs, 0, bits)
+        _CASES[key] = (w, s, b, to_dev(w))
+    return _CASES[key]
+
+
+@pytest.mark.parametrize("bits,gs,m,kn,dt", sorted(SWEEP, key=lambda c: (c[0], c[1], c[3])))
+def test_sweep(bits, gs, m, kn, dt):
+    """The benchmark's sweep grid: bits x group x M x K = N x dtype.  At 2048 every output is compared with the
+    oracle; at 4096 and 8192 the first, a middle and the last band of 32 weight rows (the CPU oracle is a scalar
+    loop), which covers the first and last row group of the first, a middle and the last CTA of every kernel."""
+    from metaltile_b200 import ops, synth
+    import torch
+    w, s, b, wd = _sweep_weights(bits, gs, kn)
+    x = synth.activations(m, kn, 0, bits)
+    s, b, x = (oracle.round_through(a, ODT[dt]) for a in (s, b, x))
+    out = ops.qmv(wd, to_dev(s, dt), to_dev(b, dt), to_dev(x, dt), bits, gs)
+    torch.cuda.synchronize()
+    got = out.float().cpu().numpy()
+    bands = [(0, kn)] if kn == 2048 else [(0, 32), (kn // 2 + 5, kn // 2 + 37), (kn - 32, kn)]
+    for (n0, n1) in bands:
+        ref = oracle.qmm(w, s, b, x, m, kn, kn, bits, gs, rows=(n0, n1))
+        assert rel_err(got[:, n0:n1], ref[:, n0:n1]) <= TOL[dt], (n0, n1)
 
 
 @pytest.mark.parametrize("bits,gs,m,kn,dt", [
@@ -149,19 +179,24 @@ def test_shapes_and_edges(m, n, k, bits, gs, dt):
     (12, 8, 128, 64, "bf16"),                                   # fewer rows than one 16-row tile
 ])
 def test_small_m_tensor_core_path(ctx, m, n, k, gs, dt):
-    """2 <= M <= 16 with 4-bit codes runs on warp-level MMAs; same oracle, and within round-off of the
-    CUDA-core kernel for the same call."""
-    assert ctx.qmm_route(m, n, k, 4, gs, dt) == "qmv_mma_sync"
+    """2 <= M <= 16 with 4-bit codes runs on warp-level MMAs (the register / cp.async ring kernels of qmv_mma.cu once
+    the streaming kernel is switched off); same oracle, and within round-off of the CUDA-core kernel for the same call."""
+    assert ctx.qmm_route(m, n, k, 4, gs, dt) in ("qmv_mma_sync", "qmv_stream")
     w, s, b, x = dense_case(m, n, k, 4, gs, dt, seed=6, salt=m * 31 + n)
     ref = oracle.qmm(w, s, b, x, m, n, k, 4, gs)
-    got = run_qmv(w, s, b, x, 4, gs, dt)
-    assert got.shape == (m, n)
-    assert rel_err(got, ref) <= TOL[dt]
-    ctx.set_option("qmv_small_m_mma", 0)
+    assert rel_err(run_qmv(w, s, b, x, 4, gs, dt), ref) <= TOL[dt]          # the default route
+    ctx.set_option("qmv_stream", 0)
     try:
-        cores = run_qmv(w, s, b, x, 4, gs, dt)
+        got = run_qmv(w, s, b, x, 4, gs, dt)
+        assert got.shape == (m, n)
+        assert rel_err(got, ref) <= TOL[dt]
+        ctx.set_option("qmv_small_m_mma", 0)
+        try:
+            cores = run_qmv(w, s, b, x, 4, gs, dt)
+        finally:
+            ctx.set_option("qmv_small_m_mma", 1)
     finally:
-        ctx.set_option("qmv_small_m_mma", 1)
+        ctx.set_option("qmv_stream", 1)
     assert rel_err(cores, ref) <= TOL[dt]
     assert rel_err(got, cores) <= TOL[dt]
 
@@ -172,10 +207,12 @@ def test_single_row_through_tensor_core_path(ctx, n, k, dt):
     w, s, b, x = dense_case(1, n, k, 4, 64, dt, seed=8, salt=n)
     ref = oracle.qmm(w, s, b, x, 1, n, k, 4, 64)
     ctx.set_option("qmv_small_m_mma", 2)
+    ctx.set_option("qmv_stream", 0)
     try:
         got = run_qmv(w, s, b, x, 4, 64, dt)
     finally:
         ctx.set_option("qmv_small_m_mma", 1)
+        ctx.set_option("qmv_stream", 1)
     assert rel_err(got, ref) <= TOL[dt]
 
 
@@ -219,10 +256,14 @@ def test_multi_output_store_and_single_rank_barrier(ctx):
     from metaltile_b200 import MetalTileError
     with pytest.raises(MetalTileError):
         ctx.peer_barrier([flags.data_ptr()] * 9, 0, flags.data_ptr(), flags.data_ptr() + 128, stream=st)
-    with pytest.raises(MetalTileError) as ei:      # several destinations are the M = 1 decode case only
-        ctx.qmv_multi(wd.data_ptr(), sd.data_ptr(), bd.data_ptr(), xd.data_ptr(), [o.data_ptr() for o in outs], 3, n, k, 4, 64,
-                      _TORCH_DT[xd.dtype], stream=st)
-    assert ei.value.variant == "Unsupported"
+    ctx.set_option("qmv_stream", 0)
+    try:
+        with pytest.raises(MetalTileError) as ei:      # on the CUDA-core kernel several destinations are the M = 1 case only
+            ctx.qmv_multi(wd.data_ptr(), sd.data_ptr(), bd.data_ptr(), xd.data_ptr(), [o.data_ptr() for o in outs], 3, n, k, 4, 64,
+                          _TORCH_DT[xd.dtype], stream=st)
+        assert ei.value.variant == "Unsupported"
+    finally:
+        ctx.set_option("qmv_stream", 1)
 
 
 def test_generic_fallback_paths(ctx):

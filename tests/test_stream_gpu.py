@@ -1,0 +1,250 @@
+"""Parity of the streaming decode kernel (qmv_stream.cu) with the CPU oracle: single projections through
+mtc_qmv, projections that share x through mtc_qmv_batched, and prepared chains through mtc_chain_*."""
+import numpy as np
+import pytest
+
+import oracle
+from helpers import ODT, TOL, dense_case, rel_err, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    from metaltile_b200 import ops
+    return ops.context(0)
+
+
+def _bands(n, width=32):
+    """First, middle and last row band of a matrix: what the oracle computes for the large shapes."""
+    if n <= 3 * width:
+        return [(0, n)]
+    mid = (n // 2) // 16 * 16 + 5
+    return [(0, width), (mid, mid + width), (n - width, n)]
+
+
+def _check(got, w, s, b, x, m, n, k, bits, gs, dt):
+    for (n0, n1) in _bands(n):
+        ref = oracle.qmm(w, s, b, x, m, n, k, bits, gs, rows=(n0, n1))
+        assert rel_err(got[:, n0:n1], ref[:, n0:n1]) <= TOL[dt], (n0, n1)
+
+
+@pytest.mark.parametrize("m,n,k,gs,dt", [
+    (1, 4096, 4096, 64, "bf16"), (1, 4096, 4096, 64, "f16"), (1, 1024, 4096, 64, "bf16"), (1, 14336, 4096, 64, "bf16"),
+    (1, 4096, 14336, 64, "bf16"), (1, 8192, 8192, 64, "bf16"), (1, 2048, 2048, 128, "f16"), (1, 4096, 4096, 128, "bf16"),
+    (2, 4096, 4096, 64, "bf16"), (3, 1000, 2048, 64, "f16"), (4, 4096, 4096, 64, "bf16"), (5, 777, 1024, 128, "bf16"),
+    (8, 4096, 4096, 64, "bf16"), (8, 4096, 4096, 64, "f16"), (7, 37, 512, 64, "bf16"), (1, 5, 512, 64, "f16"),
+    (1, 128, 4096, 64, "bf16"), (8, 1024, 4096, 128, "f16"), (1, 2048, 1536, 64, "bf16"), (6, 300, 512, 64, "bf16"),
+    (1, 31, 3584, 128, "bf16"), (2, 16, 14336, 64, "f16"),
+])
+def test_stream_matches_oracle(ctx, m, n, k, gs, dt):
+    import torch
+    from metaltile_b200 import ops
+    w, s, b, x = dense_case(m, n, k, 4, gs, dt, seed=2, salt=m + n % 7)
+    assert ctx.qmm_route(m, n, k, 4, gs, dt) == "qmv_stream"
+    got = ops.qmv(to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt), 4, gs, ctx=ctx)
+    torch.cuda.synchronize()
+    assert ctx.status_word() == 0
+    _check(got.float().cpu().numpy(), w, s, b, x, m, n, k, 4, gs, dt)
+
+
+def test_stream_is_exact_before_rounding(ctx):
+    """Codes times activations are exact products accumulated in f32: the result equals the rounded oracle
+    almost everywhere (differences only where the oracle sits on a rounding boundary)."""
+    import torch
+    from metaltile_b200 import ops
+    m, n, k = 1, 512, 4096
+    w, s, b, x = dense_case(m, n, k, 4, 64, "bf16", seed=0)
+    ref = oracle.qmm(w, s, b, x, m, n, k, 4, 64)
+    got = ops.qmv(to_dev(w), to_dev(s, "bf16"), to_dev(b, "bf16"), to_dev(x, "bf16"), 4, 64, ctx=ctx)
+    torch.cuda.synchronize()
+    exp = oracle.round_through(ref, oracle.BF16)
+    assert np.mean(got.float().cpu().numpy() == exp) > 0.99
+
+
+def test_stream_equals_the_cuda_core_kernel_within_rounding(ctx):
+    import torch
+    from metaltile_b200 import ops
+    m, n, k = 1, 4096, 4096
+    w, s, b, x = dense_case(m, n, k, 4, 64, "bf16", seed=5)
+    args = (to_dev(w), to_dev(s, "bf16"), to_dev(b, "bf16"), to_dev(x, "bf16"), 4, 64)
+    a = ops.qmv(*args, ctx=ctx)
+    ctx.set_option("qmv_stream", 0)
+    try:
+        c = ops.qmv(*args, ctx=ctx)
+    finally:
+        ctx.set_option("qmv_stream", 1)
+    torch.cuda.synchronize()
+    assert rel_err(a.float().cpu().numpy(), c.float().cpu().numpy()) <= 1e-2
+    assert torch.mean((a == c).float()).item() > 0.98
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+@pytest.mark.parametrize("m", [1, 4])
+def test_batched_qkv_is_three_qmv(ctx, m, dt):
+    """q, k, v in one launch == three oracle products side by side
+    (ffai_batched_qkv_qgemv, crates/metaltile-std/src/ffai/batched_qkv_qgemv.rs:1-35)."""
+    import torch
+    from metaltile_b200 import ops
+    k, ns = 4096, (4096, 1024, 1024)
+    x = oracle.round_through(__import__("metaltile_b200").synth.activations(m, k, seed=3), ODT[dt])
+    mats, refs = [], []
+    for i, n in enumerate(ns):
+        w, s, b, _ = dense_case(m, n, k, 4, 64, dt, seed=3, salt=10 + i)
+        mats.append((to_dev(w), to_dev(s, dt), to_dev(b, dt)))
+        refs.append((w, s, b, n))
+    out = ops.qmv_batched(mats, to_dev(x, dt), 4, 64, ctx=ctx)
+    torch.cuda.synchronize()
+    assert ctx.status_word() == 0
+    tiles = [out[:, 0:4096], out[:, 4096:5120], out[:, 5120:6144]] if m == 1 else out
+    for t, (w, s, b, n) in zip(tiles, refs):
+        _check(t.float().cpu().numpy(), w, s, b, x, m, n, k, 4, 64, dt)
+    # and bit-identical to three separate launches of the same kernel
+    for t, (wd, sd, bd) in zip(tiles, mats):
+        one = ops.qmv(wd, sd, bd, to_dev(x, dt), 4, 64, ctx=ctx)
+        assert torch.equal(one, t.reshape(one.shape))
+
+
+def _layer(dt, seed, k_small=4096, k_big=14336, scale=8):
+    """A decode layer's projection list at 1/scale of the Llama-3-8B widths (same structure, same phases)."""
+    shapes = [("q", k_small, 4096 // scale, 0), ("k", k_small, 1024 // scale, 0), ("v", k_small, 1024 // scale, 0),
+              ("o", k_small, 4096 // scale, 1), ("gate", k_small, 14336 // scale, 2), ("up", k_small, 14336 // scale, 2),
+              ("down", k_big, 4096 // scale, 3)]
+    mats = []
+    for i, (_, k, n, ph) in enumerate(shapes):
+        w, s, b, _ = dense_case(1, n, k, 4, 64, dt, seed=seed, salt=20 + i)
+        mats.append((w, s, b, k, n, ph))
+    return mats
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+def test_chain_matches_oracle_per_projection(ctx, dt):
+    """Two layers (8 phases, 14 projections) in one persistent launch, run twice: every projection equals its
+    oracle, and the second run (counters reset by the first) reproduces the first bit for bit."""
+    import torch
+    from metaltile_b200 import ops, synth
+    from metaltile_b200.ops import _projection
+    m = 1
+    layers = [_layer(dt, 4), _layer(dt, 5)]
+    xs = {k: oracle.round_through(synth.activations(m, k, seed=9, salt=k), ODT[dt]) for k in (4096, 14336)}
+    xd = {k: to_dev(v, dt) for k, v in xs.items()}
+    projs, keep, outs = [], [], []
+    for li, mats in enumerate(layers):
+        for (w, s, b, k, n, ph) in mats:
+            wd, sd, bd = to_dev(w), to_dev(s, dt), to_dev(b, dt)
+            o = torch.zeros((m, n), dtype=xd[k].dtype, device="cuda")
+            keep.append((wd, sd, bd))
+            outs.append((o, w, s, b, k, n))
+            projs.append(_projection(wd, sd, bd, xd[k], 4, 64, [o], phase=li * 4 + ph))
+    chain = ctx.chain_create(projs)
+    assert chain.fused
+    chain.run(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert ctx.status_word() == 0
+    first = [o.clone() for (o, *_r) in outs]
+    for (o, w, s, b, k, n) in outs:
+        _check(o.float().cpu().numpy(), w, s, b, xs[k], m, n, k, 4, 64, dt)
+        o.zero_()
+    chain.run(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert ctx.status_word() == 0
+    for f, (o, *_r) in zip(first, outs):
+        assert torch.equal(f, o)
+    chain.close()
+
+
+def test_chain_phases_order_dependent_projections(ctx):
+    """Phase p + 1 reads what phase p wrote: y1 = W1 x, y2 = W2 y1 in one launch equals two separate launches."""
+    import torch
+    from metaltile_b200 import ops
+    from metaltile_b200.ops import _projection
+    dt, k = "bf16", 2048
+    w1, s1, b1, x = dense_case(1, k, k, 4, 64, dt, seed=6, salt=1)
+    w2, s2, b2, _ = dense_case(1, 1024, k, 4, 64, dt, seed=6, salt=2)
+    d = [to_dev(w1), to_dev(s1, dt), to_dev(b1, dt), to_dev(w2), to_dev(s2, dt), to_dev(b2, dt)]
+    xd = to_dev(x, dt)
+    y1 = torch.zeros((1, k), dtype=torch.bfloat16, device="cuda")
+    y2 = torch.zeros((1, 1024), dtype=torch.bfloat16, device="cuda")
+    chain = ctx.chain_create([_projection(d[0], d[1], d[2], xd, 4, 64, [y1], phase=0),
+                              _projection(d[3], d[4], d[5], y1, 4, 64, [y2], phase=1)])
+    assert chain.fused
+    for _ in range(3):
+        y1.zero_()
+        y2.zero_()
+        chain.run(torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        r1 = ops.qmv(d[0], d[1], d[2], xd, 4, 64, ctx=ctx)
+        r2 = ops.qmv(d[3], d[4], d[5], r1, 4, 64, ctx=ctx)
+        torch.cuda.synchronize()
+        assert torch.equal(y1, r1) and torch.equal(y2, r2)
+    assert ctx.status_word() == 0
+    chain.close()
+
+
+def test_chain_outside_the_contract_falls_back_to_launches(ctx):
+    """A 3-bit projection cannot run on the streaming kernel: the chain still runs, one launch per projection."""
+    import torch
+    from metaltile_b200.ops import _projection
+    dt = "bf16"
+    w, s, b, x = dense_case(2, 96, 512, 3, 32, dt, seed=8)
+    wd, sd, bd, xd = to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt)
+    o = torch.zeros((2, 96), dtype=torch.bfloat16, device="cuda")
+    chain = ctx.chain_create([_projection(wd, sd, bd, xd, 3, 32, [o])])
+    assert not chain.fused
+    chain.run(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    ref = oracle.qmm(w, s, b, x, 2, 96, 512, 3, 32)
+    assert rel_err(o.float().cpu().numpy(), ref) <= TOL[dt]
+    chain.close()
+
+
+def test_chain_rejects_bad_phases(ctx):
+    import torch
+    from metaltile_b200.context import MetalTileError
+    from metaltile_b200.ops import _projection
+    dt = "bf16"
+    w, s, b, x = dense_case(1, 64, 256, 4, 64, dt, seed=8)
+    wd, sd, bd, xd = to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt)
+    o = torch.zeros((1, 64), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(MetalTileError) as ei:
+        ctx.chain_create([_projection(wd, sd, bd, xd, 4, 64, [o], phase=1)])
+    assert ei.value.variant == "Invalid"
+    with pytest.raises(MetalTileError):
+        ctx.chain_create([_projection(wd, sd, bd, xd, 4, 64, [o], phase=0), _projection(wd, sd, bd, xd, 4, 64, [o], phase=2)])
+
+
+def test_chain_in_a_cuda_graph(ctx):
+    """The chain launch is capturable: graph replays give the same bytes as a direct run."""
+    import torch
+    from metaltile_b200.ops import _projection
+    dt = "bf16"
+    mats = _layer(dt, 11, scale=16)
+    from metaltile_b200 import synth
+    xs = {k: to_dev(oracle.round_through(synth.activations(1, k, seed=1, salt=k), ODT[dt]), dt) for k in (4096, 14336)}
+    keep, outs, projs = [], [], []
+    for (w, s, b, k, n, ph) in mats:
+        wd, sd, bd = to_dev(w), to_dev(s, dt), to_dev(b, dt)
+        o = torch.zeros((1, n), dtype=torch.bfloat16, device="cuda")
+        keep.append((wd, sd, bd))
+        outs.append(o)
+        projs.append(_projection(wd, sd, bd, xs[k], 4, 64, [o], phase=ph))
+    chain = ctx.chain_create(projs)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        chain.run(side.cuda_stream)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    direct = [o.clone() for o in outs]
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        chain.run(torch.cuda.current_stream().cuda_stream)
+    for _ in range(3):
+        for o in outs:
+            o.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        for a, o in zip(direct, outs):
+            assert torch.equal(a, o)
+    assert ctx.status_word() == 0
+    chain.close()
