@@ -7,6 +7,7 @@
 #include <stdint.h>
 
 #include <string>
+#include <vector>
 
 #include "../../include/mtcuda.h"
 
@@ -31,6 +32,11 @@ struct Ctx {
     int qmm_raw = 1;               // option "qmm_raw": 0 = dequant warps load their packed words straight from global memory
     int qmm_pair = 0;              // option "qmm_pair": 1 = give a work item two adjacent weight-row tiles
     uint32_t peer_poll_limit = 1u << 22;   // option "peer_poll_limit": polls of mtc_peer_barrier before it gives up on a peer
+    int qmv_tc = 0;                // option "qmv_tc": 1 = M <= 8 decode shapes run on the tcgen05 decode kernel (qmv_tc.cu; slower than the stream kernel today)
+    float *d_tc_scratch = nullptr; // partial sums of the tcgen05 decode kernel's K chunks (grow-only; outgrown blocks stay alive)
+    size_t tc_scratch_bytes = 0;
+    uint32_t *d_tc_counters = nullptr;   // its arrival counters, zero between launches
+    std::vector<void *> retired;   // outgrown scratch blocks: freed by mtc_destroy, so that captured graphs never see freed memory
     int qmv_stream = 1;            // option "qmv_stream": 0 = never use the streaming decode kernel (qmv_stream.cu)
     int pdl_early_weights = 1;     // option "pdl_early_weights": 0 = no load of w / scales / biases before the previous kernel of the stream is complete
     void *d_worklist = nullptr;    // gather_qmm work list (grow-only, owned by the context)
@@ -106,6 +112,14 @@ bool qmv_stream_supported(int M, int N, int K, int bits, int group_size, int dt,
                           const void *biases, const void *x);
 cudaError_t qmv_stream_init_device();
 cudaError_t launch_qmv_stream(Ctx *ctx, cudaStream_t st, const mtc_qmv_desc *descs, int n);
+bool qmv_tc_supported(int M, int N, int K, int bits, int group_size, int dt, const void *w, const void *scales,
+                      const void *biases, const void *x);
+cudaError_t qmv_tc_init_device();
+size_t qmv_tc_scratch_bytes(int M, int N, int K);
+size_t qmv_tc_counter_bytes(int N);
+cudaError_t launch_qmv_tc(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases, const void *x,
+                          void *const *outs, int n_out, int M, int N, int K, int group_size, int dt, float *scratch,
+                          uint32_t *counters);
 struct StreamChain;
 cudaError_t stream_chain_create(Ctx *ctx, const mtc_qmv_desc *descs, int n, StreamChain **out, std::string *why);
 cudaError_t stream_chain_run(Ctx *ctx, cudaStream_t st, StreamChain *c);

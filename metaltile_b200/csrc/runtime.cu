@@ -127,6 +127,25 @@ bool read_const(mtc_named_buf *bufs, int n, const char *name, uint32_t *out) {
     return true;
 }
 
+constexpr size_t kTcCounterBytes = 1u << 20;       // (tile, quarter) counters of the tcgen05 decode kernel: N up to 8 Mi rows
+
+// Partial-sum planes of the tcgen05 decode kernel.  Grow-only; an outgrown block is kept until mtc_destroy, so a CUDA
+// graph captured earlier never reads freed memory.  Growing allocates: not during stream capture.
+int ensure_tc_scratch(Ctx *ctx, size_t bytes, cudaStream_t st) {
+    if (bytes <= ctx->tc_scratch_bytes) return MTC_OK;
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) == cudaSuccess && cs != cudaStreamCaptureStatusNone)
+        return fail(ctx, MTC_ERR_BUFFER, "qmv: the partial-sum scratch has to grow, which cannot happen during stream capture; "
+                                          "run the shape once before capturing");
+    const size_t want = bytes + (bytes >> 1) + (1u << 20);
+    void *p = nullptr;
+    MTC_CUDA(ctx, cudaMalloc(&p, want), MTC_ERR_BUFFER);
+    if (ctx->d_tc_scratch) ctx->retired.push_back(ctx->d_tc_scratch);
+    ctx->d_tc_scratch = static_cast<float *>(p);
+    ctx->tc_scratch_bytes = want;
+    return MTC_OK;
+}
+
 int ensure_scratch(Ctx *ctx, size_t bytes) {
     if (bytes <= ctx->scratch_bytes) return MTC_OK;
     if (ctx->d_scratch) cudaFree(ctx->d_scratch);
@@ -195,6 +214,9 @@ int mtc_init(int device, mtc_ctx **out_ctx) {
         (e = cudaMemset(ctx->d_status, 0, sizeof(uint32_t))) != cudaSuccess ||
         (e = mtc::qmv_init_device()) != cudaSuccess ||
         (e = mtc::qmv_stream_init_device()) != cudaSuccess ||
+        (e = mtc::qmv_tc_init_device()) != cudaSuccess ||
+        (e = cudaMalloc(&ctx->d_tc_counters, kTcCounterBytes)) != cudaSuccess ||
+        (e = cudaMemset(ctx->d_tc_counters, 0, kTcCounterBytes)) != cudaSuccess ||
         (e = cudaMalloc(&ctx->d_worklist, 4u << 20)) != cudaSuccess) {
         g_no_ctx_error = std::string("context set-up: ") + cudaGetErrorString(e);
         delete ctx;
@@ -212,6 +234,9 @@ int mtc_destroy(mtc_ctx *ctx) {
     if (ctx->d_scratch) cudaFree(ctx->d_scratch);
     if (ctx->d_worklist) cudaFree(ctx->d_worklist);
     if (ctx->d_xconv) cudaFree(ctx->d_xconv);
+    if (ctx->d_tc_scratch) cudaFree(ctx->d_tc_scratch);
+    if (ctx->d_tc_counters) cudaFree(ctx->d_tc_counters);
+    for (void *p : ctx->retired) cudaFree(p);
     delete ctx;
     return MTC_OK;
 }
@@ -337,6 +362,20 @@ int mtc_status_clear(mtc_ctx *ctx) {
     return MTC_OK;
 }
 
+// The tcgen05 decode kernel, when it takes the shape: 0 = launched, 1 = not its shape, < 0 = error.
+static int try_qmv_tc(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x,
+                      void *const *outs, int n_outs, int M, int N, int K, int bits, int group_size, int dtype) {
+    if (!ctx->qmv_tc || M < 1 || N < 1 || !mtc::qmv_tc_supported(M, N, K, bits, group_size, dtype, w, scales, biases, x)) return 1;
+    if (mtc::qmv_tc_counter_bytes(N) > kTcCounterBytes) return 1;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int rc = ensure_tc_scratch(ctx, mtc::qmv_tc_scratch_bytes(M, N, K), st);
+    if (rc != MTC_OK) return rc;
+    cudaError_t e = mtc::launch_qmv_tc(ctx, st, w, scales, biases, x, outs, n_outs, M, N, K, group_size, dtype, ctx->d_tc_scratch,
+                                       ctx->d_tc_counters);
+    if (e != cudaSuccess) return fail(ctx, MTC_ERR_DISPATCH, std::string("qmv (tcgen05) launch: ") + cudaGetErrorString(e));
+    return 0;
+}
+
 int mtc_qmv(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x,
             void *out, int M, int N, int K, int bits, int group_size, int dtype) {
     if (!ctx) return MTC_ERR_INVALID;
@@ -344,6 +383,11 @@ int mtc_qmv(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
     if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "qmv: dtype must be f32, f16 or bf16");
     if (M > 0 && N > 0 && (!w || !scales || !biases || !x || !out)) return fail(ctx, MTC_ERR_INVALID, "qmv: null pointer");
     std::string why;
+    {
+        void *outs1[1] = {out};
+        const int t = try_qmv_tc(ctx, stream, w, scales, biases, x, outs1, 1, M, N, K, bits, group_size, dtype);
+        if (t <= 0) return t;
+    }
     if (ctx->qmv_stream && mtc::qmv_stream_supported(M, N, K, bits, group_size, dtype, w, scales, biases, x)) {
         mtc_qmv_desc d{};
         d.w = w; d.scales = scales; d.biases = biases; d.x = x;
@@ -377,6 +421,10 @@ int mtc_qmv_multi(mtc_ctx *ctx, void *stream, const void *w, const void *scales,
         if (!outs[i]) return fail(ctx, MTC_ERR_INVALID, "qmv_multi: null output");
     if (M > 0 && N > 0 && (!w || !scales || !biases || !x)) return fail(ctx, MTC_ERR_INVALID, "qmv_multi: null pointer");
     std::string why;
+    {
+        const int t = try_qmv_tc(ctx, stream, w, scales, biases, x, outs, n_outs, M, N, K, bits, group_size, dtype);
+        if (t <= 0) return t;
+    }
     if (ctx->qmv_stream && M > 0 && N > 0 && mtc::qmv_stream_supported(M, N, K, bits, group_size, dtype, w, scales, biases, x)) {
         mtc_qmv_desc d{};
         d.w = w; d.scales = scales; d.biases = biases; d.x = x;
@@ -623,6 +671,10 @@ int mtc_set_option(mtc_ctx *ctx, const char *name, int value) {
     }
     if (std::strcmp(name, "peer_poll_limit") == 0) {
         ctx->peer_poll_limit = value < 1 ? 1u : static_cast<uint32_t>(value);
+        return MTC_OK;
+    }
+    if (std::strcmp(name, "qmv_tc") == 0) {
+        ctx->qmv_tc = value ? 1 : 0;
         return MTC_OK;
     }
     if (std::strcmp(name, "qmv_stream") == 0) {

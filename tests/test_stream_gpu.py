@@ -37,15 +37,44 @@ def _check(got, w, s, b, x, m, n, k, bits, gs, dt):
     (1, 128, 4096, 64, "bf16"), (8, 1024, 4096, 128, "f16"), (1, 2048, 1536, 64, "bf16"), (6, 300, 512, 64, "bf16"),
     (1, 31, 3584, 128, "bf16"), (2, 16, 14336, 64, "f16"),
 ])
-def test_stream_matches_oracle(ctx, m, n, k, gs, dt):
+@pytest.mark.parametrize("engine", ["tcgen05", "stream"])
+def test_stream_matches_oracle(ctx, m, n, k, gs, dt, engine):
+    """The two decode kernels for M <= 8: the warp-level MMA stream kernel (the default) and the kernel with the codes
+    as the A operand in tensor memory (tcgen05; option `qmv_tc` = 1; shapes whose activations do not fit its shared
+    memory fall through to the stream kernel)."""
     import torch
     from metaltile_b200 import ops
     w, s, b, x = dense_case(m, n, k, 4, gs, dt, seed=2, salt=m + n % 7)
     assert ctx.qmm_route(m, n, k, 4, gs, dt) == "qmv_stream"
-    got = ops.qmv(to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt), 4, gs, ctx=ctx)
-    torch.cuda.synchronize()
+    ctx.set_option("qmv_tc", 1 if engine == "tcgen05" else 0)
+    try:
+        got = ops.qmv(to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt), 4, gs, ctx=ctx)
+        torch.cuda.synchronize()
+    finally:
+        ctx.set_option("qmv_tc", 0)
     assert ctx.status_word() == 0
     _check(got.float().cpu().numpy(), w, s, b, x, m, n, k, 4, gs, dt)
+
+
+def test_tcgen05_decode_twice_and_exact(ctx):
+    """Back-to-back launches reuse the arrival counters (left at zero by the kernel) and the partial-sum planes; the
+    result equals the rounded oracle almost everywhere (exact products, f32 sums)."""
+    import torch
+    from metaltile_b200 import ops
+    m, n, k = 1, 1000, 4096
+    w, s, b, x = dense_case(m, n, k, 4, 64, "bf16", seed=12)
+    ref = oracle.qmm(w, s, b, x, m, n, k, 4, 64)
+    args = (to_dev(w), to_dev(s, "bf16"), to_dev(b, "bf16"), to_dev(x, "bf16"), 4, 64)
+    ctx.set_option("qmv_tc", 1)
+    try:
+        outs = [ops.qmv(*args, ctx=ctx) for _ in range(3)]
+        torch.cuda.synchronize()
+    finally:
+        ctx.set_option("qmv_tc", 0)
+    assert ctx.status_word() == 0
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    exp = oracle.round_through(ref, oracle.BF16)
+    assert np.mean(outs[0].float().cpu().numpy() == exp) > 0.99
 
 
 def test_stream_is_exact_before_rounding(ctx):
@@ -68,12 +97,18 @@ def test_stream_equals_the_cuda_core_kernel_within_rounding(ctx):
     m, n, k = 1, 4096, 4096
     w, s, b, x = dense_case(m, n, k, 4, 64, "bf16", seed=5)
     args = (to_dev(w), to_dev(s, "bf16"), to_dev(b, "bf16"), to_dev(x, "bf16"), 4, 64)
-    a = ops.qmv(*args, ctx=ctx)
+    a = ops.qmv(*args, ctx=ctx)                    # the warp-level MMA stream kernel
+    ctx.set_option("qmv_tc", 1)
+    try:
+        t2 = ops.qmv(*args, ctx=ctx)               # the tcgen05 decode kernel
+    finally:
+        ctx.set_option("qmv_tc", 0)
     ctx.set_option("qmv_stream", 0)
     try:
-        c = ops.qmv(*args, ctx=ctx)
+        c = ops.qmv(*args, ctx=ctx)                # the CUDA-core kernel
     finally:
         ctx.set_option("qmv_stream", 1)
+    assert torch.mean((a == t2).float()).item() > 0.98
     torch.cuda.synchronize()
     assert rel_err(a.float().cpu().numpy(), c.float().cpu().numpy()) <= 1e-2
     assert torch.mean((a == c).float()).item() > 0.98
