@@ -106,7 +106,8 @@ def cpu_reference_arm(args):
     import numpy as np
     import oracle
     from metaltile_b200 import synth
-    threads = oracle.max_threads()
+    # all host cores, whatever OMP_NUM_THREADS the launcher exported (torch.distributed.run sets it to 1)
+    threads = os.cpu_count() or oracle.max_threads()
     layers = 1
     mats = []
     for li in range(layers):
@@ -128,6 +129,32 @@ def cpu_reference_arm(args):
     dt = (time.perf_counter() - t0) / args.steps
     nbytes = step_bytes(args.m, layers)
     return nbytes / dt / 1e9, dt * 1e3, threads, f"{layers} of {LAYERS} layers ({len(mats)} matrices) per step"
+
+
+def spot_check(layers, xs, tiles, out_local, out_full, M, world, phase_cols):
+    """Untimed: 64 weight rows of the first and of the last projection of the step against the CPU oracle (rank 0's
+    shard).  Returns True / False; the benchmark number is a claim only if the kernels computed the right thing."""
+    import numpy as np
+    import torch
+    import oracle
+    ok = True
+    for li, pi in ((0, 0), (len(layers) - 1, len(PROJ) - 1)):
+        w, sc, bi, k, nl, phase = layers[li][pi]
+        rows = min(64, nl)
+        x = xs[k].float().cpu().numpy()
+        kl = x.shape[1]
+        ref = oracle.qmm(w[:rows].cpu().numpy().view(np.uint32), sc[:rows].float().cpu().numpy(), bi[:rows].float().cpu().numpy(),
+                         np.ascontiguousarray(x), M, rows, kl, BITS, GROUP)
+        col = sum(n for (_, _, _, _, n, p) in layers[li][:pi] if p == phase)
+        if M == 1 or world > 1:
+            got = out_local[li][phase][:, col:col + rows]
+            if out_full is not None:      # peer-store gather: this rank's slot of the gathered block
+                got = out_full[li][phase].view(world, M, phase_cols[phase])[0][:, col:col + rows]
+        else:
+            got = tiles[li][pi][:, :rows]
+        err = np.abs(got.float().cpu().numpy() - ref) / np.maximum(np.abs(ref), 1.0)
+        ok = ok and bool(np.all(err <= 1e-2))
+    return ok
 
 
 def p2p_trial(ctx, dev, rank, world):
@@ -167,8 +194,8 @@ def p2p_trial(ctx, dev, rank, world):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes for one launch of the step's kernel
-# (profiles/qmv_pipe_m1_14336x4096_4bit_g64_bf16.md: 33.09 MB / 33.07 MB)
-NCU_TRAFFIC_RATIO = 1.001
+# (qmv_stream_kernel on the 14336 x 4096 projection, ncu --set full, cold L2: 33.68 MB read, 0 written, 33.07 MB algorithmic)
+NCU_TRAFFIC_RATIO = 1.018
 
 
 def main():
@@ -189,8 +216,9 @@ def main():
                          "a small trial of it on every rank reproduces the NCCL all-gather, else nccl")
     ap.add_argument("--verify", action="store_true", help="N > 1: check the p2p gather against the NCCL all-gather once")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE", help="mtc_set_option before running")
-    ap.add_argument("--mode", default="chain", choices=["chain", "launches"],
-                    help="one GPU: the whole step as one prepared chain (mtc_chain_run) or as one mtc_qmv launch per projection")
+    ap.add_argument("--mode", default="batched", choices=["batched", "chain", "launches"],
+                    help="one GPU: projections that share their activations fused (q/k/v and gate/up: mtc_qmv_batched, 4 launches "
+                         "per layer), the whole step as one prepared chain (mtc_chain_run), or one mtc_qmv launch per projection")
     ap.add_argument("--streams", type=int, default=1, help="parallel streams for the independent projections of a phase")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary single-kernel measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
@@ -348,26 +376,48 @@ def main():
                     dist.all_reduce(out_local[li][ph])
 
     launches_per_step = 7 * args.layers
+    run_info = {"dispatch": "one launch per projection"}
     chain = None
-    if world == 1 and args.mode == "chain":
-        # one prepared chain for the whole step: a persistent grid walks the 224 projections, the four dependent
-        # phases of every layer are device-side counters instead of launch boundaries
+    if world == 1 and args.mode in ("chain", "batched"):
         from metaltile_b200.ops import _projection
-        projs = []
-        for li, mats in enumerate(layers):
-            col = [0, 0, 0, 0]
-            for pi, (w, sc, bi, k, nl, phase) in enumerate(mats):
-                o = out_local[li][phase][:, col[phase]:col[phase] + nl] if M == 1 else tiles[li][pi]
-                col[phase] += nl
-                projs.append(_projection(w, sc, bi, xs[k], BITS, GROUP, [o], phase=li * 4 + phase))
-        chain = ctx.chain_create(projs)
-        if chain.fused:
-            launches_per_step = 1
+
+        def out_of(li, pi, phase, col, nl):
+            return out_local[li][phase][:, col:col + nl] if M == 1 else tiles[li][pi]
+
+        if args.mode == "chain":
+            # one prepared chain for the whole step: a persistent grid walks the 224 projections, the four dependent
+            # phases of every layer are device-side counters instead of launch boundaries
+            projs = []
+            for li, mats in enumerate(layers):
+                col = [0, 0, 0, 0]
+                for pi, (w, sc, bi, k, nl, phase) in enumerate(mats):
+                    projs.append(_projection(w, sc, bi, xs[k], BITS, GROUP, [out_of(li, pi, phase, col[phase], nl)], phase=li * 4 + phase))
+                    col[phase] += nl
+            chain = ctx.chain_create(projs)
+            if chain.fused:
+                launches_per_step = 1
+
+                def step():      # noqa: F811
+                    chain.run(torch.cuda.current_stream().cuda_stream)
+            run_info["dispatch"] = "one chain per step" if chain.fused else "one launch per projection"
+        else:
+            # projections of a phase read the same activations: one launch per phase (q/k/v, o, gate/up, down),
+            # the counterpart of ffai_batched_qkv_qgemv (crates/metaltile-std/src/ffai/batched_qkv_qgemv.rs:1-35)
+            groups = []
+            for li, mats in enumerate(layers):
+                col = [0, 0, 0, 0]
+                per_phase = [[], [], [], []]
+                for pi, (w, sc, bi, k, nl, phase) in enumerate(mats):
+                    per_phase[phase].append(_projection(w, sc, bi, xs[k], BITS, GROUP, [out_of(li, pi, phase, col[phase], nl)]))
+                    col[phase] += nl
+                groups.extend(g for g in per_phase if g)
+            launches_per_step = len(groups)
 
             def step():      # noqa: F811
-                chain.run(torch.cuda.current_stream().cuda_stream)
-        config["dispatch"] = "one chain per step" if chain.fused else "one launch per projection"
-
+                st = torch.cuda.current_stream().cuda_stream
+                for g in groups:
+                    ctx.qmv_batched(g, st)
+            run_info["dispatch"] = "one launch per phase (projections that share x fused)"
     # capture the step in a CUDA graph: 224 launches of ~1-5 us each are otherwise host-bound
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
@@ -422,6 +472,10 @@ def main():
 
     for _ in range(args.warmup):
         graph.replay()
+    verified = None
+    if rank == 0:
+        if not (world > 1 and args.tp == "megatron"):      # row-parallel outputs are sums over ranks: nothing local to compare
+            verified = spot_check(layers, xs, tiles, out_local, out_full if p2p else None, M, world, phase_cols)
     sampler = ClockSampler(local_rank)
     sampler.start()
     ms = timed(graph.replay, args.steps)
@@ -457,33 +511,42 @@ def main():
         if world > 1:
             os._exit(0)
 
+    multi = None
+    if world > 1 and not args.no_extra:
+        try:
+            multi = multi_gpu_extras(ctx, dev, rank, world, timed)
+        except Exception as e:  # all ranks take the same path: an exception here is raised on every rank or on none
+            multi = {"error": repr(e)}
     if rank != 0:
         finish()
         return
 
     if world > 1:
-        config["collective"] = config_collective
+        run_info["collective"] = config_collective
     hbm_peak, tf_burst, tf_sus, peak_kind = measured_peaks()
     per_launch_bytes = total_bytes / world / launches_per_step
     us_per_launch = ms * 1e3 / launches_per_step
     roofline = {"bound": "hbm", "achieved": value / world, "peak": hbm_peak, "unit": "GB/s",
                 "frac": value / world / hbm_peak, "traffic": per_launch_bytes * NCU_TRAFFIC_RATIO, "peak_kind": peak_kind,
                 "traffic_source": "ncu dram bytes / algorithmic bytes = 1.001 on the 14336x4096 launch, scaled to the average launch",
-                "kernel": "qmv_pipe_kernel<4,1,4,2,2>", "alg_bytes_per_launch": per_launch_bytes,
+                "kernel": "qmv_stream_kernel<bf16, g64, M1>", "alg_bytes_per_launch": per_launch_bytes,
                 "avg_us_per_launch": us_per_launch,
                 "note": "per-GPU; launch-averaged over the 4 matrix shapes of the step (graph replay, events)"}
     line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config, "clocks": clocks,
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config, "run": run_info, "verified": verified,
+            "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms},
             "gpu_launches": (launches_per_step + (4 * args.layers if p2p else 0)) * args.steps, "roofline": roofline}
 
     if not args.no_extra:
         try:
-            line["extra"] = extra_measurements(ctx, dev, hbm_peak, tf_burst)
+            line["extra"] = extra_measurements(ctx, dev, hbm_peak, tf_burst, local_rank, layers if world == 1 else None)
         except Exception as e:  # secondary numbers must never sink the headline line
             line["extra"] = {"error": repr(e)}
+        if multi is not None:
+            line["extra"].update(multi)
     if not args.no_cpu and world == 1:
         try:
             ns = argparse.Namespace(m=M, steps=3, warmup=1)
@@ -496,11 +559,93 @@ def main():
     finish()
 
 
-def extra_measurements(ctx, dev, hbm_peak, tf_peak):
-    """Single-kernel numbers for the other configurations (cold L2: buffers rotate through > 126 MB)."""
+def multi_gpu_extras(ctx, dev, rank, world, timed):
+    """The sharded forms of the prefill matmul (config 3: N-split + all-gather) and of the MoE layer (config 4: expert
+    parallel, all-to-all dispatch and combine), run by every rank; rank 0 checks its result against the unsharded
+    kernels on the same data (sharding changes no row's arithmetic, so the comparison is for equality)."""
+    import torch
+    import torch.distributed as dist
+    from metaltile_b200 import ops
+    from metaltile_b200.parallel import ColumnParallelLinear, ExpertParallelMoE, ExpertShard, CudaBackend, shard_rows
+    out = {}
+    be = CudaBackend(ctx)
+
+    def same_on_all_ranks(seed):
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed)          # same generator, same device type: every rank draws the same numbers
+        return g
+
+    # ---- config 3: x bf16 [2048, K], W K -> N, every rank owns N / world weight rows
+    for name, (m, n, k) in {"c3_qmm_nsplit_4096to14336": (2048, 14336, 4096), "c3_qmm_nsplit_14336to4096": (2048, 4096, 14336)}.items():
+        g = same_on_all_ranks(4242)
+        w = torch.randint(-2 ** 31, 2 ** 31 - 1, (n, k * BITS // 32), dtype=torch.int32, device=dev, generator=g)
+        sc = (0.002 + 0.018 * torch.rand((n, k // GROUP), device=dev, generator=g)).to(torch.bfloat16)
+        bi = (-8.0 * sc.float()).to(torch.bfloat16)
+        x = torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16)
+        r0, r1 = shard_rows(n, world, rank)
+        lin = ColumnParallelLinear(w[r0:r1].contiguous(), sc[r0:r1].contiguous(), bi[r0:r1].contiguous(), BITS, GROUP, backend=be)
+        got = lin.forward(x)
+        torch.cuda.synchronize()
+        verified = None
+        if rank == 0:
+            ref = ops.qmm(w, sc, bi, x, BITS, GROUP, ctx=ctx)
+            torch.cuda.synchronize()
+            verified = bool(torch.equal(ref, got))
+        ms = timed(lambda: lin.forward(x), 5)
+        tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+        out[name] = {"us": ms * 1e3, "TFLOP/s": tf, "ranks": world, "verified": verified,
+                     "note": "aggregate over all ranks, NCCL all-gather of the [M, N / ranks] slices and the row-major interleave included"}
+        del w, sc, bi, x, lin, got
+    # ---- config 4: 512 tokens (data parallel), 128 experts split over the ranks, top-8
+    T, H, I, E, K8 = 512, 2048, 768, 128, 8
+    if E % world == 0 and T % world == 0:
+        g = same_on_all_ranks(777)
+
+        def experts(n, k):
+            w = torch.randint(-2 ** 31, 2 ** 31 - 1, (E, n, k * BITS // 32), dtype=torch.int32, device=dev, generator=g)
+            sc = (0.002 + 0.018 * torch.rand((E, n, k // GROUP), device=dev, generator=g)).to(torch.bfloat16)
+            return w, sc, (-8.0 * sc.float()).to(torch.bfloat16)
+
+        gate, up, down = experts(I, H), experts(I, H), experts(H, I)
+        tok = torch.randn((T, H), device=dev, generator=g).to(torch.bfloat16)
+        logits = torch.randn((T, E), device=dev, generator=g).to(torch.bfloat16)
+        e0, e1 = rank * (E // world), (rank + 1) * (E // world)
+        t0, t1 = rank * (T // world), (rank + 1) * (T // world)
+        cut = lambda trip: tuple(a[e0:e1].contiguous() for a in trip)
+        moe = ExpertParallelMoE(ExpertShard(cut(gate), cut(up), cut(down), BITS, GROUP), E, K8, 1, backend=be)
+        tl, ll = tok[t0:t1].contiguous(), logits[t0:t1].contiguous()
+        got = moe.forward(tl, ll)
+        torch.cuda.synchronize()
+        verified = None
+        if rank == 0:
+            one = ExpertParallelMoE(ExpertShard(gate, up, down, BITS, GROUP), E, K8, 1, backend=be, group=None)
+            one.world, one.e_local = 1, E          # the unsharded layer on this rank's tokens
+            ref = one.forward(tl, ll)
+            torch.cuda.synchronize()
+            verified = bool(torch.equal(ref, got))
+            if not verified:
+                verified = {"max_abs_diff": float((ref.float() - got.float()).abs().max())}
+        ms = timed(lambda: moe.forward(tl, ll), 5)
+        flops = 2.0 * T * K8 * 3 * H * I
+        out["c4_moe_ep"] = {"us": ms * 1e3, "TFLOP/s": flops / (ms * 1e-3) / 1e12, "ranks": world, "verified": verified,
+                            "tokens_per_rank": T // world, "experts_per_rank": E // world,
+                            "note": "per layer, both all-to-alls (dispatch, combine) and the count exchange included"}
+    return out
+
+
+def extra_measurements(ctx, dev, hbm_peak, tf_peak, local_rank=0, layers=None):
+    """Single-kernel numbers for the other configurations (cold L2: buffers rotate through > 126 MB).  Every entry
+    carries the SM clock sampled while it ran."""
     import torch
     from metaltile_b200 import ops
     out = {}
+
+    def with_clocks(fn):
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        val = fn()
+        c = sampler.stop()
+        return val, {"sm_mhz": c["sm_mhz"], "reasons": c["reasons"]}
     gen = torch.Generator(device=dev)
     gen.manual_seed(99)
 
@@ -543,9 +688,9 @@ def extra_measurements(ctx, dev, hbm_peak, tf_peak):
         copies = max(2, int(300e6 // alg_bytes(m, n, k)) + 1)   # > 2x L2 in rotation
         sets, x, o = make(n, k, m, copies)
         fns = [(lambda w=w, sc=sc, bi=bi: ops.qmv(w, sc, bi, x, BITS, GROUP, out=o, ctx=ctx)) for (w, sc, bi) in sets]
-        us = time_rot(fns, 20)
+        us, clk = with_clocks(lambda: time_rot(fns, 20))
         gbs = alg_bytes(m, n, k) / us / 1e3
-        out[name] = {"us": us, "GB/s": gbs, "frac_of_hbm_peak": gbs / hbm_peak, "cold_l2_copies": copies}
+        out[name] = {"us": us, "GB/s": gbs, "frac_of_hbm_peak": gbs / hbm_peak, "cold_l2_copies": copies, "clocks": clk}
         del sets, fns
     # ---- prefill qmm on the tensor cores (M = 2048), TFLOP/s = 2*M*N*K / time
     def time_calls(fn, reps=10):
@@ -563,9 +708,10 @@ def extra_measurements(ctx, dev, hbm_peak, tf_peak):
     for name, (m, n, k) in {"c3_qmm_m2048_4096to14336": (2048, 14336, 4096), "c3_qmm_m2048_14336to4096": (2048, 4096, 14336)}.items():
         sets, x, o = make(n, k, m, 1)
         w, sc, bi = sets[0]
-        us = time_calls(lambda: ops.qmm(w, sc, bi, x, BITS, GROUP, out=o, ctx=ctx))
+        us, clk = with_clocks(lambda: time_calls(lambda: ops.qmm(w, sc, bi, x, BITS, GROUP, out=o, ctx=ctx)))
         tf = 2.0 * m * n * k / us / 1e6
-        out[name] = {"us": us, "TFLOP/s": tf, "frac_of_bf16_peak": tf / tf_peak, "route": ctx.qmm_route(m, n, k, BITS, GROUP, "bf16")}
+        out[name] = {"us": us, "TFLOP/s": tf, "frac_of_bf16_peak": tf / tf_peak, "route": ctx.qmm_route(m, n, k, BITS, GROUP, "bf16"),
+                     "clocks": clk}
         del sets
 
     # ---- MoE layer: 512 tokens x hidden 2048, 128 experts (gate/up 2048->768, down 768->2048), top-8
@@ -590,12 +736,35 @@ def extra_measurements(ctx, dev, hbm_peak, tf_peak):
         y = ops.gather_qmm(a, *down, BITS, GROUP, expert_offsets=off, ctx=ctx)
         return ops.moe_unpermute(y, inv, wts, ctx=ctx)
 
-    us = time_calls(moe_layer)
+    us, clk = with_clocks(lambda: time_calls(moe_layer))
     flops = 2.0 * T * K8 * 3 * H * I
     wbytes = 3 * E * (H * I * BITS // 8 + 2 * (H * I // GROUP) * 2)
     out["c4_moe_layer_512tok_128e_top8"] = {"us": us, "TFLOP/s": flops / us / 1e6, "weight_GB/s": wbytes / us / 1e3,
                                             "frac_of_hbm_peak": wbytes / us / 1e3 / hbm_peak,
-                                            "note": "HBM-bound: 340 MB of expert weights per layer (L2-warm repeats)"}
+                                            "note": "HBM-bound: 340 MB of expert weights per layer (L2-warm repeats)", "clocks": clk}
+    # ---- the decode set at M = 8 (config 2 names M = 1 and 8): the step's own weights, 8 activation rows
+    if layers is not None:
+        from metaltile_b200.ops import _projection
+        m8 = 8
+        x8 = {k: torch.randn((m8, k), device=dev, generator=gen).to(torch.bfloat16) for k in (4096, 14336)}
+        groups, keep = [], []
+        for mats in layers:
+            per_phase = [[], [], [], []]
+            for (w, sc, bi, k, nl, phase) in mats:
+                o = torch.empty((m8, nl), dtype=torch.bfloat16, device=dev)
+                keep.append(o)
+                per_phase[phase].append(_projection(w, sc, bi, x8[k[0]], BITS, GROUP, [o]))
+            groups.extend(g for g in per_phase if g)
+
+        def step8():
+            st = torch.cuda.current_stream().cuda_stream
+            for g in groups:
+                ctx.qmv_batched(g, st)
+
+        us, clk = with_clocks(lambda: time_rot([step8], 10))
+        nbytes = step_bytes(m8, len(layers))
+        out["c2_decode_set_m8"] = {"ms": us / 1e3, "GB/s": nbytes / us / 1e3, "frac_of_hbm_peak": nbytes / us / 1e3 / hbm_peak,
+                                   "launches": len(groups), "clocks": clk}
     return out
 
 

@@ -1,0 +1,91 @@
+"""Runtime behaviour of the C ABI on a GPU: a bounded device-side wait that really runs out and reaches the caller as
+Timeout, the host deadline of mtc_sync_deadline, and one context per device in one process."""
+import numpy as np
+import pytest
+
+import oracle
+from helpers import TOL, dense_case, rel_err, to_dev
+
+pytestmark = pytest.mark.gpu
+
+
+def test_a_bounded_wait_expires_and_reaches_the_caller():
+    """A peer barrier for two ranks whose second rank never arrives (its flag array is a local buffer nobody writes):
+    with a poll limit of a few thousand the kernel gives up, records 0x601 + the missing rank and returns; the next
+    synchronising call reports Timeout; after mtc_status_clear the context works as before.  Nothing faults or spins
+    without a bound."""
+    import torch
+    from metaltile_b200 import MetalTileError, ops
+    ctx = ops.context(0)
+    assert ctx.status_word() == 0
+    mine = torch.zeros(64, dtype=torch.int32, device="cuda")       # 8 flag words, the epoch counter at byte 128
+    absent = torch.zeros(64, dtype=torch.int32, device="cuda")     # "rank 1": never written by anybody
+    st = torch.cuda.current_stream().cuda_stream
+    ctx.set_option("peer_poll_limit", 4000)
+    try:
+        ctx.peer_barrier([mine.data_ptr(), absent.data_ptr()], 0, mine.data_ptr(), mine.data_ptr() + 128, stream=st)
+        with pytest.raises(MetalTileError) as ei:
+            ctx.sync(st)
+        assert ei.value.variant == "Timeout" and "0x602" in str(ei.value)
+        assert ctx.status_word() == 0x602
+        # the name-keyed dispatch reports it too, instead of returning whatever the buffers hold
+        w, s, b, x = dense_case(1, 8, 64, 4, 64, "f32")
+        bufs = {"w": w.tobytes(), "scales": s.tobytes(), "biases": b.tobytes(), "x": x.tobytes(), "out": bytes(32)}
+        with pytest.raises(MetalTileError) as ei:
+            ctx.dispatch_with_grid("mt_qmm", bufs, {"k": 64, "n": 8, "gs_per_row": 1})
+        assert ei.value.variant == "Timeout"
+    finally:
+        ctx.set_option("peer_poll_limit", 1 << 22)
+        ctx.status_clear()
+    assert ctx.status_word() == 0
+    ctx.sync(st)
+    res = ctx.dispatch_with_grid("mt_qmm", bufs, {"k": 64, "n": 8, "gs_per_row": 1})
+    ref = oracle.qmm(w, s, b, x, 1, 8, 64, 4, 64)
+    assert rel_err(np.frombuffer(res.outputs["out"], dtype=np.float32).reshape(1, 8), ref) <= TOL["f32"]
+
+
+def test_sync_deadline():
+    """mtc_sync_deadline returns when the stream is done (well inside the deadline here); a deadline of 0 ms on a
+    stream with queued work either finds it finished or reports Timeout while the work carries on."""
+    import torch
+    from metaltile_b200 import MetalTileError, ops
+    ctx = ops.context(0)
+    st = torch.cuda.current_stream().cuda_stream
+    w, s, b, x = dense_case(1, 8192, 8192, 4, 64, "bf16", seed=1)
+    args = (to_dev(w), to_dev(s, "bf16"), to_dev(b, "bf16"), to_dev(x, "bf16"), 4, 64)
+    out = ops.qmv(*args, ctx=ctx)
+    ctx.sync(st, timeout_ms=10000)
+    for _ in range(200):
+        out = ops.qmv(*args, out=out, ctx=ctx)
+    try:
+        ctx.sync(st, timeout_ms=0)
+    except MetalTileError as e:
+        assert e.variant == "Timeout" and "did not finish" in str(e)
+    ctx.sync(st)
+    assert ctx.status_word() == 0
+
+
+def test_one_context_per_device():
+    """Contexts on two devices in one process: qmv, qmm and gather_qmm on both (per-device kernel attributes, every
+    entry makes its context's device current)."""
+    import torch
+    from metaltile_b200 import ops
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two devices")
+    w, s, b, x = dense_case(40, 256, 512, 4, 64, "bf16", seed=3)
+    ref = oracle.qmm(w, s, b, x, 40, 256, 512, 4, 64)
+    off = np.array([0, 25, 40], dtype=np.uint32)
+    gw, gs_, gb = (np.stack([a, a]) for a in (w, s, b))          # two experts with the same matrix
+    for d in (1, 0, 1):
+        dev = torch.device("cuda", d)
+        ctx = ops.context(dev)
+        with torch.cuda.device(dev):
+            td = lambda a, dt=None: to_dev(a, dt).to(dev)
+            one = ops.qmv(td(w), td(s, "bf16"), td(b, "bf16"), td(x[:1], "bf16"), 4, 64, ctx=ctx)
+            full = ops.qmm(td(w), td(s, "bf16"), td(b, "bf16"), td(x, "bf16"), 4, 64, ctx=ctx)
+            gat = ops.gather_qmm(td(x, "bf16"), td(gw), td(gs_, "bf16"), td(gb, "bf16"), 4, 64, expert_offsets=td(off), ctx=ctx)
+            torch.cuda.synchronize(dev)
+            assert rel_err(one.float().cpu().numpy(), ref[:1]) <= TOL["bf16"]
+            assert rel_err(full.float().cpu().numpy(), ref) <= TOL["bf16"]
+            assert rel_err(gat.float().cpu().numpy(), ref) <= TOL["bf16"]
+            assert ctx.status_word() == 0

@@ -67,3 +67,20 @@ def test_static_scratch_matches_regular_entry_twice_in_a_row():
     with pytest.raises(MetalTileError) as ei:
         ctx.gather_qmm_static(xd.data_ptr(), 256, 256, 256, 256, 16, 256, 96, 4, 4, 32, "bf16", expert_offsets=256)
     assert ei.value.variant == "Unsupported"
+
+
+def test_static_scratch_refuses_what_does_not_fit():
+    """The other two limits of the fixed array: more than 16384 work items, and more than 65536 bf16 rows.  Both are
+    refused before anything is launched (the pointers below are never dereferenced)."""
+    import torch
+    from metaltile_b200 import MetalTileError, ops
+    ctx = ops.context(0)
+    dummy = 256
+    with pytest.raises(MetalTileError) as ei:      # 5 row tiles x (1 + 4096 experts) items
+        ctx.gather_qmm_static(dummy, dummy, dummy, dummy, dummy, 16, 640, 64, 4096, 4, 64, "f16", expert_offsets=dummy)
+    assert ei.value.variant == "BufferSize" and "16384 work items" in str(ei.value)
+    with pytest.raises(MetalTileError) as ei:      # 65537 rows of 64 elements: within the element limit, over the row limit
+        ctx.gather_qmm_static(dummy, dummy, dummy, dummy, dummy, 65537, 128, 64, 4, 4, 64, "bf16", expert_offsets=dummy)
+    assert ei.value.variant == "BufferSize" and "65536" in str(ei.value)
+    torch.cuda.synchronize()
+    assert ctx.status_word() == 0
