@@ -238,13 +238,13 @@ def main():
         if rank != 0:
             return
         val, ms, threads, sample = cpu_reference_arm(args)
-        print(json.dumps({
+        emit({
             "impl": "reference", "metric": METRIC, "value": val, "unit": "GB/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
             "cpu_baseline": {"value": val, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}))
+            "gpu_launches": 0})
         return
 
     import torch
@@ -418,6 +418,31 @@ def main():
                 for g in groups:
                     ctx.qmv_batched(g, st)
             run_info["dispatch"] = "one launch per phase (projections that share x fused)"
+    barrier_launches = 4 * args.layers if p2p else 0
+    if p2p and args.mode == "batched":
+        # sharded decode: one launch per phase whose kernel stores this rank's tiles into every rank's gathered block
+        # and carries the hand-off itself (wait for the peers' previous launch, publish its own completion); one barrier
+        # kernel at the end of the step, before anything outside the chain of launches reads the blocks
+        pgroups = []
+        for li, mats in enumerate(layers):
+            for ph in range(4):
+                col, g, offs, k0 = 0, [], [], None
+                for (w, sc, bi, k, nl, phase) in mats:
+                    if phase != ph:
+                        continue
+                    g.append((w, sc, bi))
+                    offs.append((full_off[li * 4 + ph] + rank * M * phase_cols[ph] + col) * 2)
+                    col += nl
+                    k0 = k
+                pgroups.append((g, xs[k0], offs))
+
+        def step():      # noqa: F811
+            st = torch.cuda.current_stream().cuda_stream
+            for g, x, offs in pgroups:
+                peer.batched_into(g, x, BITS, GROUP, offs, st)
+            peer.barrier(st)
+        launches_per_step, barrier_launches = len(pgroups), 1
+        run_info["dispatch"] = "one launch per phase (projections that share x fused), hand-off between the GPUs inside the kernel"
     # capture the step in a CUDA graph: 224 launches of ~1-5 us each are otherwise host-bound
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
@@ -528,7 +553,7 @@ def main():
     us_per_launch = ms * 1e3 / launches_per_step
     roofline = {"bound": "hbm", "achieved": value / world, "peak": hbm_peak, "unit": "GB/s",
                 "frac": value / world / hbm_peak, "traffic": per_launch_bytes * NCU_TRAFFIC_RATIO, "peak_kind": peak_kind,
-                "traffic_source": "ncu dram bytes / algorithmic bytes = 1.001 on the 14336x4096 launch, scaled to the average launch",
+                "traffic_source": f"ncu dram bytes / algorithmic bytes = {NCU_TRAFFIC_RATIO} on the 14336x4096 launch of the streaming kernel, scaled to the average launch",
                 "kernel": "qmv_stream_kernel<bf16, g64, M1>", "alg_bytes_per_launch": per_launch_bytes,
                 "avg_us_per_launch": us_per_launch,
                 "note": "per-GPU; launch-averaged over the 4 matrix shapes of the step (graph replay, events)"}
@@ -538,7 +563,7 @@ def main():
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms},
-            "gpu_launches": (launches_per_step + (4 * args.layers if p2p else 0)) * args.steps, "roofline": roofline}
+            "gpu_launches": (launches_per_step + barrier_launches) * args.steps, "roofline": roofline}
 
     if not args.no_extra:
         try:
@@ -555,7 +580,7 @@ def main():
                                     "sample": sample, "ms_per_sample": cms}
         except Exception as e:
             line["cpu_baseline"] = {"error": repr(e)}
-    print(json.dumps(line))
+    emit(line)
     finish()
 
 
@@ -768,5 +793,16 @@ def extra_measurements(ctx, dev, hbm_peak, tf_peak, local_rank=0, layers=None):
     return out
 
 
+def emit(line: dict):
+    """The result line goes to the process's original stdout; everything else any library prints goes to stderr."""
+    _RESULT_OUT.write(json.dumps(line) + "\n")
+    _RESULT_OUT.flush()
+
+
 if __name__ == "__main__":
+    # libraries loaded later (NCCL prints its version line from C) write to file descriptor 1: keep a private copy of it
+    # for the one JSON line and point descriptor 1 at stderr
+    sys.stdout.flush()
+    _RESULT_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     main()

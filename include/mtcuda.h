@@ -129,6 +129,20 @@ typedef struct {
 } mtc_qmv_desc;
 typedef struct mtc_chain mtc_chain;
 int mtc_qmv_batched(mtc_ctx *ctx, void *stream, const mtc_qmv_desc *descs, int n);
+/* mtc_qmv_batched for the sharded decode path with the hand-off between the GPUs inside the kernel (no counterpart in the
+ * reference, which is a single-device library).  Every rank enqueues the same sequence of launches; a launch stores its
+ * results into every rank's buffers (descs[i].outs), waits - before it reads x - until every peer has finished the launch
+ * that matches this rank's previous one (bounded poll: status word 0x601 + peer on expiry), and when its last CTA is done
+ * publishes the next epoch into word `rank` of every peer's flag array.  peer_flags[q] = rank q's flag array (8 x uint32,
+ * shared with mtc_ipc_*), local_flags = this rank's own; epoch and ticket = one uint32 each of this rank's memory; all
+ * zeroed once.  Only shapes the streaming kernel takes (else MTC_ERR_UNSUPPORTED).  A buffer region may be rewritten only
+ * by a launch that comes after every rank's readers of it, i.e. at least one launch of this kind later. */
+typedef struct {
+    void *peer_flags[8];
+    void *local_flags, *epoch, *ticket;
+    int n_peers, rank;
+} mtc_peer_sync;
+int mtc_qmv_batched_sync(mtc_ctx *ctx, void *stream, const mtc_qmv_desc *descs, int n, const mtc_peer_sync *sync);
 int mtc_chain_create(mtc_ctx *ctx, const mtc_qmv_desc *descs, int n, mtc_chain **out_chain);
 int mtc_chain_run(mtc_ctx *ctx, void *stream, mtc_chain *chain);
 int mtc_chain_destroy(mtc_ctx *ctx, mtc_chain *chain);

@@ -28,6 +28,12 @@ class QmvDesc(ctypes.Structure):
                 ("phase", ctypes.c_int)]
 
 
+class PeerSync(ctypes.Structure):
+    """mtc_peer_sync: flag arrays and counters of the in-kernel hand-off between the GPUs of a node."""
+    _fields_ = [("peer_flags", ctypes.c_void_p * 8), ("local_flags", ctypes.c_void_p), ("epoch", ctypes.c_void_p),
+                ("ticket", ctypes.c_void_p), ("n_peers", ctypes.c_int), ("rank", ctypes.c_int)]
+
+
 class NamedBuf(ctypes.Structure):
     _fields_ = [("name", ctypes.c_char_p), ("data", ctypes.c_void_p), ("bytes", ctypes.c_size_t),
                 ("is_output", ctypes.c_int)]
@@ -56,6 +62,7 @@ SIGNATURES = {
     "mtc_qmm_route": (ctypes.c_char_p, [_i, _i, _i, _i, _i, _i]),
     "mtc_qmv_multi": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i]),
     "mtc_qmv_batched": (_i, [_vp, _vp, ctypes.POINTER(QmvDesc), _i]),
+    "mtc_qmv_batched_sync": (_i, [_vp, _vp, ctypes.POINTER(QmvDesc), _i, ctypes.POINTER(PeerSync)]),
     "mtc_chain_create": (_i, [_vp, ctypes.POINTER(QmvDesc), _i, ctypes.POINTER(_vp)]),
     "mtc_chain_run": (_i, [_vp, _vp, _vp]),
     "mtc_chain_destroy": (_i, [_vp, _vp]),

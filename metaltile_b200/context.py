@@ -17,7 +17,7 @@ from dataclasses import dataclass, field
 from typing import Dict, Mapping, Optional, Sequence
 
 from . import _lib
-from ._lib import BF16, F16, F32, NamedBuf, QmvDesc
+from ._lib import BF16, F16, F32, NamedBuf, PeerSync, QmvDesc
 
 DTYPES = {"f32": F32, "f16": F16, "bf16": BF16}
 
@@ -165,6 +165,16 @@ class Context:
         """1 to 4 projections that read the same activations, one launch (``mtc_qmv_batched``)."""
         arr = self._descs(projections)
         self._check(self._lib.mtc_qmv_batched(self._h, stream, arr, len(projections)))
+
+    def qmv_batched_sync(self, projections, peer_flags, rank: int, local_flags: int, epoch: int, ticket: int, stream: int = 0):
+        """``qmv_batched`` whose launch also hands over to the other ranks (``mtc_qmv_batched_sync``)."""
+        arr = self._descs(projections)
+        ps = PeerSync()
+        for i, p in enumerate(peer_flags):
+            ps.peer_flags[i] = int(p)
+        ps.local_flags, ps.epoch, ps.ticket = int(local_flags), int(epoch), int(ticket)
+        ps.n_peers, ps.rank = len(peer_flags), int(rank)
+        self._check(self._lib.mtc_qmv_batched_sync(self._h, stream, arr, len(projections), ctypes.byref(ps)))
 
     def chain_create(self, projections) -> "Chain":
         """A prepared list of projections walked by one persistent grid (``mtc_chain_create``)."""

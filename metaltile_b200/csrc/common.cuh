@@ -111,7 +111,7 @@ cudaError_t qmv_init_device();
 bool qmv_stream_supported(int M, int N, int K, int bits, int group_size, int dt, const void *w, const void *scales,
                           const void *biases, const void *x);
 cudaError_t qmv_stream_init_device();
-cudaError_t launch_qmv_stream(Ctx *ctx, cudaStream_t st, const mtc_qmv_desc *descs, int n);
+cudaError_t launch_qmv_stream(Ctx *ctx, cudaStream_t st, const mtc_qmv_desc *descs, int n, const mtc_peer_sync *sync = nullptr);
 bool qmv_tc_supported(int M, int N, int K, int bits, int group_size, int dt, const void *w, const void *scales,
                       const void *biases, const void *x);
 cudaError_t qmv_tc_init_device();

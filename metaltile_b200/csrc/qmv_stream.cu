@@ -80,6 +80,15 @@ struct SArgs {
     int early_weights;       // 1: weight copies start before griddepcontrol.wait (weights are constants of the model)
     uint32_t off_xsum, off_red, off_ring;    // shared-memory layout (the activation fragments start at kOffX)
     uint32_t red_slot_floats;
+    // sharded decode (n_peers > 0): the hand-off between the GPUs of a node rides in the kernels.  Before it reads its
+    // activations a launch waits until every peer has published the epoch this rank's previous launch ended with
+    // (bounded poll, status 0x601 + peer on expiry); when its last CTA is done it publishes the next epoch to every peer.
+    uint32_t *peer_flags[8];   // peer q's flag words, mapped here; word `rank` is written by this rank
+    uint32_t *local_flags;     // this rank's flag words: word q is written by rank q
+    uint32_t *epoch;           // this rank's epoch counter (device memory, zeroed once)
+    uint32_t *ticket;          // CTAs of the current launch that are done (zero between launches)
+    int n_peers, rank;
+    uint32_t poll_limit;
 };
 
 struct __align__(16) Ctl {
@@ -391,6 +400,25 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_stream_kernel(const __grid_co
     int islot = DEPTH - 1, cslot = 0;
     // the weights do not depend on the previous kernel of the stream; the activations and every store do
     if (a.early_weights) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (a.n_peers > 0) {
+        // every peer has finished the launch that matches this rank's previous one: its stores into this rank's
+        // buffers (possibly this launch's activations) have landed
+        if (threadIdx.x < a.n_peers) {
+            const uint32_t want = *reinterpret_cast<volatile uint32_t *>(a.epoch);
+            bool seen = false;
+            for (uint32_t i = 0; i < a.poll_limit; ++i) {
+                uint32_t v;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.local_flags + threadIdx.x) : "memory");
+                if (static_cast<int32_t>(v - want) >= 0) {
+                    seen = true;
+                    break;
+                }
+                __nanosleep(20);
+            }
+            if (!seen) atomicCAS(a.status, 0u, 0x601u + threadIdx.x);      // that rank never arrived; carry on, the host is told
+        }
+        __syncthreads();
+    }
 
     // ---- arithmetic side ----------------------------------------------------------------------------------------
     const int pi = 2 * (g & 3) + (g >> 2);                      // tile row of MMA row g (and 8 + pi of MMA row g + 8)
@@ -538,6 +566,20 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_stream_kernel(const __grid_co
         }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (a.n_peers > 0) {
+        __syncthreads();                                         // every store of this CTA has been issued
+        if (threadIdx.x == 0) {
+            __threadfence();
+            if (atomicAdd(a.ticket, 1u) == gridDim.x - 1) {      // the last CTA of the launch
+                *a.ticket = 0u;
+                const uint32_t e = *reinterpret_cast<volatile uint32_t *>(a.epoch) + 1u;
+                __threadfence_system();
+                for (int q = 0; q < a.n_peers; ++q)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.peer_flags[q] + a.rank), "r"(e) : "memory");
+                *reinterpret_cast<volatile uint32_t *>(a.epoch) = e;
+            }
+        }
+    }
     if (chain) {
         // the last CTA to leave clears the counters for the next run of the chain
         __syncthreads();
@@ -674,9 +716,24 @@ static void fill_layout(SArgs &a, Ctx *ctx, const Plan &plan) {
 }
 
 // 1 to 4 projections that read the same activations (one launch; each writes its own outputs).
-cudaError_t launch_qmv_stream(Ctx *ctx, cudaStream_t st, const mtc_qmv_desc *d, int n) {
+cudaError_t launch_qmv_stream(Ctx *ctx, cudaStream_t st, const mtc_qmv_desc *d, int n, const mtc_peer_sync *sync) {
     if (n < 1 || n > kMaxInline) return cudaErrorInvalidValue;
     SArgs a{};
+    if (sync) {
+        if (sync->n_peers < 1 || sync->n_peers > 8 || sync->rank < 0 || sync->rank >= sync->n_peers || !sync->local_flags ||
+            !sync->epoch || !sync->ticket)
+            return cudaErrorInvalidValue;
+        for (int q = 0; q < sync->n_peers; ++q) {
+            if (!sync->peer_flags[q]) return cudaErrorInvalidValue;
+            a.peer_flags[q] = static_cast<uint32_t *>(sync->peer_flags[q]);
+        }
+        a.local_flags = static_cast<uint32_t *>(sync->local_flags);
+        a.epoch = static_cast<uint32_t *>(sync->epoch);
+        a.ticket = static_cast<uint32_t *>(sync->ticket);
+        a.n_peers = sync->n_peers;
+        a.rank = sync->rank;
+        a.poll_limit = ctx->peer_poll_limit;
+    }
     long long rows = 0;
     for (int i = 0; i < n; ++i) {
         if (d[i].x != d[0].x || d[i].M != d[0].M || d[i].K != d[0].K || d[i].dtype != d[0].dtype || d[i].group_size != d[0].group_size)

@@ -463,6 +463,7 @@ int mtc_qmv_batched(mtc_ctx *ctx, void *stream, const mtc_qmv_desc *descs, int n
         const mtc_qmv_desc &d = descs[i];
         if (d.x != descs[0].x || d.M != descs[0].M || d.K != descs[0].K || d.dtype != descs[0].dtype)
             return fail(ctx, MTC_ERR_INVALID, "qmv_batched: the projections must share x, M, K and dtype");
+        fused = fused && d.group_size == descs[0].group_size;
         fused = fused && d.M > 0 && d.N > 0 &&
                 mtc::qmv_stream_supported(d.M, d.N, d.K, d.bits, d.group_size, d.dtype, d.w, d.scales, d.biases, d.x);
     }
@@ -478,6 +479,27 @@ int mtc_qmv_batched(mtc_ctx *ctx, void *stream, const mtc_qmv_desc *descs, int n
                                                d.group_size, d.dtype);
         if (rc != MTC_OK) return rc;
     }
+    return MTC_OK;
+}
+
+int mtc_qmv_batched_sync(mtc_ctx *ctx, void *stream, const mtc_qmv_desc *descs, int n, const mtc_peer_sync *sync) {
+    if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    if (!sync) return mtc_qmv_batched(ctx, stream, descs, n);
+    if (!descs || n < 1 || n > 4) return fail(ctx, MTC_ERR_INVALID, "qmv_batched_sync: 1 to 4 projections");
+    for (int i = 0; i < n; ++i) {
+        int rc = check_desc(ctx, descs[i], "qmv_batched_sync");
+        if (rc != MTC_OK) return rc;
+        const mtc_qmv_desc &d = descs[i];
+        if (d.x != descs[0].x || d.M != descs[0].M || d.K != descs[0].K || d.dtype != descs[0].dtype || d.group_size != descs[0].group_size)
+            return fail(ctx, MTC_ERR_INVALID, "qmv_batched_sync: the projections must share x, M, K, dtype and group size");
+        if (!ctx->qmv_stream || !mtc::qmv_stream_supported(d.M, d.N, d.K, d.bits, d.group_size, d.dtype, d.w, d.scales, d.biases, d.x))
+            return fail(ctx, MTC_ERR_UNSUPPORTED, "qmv_batched_sync: only shapes of the streaming kernel (4-bit, f16 / bf16, M <= 8, "
+                                                  "K % 512 == 0, group 64 or 128, 16-byte aligned pointers)");
+    }
+    cudaError_t e = mtc::launch_qmv_stream(ctx, static_cast<cudaStream_t>(stream), descs, n, sync);
+    if (e == cudaErrorInvalidValue) return fail(ctx, MTC_ERR_INVALID, "qmv_batched_sync: 1 to 8 peers, rank < peers, no null pointer");
+    if (e != cudaSuccess) return fail(ctx, MTC_ERR_DISPATCH, std::string("qmv_batched_sync launch: ") + cudaGetErrorString(e));
     return MTC_OK;
 }
 

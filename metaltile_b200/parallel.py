@@ -132,8 +132,12 @@ class PeerGather:
     Each rank allocates ``nbytes`` plus a flag block with the library (plain device memory), the ranks exchange
     cudaIpc handles over ``torch.distributed`` and map each other's blocks.  ``qmv_into`` then runs a projection whose
     output tile lands in every rank's buffer at the same byte offset, and ``barrier`` enqueues the one-warp kernel that
-    makes a phase's tiles visible everywhere - the N-split all-gather without a collective launch.  The waits inside
-    are bounded; ``ctx.status_word()`` reports a rank that never arrived (0x601 + rank)."""
+    makes a phase's tiles visible everywhere - the N-split all-gather without a collective launch.  ``batched_into`` runs
+    up to four projections that share x as one launch which also carries the hand-off (no barrier launch between
+    phases; one ``barrier`` before the host reads the buffer).  A region of the buffer may be rewritten only by a launch
+    that comes after every rank's readers of it - with ``batched_into`` at least one launch later, which a decode step
+    that writes each region once satisfies.  The waits inside are bounded; ``ctx.status_word()`` reports a rank that
+    never arrived (0x601 + rank)."""
 
     def __init__(self, ctx, nbytes: int, group=None):
         self.ctx, self.group, self.nbytes = ctx, group, nbytes
@@ -147,9 +151,11 @@ class PeerGather:
         mine = None
         try:
             self.buf = ctx.alloc(nbytes)
-            self.flags = ctx.alloc(256)                   # 8 flag words, then (at +128) the epoch counter
+            # two flag blocks of 256 bytes: [0] for the barrier kernel, [1] for the hand-off inside the decode kernels;
+            # each: 8 flag words, at +128 the epoch counter, at +192 the launch's CTA ticket
+            self.flags = ctx.alloc(512)
             ctx.memset(self.buf, 0, nbytes)
-            ctx.memset(self.flags, 0, 256)
+            ctx.memset(self.flags, 0, 512)
             ctx.sync()
             mine = (ctx.ipc_export(self.buf), ctx.ipc_export(self.flags))
         except Exception as e:  # reported through the exchange below
@@ -196,6 +202,19 @@ class PeerGather:
         outs = [self.peer_bufs[self.rank] + byte_offset] + [p + byte_offset for r, p in enumerate(self.peer_bufs) if r != self.rank]
         self.ctx.qmv_multi(w.data_ptr(), scales.data_ptr(), biases.data_ptr(), x.data_ptr(), outs, m, n, k, bits,
                            group_size, _TORCH_DT[x.dtype], stream=stream)
+
+    def batched_into(self, mats, x, bits, group_size, byte_offsets, stream: int):
+        """Up to four projections ``(w, scales, biases)`` of one x -> every rank's buffer at ``byte_offsets[i]``, as one
+        launch that waits for the peers' previous launch and publishes its own completion."""
+        from .ops import _TORCH_DT
+        m, k = x.shape
+        descs = []
+        for (w, sc, bi), off in zip(mats, byte_offsets):
+            outs = [self.peer_bufs[self.rank] + off] + [p + off for r, p in enumerate(self.peer_bufs) if r != self.rank]
+            descs.append(dict(w=w.data_ptr(), scales=sc.data_ptr(), biases=bi.data_ptr(), x=x.data_ptr(), outs=outs, M=m,
+                              N=w.shape[0], K=k, bits=bits, group_size=group_size, dtype=_TORCH_DT[x.dtype]))
+        f = self.flags + 256
+        self.ctx.qmv_batched_sync(descs, [p + 256 for p in self.peer_flags], self.rank, f, f + 128, f + 192, stream=stream)
 
     def barrier(self, stream: int):
         self.ctx.peer_barrier(self.peer_flags, self.rank, self.flags, self.flags + 128, stream=stream)

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 
 import oracle
-from helpers import TOL, dense_case, rel_err, to_dev
+from helpers import ODT, TOL, dense_case, rel_err, to_dev
 
 pytestmark = pytest.mark.gpu
 
@@ -89,3 +89,72 @@ def test_one_context_per_device():
             assert rel_err(full.float().cpu().numpy(), ref) <= TOL["bf16"]
             assert rel_err(gat.float().cpu().numpy(), ref) <= TOL["bf16"]
             assert ctx.status_word() == 0
+
+
+def _sync_case(n=1024, k=4096):
+    from metaltile_b200 import synth
+    x = oracle.round_through(synth.activations(1, k, seed=5), ODT["bf16"])
+    w, s, b, _ = dense_case(1, n, k, 4, 64, "bf16", seed=5, salt=3)
+    return w, s, b, x
+
+
+def test_hand_off_inside_the_decode_kernel_single_rank():
+    """mtc_qmv_batched_sync with one rank: every launch waits for the epoch its predecessor published (already there),
+    publishes the next one and leaves the CTA ticket at zero; results are those of mtc_qmv_batched, in two destinations."""
+    import torch
+    from metaltile_b200 import ops
+    ctx = ops.context(0)
+    n, k = 1024, 4096
+    w, s, b, x = _sync_case(n, k)
+    wd, sd, bd, xd = to_dev(w), to_dev(s, "bf16"), to_dev(b, "bf16"), to_dev(x, "bf16")
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")      # flag words, epoch at byte 128, ticket at byte 192
+    outs = [torch.zeros((1, n), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    desc = dict(w=wd.data_ptr(), scales=sd.data_ptr(), biases=bd.data_ptr(), x=xd.data_ptr(), outs=[o.data_ptr() for o in outs],
+                M=1, N=n, K=k, bits=4, group_size=64, dtype="bf16")
+    st = torch.cuda.current_stream().cuda_stream
+    f = flags.data_ptr()
+    for _ in range(3):
+        ctx.qmv_batched_sync([desc], [f], 0, f, f + 128, f + 192, stream=st)
+    ctx.sync(st)
+    assert ctx.status_word() == 0
+    host = flags.cpu()
+    assert host[0].item() == 3 and host[32].item() == 3 and host[48].item() == 0
+    ref = ops.qmv(wd, sd, bd, xd, 4, 64, ctx=ctx)
+    assert torch.equal(outs[0], ref) and torch.equal(outs[1], ref)
+    assert rel_err(ref.float().cpu().numpy(), oracle.qmm(w, s, b, x, 1, n, k, 4, 64)) <= TOL["bf16"]
+
+
+def test_hand_off_wait_for_an_absent_rank_expires():
+    """Two ranks of which the second never publishes (its flag array is a local buffer nobody writes): the first launch
+    passes (epoch 0), the second waits for epoch 1 of rank 1, gives up after the poll limit, records 0x602 and still
+    finishes its own product; the caller gets Timeout."""
+    import torch
+    from metaltile_b200 import MetalTileError, ops
+    ctx = ops.context(0)
+    n, k = 1024, 4096
+    w, s, b, x = _sync_case(n, k)
+    wd, sd, bd, xd = to_dev(w), to_dev(s, "bf16"), to_dev(b, "bf16"), to_dev(x, "bf16")
+    mine = torch.zeros(64, dtype=torch.int32, device="cuda")
+    absent = torch.zeros(64, dtype=torch.int32, device="cuda")
+    out = torch.zeros((1, n), dtype=torch.bfloat16, device="cuda")
+    desc = dict(w=wd.data_ptr(), scales=sd.data_ptr(), biases=bd.data_ptr(), x=xd.data_ptr(), outs=[out.data_ptr()],
+                M=1, N=n, K=k, bits=4, group_size=64, dtype="bf16")
+    st = torch.cuda.current_stream().cuda_stream
+    f = mine.data_ptr()
+    ctx.set_option("peer_poll_limit", 2000)
+    try:
+        ctx.qmv_batched_sync([desc], [f, absent.data_ptr()], 0, f, f + 128, f + 192, stream=st)
+        ctx.sync(st)                                   # epoch 0: nothing to wait for
+        assert ctx.status_word() == 0
+        ctx.qmv_batched_sync([desc], [f, absent.data_ptr()], 0, f, f + 128, f + 192, stream=st)
+        with pytest.raises(MetalTileError) as ei:
+            ctx.sync(st)
+        assert ei.value.variant == "Timeout" and "0x602" in str(ei.value)
+    finally:
+        ctx.set_option("peer_poll_limit", 1 << 22)
+        ctx.status_clear()
+    assert torch.equal(out, ops.qmv(wd, sd, bd, xd, 4, 64, ctx=ctx))
+    with pytest.raises(MetalTileError) as ei:          # a shape outside the streaming kernel's contract is refused
+        bad = dict(desc, group_size=32)
+        ctx.qmv_batched_sync([bad], [f], 0, f, f + 128, f + 192, stream=st)
+    assert ei.value.variant in ("Unsupported", "Invalid")
