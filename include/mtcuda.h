@@ -215,7 +215,26 @@ int mtc_gather_qmm(mtc_ctx *ctx, void *stream, const void *x, const void *w, con
 int mtc_gather_qmm_static(mtc_ctx *ctx, void *stream, const void *x, const void *w, const void *scales,
                           const void *biases, const void *expert_offsets, const void *indices, void *out,
                           int m_total, int n_out, int k_in, int n_experts, int bits, int group_size, int dtype);
-const char *mtc_gather_qmm_route(int m_total, int n_out, int k_in, int bits, int group_size, int dtype);
+/* The expert MLP of a mixture-of-experts layer, rows sorted by expert - the stages the reference draws between
+ * mt_moe_permute and mt_moe_unpermute (crates/metaltile-std/src/ffai/moe.rs:11-35) with mt_swiglu
+ * (crates/metaltile-std/src/mlx/swiglu.rs:45-57) in the middle; the reference fuses the tail of it in
+ * crates/metaltile-std/src/ffai/moe_down_swiglu_accum.rs:1-110:
+ *     y[r, :] = down_e( silu(gate_e(x_r)) * up_e(x_r) ),   e = the expert that owns sorted row r (expert_offsets),
+ *     x_r = x[sort_token_idx[r]] when sort_token_idx is given (x then has n_tokens rows), else x[r].
+ * gate, up: [n_experts, inter, hidden*bits/32]; down: [n_experts, hidden, inter*bits/32]; y: [m_total, hidden].
+ * The gate and up products and the SwiGLU are rounded to the activation type exactly as the separate entries
+ * (mtc_moe_permute, mtc_gather_qmm twice, mtc_swiglu, mtc_gather_qmm) round them: same results bit for bit.
+ * Few rows per expert (m_total <= 64 n_experts; 4-bit, f16 / bf16, group 64 / 128, hidden and inter multiples of 256):
+ * four launches on the weight-streaming kernel - rows to MMA fragments with the permutation folded in, gate and up as
+ * one stream over both matrices, SwiGLU to fragments, down.  Other shapes: composed from the separate entries.
+ * The intermediates live in grow-only blocks of the context (they move only outside stream capture). */
+typedef struct {
+    const void *w, *scales, *biases;
+} mtc_qmat;
+int mtc_moe_experts(mtc_ctx *ctx, void *stream, const void *x, const void *sort_token_idx, int n_tokens, const mtc_qmat *gate,
+                    const mtc_qmat *up, const mtc_qmat *down, const void *expert_offsets, void *y, int m_total, int hidden,
+                    int inter, int n_experts, int bits, int group_size, int dtype);
+const char *mtc_gather_qmm_route(int m_total, int n_out, int k_in, int n_experts, int bits, int group_size, int dtype);
 
 /* mt_moe_router_topk (moe.rs:65-192): indices_out u32[n_rows, k], weights_out T[n_rows, k]; ties go to
  * the lower expert index, NaN never wins; norm_topk_prob 1 = softmax over the chosen k, 0 = chosen

@@ -34,6 +34,11 @@ class PeerSync(ctypes.Structure):
                 ("ticket", ctypes.c_void_p), ("n_peers", ctypes.c_int), ("rank", ctypes.c_int)]
 
 
+class QMat(ctypes.Structure):
+    """mtc_qmat: packed words, scales and biases of one stacked expert matrix."""
+    _fields_ = [("w", ctypes.c_void_p), ("scales", ctypes.c_void_p), ("biases", ctypes.c_void_p)]
+
+
 class NamedBuf(ctypes.Structure):
     _fields_ = [("name", ctypes.c_char_p), ("data", ctypes.c_void_p), ("bytes", ctypes.c_size_t),
                 ("is_output", ctypes.c_int)]
@@ -73,7 +78,9 @@ SIGNATURES = {
     "mtc_peer_barrier": (_i, [_vp, _vp, ctypes.POINTER(_vp), _i, _i, _vp, _vp]),
     "mtc_gather_qmm": (_i, [_vp] * 9 + [_i] * 7),
     "mtc_gather_qmm_static": (_i, [_vp] * 9 + [_i] * 7),
-    "mtc_gather_qmm_route": (ctypes.c_char_p, [_i] * 6),
+    "mtc_moe_experts": (_i, [_vp, _vp, _vp, _vp, _i, ctypes.POINTER(QMat), ctypes.POINTER(QMat), ctypes.POINTER(QMat), _vp, _vp,
+                            _i, _i, _i, _i, _i, _i, _i]),
+    "mtc_gather_qmm_route": (ctypes.c_char_p, [_i] * 7),
     "mtc_moe_router_topk": (_i, [_vp] * 5 + [_i] * 5),
     "mtc_moe_sort": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "mtc_moe_permute": (_i, [_vp] * 5 + [_i] * 3),

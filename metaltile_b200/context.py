@@ -17,7 +17,7 @@ from dataclasses import dataclass, field
 from typing import Dict, Mapping, Optional, Sequence
 
 from . import _lib
-from ._lib import BF16, F16, F32, NamedBuf, PeerSync, QmvDesc
+from ._lib import BF16, F16, F32, NamedBuf, PeerSync, QMat, QmvDesc
 
 DTYPES = {"f32": F32, "f16": F16, "bf16": BF16}
 
@@ -230,8 +230,16 @@ class Context:
         self._check(self._lib.mtc_gather_qmm_static(self._h, stream, x, w, scales, biases, expert_offsets, indices,
                                                     out, m_total, n_out, k_in, n_experts, bits, group_size, _dt(dtype)))
 
-    def gather_qmm_route(self, m_total, n_out, k_in, bits, group_size, dtype) -> str:
-        return self._lib.mtc_gather_qmm_route(m_total, n_out, k_in, bits, group_size, _dt(dtype)).decode()
+    def moe_experts(self, x, sort_token_idx, n_tokens, gate, up, down, expert_offsets, y, m_total, hidden, inter, n_experts,
+                    bits, group_size, dtype, stream: int = 0):
+        """``mtc_moe_experts``; gate / up / down are (w, scales, biases) device pointers."""
+        mats = [QMat(int(m[0]), int(m[1]), int(m[2])) for m in (gate, up, down)]
+        self._check(self._lib.mtc_moe_experts(self._h, stream, x, sort_token_idx, n_tokens, ctypes.byref(mats[0]),
+                                              ctypes.byref(mats[1]), ctypes.byref(mats[2]), expert_offsets, y, m_total, hidden,
+                                              inter, n_experts, bits, group_size, _dt(dtype)))
+
+    def gather_qmm_route(self, m_total, n_out, k_in, n_experts, bits, group_size, dtype) -> str:
+        return self._lib.mtc_gather_qmm_route(m_total, n_out, k_in, n_experts, bits, group_size, _dt(dtype)).decode()
 
     def moe_router_topk(self, logits, indices_out, weights_out, n_rows, n_experts, k, norm_topk_prob, dtype,
                         stream: int = 0):

@@ -43,7 +43,33 @@ struct Ctx {
     size_t worklist_bytes = 0;
     void *d_xconv = nullptr;       // scaled-f16 copy of bf16 activations for the tensor-core kernels (grow-only)
     size_t xconv_bytes = 0;
+    void *d_gfrag = nullptr;       // streaming gather: activations in fragment order, their sums, the table of passes (grow-only)
+    size_t gfrag_bytes = 0;
+    int gather_stream = 1;         // option "gather_stream": 0 = grouped products never take the streaming kernel (gather_stream.cu)
+    void *d_moe = nullptr;         // mtc_moe_experts: gate and up outputs (and permuted rows on the composed path) (grow-only)
+    size_t moe_bytes = 0;
 };
+
+// Grow-only device block of a context.  The block only ever moves outside stream capture (a captured graph holds its
+// address), and an outgrown block stays allocated until mtc_destroy: work already enqueued, or a graph captured
+// earlier, may still name it.  Kernels that use such a block run on the caller's stream in call order; two streams
+// that use one context at the same time must not both use entries that need the same block.
+inline cudaError_t grow_block(Ctx *ctx, cudaStream_t st, void **block, size_t *have, size_t need, std::string *why) {
+    if (need <= *have) return cudaSuccess;
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) == cudaSuccess && cs != cudaStreamCaptureStatusNone) {
+        if (why) *why = "a scratch block of the context must grow, which cannot happen during stream capture: run this shape once before capturing";
+        return cudaErrorStreamCaptureUnsupported;
+    }
+    const size_t want = need + (need >> 1) + (1u << 20);
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, want);
+    if (e != cudaSuccess) return e;
+    if (*block) ctx->retired.push_back(*block);
+    *block = p;
+    *have = want;
+    return cudaSuccess;
+}
 
 inline int fail(Ctx *ctx, int code, const std::string &msg) {
     if (ctx) ctx->last_error = msg;
@@ -150,6 +176,16 @@ cudaError_t launch_permute(cudaStream_t st, const void *tokens, const uint32_t *
 cudaError_t launch_unpermute(cudaStream_t st, const void *eo, const uint32_t *inv, const void *wts, void *out, int n_tokens,
                              int hidden, int k, int dt);
 cudaError_t launch_swiglu(cudaStream_t st, const void *gate, const void *up, void *out, size_t n, int dt);
+bool gather_stream_supported(int m_total, int n_out, int K, int n_experts, int bits, int group_size, int dtype, const void *w,
+                             const void *scales, const void *biases, const void *x);
+size_t gather_stream_scratch_bytes(int m_total, int K);
+struct GatherMats {
+    const void *w, *scales, *biases;
+    void *out;
+};
+cudaError_t launch_gather_stream(Ctx *ctx, cudaStream_t st, const void *x, const void *x2, const uint32_t *row_src, int n_src_rows,
+                                 const GatherMats *mats, int n_mats, const uint32_t *expert_offsets, int m_total, int n_out, int K,
+                                 int n_experts, int group_size, int dtype, void *scratch);
 cudaError_t launch_gather_generic(cudaStream_t st, const void *x, const void *w, const void *scales, const void *biases,
                                   const uint32_t *offsets, const uint32_t *indices, void *out, int t_rows, int k_in, int n_out,
                                   int n_experts, int bits, int gs, int dt);

@@ -905,20 +905,8 @@ cudaError_t stage_x(Ctx *ctx, cudaStream_t st, const void *x, int rows, int K, i
     *tok_scale = nullptr;
     if (dt == MTC_F16) return cudaSuccess;
     const size_t need = ((static_cast<size_t>(rows) * K * 2 + 255) & ~static_cast<size_t>(255)) + static_cast<size_t>(rows) * sizeof(float);
-    if (need > ctx->xconv_bytes) {
-        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
-        cudaStreamIsCapturing(st, &cs);
-        if (cs != cudaStreamCaptureStatusNone) {
-            if (why) *why = "the f16 staging buffer must grow: run this shape once outside stream capture first";
-            return cudaErrorStreamCaptureUnsupported;
-        }
-        if (ctx->d_xconv) cudaFree(ctx->d_xconv);
-        ctx->d_xconv = nullptr;
-        ctx->xconv_bytes = 0;
-        cudaError_t e = cudaMalloc(&ctx->d_xconv, need);
-        if (e != cudaSuccess) return e;
-        ctx->xconv_bytes = need;
-    }
+    cudaError_t ge = grow_block(ctx, st, &ctx->d_xconv, &ctx->xconv_bytes, need, why);
+    if (ge != cudaSuccess) return ge;
     __half *y = static_cast<__half *>(ctx->d_xconv);
     float *scale = reinterpret_cast<float *>(static_cast<char *>(ctx->d_xconv) + ((static_cast<size_t>(rows) * K * 2 + 255) & ~static_cast<size_t>(255)));
     rows_to_f16_kernel<<<(rows + 7) / 8, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), y, scale, rows, K);

@@ -46,7 +46,7 @@ bool dtype_ok(int dt) { return dt == MTC_F32 || dt == MTC_F16 || dt == MTC_BF16;
 // "gs_per_row" (hand-tuned int4/int8/mma kernels: group_size = k / gs_per_row) or
 // "group_size" (generic _b* family).  has_n: whether an `n` constexpr is bound
 // (mt_qmv / mt_qmv_int8_fast take N from the size of `out`).
-enum Family { DENSE_QMV, DENSE_QMM, GATHER_CSR, GATHER_IDX, ROUTER_TOPK, MOE_PERMUTE, MOE_UNPERMUTE, SWIGLU };
+enum Family { DENSE_QMV, DENSE_QMM, GATHER_CSR, GATHER_IDX, ROUTER_TOPK, MOE_PERMUTE, MOE_UNPERMUTE, SWIGLU, BATCHED_QKV, BATCHED_4 };
 struct KernelRow {
     const char *name;
     Family family;
@@ -84,6 +84,11 @@ const KernelRow kKernels[] = {
     {"mt_qmm_b5", DENSE_QMV, 5, "group_size", true},
     {"mt_qmm_b6", DENSE_QMV, 6, "group_size", true},
     {"mt_qmm_b8", DENSE_QMV, 8, "group_size", true},
+    // decode projections that share x: crates/metaltile-std/src/ffai/batched_qkv_qgemv.rs:40-57,141-158 (one
+    // concatenated out), crates/metaltile-std/src/ffai/batched_4_qgemv.rs:59-84 (four outputs)
+    {"ffai_batched_qkv_qgemv", BATCHED_QKV, 4, "group_size", false},
+    {"ffai_batched_qkv_qgemv_fast", BATCHED_QKV, 4, "group_size", false},
+    {"ffai_batched_4_qgemv_fast", BATCHED_4, 4, "group_size", false},
     // MoE: crates/metaltile-std/src/ffai/moe.rs:65,222,283 (routing), :358,602-605,634,900,1363 (CSR gather),
     // :2256,2832-2835,2857,3231 (per-row-index gather); crates/metaltile-std/src/mlx/swiglu.rs:45
     {"mt_moe_router_topk", ROUTER_TOPK, -1, "", false},
@@ -159,14 +164,10 @@ int ensure_scratch(Ctx *ctx, size_t bytes) {
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-int ensure_worklist(Ctx *ctx, size_t bytes) {
-    if (bytes <= ctx->worklist_bytes) return MTC_OK;
-    if (ctx->d_worklist) cudaFree(ctx->d_worklist);
-    ctx->d_worklist = nullptr;
-    ctx->worklist_bytes = 0;
-    const size_t want = bytes * 2 + (1u << 20);
-    MTC_CUDA(ctx, cudaMalloc(&ctx->d_worklist, want), MTC_ERR_BUFFER);
-    ctx->worklist_bytes = want;
+int ensure_worklist(Ctx *ctx, size_t bytes, cudaStream_t st) {
+    std::string why;
+    cudaError_t e = mtc::grow_block(ctx, st, &ctx->d_worklist, &ctx->worklist_bytes, bytes, &why);
+    if (e != cudaSuccess) return fail(ctx, MTC_ERR_BUFFER, "gather_qmm work list: " + (why.empty() ? std::string(cudaGetErrorString(e)) : why));
     return MTC_OK;
 }
 
@@ -234,6 +235,8 @@ int mtc_destroy(mtc_ctx *ctx) {
     if (ctx->d_scratch) cudaFree(ctx->d_scratch);
     if (ctx->d_worklist) cudaFree(ctx->d_worklist);
     if (ctx->d_xconv) cudaFree(ctx->d_xconv);
+    if (ctx->d_gfrag) cudaFree(ctx->d_gfrag);
+    if (ctx->d_moe) cudaFree(ctx->d_moe);
     if (ctx->d_tc_scratch) cudaFree(ctx->d_tc_scratch);
     if (ctx->d_tc_counters) cudaFree(ctx->d_tc_counters);
     for (void *p : ctx->retired) cudaFree(p);
@@ -707,6 +710,10 @@ int mtc_set_option(mtc_ctx *ctx, const char *name, int value) {
         ctx->pdl_early_weights = value ? 1 : 0;
         return MTC_OK;
     }
+    if (std::strcmp(name, "gather_stream") == 0) {
+        ctx->gather_stream = value ? 1 : 0;
+        return MTC_OK;
+    }
     if (std::strcmp(name, "qmm_pair") == 0) {
         ctx->qmm_pair = value ? 1 : 0;
         return MTC_OK;
@@ -730,8 +737,20 @@ int mtc_gather_qmm(mtc_ctx *ctx, void *stream, const void *x, const void *w, con
     if (m_total == 0 || n_out == 0) return MTC_OK;
     if (!x || !w || !scales || !biases || !out) return fail(ctx, MTC_ERR_INVALID, "gather_qmm: null pointer");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // few rows per expert: the layer is bound by reading every expert's matrix once - the streaming kernel
+    if (ctx->gather_stream && expert_offsets && static_cast<long long>(m_total) <= 64ll * n_experts &&
+        mtc::gather_stream_supported(m_total, n_out, k_in, n_experts, bits, group_size, dtype, w, scales, biases, x)) {
+        std::string why;
+        cudaError_t e = mtc::grow_block(ctx, st, &ctx->d_gfrag, &ctx->gfrag_bytes, mtc::gather_stream_scratch_bytes(m_total, k_in), &why);
+        if (e != cudaSuccess) return fail(ctx, MTC_ERR_BUFFER, "gather_qmm staging: " + (why.empty() ? std::string(cudaGetErrorString(e)) : why));
+        const mtc::GatherMats one{w, scales, biases, out};
+        e = mtc::launch_gather_stream(ctx, st, x, nullptr, nullptr, 0, &one, 1, static_cast<const uint32_t *>(expert_offsets), m_total,
+                                      n_out, k_in, n_experts, group_size, dtype, ctx->d_gfrag);
+        if (e != cudaSuccess) return fail(ctx, MTC_ERR_DISPATCH, std::string("gather_qmm (stream) launch: ") + cudaGetErrorString(e));
+        return MTC_OK;
+    }
     if (mtc::qmm_tcgen05_supported(m_total, n_out, k_in, bits, group_size, dtype, w, x, out) && n_experts <= 4096) {
-        int rc = ensure_worklist(ctx, mtc::gather_items_bytes(m_total, n_experts, n_out, 16));
+        int rc = ensure_worklist(ctx, mtc::gather_items_bytes(m_total, n_experts, n_out, 16), st);
         if (rc != MTC_OK) return rc;
         std::string why;
         cudaError_t e = mtc::launch_gather_qmm_tcgen05(ctx, st, x, w, scales, biases,
@@ -747,6 +766,62 @@ int mtc_gather_qmm(mtc_ctx *ctx, void *stream, const void *x, const void *w, con
                                              static_cast<const uint32_t *>(indices), out, m_total, k_in, n_out, n_experts,
                                              bits, group_size, dtype), MTC_ERR_DISPATCH);
     return MTC_OK;
+}
+
+int mtc_moe_experts(mtc_ctx *ctx, void *stream, const void *x, const void *sort_token_idx, int n_tokens, const mtc_qmat *gate,
+                    const mtc_qmat *up, const mtc_qmat *down, const void *expert_offsets, void *y, int m_total, int hidden,
+                    int inter, int n_experts, int bits, int group_size, int dtype) {
+    if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "moe_experts: dtype must be f32, f16 or bf16");
+    if (m_total < 0 || hidden <= 0 || inter <= 0 || n_experts <= 0 || (sort_token_idx && n_tokens <= 0))
+        return fail(ctx, MTC_ERR_INVALID, "moe_experts: sizes must be positive");
+    if (m_total == 0) return MTC_OK;
+    if (!x || !gate || !up || !down || !expert_offsets || !y || !gate->w || !gate->scales || !gate->biases || !up->w || !up->scales ||
+        !up->biases || !down->w || !down->scales || !down->biases)
+        return fail(ctx, MTC_ERR_INVALID, "moe_experts: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t esz = mtc::dtype_size(dtype);
+    const size_t act_bytes = align_up(static_cast<size_t>(m_total) * inter * esz, 256), xp_bytes = align_up(static_cast<size_t>(m_total) * hidden * esz, 256);
+    const bool streamed = ctx->gather_stream && static_cast<long long>(m_total) <= 64ll * n_experts &&
+                          mtc::gather_stream_supported(m_total, inter, hidden, n_experts, bits, group_size, dtype, gate->w, gate->scales, gate->biases, x) &&
+                          mtc::gather_stream_supported(m_total, inter, hidden, n_experts, bits, group_size, dtype, up->w, up->scales, up->biases, x) &&
+                          mtc::gather_stream_supported(m_total, hidden, inter, n_experts, bits, group_size, dtype, down->w, down->scales, down->biases, nullptr);
+    std::string why;
+    cudaError_t e = mtc::grow_block(ctx, st, &ctx->d_moe, &ctx->moe_bytes, 2 * act_bytes + (streamed ? 0 : xp_bytes), &why);
+    if (e != cudaSuccess) return fail(ctx, MTC_ERR_BUFFER, "moe_experts intermediates: " + (why.empty() ? std::string(cudaGetErrorString(e)) : why));
+    char *g = static_cast<char *>(ctx->d_moe), *u = g + act_bytes, *xp = u + act_bytes;
+    if (streamed) {
+        // four launches: rows -> fragments (the permutation folded in), gate and up as one stream, SwiGLU -> fragments, down
+        const size_t need = std::max(mtc::gather_stream_scratch_bytes(m_total, hidden), mtc::gather_stream_scratch_bytes(m_total, inter));
+        e = mtc::grow_block(ctx, st, &ctx->d_gfrag, &ctx->gfrag_bytes, need, &why);
+        if (e != cudaSuccess) return fail(ctx, MTC_ERR_BUFFER, "moe_experts staging: " + (why.empty() ? std::string(cudaGetErrorString(e)) : why));
+        const mtc::GatherMats gu[2] = {{gate->w, gate->scales, gate->biases, g}, {up->w, up->scales, up->biases, u}};
+        e = mtc::launch_gather_stream(ctx, st, x, nullptr, static_cast<const uint32_t *>(sort_token_idx), n_tokens, gu, 2,
+                                      static_cast<const uint32_t *>(expert_offsets), m_total, inter, hidden, n_experts, group_size, dtype,
+                                      ctx->d_gfrag);
+        if (e != cudaSuccess) return fail(ctx, MTC_ERR_DISPATCH, std::string("moe_experts (gate, up) launch: ") + cudaGetErrorString(e));
+        const mtc::GatherMats dn{down->w, down->scales, down->biases, y};
+        e = mtc::launch_gather_stream(ctx, st, g, u, nullptr, 0, &dn, 1, static_cast<const uint32_t *>(expert_offsets), m_total, hidden, inter,
+                                      n_experts, group_size, dtype, ctx->d_gfrag);
+        if (e != cudaSuccess) return fail(ctx, MTC_ERR_DISPATCH, std::string("moe_experts (down) launch: ") + cudaGetErrorString(e));
+        return MTC_OK;
+    }
+    // composed from the separate entries, same results
+    const void *rows = x;
+    int rc = MTC_OK;
+    if (sort_token_idx) {
+        rc = mtc_moe_permute(ctx, stream, x, sort_token_idx, xp, m_total, hidden, dtype);
+        if (rc != MTC_OK) return rc;
+        rows = xp;
+    }
+    rc = mtc_gather_qmm(ctx, stream, rows, gate->w, gate->scales, gate->biases, expert_offsets, nullptr, g, m_total, inter, hidden, n_experts, bits, group_size, dtype);
+    if (rc != MTC_OK) return rc;
+    rc = mtc_gather_qmm(ctx, stream, rows, up->w, up->scales, up->biases, expert_offsets, nullptr, u, m_total, inter, hidden, n_experts, bits, group_size, dtype);
+    if (rc != MTC_OK) return rc;
+    rc = mtc_swiglu(ctx, stream, g, u, g, static_cast<size_t>(m_total) * inter, dtype);
+    if (rc != MTC_OK) return rc;
+    return mtc_gather_qmm(ctx, stream, g, down->w, down->scales, down->biases, expert_offsets, nullptr, y, m_total, hidden, inter, n_experts, bits, group_size, dtype);
 }
 
 int mtc_gather_qmm_static(mtc_ctx *ctx, void *stream, const void *x, const void *w, const void *scales,
@@ -777,7 +852,10 @@ int mtc_gather_qmm_static(mtc_ctx *ctx, void *stream, const void *x, const void 
     return MTC_OK;
 }
 
-const char *mtc_gather_qmm_route(int m_total, int n_out, int k_in, int bits, int group_size, int dtype) {
+const char *mtc_gather_qmm_route(int m_total, int n_out, int k_in, int n_experts, int bits, int group_size, int dtype) {
+    if (n_experts > 0 && static_cast<long long>(m_total) <= 64ll * n_experts &&
+        mtc::gather_stream_supported(m_total, n_out, k_in, n_experts, bits, group_size, dtype, nullptr, nullptr, nullptr, nullptr))
+        return "gather_qmm_stream";        // the CSR form with option "gather_stream" at its default
     return mtc::qmm_tcgen05_supported(m_total, n_out, k_in, bits, group_size, dtype, nullptr, nullptr, nullptr)
                ? "gather_qmm_tcgen05" : "gather_qmm_cuda_core";
 }
@@ -879,7 +957,10 @@ int mtc_dispatch(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_buf
     auto need_const = [&](const char *name, uint32_t *v) {
         if (!read_const(bufs, n_bufs, name, v) && err.empty()) err = kn + ": constexpr " + name + " missing";
     };
-    st_bufs.reserve(8);
+    st_bufs.reserve(20);
+    int nb = 0;                          // fused decode projections: count, rows of each, buffer names of each
+    uint32_t b_out[4] = {0, 0, 0, 0};
+    std::string b_names[4][4];
     uint32_t k = 0, n = 0, gsc = 0, k_in = 0, m_out = 0, n_exp = 0, gs = 0, hidden = 0, topk = 0, norm = 1, m_total = 0;
     size_t m = 0, rows = 0;
     switch (row->family) {
@@ -929,6 +1010,33 @@ int mtc_dispatch(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_buf
             need_buf("biases", static_cast<size_t>(n_exp) * m_out * (k_in / gs) * esz);
             need_buf(csr ? "expert_offsets" : "indices", csr ? (static_cast<size_t>(n_exp) + 1) * 4 : rows * 4);
             need_buf("out", rows * m_out * esz);
+            break;
+        }
+        case BATCHED_QKV:
+        case BATCHED_4: {
+            const bool qkv = row->family == BATCHED_QKV;
+            nb = qkv ? 3 : 4;
+            static const char *const sfx_qkv[3] = {"q", "k", "v"}, *const sfx_4[4] = {"a", "b", "c", "d"};
+            for (int i = 0; i < nb; ++i) need_const((std::string("out_") + (qkv ? sfx_qkv[i] : sfx_4[i])).c_str(), &b_out[i]);
+            need_const("in_dim", &k);
+            need_const("group_size", &gs);
+            if (!err.empty()) break;
+            if (k == 0 || gs == 0 || k % gs != 0 || k % 8 != 0) return fail(ctx, MTC_ERR_UNSUPPORTED, kn + ": need group_size | in_dim and in_dim % 8 == 0");
+            need_buf("x", static_cast<size_t>(k) * esz);
+            size_t sum = 0;
+            for (int i = 0; i < nb; ++i) {
+                const std::string sf = qkv ? sfx_qkv[i] : sfx_4[i];
+                b_names[i][0] = "w_" + sf;
+                b_names[i][1] = "scales_" + sf;
+                b_names[i][2] = "biases_" + sf;
+                b_names[i][3] = sf + "_out";
+                need_buf(b_names[i][0].c_str(), static_cast<size_t>(b_out[i]) * k / 2);
+                need_buf(b_names[i][1].c_str(), static_cast<size_t>(b_out[i]) * (k / gs) * esz);
+                need_buf(b_names[i][2].c_str(), static_cast<size_t>(b_out[i]) * (k / gs) * esz);
+                if (!qkv) need_buf(b_names[i][3].c_str(), static_cast<size_t>(b_out[i]) * esz);
+                sum += b_out[i];
+            }
+            if (qkv) need_buf("out", sum * esz);
             break;
         }
         case ROUTER_TOPK: {
@@ -1027,6 +1135,29 @@ int mtc_dispatch(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_buf
                                 static_cast<int>(rows), static_cast<int>(m_out), static_cast<int>(k_in), static_cast<int>(n_exp),
                                 row->bits, static_cast<int>(gs), dtype);
             break;
+        case BATCHED_QKV:
+        case BATCHED_4: {
+            // one launch for all projections (mtc_qmv_batched); y of the q / k / v form is one concatenated vector
+            mtc_qmv_desc ds[4] = {};
+            size_t off = 0;
+            for (int i = 0; i < nb; ++i) {
+                ds[i].w = dev(b_names[i][0].c_str());
+                ds[i].scales = dev(b_names[i][1].c_str());
+                ds[i].biases = dev(b_names[i][2].c_str());
+                ds[i].x = dev("x");
+                ds[i].outs[0] = row->family == BATCHED_QKV ? dev("out") + off * esz : dev(b_names[i][3].c_str());
+                ds[i].n_outs = 1;
+                ds[i].M = 1;
+                ds[i].N = static_cast<int>(b_out[i]);
+                ds[i].K = static_cast<int>(k);
+                ds[i].bits = 4;
+                ds[i].group_size = static_cast<int>(gs);
+                ds[i].dtype = dtype;
+                off += b_out[i];
+            }
+            rc = mtc_qmv_batched(ctx, st, ds, nb);
+            break;
+        }
         case ROUTER_TOPK:
             rc = mtc_moe_router_topk(ctx, st, dev("router_logits"), dev("indices_out"), dev("weights_out"), static_cast<int>(rows),
                                      static_cast<int>(n_exp), static_cast<int>(topk), static_cast<int>(norm), dtype);

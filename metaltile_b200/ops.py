@@ -203,3 +203,27 @@ def gather_qmm(x, w, scales, biases, bits: int, group_size: int, expert_offsets=
                    expert_offsets=None if expert_offsets is None else expert_offsets.data_ptr(),
                    indices=None if indices is None else indices.data_ptr(), stream=_stream())
     return out
+
+
+def moe_experts(x, gate, up, down, bits: int, group_size: int, expert_offsets, sort_token_idx=None, out=None, ctx: Context = None):
+    """y[r] = down_e(silu(gate_e(x_r)) * up_e(x_r)) for rows sorted by expert; gate / up / down are (w, scales, biases)
+    with w [E, inter, hidden*bits/32] (gate, up) and [E, hidden, inter*bits/32] (down).  ``sort_token_idx`` folds the
+    permutation in: row r reads ``x[sort_token_idx[r]]``."""
+    n_experts, inter = gate[0].shape[0], gate[0].shape[1]
+    hidden = down[0].shape[1]
+    m_total = x.shape[0] if sort_token_idx is None else sort_token_idx.numel()
+    if x.shape[1] != hidden or gate[0].shape[2] * 32 != hidden * bits or down[0].shape[2] * 32 != inter * bits:
+        raise ValueError("gate / up must be [E, inter, hidden*bits/32] and down [E, hidden, inter*bits/32] for x [rows, hidden]")
+    for t in (x, *gate, *up, *down):
+        if not t.is_contiguous():
+            raise ValueError("operands must be contiguous")
+    if out is None:
+        out = torch.empty((m_total, hidden), dtype=x.dtype, device=x.device)
+    else:
+        _check_out(out, m_total, hidden, x)
+    ctx = ctx or context(x.device)
+    ptr = lambda m: tuple(t.data_ptr() for t in m)
+    ctx.moe_experts(x.data_ptr(), None if sort_token_idx is None else sort_token_idx.data_ptr(), x.shape[0], ptr(gate), ptr(up),
+                    ptr(down), expert_offsets.data_ptr(), out.data_ptr(), m_total, hidden, inter, n_experts, bits, group_size,
+                    _TORCH_DT[x.dtype], stream=_stream())
+    return out

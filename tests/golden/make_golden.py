@@ -23,6 +23,8 @@ Reference sources restated here
   top-k literal cases ........ crates/metaltile-std/tests/moe_gpu_correctness.rs:96-108,288-335,441-470,524-597
   unpermute reference ........ crates/metaltile-std/tests/moe_gpu_correctness.rs:164-198
   swiglu setup ............... crates/metaltile-std/src/mlx/swiglu.rs:65-72
+  batched q/k/v decode ....... crates/metaltile-std/tests/batched_qkv_qgemv_gpu_correctness.rs:30-127,167-181,312-321
+  batched 4-way decode ....... crates/metaltile-std/src/ffai/batched_4_qgemv.rs:342-440
 """
 from __future__ import annotations
 
@@ -227,8 +229,69 @@ def topk_ref(logits, k, norm=1):
     return idx, wts
 
 
+def xorshift_source(n, seed, scale, off):
+    """`source` of batched_qkv_qgemv_gpu_correctness.rs:100-110: xorshift64 (13, 7, 17) on a u64, value
+    ((s % 20000) / 20000 - 0.5) * scale + off in f32."""
+    s = seed
+    mask = (1 << 64) - 1
+    vals = np.empty(n, dtype=np.float32)
+    for i in range(n):
+        s ^= (s << 13) & mask
+        s ^= s >> 7
+        s ^= (s << 17) & mask
+        v = f32(f32(s % 20000) / f32(20000.0))
+        vals[i] = f32(f32(f32(v - f32(0.5)) * f32(scale)) + f32(off))
+    return vals
+
+
+def quantize_int4_matrix(rows, out_dim, in_dim, gs):
+    """quantize_matrix / quantize_int4_row of the same file (:30-70): per group min / (max - min) / 15, round half away."""
+    codes = np.zeros((out_dim, in_dim), dtype=np.uint32)
+    scales = np.zeros((out_dim, in_dim // gs), dtype=np.float32)
+    biases = np.zeros((out_dim, in_dim // gs), dtype=np.float32)
+    w = rows.reshape(out_dim, in_dim)
+    for r in range(out_dim):
+        for g in range(in_dim // gs):
+            c, sc, mn = quantize_group(w[r, g * gs:(g + 1) * gs], 4)
+            codes[r, g * gs:(g + 1) * gs] = c
+            scales[r, g] = sc
+            biases[r, g] = mn
+    return codes, scales, biases
+
+
+def batched_case(dt, in_dim, gs, outs, seeds):
+    """Fused decode projections that share x: run_case (:112-127) and test_batched_4_qgemv_fast (batched_4_qgemv.rs:421-440).
+    The expected vector is naive_gemv per matrix with scales, biases and x rounded through the dtype."""
+    x = round_dt(xorshift_source(in_dim, 0x11, 2.0, 0.05), dt).reshape(1, in_dim)
+    d = dict(x=x, meta=np.array([in_dim, gs] + list(outs)))
+    for i, (n, seed) in enumerate(zip(outs, seeds)):
+        codes, sc, bi = quantize_int4_matrix(xorshift_source(n * in_dim, seed, 3.0, 0.0), n, in_dim, gs)
+        words = pack_rows(codes, 4)
+        acc = qmm_ref(codes, round_dt(sc, dt), round_dt(bi, dt), x, gs)
+        d[f"w{i}"], d[f"scales{i}"], d[f"biases{i}"], d[f"acc{i}"] = words, sc, bi, acc.reshape(-1)
+    return d
+
+
+def save_new(path, **arrays):
+    """Write a fixture unless the file already holds exactly these arrays (keeps unchanged fixtures byte-stable)."""
+    if os.path.exists(path):
+        old = dict(np.load(path))
+        if old.keys() == arrays.keys() and all(np.array_equal(old[k], np.asarray(v), equal_nan=True) for k, v in arrays.items()):
+            return
+    np.savez_compressed(path, **arrays)
+
+
 def main():
     out = {}
+    # fused decode projections (N1): the reference's own cases
+    for dt, in_dim, gs, oq, ok in (("f32", 256, 64, 16, 4), ("f32", 512, 128, 12, 6), ("f16", 256, 64, 16, 4),
+                                   ("bf16", 256, 64, 16, 4), ("f32", 512, 64, 16, 8), ("f16", 512, 64, 16, 8),
+                                   ("bf16", 512, 64, 16, 8)):
+        save_new(os.path.join(HERE, f"batched_qkv_k{in_dim}_g{gs}_q{oq}_kv{ok}_{dt}.npz"),
+                 **batched_case(dt, in_dim, gs, (oq, ok, ok), (0x22, 0x33, 0x44)))
+    for dt in ("f32", "f16", "bf16"):
+        save_new(os.path.join(HERE, f"test_batched_4_qgemv_fast_{dt}.npz"),
+                 **batched_case(dt, 512, 64, (16, 8, 8, 8), (0x22, 0x33, 0x44, 0x55)))
     for dt in ("f32", "f16", "bf16"):
         # registered #[test_kernel] shapes (quantized.rs:5449-5605)
         for name, (m, n, k, bits, gs) in {
@@ -241,11 +304,11 @@ def main():
             "test_qmm_mma_int8": (32, 64, 512, 8, 64),
             "test_qmm_mma_int2": (32, 64, 512, 2, 64),
         }.items():
-            np.savez_compressed(os.path.join(HERE, f"{name}_{dt}.npz"), **qx_case(m, n, k, bits, gs, dt))
-        np.savez_compressed(os.path.join(HERE, f"test_moe_gather_qmm_int4_{dt}.npz"), **gather_case(dt))
+            save_new(os.path.join(HERE, f"{name}_{dt}.npz"), **qx_case(m, n, k, bits, gs, dt))
+        save_new(os.path.join(HERE, f"test_moe_gather_qmm_int4_{dt}.npz"), **gather_case(dt))
     for bits in (3, 4, 5, 6, 8):
         for dt in ("f32", "bf16"):
-            np.savez_compressed(os.path.join(HERE, f"family_qmv_b{bits}_{dt}.npz"), **family_case(bits, dt))
+            save_new(os.path.join(HERE, f"family_qmv_b{bits}_{dt}.npz"), **family_case(bits, dt))
 
     # router top-k cases (moe_gpu_correctness.rs)
     i = np.arange(8 * 64).astype(f32)

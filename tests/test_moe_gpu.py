@@ -160,12 +160,69 @@ def test_gather_qmm_matches_oracle(ctx, n_experts, n_out, k_in, bits, gs, dt, co
     total = x.shape[0]
     ref = oracle.gather_qmm(x, w, s, b, total, k_in, n_out, n_experts, bits, gs, expert_offsets=off)
     wd, sd, bd, xd = to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt)
-    got_csr = ops.gather_qmm(xd, wd, sd, bd, bits, gs, expert_offsets=to_dev(off))
-    got_idx = ops.gather_qmm(xd, wd, sd, bd, bits, gs, indices=to_dev(idx))
+    got_stream = ops.gather_qmm(xd, wd, sd, bd, bits, gs, expert_offsets=to_dev(off))    # small groups may take the streaming kernel
+    ctx.set_option("gather_stream", 0)
+    try:
+        got_csr = ops.gather_qmm(xd, wd, sd, bd, bits, gs, expert_offsets=to_dev(off))
+        got_idx = ops.gather_qmm(xd, wd, sd, bd, bits, gs, indices=to_dev(idx))
+    finally:
+        ctx.set_option("gather_stream", 1)
     torch.cuda.synchronize()
+    assert rel_err(got_stream.float().cpu().numpy(), ref) <= TOL[dt]
     assert rel_err(got_csr.float().cpu().numpy(), ref) <= TOL[dt]
     assert torch.equal(got_csr, got_idx)                     # CSR and per-row-index forms agree bit for bit
     assert ctx.status_word() == 0
+
+
+@pytest.mark.parametrize("n_experts,n_out,k_in,gs,dt,counts", [
+    (6, 768, 2048, 64, "bf16", [31, 32, 33, 0, 1, 65]),                 # one, two and three passes per expert; an empty one
+    (5, 2048, 768, 64, "bf16", [8, 9, 40, 17, 24]),                     # K = 1.5 x 512: runs of 256 codes
+    (4, 130, 512, 128, "f16", [3, 70, 0, 12]),                          # group 128, ragged n_out (last tile has 2 rows)
+    (3, 96, 4096, 64, "bf16", [16, 17, 5]),                             # K = 4096: 16 rows per pass
+    (2, 48, 8192, 128, "f16", [9, 2]),                                  # K = 8192: 8 rows per pass
+    (40, 64, 256, 64, "bf16", [(7 * i) % 11 for i in range(40)]),       # many small experts, more experts than a scan round
+    (1, 16, 256, 64, "f16", [1]),
+])
+def test_gather_stream_matches_oracle(ctx, n_experts, n_out, k_in, gs, dt, counts):
+    """The weight-streaming grouped product (few rows per expert) against the oracle, and - where the tensor-memory kernel
+    takes the shape too - against that kernel within rounding."""
+    import torch
+    from metaltile_b200 import ops
+    w, s, b, x, off, _ = _gather_case(n_experts, n_out, k_in, 4, gs, dt, counts, seed=2)
+    total = x.shape[0]
+    ref = oracle.gather_qmm(x, w, s, b, total, k_in, n_out, n_experts, 4, gs, expert_offsets=off)
+    wd, sd, bd, xd = to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt)
+    out = torch.full((total, n_out), float("nan"), dtype=xd.dtype, device="cuda")
+    ops.gather_qmm(xd, wd, sd, bd, 4, gs, expert_offsets=to_dev(off), out=out)
+    again = ops.gather_qmm(xd, wd, sd, bd, 4, gs, expert_offsets=to_dev(off))
+    torch.cuda.synchronize()
+    assert ctx.status_word() == 0
+    assert not torch.isnan(out).any()                        # every element is written
+    assert torch.equal(out, again)                           # and the same on every run
+    assert rel_err(out.float().cpu().numpy(), ref) <= TOL[dt]
+    ctx.set_option("gather_stream", 0)
+    try:
+        other = ops.gather_qmm(xd, wd, sd, bd, 4, gs, expert_offsets=to_dev(off))
+    finally:
+        ctx.set_option("gather_stream", 1)
+    assert rel_err(out.float().cpu().numpy(), other.float().cpu().numpy()) <= 2 * TOL[dt]
+
+
+def test_gather_stream_reports_bad_offsets(ctx):
+    """expert_offsets that run past m_total or backwards are clamped (no out-of-range access) and reported: 0x901."""
+    import torch
+    from metaltile_b200 import MetalTileError, ops
+    w, s, b, x, off, _ = _gather_case(3, 32, 256, 4, 64, "bf16", [4, 4, 4], seed=3)
+    bad = off.copy()
+    bad[2] = 1000                                            # beyond m_total = 12
+    wd, sd, bd, xd = to_dev(w), to_dev(s, "bf16"), to_dev(b, "bf16"), to_dev(x, "bf16")
+    try:
+        ops.gather_qmm(xd, wd, sd, bd, 4, 64, expert_offsets=to_dev(bad))
+        with pytest.raises(MetalTileError):
+            ctx.sync(torch.cuda.current_stream().cuda_stream)
+        assert ctx.status_word() == 0x901
+    finally:
+        ctx.status_clear()
 
 
 def test_moe_layer_config4(ctx):
@@ -216,3 +273,71 @@ def test_moe_layer_config4(ctx):
     ref_out = oracle.moe_unpermute(y_h, r_inv, wts.float().cpu().numpy())
     assert rel_err(out.float().cpu().numpy(), ref_out) <= TOL[dt]
     assert ctx.status_word() == 0
+
+
+@pytest.mark.parametrize("dt,hidden,inter,gs,bits,counts", [
+    ("bf16", 512, 256, 64, 4, [9, 0, 33, 20, 2]),          # the streamed form (four launches)
+    ("f16", 256, 512, 128, 4, [5, 17, 1]),
+    ("bf16", 128, 64, 32, 4, [4, 6]),                      # outside the streaming kernel's contract: composed from the entries
+    ("f32", 128, 64, 32, 8, [3, 0, 5]),
+])
+def test_moe_experts_equals_the_separate_entries(ctx, dt, hidden, inter, gs, bits, counts):
+    """mtc_moe_experts == permute -> gather_qmm(gate), gather_qmm(up) -> swiglu -> gather_qmm(down), bit for bit, with and
+    without the permutation folded in; and against the oracle for one expert."""
+    import torch
+    from metaltile_b200 import ops, synth
+    E, total = len(counts), int(np.sum(counts))
+    n_tok = max(4, total // 2)
+    mk = lambda n, k, salt: synth.quantized_matrix(E * n, k, bits, gs, seed=4, salt=salt)
+    mats_h = [mk(inter, hidden, 31), mk(inter, hidden, 32), mk(hidden, inter, 33)]
+    dev3 = lambda m, n: (to_dev(m[0].reshape(E, n, -1)), to_dev(oracle.round_through(m[1], ODT[dt]).reshape(E, n, -1), dt),
+                         to_dev(oracle.round_through(m[2], ODT[dt]).reshape(E, n, -1), dt))
+    gate, up, down = dev3(mats_h[0], inter), dev3(mats_h[1], inter), dev3(mats_h[2], hidden)
+    tok = to_dev(oracle.round_through(synth.activations(n_tok, hidden, seed=4), ODT[dt]), dt)
+    rng = np.random.default_rng(4)
+    sti = to_dev(rng.integers(0, n_tok, size=total).astype(np.uint32))
+    off = to_dev(np.concatenate([[0], np.cumsum(counts)]).astype(np.uint32))
+
+    xp = ops.moe_permute(tok, sti, ctx=ctx)
+    g = ops.gather_qmm(xp, *gate, bits, gs, expert_offsets=off, ctx=ctx)
+    u = ops.gather_qmm(xp, *up, bits, gs, expert_offsets=off, ctx=ctx)
+    act = ops.swiglu(g, u, ctx=ctx)
+    ref = ops.gather_qmm(act, *down, bits, gs, expert_offsets=off, ctx=ctx)
+    got_perm = ops.moe_experts(tok, gate, up, down, bits, gs, off, sort_token_idx=sti, ctx=ctx)
+    got_rows = ops.moe_experts(xp, gate, up, down, bits, gs, off, ctx=ctx)
+    torch.cuda.synchronize()
+    assert ctx.status_word() == 0
+    assert torch.equal(got_perm, ref) and torch.equal(got_rows, ref)
+    # one expert against the oracle, stage by stage on the device's own rounded inputs
+    e = int(np.argmax(counts))
+    r0, r1 = int(np.sum(counts[:e])), int(np.sum(counts[:e + 1]))
+    rnd = lambda a: oracle.round_through(a, ODT[dt])
+    sl = slice(e * inter, (e + 1) * inter)
+    xh = xp.float().cpu().numpy()[r0:r1]
+    gh = rnd(oracle.qmm(mats_h[0][0][sl], rnd(mats_h[0][1][sl]), rnd(mats_h[0][2][sl]), xh, r1 - r0, inter, hidden, bits, gs))
+    uh = rnd(oracle.qmm(mats_h[1][0][sl], rnd(mats_h[1][1][sl]), rnd(mats_h[1][2][sl]), xh, r1 - r0, inter, hidden, bits, gs))
+    assert rel_err(g.float().cpu().numpy()[r0:r1], gh) <= TOL[dt]
+    ah = act.float().cpu().numpy()[r0:r1]
+    sl = slice(e * hidden, (e + 1) * hidden)
+    yh = oracle.qmm(mats_h[2][0][sl], rnd(mats_h[2][1][sl]), rnd(mats_h[2][2][sl]), ah, r1 - r0, hidden, inter, bits, gs)
+    assert rel_err(got_perm.float().cpu().numpy()[r0:r1], yh) <= TOL[dt]
+
+
+def test_moe_experts_reports_a_bad_row_index(ctx):
+    """sort_token_idx naming a row that x does not have: row 0 is read instead (no out-of-range access), status 0x903."""
+    import torch
+    from metaltile_b200 import MetalTileError, ops, synth
+    E, hidden, inter = 2, 256, 256
+    mk = lambda n, k, salt: synth.quantized_matrix(E * n, k, 4, 64, seed=5, salt=salt)
+    dev3 = lambda m, n: (to_dev(m[0].reshape(E, n, -1)), to_dev(m[1].reshape(E, n, -1), "bf16"), to_dev(m[2].reshape(E, n, -1), "bf16"))
+    gate, up, down = dev3(mk(inter, hidden, 1), inter), dev3(mk(inter, hidden, 2), inter), dev3(mk(hidden, inter, 3), hidden)
+    tok = to_dev(synth.activations(4, hidden, seed=5), "bf16")
+    sti = to_dev(np.array([0, 3, 99, 1], dtype=np.uint32))
+    off = to_dev(np.array([0, 2, 4], dtype=np.uint32))
+    try:
+        ops.moe_experts(tok, gate, up, down, 4, 64, off, sort_token_idx=sti, ctx=ctx)
+        with pytest.raises(MetalTileError):
+            ctx.sync(torch.cuda.current_stream().cuda_stream)
+        assert ctx.status_word() == 0x903
+    finally:
+        ctx.status_clear()
