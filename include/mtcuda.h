@@ -286,6 +286,19 @@ typedef struct {
 
 int mtc_dispatch(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_buf *bufs, int n_bufs,
                  const uint32_t grid[3], const uint32_t tpg[3], float *elapsed_us);
+/* Several passes committed together - Context::dispatch_chain (crates/metaltile-runtime/src/context.rs:347-395):
+ * the passes run in order on the device with no host round trip between them.  A buffer that pass i marks is_output
+ * and that a later pass binds under the same name as an input stays on the device (the later pass's host bytes for it
+ * are ignored); only outputs that no later pass consumed are copied back, after the last pass, with one
+ * synchronisation.  Every pass is checked (names, constexprs, sizes) before anything is enqueued.  elapsed_us (may be
+ * NULL): device time of the whole chain.  Errors as mtc_dispatch. */
+typedef struct {
+    const char *kernel_name;
+    int dtype;
+    mtc_named_buf *bufs;
+    int n_bufs;
+} mtc_dispatch_spec;
+int mtc_dispatch_chain(mtc_ctx *ctx, const mtc_dispatch_spec *specs, int n_specs, float *elapsed_us);
 /* Number of kernel names mtc_dispatch knows, and the i-th name (registry walk:
  * all_kernels(), crates/metaltile-core/src/toolchain/registry.rs:56-78). */
 int mtc_kernel_count(void);

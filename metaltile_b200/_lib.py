@@ -34,6 +34,11 @@ class PeerSync(ctypes.Structure):
                 ("ticket", ctypes.c_void_p), ("n_peers", ctypes.c_int), ("rank", ctypes.c_int)]
 
 
+class DispatchSpec(ctypes.Structure):
+    """mtc_dispatch_spec: one pass of mtc_dispatch_chain."""
+    _fields_ = [("kernel_name", ctypes.c_char_p), ("dtype", ctypes.c_int), ("bufs", ctypes.c_void_p), ("n_bufs", ctypes.c_int)]
+
+
 class QMat(ctypes.Structure):
     """mtc_qmat: packed words, scales and biases of one stacked expert matrix."""
     _fields_ = [("w", ctypes.c_void_p), ("scales", ctypes.c_void_p), ("biases", ctypes.c_void_p)]
@@ -78,6 +83,7 @@ SIGNATURES = {
     "mtc_peer_barrier": (_i, [_vp, _vp, ctypes.POINTER(_vp), _i, _i, _vp, _vp]),
     "mtc_gather_qmm": (_i, [_vp] * 9 + [_i] * 7),
     "mtc_gather_qmm_static": (_i, [_vp] * 9 + [_i] * 7),
+    "mtc_dispatch_chain": (_i, [_vp, ctypes.POINTER(DispatchSpec), _i, ctypes.POINTER(ctypes.c_float)]),
     "mtc_moe_experts": (_i, [_vp, _vp, _vp, _vp, _i, ctypes.POINTER(QMat), ctypes.POINTER(QMat), ctypes.POINTER(QMat), _vp, _vp,
                             _i, _i, _i, _i, _i, _i, _i]),
     "mtc_gather_qmm_route": (ctypes.c_char_p, [_i] * 7),

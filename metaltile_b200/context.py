@@ -17,7 +17,7 @@ from dataclasses import dataclass, field
 from typing import Dict, Mapping, Optional, Sequence
 
 from . import _lib
-from ._lib import BF16, F16, F32, NamedBuf, PeerSync, QMat, QmvDesc
+from ._lib import BF16, F16, F32, DispatchSpec, NamedBuf, PeerSync, QMat, QmvDesc
 
 DTYPES = {"f32": F32, "f16": F16, "bf16": BF16}
 
@@ -129,6 +129,46 @@ class Context:
             if arr[i].is_output:
                 res.outputs[name] = keep[i].raw
         return res
+
+    def dispatch_chain(self, passes) -> list:
+        """``Context::dispatch_chain`` (context.rs:347-395): ``passes`` is a list of
+        ``(kernel, buffers, fn_consts, dtype, outputs)``; a buffer that one pass outputs and a later pass binds under the
+        same name stays on the device.  Returns one ``DispatchResult`` per pass; outputs consumed by a later pass are
+        not read back (their entry is absent), ``elapsed_us`` of the last result is the device time of the chain."""
+        specs = (DispatchSpec * len(passes))()
+        keep, per_pass = [], []
+        for si, (kernel, buffers, fn_consts, dtype, outputs) in enumerate(passes):
+            items = dict(buffers)
+            for k, v in (fn_consts or {}).items():
+                items[k] = int(v).to_bytes(4, "little")
+            arr = (NamedBuf * len(items))()
+            raws = []
+            for i, (name, data) in enumerate(items.items()):
+                raw = ctypes.create_string_buffer(bytes(data), len(data))
+                raws.append(raw)
+                arr[i].name = name.encode()
+                arr[i].data = ctypes.cast(raw, ctypes.c_void_p)
+                arr[i].bytes = len(data)
+                arr[i].is_output = 1 if name in outputs else 0
+            keep.append((arr, raws))
+            per_pass.append((list(items), set(outputs)))
+            specs[si].kernel_name = kernel.encode()
+            specs[si].dtype = _dt(dtype)
+            specs[si].bufs = ctypes.cast(arr, ctypes.c_void_p)
+            specs[si].n_bufs = len(items)
+        us = ctypes.c_float(0.0)
+        self._check(self._lib.mtc_dispatch_chain(self._h, specs, len(passes), ctypes.byref(us)))
+        results = []
+        for si, (names, outs) in enumerate(per_pass):
+            later = set()
+            for names2, outs2 in per_pass[si + 1:]:
+                later |= {n for n in names2 if n not in outs2}
+            res = DispatchResult(elapsed_us=float(us.value) if si == len(per_pass) - 1 else 0.0)
+            for i, name in enumerate(names):
+                if name in outs and name not in later:
+                    res.outputs[name] = keep[si][1][i].raw
+            results.append(res)
+        return results
 
     def kernel_names(self):
         return [self._lib.mtc_kernel_name(i).decode() for i in range(self._lib.mtc_kernel_count())]

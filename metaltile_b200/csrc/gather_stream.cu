@@ -289,22 +289,40 @@ __device__ __forceinline__ void g_segment(const unsigned char *w_lo, const uint2
         b_lo[h] = g_f32_of_half<BF16>(gi >> 1 ? sc[h][2].y : sc[h][2].x, gi & 1);
         b_hi[h] = g_f32_of_half<BF16>(gi >> 1 ? sc[h][3].y : sc[h][3].x, gi & 1);
     }
+    // the MMAs of one step (nibble class) go to 2 NT different accumulators: consecutive MMAs never depend on each other
+    uint4 f01[NT], f23[NT];
+    float2 x_sum[NT];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-        const uint4 f01 = *reinterpret_cast<const uint4 *>(xa + nt * 1024);
-        const uint4 f23 = *reinterpret_cast<const uint4 *>(xb + nt * 1024);
-        const float2 x_sum = *reinterpret_cast<const float2 *>(xs + nt * 8);
+        f01[nt] = *reinterpret_cast<const uint4 *>(xa + nt * 1024);
+        f23[nt] = *reinterpret_cast<const uint4 *>(xb + nt * 1024);
+        x_sum[nt] = *reinterpret_cast<const float2 *>(xs + nt * 8);
+    }
+    float d[NT][2][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) g_hmma<BF16, true>(d[nt][h], f[h].a[0][0], f[h].a[0][1], f[h].a[0][2], f[h].a[0][3], f01[nt].x, f01[nt].y);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) g_hmma<BF16, false>(d[nt][h], f[h].a[1][0], f[h].a[1][1], f[h].a[1][2], f[h].a[1][3], f01[nt].z, f01[nt].w);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) g_hmma<BF16, false>(d[nt][h], f[h].a[2][0], f[h].a[2][1], f[h].a[2][2], f[h].a[2][3], f23[nt].x, f23[nt].y);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) g_hmma<BF16, false>(d[nt][h], f[h].a[3][0], f[h].a[3][1], f[h].a[3][2], f[h].a[3][3], f23[nt].z, f23[nt].w);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            float d[4];
-            g_hmma<BF16, true>(d, f[h].a[0][0], f[h].a[0][1], f[h].a[0][2], f[h].a[0][3], f01.x, f01.y);
-            g_hmma<BF16, false>(d, f[h].a[1][0], f[h].a[1][1], f[h].a[1][2], f[h].a[1][3], f01.z, f01.w);
-            g_hmma<BF16, false>(d, f[h].a[2][0], f[h].a[2][1], f[h].a[2][2], f[h].a[2][3], f23.x, f23.y);
-            g_hmma<BF16, false>(d, f[h].a[3][0], f[h].a[3][1], f[h].a[3][2], f[h].a[3][3], f23.z, f23.w);
-            acc[h][nt][0] = fmaf(s_lo[h], d[0], fmaf(b_lo[h], x_sum.x, acc[h][nt][0]));
-            acc[h][nt][1] = fmaf(s_lo[h], d[1], fmaf(b_lo[h], x_sum.y, acc[h][nt][1]));
-            acc[h][nt][2] = fmaf(s_hi[h], d[2], fmaf(b_hi[h], x_sum.x, acc[h][nt][2]));
-            acc[h][nt][3] = fmaf(s_hi[h], d[3], fmaf(b_hi[h], x_sum.y, acc[h][nt][3]));
+            acc[h][nt][0] = fmaf(s_lo[h], d[nt][h][0], fmaf(b_lo[h], x_sum[nt].x, acc[h][nt][0]));
+            acc[h][nt][1] = fmaf(s_lo[h], d[nt][h][1], fmaf(b_lo[h], x_sum[nt].y, acc[h][nt][1]));
+            acc[h][nt][2] = fmaf(s_hi[h], d[nt][h][2], fmaf(b_hi[h], x_sum[nt].x, acc[h][nt][2]));
+            acc[h][nt][3] = fmaf(s_hi[h], d[nt][h][3], fmaf(b_hi[h], x_sum[nt].y, acc[h][nt][3]));
         }
     }
 }

@@ -279,12 +279,12 @@ gather_generic_kernel(const void *x, const uint32_t *w, const void *scales, cons
     const long long gw = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (gw >= static_cast<long long>(t_rows) * n_out) return;
     const int row = static_cast<int>(gw / n_out), n = static_cast<int>(gw % n_out);
-    int expert = 0;
+    int expert = -1;                      // a row that no expert's range covers is left untouched, as on the tensor-core paths
     if (indices) {
         expert = static_cast<int>(indices[row]);
     } else {
         for (int e = 0; e < n_experts; ++e)
-            if (static_cast<uint32_t>(row) < expert_offsets[e + 1]) { expert = e; break; }
+            if (static_cast<uint32_t>(row) >= expert_offsets[e] && static_cast<uint32_t>(row) < expert_offsets[e + 1]) { expert = e; break; }
     }
     if (expert < 0 || expert >= n_experts) return;
     const size_t wpr = static_cast<size_t>(k_in) * bits / 32, gpr = k_in / gs;

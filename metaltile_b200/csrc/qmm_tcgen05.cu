@@ -753,13 +753,17 @@ __global__ void __launch_bounds__(256) rows_to_f16_kernel(const __nv_bfloat16 *x
 // row whose id is >= e).  Layout of the scratch block: int count; int pad[3]; int4 items[].
 // Expert-major order: the token chunks and weight-row tiles of one expert are adjacent, so the
 // CTAs working at the same time share that expert's X rows in L2.
+// Offsets that reach past total_rows are clamped to it (the rows they would have named do not exist: nothing is read or
+// written for them) and reported in the status word, 0x901, like offsets that run backwards (those experts get no rows).
 __global__ void build_items_kernel(const uint32_t *expert_offsets, const uint32_t *indices, int total_rows, int n_experts,
-                                   int n_tiles, int TN, int *count_out, int4 *items, int max_items) {
+                                   int n_tiles, int TN, int *count_out, int4 *items, int max_items, uint32_t *status) {
     extern __shared__ int sh[];          // [n_experts + 1] offsets, then [n_experts + 1] item bases
     int *off = sh, *base = sh + n_experts + 1;
     for (int e = threadIdx.x; e <= n_experts; e += blockDim.x) {
         if (expert_offsets) {
-            off[e] = static_cast<int>(expert_offsets[e]);
+            const uint32_t o = expert_offsets[e];
+            if (o > static_cast<uint32_t>(total_rows) || (e > 0 && o < expert_offsets[e - 1])) atomicCAS(status, 0u, 0x901u);
+            off[e] = static_cast<int>(min(o, static_cast<uint32_t>(total_rows)));
         } else {                          // lower bound of e in the sorted per-row ids
             int lo = 0, hi = total_rows;
             while (lo < hi) {
@@ -998,7 +1002,7 @@ cudaError_t launch_gather_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *x, 
     int *count = static_cast<int *>(scratch);
     int4 *items = reinterpret_cast<int4 *>(static_cast<char *>(scratch) + 16);
     build_items_kernel<<<1, 256, 2 * (n_experts + 1) * sizeof(int), st>>>(expert_offsets, indices, total_rows, n_experts,
-                                                                         n_tiles, TN, count, items, max_items);
+                                                                         n_tiles, TN, count, items, max_items, ctx->d_status);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     const void *x_op = nullptr;
@@ -1080,7 +1084,7 @@ cudaError_t launch_gather_qmm_static(Ctx *ctx, cudaStream_t st, const void *x, c
     int4 *items = reinterpret_cast<int4 *>(base + 16);
     // the list and its count are rewritten by every call; nothing in the array has to start at zero
     build_items_kernel<<<1, 256, 2 * (n_experts + 1) * sizeof(int), st>>>(expert_offsets, indices, total_rows, n_experts,
-                                                                         n_tiles, TN, count, items, static_cast<int>(kStaticItems));
+                                                                         n_tiles, TN, count, items, static_cast<int>(kStaticItems), ctx->d_status);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     const void *x_op = x;
     const float *tok_scale = nullptr;

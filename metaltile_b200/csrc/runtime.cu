@@ -934,11 +934,29 @@ int mtc_unpack_codes(mtc_ctx *ctx, void *stream, const void *w, void *codes_u8, 
 int mtc_kernel_count(void) { return kNumKernels; }
 const char *mtc_kernel_name(int i) { return (i >= 0 && i < kNumKernels) ? kKernels[i].name : nullptr; }
 
-int mtc_dispatch(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_buf *bufs, int n_bufs,
-                 const uint32_t grid[3], const uint32_t tpg[3], float *elapsed_us) {
-    (void)grid; (void)tpg;  // launch geometry belongs to the back end
+}  // extern "C"
+
+namespace {
+
+// A chain of passes (mtc_dispatch_chain): what earlier passes produced, by buffer name, and where the next pass stages.
+struct Produced {
+    std::string name;
+    char *dev;
+    size_t bytes;
+    mtc_named_buf *host;     // the output buffer of the producing pass; read back at the end unless a later pass consumes it
+    bool consumed;
+};
+struct ChainCtx {
+    bool measure = true;             // first walk: only the bytes every pass stages
+    size_t offset = 0;               // scratch bytes taken by the passes walked so far
+    std::vector<Produced> produced;
+};
+
+// One pass.  Stand-alone (cc == nullptr): stage, launch, read the outputs back, synchronise.  In a chain: an input that an
+// earlier pass produced under the same name is that pass's device buffer (no host copy), nothing is read back and nothing
+// synchronises here.
+int dispatch_pass(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_buf *bufs, int n_bufs, float *elapsed_us, ChainCtx *cc) {
     if (!ctx || !kernel_name || (!bufs && n_bufs > 0)) return MTC_ERR_INVALID;
-    MTC_ENTER(ctx);
     if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "dispatch: dtype must be f32, f16 or bf16");
     const KernelRow *row = find_kernel(kernel_name);
     if (!row) return fail(ctx, MTC_ERR_FUNCTION_NOT_FOUND, std::string("unknown kernel: ") + kernel_name);
@@ -1098,12 +1116,33 @@ int mtc_dispatch(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_buf
         total += align_up(sb.need ? sb.need : 1, 256);
     }
     MTC_CUDA(ctx, cudaSetDevice(ctx->device), MTC_ERR_NO_DEVICE);
-    int rc = ensure_scratch(ctx, total);
-    if (rc != MTC_OK) return rc;
+    int rc = MTC_OK;
+    if (cc && cc->measure) {
+        cc->offset += total;
+        return MTC_OK;
+    }
+    if (!cc) {
+        rc = ensure_scratch(ctx, total);
+        if (rc != MTC_OK) return rc;
+    }
+    const size_t base_off = cc ? cc->offset : 0;
+    if (cc) cc->offset += total;
     cudaStream_t st = nullptr;
     for (Staged &sb : st_bufs) {
-        sb.dev = static_cast<char *>(ctx->d_scratch) + sb.offset;
-        if (sb.need) MTC_CUDA(ctx, cudaMemcpyAsync(sb.dev, sb.buf->data, sb.need, cudaMemcpyHostToDevice, st), MTC_ERR_BUFFER);
+        sb.dev = static_cast<char *>(ctx->d_scratch) + base_off + sb.offset;
+        Produced *from = nullptr;
+        if (cc && !sb.buf->is_output)
+            for (Produced &pr : cc->produced)
+                if (pr.name == sb.buf->name) from = &pr;          // the latest producer of that name
+        if (from) {
+            if (from->bytes < sb.need)
+                return fail(ctx, MTC_ERR_BUFFER_SIZE, kn + ": buffer '" + sb.buf->name + "' was produced with " + std::to_string(from->bytes) +
+                                                         " bytes by an earlier pass, this pass needs " + std::to_string(sb.need));
+            sb.dev = from->dev;
+            from->consumed = true;
+        } else if (sb.need) {
+            MTC_CUDA(ctx, cudaMemcpyAsync(sb.dev, sb.buf->data, sb.need, cudaMemcpyHostToDevice, st), MTC_ERR_BUFFER);
+        }
     }
     auto dev = [&](const char *name) -> char * {
         for (Staged &sb : st_bufs)
@@ -1175,6 +1214,16 @@ int mtc_dispatch(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_buf
             break;
     }
     if (elapsed_us) cudaEventRecord(e1, st);
+    if (cc) {
+        if (rc == MTC_OK)
+            for (Staged &sb : st_bufs)
+                if (sb.buf->is_output) cc->produced.push_back(Produced{sb.buf->name, sb.dev, sb.need, sb.buf, false});
+        if (elapsed_us) {
+            cudaEventDestroy(e0);
+            cudaEventDestroy(e1);
+        }
+        return rc;
+    }
     if (rc == MTC_OK) {
         // every is_output parameter is read back (crates/metaltile-runtime/src/dispatch/single_dispatch.rs:100-117)
         for (Staged &sb : st_bufs)
@@ -1182,6 +1231,60 @@ int mtc_dispatch(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_buf
         cudaError_t e = cudaStreamSynchronize(st);
         if (e != cudaSuccess) rc = fail(ctx, MTC_ERR_DISPATCH, std::string("dispatch: ") + cudaGetErrorString(e));
         else rc = check_status(ctx, "dispatch");
+    }
+    if (elapsed_us) {
+        float ms = 0.f;
+        if (rc == MTC_OK && cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess) *elapsed_us = ms * 1000.0f;
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+    }
+    return rc;
+}
+
+}  // namespace
+
+extern "C" {
+
+int mtc_dispatch(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_buf *bufs, int n_bufs,
+                 const uint32_t grid[3], const uint32_t tpg[3], float *elapsed_us) {
+    (void)grid; (void)tpg;  // launch geometry belongs to the back end
+    if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    return dispatch_pass(ctx, kernel_name, dtype, bufs, n_bufs, elapsed_us, nullptr);
+}
+
+int mtc_dispatch_chain(mtc_ctx *ctx, const mtc_dispatch_spec *specs, int n_specs, float *elapsed_us) {
+    if (!ctx || (!specs && n_specs > 0) || n_specs < 0) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    if (n_specs == 0) return MTC_OK;
+    ChainCtx cc;
+    for (int i = 0; i < n_specs; ++i) {              // every pass is checked and sized before anything is enqueued
+        int rc = dispatch_pass(ctx, specs[i].kernel_name, specs[i].dtype, specs[i].bufs, specs[i].n_bufs, nullptr, &cc);
+        if (rc != MTC_OK) return rc;
+    }
+    int rc = ensure_scratch(ctx, cc.offset);
+    if (rc != MTC_OK) return rc;
+    cc.measure = false;
+    cc.offset = 0;
+    cudaStream_t st = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (elapsed_us) {
+        MTC_CUDA(ctx, cudaEventCreate(&e0), MTC_ERR_DISPATCH);
+        MTC_CUDA(ctx, cudaEventCreate(&e1), MTC_ERR_DISPATCH);
+        cudaEventRecord(e0, st);
+    }
+    for (int i = 0; i < n_specs && rc == MTC_OK; ++i)
+        rc = dispatch_pass(ctx, specs[i].kernel_name, specs[i].dtype, specs[i].bufs, specs[i].n_bufs, nullptr, &cc);
+    if (elapsed_us) cudaEventRecord(e1, st);
+    if (rc == MTC_OK) {
+        // only buffers that no later pass consumed go back to the host (context.rs:347-353); one synchronisation for the chain
+        for (Produced &pr : cc.produced)
+            if (!pr.consumed && pr.bytes) cudaMemcpyAsync(pr.host->data, pr.dev, pr.bytes, cudaMemcpyDeviceToHost, st);
+    }
+    cudaError_t e = cudaStreamSynchronize(st);       // also on failure: nothing of the chain is in flight when this returns
+    if (rc == MTC_OK) {
+        if (e != cudaSuccess) rc = fail(ctx, MTC_ERR_DISPATCH, std::string("dispatch_chain: ") + cudaGetErrorString(e));
+        else rc = check_status(ctx, "dispatch_chain");
     }
     if (elapsed_us) {
         float ms = 0.f;

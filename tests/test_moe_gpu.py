@@ -208,21 +208,28 @@ def test_gather_stream_matches_oracle(ctx, n_experts, n_out, k_in, gs, dt, count
     assert rel_err(out.float().cpu().numpy(), other.float().cpu().numpy()) <= 2 * TOL[dt]
 
 
-def test_gather_stream_reports_bad_offsets(ctx):
-    """expert_offsets that run past m_total or backwards are clamped (no out-of-range access) and reported: 0x901."""
+@pytest.mark.parametrize("stream_kernel", [1, 0])
+def test_gather_reports_bad_offsets(ctx, stream_kernel):
+    """expert_offsets that run past m_total are clamped to it on both tensor-core paths (nothing outside x or out is
+    touched: the rows that exist get their expert's product, the others do not exist) and reported: 0x901."""
     import torch
     from metaltile_b200 import MetalTileError, ops
     w, s, b, x, off, _ = _gather_case(3, 32, 256, 4, 64, "bf16", [4, 4, 4], seed=3)
     bad = off.copy()
-    bad[2] = 1000                                            # beyond m_total = 12
+    bad[2] = 1000                                            # beyond m_total = 12: expert 1 owns rows 4..11, expert 2 none
     wd, sd, bd, xd = to_dev(w), to_dev(s, "bf16"), to_dev(b, "bf16"), to_dev(x, "bf16")
+    ctx.set_option("gather_stream", stream_kernel)
     try:
-        ops.gather_qmm(xd, wd, sd, bd, 4, 64, expert_offsets=to_dev(bad))
+        got = ops.gather_qmm(xd, wd, sd, bd, 4, 64, expert_offsets=to_dev(bad))
         with pytest.raises(MetalTileError):
             ctx.sync(torch.cuda.current_stream().cuda_stream)
         assert ctx.status_word() == 0x901
     finally:
+        ctx.set_option("gather_stream", 1)
         ctx.status_clear()
+    clamped = np.array([0, 4, 12, 12], dtype=np.uint32)
+    ref = oracle.gather_qmm(x, w, s, b, 12, 256, 32, 3, 4, 64, expert_offsets=clamped)
+    assert rel_err(got.float().cpu().numpy(), ref) <= TOL["bf16"]
 
 
 def test_moe_layer_config4(ctx):

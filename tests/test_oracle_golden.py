@@ -153,3 +153,23 @@ def test_rounding_matches_torch():
         bits = oracle.to_bits16(a, dt)
         assert np.array_equal(bits.view(np.int16), t.to(tdt).view(torch.int16).numpy())
         assert np.array_equal(_bits(oracle.from_bits16(bits, dt)), _bits(ref))
+
+
+BATCHED = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "batched_qkv_*.npz")) +
+                 glob.glob(os.path.join(os.path.dirname(__file__), "golden", "test_batched_4_*.npz")))
+
+
+@pytest.mark.parametrize("path", BATCHED, ids=[os.path.basename(p)[:-4] for p in BATCHED])
+def test_batched_decode_fixtures(path):
+    """Fused decode projections (batched_qkv_qgemv_gpu_correctness.rs:112-127, batched_4_qgemv.rs:421-440): the C oracle
+    reproduces every matrix's naive_gemv accumulator bit for bit."""
+    fx = _load(path)
+    dt = DT[os.path.basename(path)[:-4].rsplit("_", 1)[1]]
+    in_dim, gs, outs = int(fx["meta"][0]), int(fx["meta"][1]), [int(v) for v in fx["meta"][2:]]
+    assert len(outs) in (3, 4)
+    for i, n in enumerate(outs):
+        s, b = oracle.round_through(fx[f"scales{i}"], dt), oracle.round_through(fx[f"biases{i}"], dt)
+        codes = oracle.unpack_matrix(fx[f"w{i}"], in_dim, 4)
+        assert codes.max() <= 15 and fx[f"w{i}"].shape == (n, in_dim // 8)
+        acc = oracle.qmm(fx[f"w{i}"], s, b, fx["x"], 1, n, in_dim, 4, gs)
+        assert np.array_equal(_bits(acc.reshape(-1)), _bits(fx[f"acc{i}"]))

@@ -283,3 +283,100 @@ def test_chain_in_a_cuda_graph(ctx):
             assert torch.equal(a, o)
     assert ctx.status_word() == 0
     chain.close()
+
+
+def _batched_fixture(name):
+    import os
+    return dict(np.load(os.path.join(os.path.dirname(__file__), "golden", name)))
+
+
+# the reference's tolerances: max |a - e| / max(|e|, 1e-3) (batched_qkv_qgemv_gpu_correctness.rs:159-181)
+REF_TOL = {"f32": 5e-3, "f16": 2e-2, "bf16": 5e-2}
+
+
+def _ref_rel(got, exp):
+    return float(np.max(np.abs(got - exp) / np.maximum(np.abs(exp), 1e-3)))
+
+
+@pytest.mark.parametrize("kernel,fixture,dt", [
+    ("ffai_batched_qkv_qgemv", "batched_qkv_k256_g64_q16_kv4", "f32"), ("ffai_batched_qkv_qgemv", "batched_qkv_k512_g128_q12_kv6", "f32"),
+    ("ffai_batched_qkv_qgemv", "batched_qkv_k256_g64_q16_kv4", "f16"), ("ffai_batched_qkv_qgemv", "batched_qkv_k256_g64_q16_kv4", "bf16"),
+    ("ffai_batched_qkv_qgemv_fast", "batched_qkv_k512_g64_q16_kv8", "f32"), ("ffai_batched_qkv_qgemv_fast", "batched_qkv_k512_g64_q16_kv8", "f16"),
+    ("ffai_batched_qkv_qgemv_fast", "batched_qkv_k512_g64_q16_kv8", "bf16"),
+])
+def test_batched_qkv_via_dispatch(ctx, kernel, fixture, dt):
+    """The reference's own cases of the fused q / k / v decode projection under its kernel and buffer names: one
+    concatenated `out` (batched_qkv_qgemv_gpu_correctness.rs:112-181,312-321)."""
+    from helpers import bytes_to_f32, dt_bytes
+    fx = _batched_fixture(f"{fixture}_{dt}.npz")
+    in_dim, gs, (oq, ok, ov) = int(fx["meta"][0]), int(fx["meta"][1]), (int(v) for v in fx["meta"][2:])
+    bufs = {"x": dt_bytes(fx["x"], dt), "out": bytes((oq + ok + ov) * (4 if dt == "f32" else 2))}
+    for i, sfx in enumerate("qkv"):
+        bufs[f"w_{sfx}"], bufs[f"scales_{sfx}"], bufs[f"biases_{sfx}"] = fx[f"w{i}"].tobytes(), dt_bytes(fx[f"scales{i}"], dt), dt_bytes(fx[f"biases{i}"], dt)
+    consts = {"out_q": oq, "out_k": ok, "out_v": ov, "in_dim": in_dim, "group_size": gs}
+    res = ctx.dispatch_with_grid(kernel, bufs, consts, (max(oq, ok, ov), 1, 3), (128, 1, 1), dtype=dt)
+    got = bytes_to_f32(res.outputs["out"], dt)
+    exp = oracle.round_through(np.concatenate([fx["acc0"], fx["acc1"], fx["acc2"]]), ODT[dt])
+    assert np.any(got != 0.0) and got.shape == exp.shape
+    assert _ref_rel(got, exp) <= REF_TOL[dt]
+    assert rel_err(got, exp) <= TOL[dt]                     # and this build's own, tighter bound
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+def test_batched_4_via_dispatch(ctx, dt):
+    """test_batched_4_qgemv_fast (crates/metaltile-std/src/ffai/batched_4_qgemv.rs:421-472): four outputs a_out .. d_out."""
+    from helpers import bytes_to_f32, dt_bytes
+    fx = _batched_fixture(f"test_batched_4_qgemv_fast_{dt}.npz")
+    in_dim, gs, outs = int(fx["meta"][0]), int(fx["meta"][1]), [int(v) for v in fx["meta"][2:]]
+    esz = 4 if dt == "f32" else 2
+    bufs, consts = {"x": dt_bytes(fx["x"], dt)}, {"in_dim": in_dim, "group_size": gs}
+    for i, sfx in enumerate("abcd"):
+        bufs[f"w_{sfx}"], bufs[f"scales_{sfx}"], bufs[f"biases_{sfx}"] = fx[f"w{i}"].tobytes(), dt_bytes(fx[f"scales{i}"], dt), dt_bytes(fx[f"biases{i}"], dt)
+        bufs[f"{sfx}_out"] = bytes(outs[i] * esz)
+        consts[f"out_{sfx}"] = outs[i]
+    res = ctx.dispatch_with_grid("ffai_batched_4_qgemv_fast", bufs, consts, (2, 1, 4), (64, 1, 1), dtype=dt,
+                                 outputs=("a_out", "b_out", "c_out", "d_out"))
+    for i, sfx in enumerate("abcd"):
+        got = bytes_to_f32(res.outputs[f"{sfx}_out"], dt)
+        exp = oracle.round_through(fx[f"acc{i}"], ODT[dt])
+        assert np.any(got != 0.0)
+        assert _ref_rel(got, exp) <= 2e-1 and rel_err(got, exp) <= TOL[dt]     # the reference's tol = 2e-1; ours
+
+
+def test_batched_dispatch_refuses_missing_pieces(ctx):
+    from metaltile_b200 import MetalTileError
+    fx = _batched_fixture("batched_qkv_k256_g64_q16_kv4_f32.npz")
+    from helpers import dt_bytes
+    bufs = {"x": dt_bytes(fx["x"], "f32"), "out": bytes(24 * 4)}
+    for i, sfx in enumerate("qk"):                          # v is missing
+        bufs[f"w_{sfx}"], bufs[f"scales_{sfx}"], bufs[f"biases_{sfx}"] = fx[f"w{i}"].tobytes(), dt_bytes(fx[f"scales{i}"], "f32"), dt_bytes(fx[f"biases{i}"], "f32")
+    with pytest.raises(MetalTileError) as ei:
+        ctx.dispatch_with_grid("ffai_batched_qkv_qgemv", bufs, {"out_q": 16, "out_k": 4, "out_v": 4, "in_dim": 256, "group_size": 64})
+    assert ei.value.variant == "Buffer" and "w_v" in str(ei.value)
+    bufs["w_v"], bufs["scales_v"], bufs["biases_v"] = bufs["w_k"], bufs["scales_k"], bufs["biases_k"]
+    bufs["out"] = bytes(23 * 4)                             # one element short
+    with pytest.raises(MetalTileError) as ei:
+        ctx.dispatch_with_grid("ffai_batched_qkv_qgemv", bufs, {"out_q": 16, "out_k": 4, "out_v": 4, "in_dim": 256, "group_size": 64})
+    assert ei.value.variant == "BufferSize"
+
+
+def test_dispatch_chain_is_the_passes_in_order(ctx):
+    """Context::dispatch_chain (crates/metaltile-runtime/src/context.rs:347-395): several passes, one commit.  No two
+    registered kernels of this path share an output and an input name, so nothing links here: every pass's outputs come
+    back, equal to the same passes dispatched one by one."""
+    from helpers import bytes_to_f32, dt_bytes
+    w, s, b, x = dense_case(1, 64, 512, 4, 64, "bf16", seed=7)
+    p1 = ("mt_qmv", {"w": w.tobytes(), "scales": dt_bytes(s, "bf16"), "biases": dt_bytes(b, "bf16"), "x": dt_bytes(x, "bf16"),
+                     "out": bytes(64 * 2)}, {"k": 512, "gs_per_row": 8}, "bf16", ("out",))
+    g = np.linspace(-3, 3, 256, dtype=np.float32)
+    p2 = ("mt_swiglu", {"gate": dt_bytes(g, "f32"), "up": dt_bytes(g[::-1].copy(), "f32"), "out": bytes(256 * 4)}, {}, "f32", ("out",))
+    res = ctx.dispatch_chain([p1, p2])
+    one = [ctx.dispatch_with_grid(k, bufs, consts, dtype=dt, outputs=outs) for (k, bufs, consts, dt, outs) in (p1, p2)]
+    assert len(res) == 2 and res[1].elapsed_us > 0.0
+    for r, o in zip(res, one):
+        assert r.outputs["out"] == o.outputs["out"]
+    assert rel_err(bytes_to_f32(res[0].outputs["out"], "bf16").reshape(1, 64), oracle.qmm(w, s, b, x, 1, 64, 512, 4, 64)) <= TOL["bf16"]
+    from metaltile_b200 import MetalTileError
+    with pytest.raises(MetalTileError) as ei:               # checked before anything runs: the second pass names no kernel
+        ctx.dispatch_chain([p1, ("mt_nothing", {}, {}, "f32", ())])
+    assert ei.value.variant == "FunctionNotFound"

@@ -31,7 +31,11 @@ def _run_both(ctx, w, s, b, x, off, bits, gs, dt):
     from metaltile_b200 import ops
     from metaltile_b200.ops import _TORCH_DT
     wd, sd, bd, xd, od = to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt), to_dev(off)
-    ref = ops.gather_qmm(xd, wd, sd, bd, bits, gs, expert_offsets=od, ctx=ctx)
+    ctx.set_option("gather_stream", 0)      # the static entry is the tensor-memory kernel: compare with that kernel's regular entry
+    try:
+        ref = ops.gather_qmm(xd, wd, sd, bd, bits, gs, expert_offsets=od, ctx=ctx)
+    finally:
+        ctx.set_option("gather_stream", 1)
     out = torch.zeros_like(ref)
     e, n_out, _ = w.shape
     ctx.gather_qmm_static(xd.data_ptr(), wd.data_ptr(), sd.data_ptr(), bd.data_ptr(), out.data_ptr(), x.shape[0], n_out,
