@@ -177,19 +177,35 @@ int mtc_peer_barrier(mtc_ctx *ctx, void *stream, void *const *peer_flags, int n_
  * crates/metaltile-core/src/toolchain/config.rs:11-96).  Options:
  *   "qmm_tile_tokens"  token rows per tensor-core work item (0 = chosen per shape; else a multiple
  *                      of 16 in [16, 256])
- *   "qmv_max_ctas_per_sm"  > 0 caps the CTAs per SM of the M = 1 kernel's grid (diagnostic; default 0 = 2)
  *   "qmm_wait_hint_ns" suspend-time hint (ns) of the tensor-core kernel's waits that have slack: the TMA producer and the
  *                      epilogue warps (default 5000; 0 = plain polling)
  *   "qmv_small_m_mma"  0: keep 2 <= M <= 16 on the CUDA-core kernel (default 1: 4-bit codes with f16/bf16
  *                      activations and a group that is a multiple of 64 use the warp-level tensor cores);
  *                      2: M = 1 takes that path too (same results within round-off; not faster on B200)
- *   "qmm_max_stages"   > 0 caps the depth of the shared-memory ring of the tensor-core kernel (diagnostic)
  *   "qmm_mma_chunks"   0: 17 <= M <= 64 always runs on the tcgen05 kernel (default 1: 4-bit, f16/bf16, group >= 64
  *                      shapes run as 16-row chunks of the small-M tensor-core qmv when that fills the GPU better)
  *   "qmm_raw"          0: the dequant warps of the tensor-core kernel load packed words straight from global
  *                      memory instead of through the shared-memory staging buffers (default 1)
  *   "qmm_pair"         1: a work item covers two adjacent weight-row tiles that share every
- *                      activation stage (dense qmm only; default 0) */
+ *                      activation stage (dense qmm only; default 0)
+ *   "qmv_stream"       0: M <= 8 decode shapes never take the streaming kernel (default 1: 4-bit, f16 / bf16,
+ *                      K % 512 == 0, group 64 or 128, 16-byte aligned pointers do)
+ *   "qmv_tc"           1: those shapes run on the tensor-memory decode kernel instead (slower today; default 0)
+ *   "gather_stream"    0: grouped products never take the weight-streaming kernel (default 1: the CSR form with
+ *                      4-bit codes, f16 / bf16, k_in % 256 == 0, group 64 or 128 and m_total <= 64 n_experts does)
+ *   "pdl_early_weights" 0: no decode kernel reads w, scales or biases before the previous kernel of its stream is
+ *                      complete.  Default 1: the decode kernels are launched with programmatic dependent launch and
+ *                      start copying WEIGHTS while the previous kernel drains - weights are constants of the model;
+ *                      a caller whose previous kernel on the stream WRITES them (an on-stream repack, dequant or
+ *                      copy of the shard) must set this to 0 or synchronise first.  x and every store always wait.
+ *   "peer_poll_limit"  polls of a wait on another GPU (mtc_peer_barrier, mtc_qmv_batched_sync) before it gives up
+ *                      and records 0x601 + rank in the status word (default 4194304)
+ * Scratch blocks.  bf16 mtc_qmm, mtc_gather_qmm, mtc_moe_experts and the tensor-memory decode kernel keep work lists
+ * and staged activations in grow-only blocks of the context.  A block moves only outside stream capture (a call that
+ * would have to grow one during capture fails with MTC_ERR_BUFFER: run the shape once before capturing), and an outgrown
+ * block stays allocated until mtc_destroy, so graphs captured earlier and work already enqueued never see freed memory.
+ * The blocks are per context, not per stream: calls of these entries from two streams that may overlap on the GPU race
+ * on them - keep them on one stream, or order the streams with events, or use one context per stream. */
 int mtc_set_option(mtc_ctx *ctx, const char *name, int value);
 
 /* mt_moe_gather_qmm_int4 / _b{3,5,6,8} / _m8 / _m16 / _m32 (CSR form: expert_offsets u32[E+1],
@@ -197,7 +213,10 @@ int mtc_set_option(mtc_ctx *ctx, const char *name, int value);
  * (per-row form: indices u32[m_total], moe.rs:2256-2533,2552-2835): out[t, n] = sum_k x[t,k] * w(E(t), n, k).
  * x rows are sorted by expert; w is stacked u32[E, n_out, k_in*bits/32], scales/biases T[E, n_out, k_in/group].
  * Exactly one of expert_offsets / indices is non-NULL.  f16/bf16 activations with k_in % 64 == 0 and a
- * power-of-two group >= 32 run on the tensor cores, everything else on CUDA cores. */
+ * power-of-two group >= 32 run on the tensor cores (few rows per expert - see "gather_stream" - on the
+ * weight-streaming kernel, else on the tensor-memory kernel), everything else on CUDA cores.  Offsets that reach
+ * past m_total or run backwards are clamped (rows that do not exist are neither read nor written) and reported
+ * through the status word (0x901). */
 int mtc_gather_qmm(mtc_ctx *ctx, void *stream, const void *x, const void *w, const void *scales,
                    const void *biases, const void *expert_offsets, const void *indices, void *out,
                    int m_total, int n_out, int k_in, int n_experts, int bits, int group_size, int dtype);
