@@ -73,6 +73,8 @@ struct QmmParams {
     uint32_t hint_ns;            // base suspend-time hint of the waits (0: plain polling)
     int raw;                     // 1: packed words reach the dequant warps through shared memory (cp.async, whole lines)
     uint32_t raw_off, raw_tile;  // byte offset of the raw buffers in shared memory; bytes of one tile of one buffer
+    int wide;                    // 1: a dense item covers up to 2 TN token rows: one dequantised W stage meets two X chunks, both
+                                 //    accumulators belong to the item (the dequant work per flop halves; no epilogue overlap)
     int pair;                    // 1: an item covers two adjacent weight-row tiles that share every X stage
     int pair_items;              // dense + pair: items [0, pair_items) are pairs, the rest single tiles
     int n_tiles;                 // dense: weight-row tiles
@@ -341,6 +343,7 @@ __device__ __forceinline__ void dequant_half(const uint32_t (&w)[BITS], float s,
 
 struct Item {
     int n_tile, expert, row0, rows, nt;     // nt: weight-row tiles covered (1 or 2)
+    int nc;                                 // token chunks of TN rows covered (1 or 2); nt * nc <= 2 accumulators
 };
 
 __device__ __forceinline__ Item get_item(const QmmParams &p, int i) {
@@ -348,7 +351,19 @@ __device__ __forceinline__ Item get_item(const QmmParams &p, int i) {
     if (p.items) {
         const int4 v = __ldg(p.items + i);
         it.n_tile = v.x; it.expert = v.y & 0xFFFFFF; it.nt = 1 + ((v.y >> 24) & 1); it.row0 = v.z; it.rows = v.w;
+        it.nc = 1;
+    } else if (p.wide) {
+        // dense, wide: m_chunks items of up to 2 TN token rows per weight-row tile, adjacent so that CTAs running at
+        // the same time share the tile's packed words in L2
+        const int unit = i / p.m_chunks, chunk = i - unit * p.m_chunks;
+        it.expert = 0;
+        it.n_tile = unit;
+        it.nt = 1;
+        it.row0 = chunk * 2 * p.TN;
+        it.rows = min(2 * p.TN, p.M - it.row0);
+        it.nc = it.rows > p.TN ? 2 : 1;
     } else {
+        it.nc = 1;
         // dense: the token chunks of one weight-row tile (pair) are adjacent, so CTAs running at the same time
         // share its packed words in L2.  Pairs first; what does not fill a whole wave of pairs runs as single
         // tiles so that the last wave is short.
@@ -377,9 +392,10 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     const int nst = p.nst;
     const uint32_t w_stage = (p.pair ? 2 : 1) * A_BYTES;                // one or two dequantised W tiles per stage
-    const uint32_t x_stage = static_cast<uint32_t>(p.TN) * BK * 2;      // multiple of 2 KB
+    const uint32_t x_stage = static_cast<uint32_t>(p.TN) * BK * 2;      // one X chunk; multiple of 2 KB
+    const uint32_t x_slot = (p.wide ? 2 : 1) * x_stage;                 // one or two X chunks per stage
     uint8_t *sW = smem;                                  // nst x w_stage: dequantised weights (A operand)
-    uint8_t *sX = smem + nst * w_stage;                  // nst x x_stage: activations (B operand)
+    uint8_t *sX = smem + nst * w_stage;                  // nst x x_slot: activations (B operand)
     SmemCtrl *ctl = reinterpret_cast<SmemCtrl *>(smem + RING_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -419,8 +435,9 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                 const Item item = get_item(p, i);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!(ok = mbar_wait(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x101, p.hint_ns))) break;
-                    mbar_expect_tx(&ctl->full[s], x_bytes);
-                    tma_load_2d(sX + s * x_stage, &tmap_x, kb * BK, item.row0, &ctl->full[s]);
+                    mbar_expect_tx(&ctl->full[s], x_bytes * item.nc);
+                    for (int c = 0; c < item.nc; ++c)
+                        tma_load_2d(sX + s * x_slot + c * x_stage, &tmap_x, kb * BK, item.row0 + c * p.TN, &ctl->full[s]);
                     if (++s == nst) {
                         s = 0;
                         ph ^= 1;
@@ -446,13 +463,14 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
             bool ok = true;
             const bool leader = elect_one();
             const uint64_t adesc0 = make_desc_sw128(smem_u32(sW)), bdesc0 = make_desc_sw128(smem_u32(sX));
-            const uint32_t a_step = w_stage >> 4, b_step = x_stage >> 4;      // descriptor address units per stage
+            const uint32_t a_step = w_stage >> 4, b_step = x_slot >> 4;       // descriptor address units per stage
             for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x, ++tile_i) {
                 const Item item = get_item(p, i);
                 // pairs: both 256-column accumulators belong to one item (no double buffering);
                 // single tiles: the two accumulators alternate so the epilogue overlaps the next item
-                const int buf = p.pair ? 0 : (tile_i & 1);
-                const uint32_t acc_ph = (p.pair ? tile_i : (tile_i >> 1)) & 1;
+                const bool both = p.pair || p.wide;
+                const int buf = both ? 0 : (tile_i & 1);
+                const uint32_t acc_ph = (both ? tile_i : (tile_i >> 1)) & 1;
                 if (!(ok = mbar_wait_warp(&ctl->acc_empty[buf], acc_ph ^ 1, ctl, p.status, 0x201, 0))) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * TN_MAX;
@@ -463,9 +481,12 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                         const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * b_step);
                         for (int t = 0; t < item.nt; ++t) {
                             const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * a_step + t * (A_BYTES >> 4));
+                            for (int c = 0; c < item.nc; ++c) {      // nt * nc <= 2: accumulator half t + c
+                                const uint64_t bd = bdesc + static_cast<uint64_t>(c * (x_stage >> 4));
 #pragma unroll
-                            for (int k = 0; k < BK / 16; ++k)   // 16 elements = 32 bytes further along the swizzled row
-                                umma_f16(tmem_d + t * TN_MAX, adesc + 2 * k, bdesc + 2 * k, p.idesc, (kb | k) ? 1u : 0u);
+                                for (int k = 0; k < BK / 16; ++k)   // 16 elements = 32 bytes further along the swizzled row
+                                    umma_f16(tmem_d + (t + c) * TN_MAX, adesc + 2 * k, bd + 2 * k, p.idesc, (kb | k) ? 1u : 0u);
+                            }
                         }
                         umma_commit(&ctl->empty[s]);         // frees the stage when these MMAs have read it
                     }
@@ -485,34 +506,39 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
         uint32_t tile_i = 0;
         bool ok = true;
         for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x, ++tile_i) {
-            const int buf = p.pair ? 0 : (tile_i & 1);
-            const uint32_t acc_ph = (p.pair ? tile_i : (tile_i >> 1)) & 1;
+            const bool both = p.pair || p.wide;
+            const int buf = both ? 0 : (tile_i & 1);
+            const uint32_t acc_ph = (both ? tile_i : (tile_i >> 1)) & 1;
             const Item item = get_item(p, i);
             if (!(ok = mbar_wait_warp(&ctl->acc_full[buf], acc_ph, ctl, p.status, 0x301, p.hint_ns))) break;
             tc_fence_after();
-            const int cols = (item.rows + 15) & ~15;
-            for (int t = 0; t < item.nt; ++t) {
+            const int halves = item.nt * item.nc;               // accumulators of this item: 1 or 2
+            for (int hh = 0; hh < halves; ++hh) {
+                const int t = item.nt == 2 ? hh : 0, c = item.nc == 2 ? hh : 0;
                 const int n = (item.n_tile + t) * BMW + q * 32 + lane;     // output column owned by this thread
                 const bool n_ok = n < p.N;
+                const int row_base = item.row0 + c * p.TN;
+                const int rows_h = item.nc == 2 ? min(p.TN, item.rows - c * p.TN) : item.rows;
+                const int cols = (rows_h + 15) & ~15;
                 for (int c0 = 0; c0 < cols; c0 += 16) {
                     float ts[16];                  // per-token factors first, so their latency hides behind the TMEM load
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        ts[j] = (p.tok_scale && c0 + j < item.rows) ? __ldg(p.tok_scale + item.row0 + c0 + j) : 1.0f;
+                        ts[j] = (p.tok_scale && c0 + j < rows_h) ? __ldg(p.tok_scale + row_base + c0 + j) : 1.0f;
                     uint32_t v[16];
-                    tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (buf + t) * TN_MAX + c0, v);
+                    tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (buf + hh) * TN_MAX + c0, v);
                     if (n_ok) {
                         // lanes of a warp hold 32 consecutive columns of the same output row: 64-byte segments
                         if (p.out_dt == MTC_F16) {
-                            __half *o = static_cast<__half *>(p.out) + static_cast<size_t>(item.row0 + c0) * p.N + n;
+                            __half *o = static_cast<__half *>(p.out) + static_cast<size_t>(row_base + c0) * p.N + n;
 #pragma unroll
                             for (int j = 0; j < 16; ++j)
-                                if (c0 + j < item.rows) o[static_cast<size_t>(j) * p.N] = __float2half_rn(__uint_as_float(v[j]) * ts[j]);
+                                if (c0 + j < rows_h) o[static_cast<size_t>(j) * p.N] = __float2half_rn(__uint_as_float(v[j]) * ts[j]);
                         } else {
-                            __nv_bfloat16 *o = static_cast<__nv_bfloat16 *>(p.out) + static_cast<size_t>(item.row0 + c0) * p.N + n;
+                            __nv_bfloat16 *o = static_cast<__nv_bfloat16 *>(p.out) + static_cast<size_t>(row_base + c0) * p.N + n;
 #pragma unroll
                             for (int j = 0; j < 16; ++j)
-                                if (c0 + j < item.rows) o[static_cast<size_t>(j) * p.N] = __float2bfloat16_rn(__uint_as_float(v[j]) * ts[j]);
+                                if (c0 + j < rows_h) o[static_cast<size_t>(j) * p.N] = __float2bfloat16_rn(__uint_as_float(v[j]) * ts[j]);
                         }
                     }
                 }
@@ -866,7 +892,7 @@ cudaError_t make_x_map(CUtensorMap *tmap, const void *x, int rows, int K, int TN
 // two buffers per weight tile out of the ring, which costs nothing: measured, a ring deeper than 2 stages does not
 // change the time of any shape.
 void plan_smem(QmmParams &p, Ctx *ctx, int bits) {
-    const int stage = (p.pair ? 2 : 1) * A_BYTES + p.TN * BK * 2;
+    const int stage = (p.pair ? 2 : 1) * A_BYTES + (p.wide ? 2 : 1) * p.TN * BK * 2;
     const auto al16 = [](const void *ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; };
     p.raw_tile = static_cast<uint32_t>(BMW * (32 * bits + 16) + RAW_SB_BYTES);
     const int raw_total = 2 * (p.pair ? 2 : 1) * static_cast<int>(p.raw_tile);
@@ -895,6 +921,7 @@ void fill_common(QmmParams &p, Ctx *ctx, const void *w, const void *scales, cons
     p.gpr = K / group_size;
     p.TN = TN;
     p.pair = 0;
+    p.wide = 0;
     plan_smem(p, ctx, bits);
     p.hint_ns = static_cast<uint32_t>(ctx->qmm_wait_hint_ns);
     const uint32_t fmt = p.op_f16 ? 0u : 1u;           // both operands carry the same 16-bit format
@@ -966,6 +993,18 @@ cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const v
         const int tiles_left = p.n_tiles > tiles_done ? p.n_tiles - tiles_done : 0;
         p.dense_items = full_units + tiles_left * p.m_chunks;
     } else {
+        // Two token chunks per item: the dequantised W stage, which sets the pace of a k block, is built once per
+        // 2 TN token rows instead of once per TN.
+        if (ctx->qmm_wide && TN == TN_MAX && M > TN_MAX) {
+            p.wide = 1;
+            plan_smem(p, ctx, bits);
+            if (p.nst < 2) {
+                p.wide = 0;
+                plan_smem(p, ctx, bits);
+            } else {
+                p.m_chunks = (M + 2 * TN - 1) / (2 * TN);
+            }
+        }
         p.pair_items = p.n_tiles * p.m_chunks;
         p.dense_items = p.pair_items;
     }

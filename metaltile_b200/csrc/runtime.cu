@@ -714,6 +714,10 @@ int mtc_set_option(mtc_ctx *ctx, const char *name, int value) {
         ctx->gather_stream = value ? 1 : 0;
         return MTC_OK;
     }
+    if (std::strcmp(name, "qmm_wide") == 0) {
+        ctx->qmm_wide = value ? 1 : 0;
+        return MTC_OK;
+    }
     if (std::strcmp(name, "qmm_pair") == 0) {
         ctx->qmm_pair = value ? 1 : 0;
         return MTC_OK;

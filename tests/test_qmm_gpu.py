@@ -208,3 +208,31 @@ def test_paired_weight_tiles_option(ctx):
         ctx.set_option("qmm_pair", 0)
     assert torch.equal(base, paired)
     assert rel_err(base.float().cpu().numpy(), oracle.qmm(w, s, b, x, m, n, k, bits, gs)) <= TOL[dt]
+
+
+@pytest.mark.parametrize("m,n,k,bits,gs,dt", [
+    (257, 300, 512, 4, 64, "bf16"),        # second token chunk holds one row
+    (512, 136, 768, 4, 64, "f16"),         # exactly two full chunks
+    (700, 520, 512, 8, 128, "bf16"),       # a wide item and a 188-row single-chunk item per weight tile
+    (1300, 129, 1024, 3, 32, "bf16"),      # three items per tile, ragged rows in the last chunk and in the last tile
+])
+def test_wide_items_equal_single_chunk_items(ctx, m, n, k, bits, gs, dt):
+    """"qmm_wide" (default 1): a dense work item covers two 256-row token chunks that share every dequantised weight
+    stage.  Every output is the same sum in the same order as with one chunk per item: bit-identical."""
+    import torch
+    from metaltile_b200 import ops
+    w, s, b, x = dense_case(m, n, k, bits, gs, dt, seed=21, salt=m)
+    args = (to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt), bits, gs)
+    wide = ops.qmm(*args)
+    again = ops.qmm(*args)
+    ctx.set_option("qmm_wide", 0)
+    try:
+        single = ops.qmm(*args)
+        torch.cuda.synchronize()
+    finally:
+        ctx.set_option("qmm_wide", 1)
+    assert ctx.status_word() == 0
+    assert torch.equal(wide, single) and torch.equal(wide, again)
+    for (r0, r1) in ((0, 64), (m - 40, m)):                  # the oracle on the first and the last rows
+        ref = oracle.qmm(w, s, b, x[r0:r1], r1 - r0, n, k, bits, gs)
+        assert rel_err(wide[r0:r1].float().cpu().numpy(), ref) <= TOL[dt]
