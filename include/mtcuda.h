@@ -188,6 +188,8 @@ int mtc_peer_barrier(mtc_ctx *ctx, void *stream, void *const *peer_flags, int n_
  *                      memory instead of through the shared-memory staging buffers (default 1)
  *   "qmm_pair"         1: a work item covers two adjacent weight-row tiles that share every
  *                      activation stage (dense qmm only; default 0)
+ *   "qmm_wide"         0: a dense work item of the tensor-core kernel never covers two 256-row token chunks
+ *                      (default 1 for M > 256: one dequantised weight stage meets two activation chunks; same results)
  *   "qmv_stream"       0: M <= 8 decode shapes never take the streaming kernel (default 1: 4-bit, f16 / bf16,
  *                      K % 512 == 0, group 64 or 128, 16-byte aligned pointers do)
  *   "qmv_tc"           1: those shapes run on the tensor-memory decode kernel instead (slower today; default 0)
