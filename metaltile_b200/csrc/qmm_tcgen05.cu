@@ -73,6 +73,7 @@ struct QmmParams {
     uint32_t hint_ns;            // base suspend-time hint of the waits (0: plain polling)
     int raw;                     // 1: packed words reach the dequant warps through shared memory (cp.async, whole lines)
     uint32_t raw_off, raw_tile;  // byte offset of the raw buffers in shared memory; bytes of one tile of one buffer
+    int wide_items;              // wide: items [0, wide_items) cover two token chunks, each later pair of items one such unit
     int wide;                    // 1: a dense item covers up to 2 TN token rows: one dequantised W stage meets two X chunks, both
                                  //    accumulators belong to the item (the dequant work per flop halves; no epilogue overlap)
     int pair;                    // 1: an item covers two adjacent weight-row tiles that share every X stage
@@ -355,12 +356,16 @@ __device__ __forceinline__ Item get_item(const QmmParams &p, int i) {
     } else if (p.wide) {
         // dense, wide: m_chunks items of up to 2 TN token rows per weight-row tile, adjacent so that CTAs running at
         // the same time share the tile's packed words in L2
-        const int unit = i / p.m_chunks, chunk = i - unit * p.m_chunks;
+        // the wide items that do not fill a whole round of the grid (items >= wide_items) run as two single-chunk
+        // items each, so that the last round is a short one
+        const int u = i < p.wide_items ? i : p.wide_items + ((i - p.wide_items) >> 1);
+        const int half = i < p.wide_items ? 0 : ((i - p.wide_items) & 1);
+        const int unit = u / p.m_chunks, chunk = u - unit * p.m_chunks;
         it.expert = 0;
         it.n_tile = unit;
         it.nt = 1;
-        it.row0 = chunk * 2 * p.TN;
-        it.rows = min(2 * p.TN, p.M - it.row0);
+        it.row0 = chunk * 2 * p.TN + half * p.TN;
+        it.rows = i < p.wide_items ? min(2 * p.TN, p.M - it.row0) : min(p.TN, p.M - it.row0);
         it.nc = it.rows > p.TN ? 2 : 1;
     } else {
         it.nc = 1;
@@ -1007,6 +1012,17 @@ cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const v
         }
         p.pair_items = p.n_tiles * p.m_chunks;
         p.dense_items = p.pair_items;
+        if (p.wide) {
+            // a k block costs the same whatever the token count, so the leftover of the last round is cheaper as
+            // single-chunk items on twice as many SMs - when those still fit in one round and every unit has two halves
+            const int units = p.n_tiles * p.m_chunks, left = units % sms;
+            const bool two_halves = M % (2 * TN) == 0 || M % (2 * TN) > TN;
+            p.wide_items = units;
+            if (units > sms && left > 0 && 2 * left <= sms && two_halves) {
+                p.wide_items = units - left;
+                p.dense_items = p.wide_items + 2 * left;
+            }
+        }
     }
     const int grid = p.dense_items < sms ? p.dense_items : sms;
     return launch_any(bits, st, tmap, p, grid);

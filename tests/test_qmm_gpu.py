@@ -215,6 +215,8 @@ def test_paired_weight_tiles_option(ctx):
     (512, 136, 768, 4, 64, "f16"),         # exactly two full chunks
     (700, 520, 512, 8, 128, "bf16"),       # a wide item and a 188-row single-chunk item per weight tile
     (1300, 129, 1024, 3, 32, "bf16"),      # three items per tile, ragged rows in the last chunk and in the last tile
+    (512, 19200, 256, 4, 64, "bf16"),      # 150 wide units on 148 SMs: the two left over run as four single-chunk items
+    (1024, 9600, 256, 4, 64, "f16"),       # the same with two units per weight tile
 ])
 def test_wide_items_equal_single_chunk_items(ctx, m, n, k, bits, gs, dt):
     """"qmm_wide" (default 1): a dense work item covers two 256-row token chunks that share every dequantised weight
