@@ -539,7 +539,7 @@ def main():
     multi = None
     if world > 1 and not args.no_extra:
         try:
-            multi = multi_gpu_extras(ctx, dev, rank, world, timed)
+            multi = multi_gpu_extras(ctx, dev, rank, world, timed, peer_ok=p2p)
         except Exception as e:  # all ranks take the same path: an exception here is raised on every rank or on none
             multi = {"error": repr(e)}
     if rank != 0:
@@ -584,7 +584,7 @@ def main():
     finish()
 
 
-def multi_gpu_extras(ctx, dev, rank, world, timed):
+def multi_gpu_extras(ctx, dev, rank, world, timed, peer_ok=False):
     """The sharded forms of the prefill matmul (config 3: N-split + all-gather) and of the MoE layer (config 4: expert
     parallel, all-to-all dispatch and combine), run by every rank; rank 0 checks its result against the unsharded
     kernels on the same data (sharding changes no row's arithmetic, so the comparison is for equality)."""
@@ -620,6 +620,33 @@ def multi_gpu_extras(ctx, dev, rank, world, timed):
         tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
         out[name] = {"us": ms * 1e3, "TFLOP/s": tf, "ranks": world, "verified": verified,
                      "note": "aggregate over all ranks, NCCL all-gather of the [M, N / ranks] slices and the row-major interleave included"}
+        # the same product with the all-gather fused into the kernel: every rank's epilogue stores its column block into
+        # every rank's [M, N] buffer through peer mappings; one barrier kernel makes the blocks visible
+        if peer_ok:
+            try:
+                from metaltile_b200.parallel import PeerGather
+                pg = PeerGather(ctx, m * n * 2)
+                wl, sl, bl = lin.w, lin.scales, lin.biases
+                st = torch.cuda.current_stream().cuda_stream
+
+                def fused():
+                    pg.qmm_into(wl, sl, bl, x, BITS, GROUP, n, r0, torch.cuda.current_stream().cuda_stream)
+                    pg.barrier(torch.cuda.current_stream().cuda_stream)
+
+                fused()
+                torch.cuda.synchronize()
+                dist.barrier()
+                v2 = None
+                if rank == 0:
+                    v2 = bool(torch.equal(ref.reshape(-1), pg.tensor(torch.bfloat16)[:m * n])) and ctx.status_word() == 0
+                ms2 = timed(fused, 5)
+                out[name + "_fused"] = {"us": ms2 * 1e3, "TFLOP/s": 2.0 * m * n * k / (ms2 * 1e-3) / 1e12, "ranks": world, "verified": v2,
+                                        "note": "aggregate over all ranks; the kernel's epilogue stores each rank's column block into "
+                                                "every rank's [M, N] buffer (peer stores), one barrier kernel; no NCCL call"}
+                dist.barrier()
+                pg.close()
+            except Exception as e:   # the peer path is optional: the NCCL figure above stands
+                print(f"[rank {rank}] fused qmm all-gather unavailable: {e!r}", file=sys.stderr, flush=True)
         del w, sc, bi, x, lin, got
     # ---- config 4: 512 tokens (data parallel), 128 experts split over the ranks, top-8
     T, H, I, E, K8 = 512, 2048, 768, 128, 8

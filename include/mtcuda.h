@@ -166,6 +166,14 @@ int mtc_chain_is_fused(const mtc_chain *chain);
  * 0x601 + the rank that never arrived and the kernel returns. */
 int mtc_qmv_multi(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x,
                   void *const *outs, int n_outs, int M, int N, int K, int bits, int group_size, int dtype);
+/* mtc_qmm whose [M, N] result is a column block of wider row-major matrices, written to 1 to 8 destinations (no
+ * counterpart in the reference): outs[i] points at row 0 of the block inside destination i, ld = elements between
+ * consecutive rows of a destination (>= N).  With the peers' mappings of one [M, N_total] buffer per rank (mtc_ipc_*) as
+ * destinations, an N-split prefill matmul gathers itself: every rank's epilogue stores its column block into every
+ * rank's copy while the next tiles are computed; mtc_peer_barrier afterwards makes the blocks visible everywhere.
+ * Plain stores through peer mappings only.  Shapes of the tensor-core kernel only (else MTC_ERR_UNSUPPORTED). */
+int mtc_qmm_multi(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x,
+                  void *const *outs, int n_outs, long long ld, int M, int N, int K, int bits, int group_size, int dtype);
 int mtc_ipc_export(mtc_ctx *ctx, void *d_ptr, void *handle64);
 int mtc_ipc_open(mtc_ctx *ctx, const void *handle64, void **d_ptr);
 int mtc_ipc_close(mtc_ctx *ctx, void *d_ptr);

@@ -158,7 +158,7 @@ bool qmm_tcgen05_supported(int M, int N, int K, int bits, int group_size, int dt
                            const void *out);
 cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases,
                                const void *x, void *out, int M, int N, int K, int bits, int group_size, int dt,
-                               std::string *why);
+                               std::string *why, void *const *outs = nullptr, int n_outs = 1, long long out_ld = 0);
 size_t gather_items_bytes(int total_rows, int n_experts, int N, int TN_hint);
 cudaError_t launch_gather_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *x, const void *w, const void *scales,
                                       const void *biases, const uint32_t *expert_offsets, const uint32_t *indices,

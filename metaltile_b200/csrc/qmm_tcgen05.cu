@@ -56,6 +56,9 @@ struct QmmParams {
     const uint32_t *w;
     const void *scales, *biases;
     void *out;
+    void *outs[8];               // destinations of the result block (outs[0] == out); further ones may be peers' memory
+    int n_outs;
+    long long out_ld;            // elements between consecutive token rows of a destination (N, or the width of a wider matrix)
     uint32_t *status;
     const int4 *items;           // gather: {n_tile, expert, row_start, row_count}; dense: nullptr
     const int *item_count;       // gather: device counter; dense: nullptr
@@ -534,16 +537,17 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                     tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (buf + hh) * TN_MAX + c0, v);
                     if (n_ok) {
                         // lanes of a warp hold 32 consecutive columns of the same output row: 64-byte segments
-                        if (p.out_dt == MTC_F16) {
-                            __half *o = static_cast<__half *>(p.out) + static_cast<size_t>(row_base + c0) * p.N + n;
+                        unsigned short hv[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float f = __uint_as_float(v[j]) * ts[j];
+                            hv[j] = p.out_dt == MTC_F16 ? __half_as_ushort(__float2half_rn(f)) : __bfloat16_as_ushort(__float2bfloat16_rn(f));
+                        }
+                        for (int d = 0; d < p.n_outs; ++d) {
+                            unsigned short *o = static_cast<unsigned short *>(p.outs[d]) + static_cast<size_t>(row_base + c0) * p.out_ld + n;
 #pragma unroll
                             for (int j = 0; j < 16; ++j)
-                                if (c0 + j < rows_h) o[static_cast<size_t>(j) * p.N] = __float2half_rn(__uint_as_float(v[j]) * ts[j]);
-                        } else {
-                            __nv_bfloat16 *o = static_cast<__nv_bfloat16 *>(p.out) + static_cast<size_t>(row_base + c0) * p.N + n;
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (c0 + j < rows_h) o[static_cast<size_t>(j) * p.N] = __float2bfloat16_rn(__uint_as_float(v[j]) * ts[j]);
+                                if (c0 + j < rows_h) o[static_cast<size_t>(j) * p.out_ld] = hv[j];
                         }
                     }
                 }
@@ -915,6 +919,9 @@ void fill_common(QmmParams &p, Ctx *ctx, const void *w, const void *scales, cons
     p.scales = scales;
     p.biases = biases;
     p.out = out;
+    p.outs[0] = out;
+    p.n_outs = 1;
+    p.out_ld = N;
     p.status = ctx->d_status;
     p.N = N; p.K = K;
     p.sb_dt = dt;
@@ -966,7 +973,7 @@ bool qmm_tcgen05_supported(int M, int N, int K, int bits, int group_size, int dt
 
 cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases,
                                const void *x, void *out, int M, int N, int K, int bits, int group_size, int dt,
-                               std::string *why) {
+                               std::string *why, void *const *outs, int n_outs, long long out_ld) {
     int TN = ctx->qmm_force_tn > 0 ? ctx->qmm_force_tn : (M >= TN_MAX ? TN_MAX : ((M + 15) / 16) * 16);
     const void *x_op = nullptr;
     const float *tok_scale = nullptr;
@@ -978,6 +985,12 @@ cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const v
     QmmParams p{};
     fill_common(p, ctx, w, scales, biases, out, N, K, bits, group_size, dt, TN);
     p.tok_scale = tok_scale;
+    if (outs) {                         // the result is a column block of wider row-major matrices, possibly on other GPUs
+        for (int i = 0; i < n_outs && i < 8; ++i) p.outs[i] = outs[i];
+        p.out = outs[0];
+        p.n_outs = n_outs;
+        p.out_ld = out_ld;
+    }
     p.M = M;
     p.m_chunks = (M + TN - 1) / TN;
     p.n_tiles = (N + BMW - 1) / BMW;

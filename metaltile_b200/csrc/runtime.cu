@@ -662,6 +662,27 @@ int mtc_qmm(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
     return mtc_qmv(ctx, stream, w, scales, biases, x, out, M, N, K, bits, group_size, dtype);
 }
 
+int mtc_qmm_multi(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x,
+                  void *const *outs, int n_outs, long long ld, int M, int N, int K, int bits, int group_size, int dtype) {
+    if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    if (!outs || n_outs < 1 || n_outs > 8) return fail(ctx, MTC_ERR_INVALID, "qmm_multi: 1 to 8 destinations");
+    if (ld < N) return fail(ctx, MTC_ERR_INVALID, "qmm_multi: the destination row stride must be at least N");
+    if (M <= 0 || N <= 0) return MTC_OK;
+    if (!w || !scales || !biases || !x) return fail(ctx, MTC_ERR_INVALID, "qmm_multi: null pointer");
+    for (int i = 0; i < n_outs; ++i)
+        if (!outs[i]) return fail(ctx, MTC_ERR_INVALID, "qmm_multi: null destination");
+    if (M <= 16 || !mtc::qmm_tcgen05_supported(M, N, K, bits, group_size, dtype, w, x, outs[0]))
+        return fail(ctx, MTC_ERR_UNSUPPORTED, "qmm_multi: only shapes of the tensor-core kernel (M > 16, f16 / bf16, K % 64 == 0, "
+                                              "power-of-two group >= 32, 16-byte aligned w and x)");
+    std::string why;
+    cudaError_t e = mtc::launch_qmm_tcgen05(ctx, static_cast<cudaStream_t>(stream), w, scales, biases, x, outs[0], M, N, K, bits,
+                                            group_size, dtype, &why, outs, n_outs, ld);
+    if (e != cudaSuccess)
+        return fail(ctx, MTC_ERR_DISPATCH, "qmm_multi launch: " + (why.empty() ? std::string(cudaGetErrorString(e)) : why));
+    return MTC_OK;
+}
+
 int mtc_set_option(mtc_ctx *ctx, const char *name, int value) {
     if (!ctx || !name) return MTC_ERR_INVALID;
     if (std::strcmp(name, "qmm_tile_tokens") == 0) {

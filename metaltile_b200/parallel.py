@@ -66,6 +66,10 @@ class CudaBackend:
     def gather_qmm(self, x, w, s, b, bits, gs, offsets):
         return self.ops.gather_qmm(x, w, s, b, bits, gs, expert_offsets=offsets, ctx=self.ctx)
 
+    def experts(self, x, gate, up, down, bits, gs, offsets):
+        """gate, up, SwiGLU and down of rows sorted by expert as one call (same results as the separate steps)."""
+        return self.ops.moe_experts(x, gate, up, down, bits, gs, offsets, ctx=self.ctx)
+
 
 class ColumnParallelLinear:
     """One N-split quantized projection: local ``w[N/G, K*bits/32]``, ``scales``/``biases[N/G, K/g]``."""
@@ -216,6 +220,19 @@ class PeerGather:
         f = self.flags + 256
         self.ctx.qmv_batched_sync(descs, [p + 256 for p in self.peer_flags], self.rank, f, f + 128, f + 192, stream=stream)
 
+    def qmm_into(self, w, scales, biases, x, bits, group_size, n_total: int, col0: int, stream: int):
+        """Prefill product of this rank's weight rows, stored by the kernel's epilogue as columns ``[col0, col0 + N_local)``
+        of the row-major ``[M, n_total]`` matrix at the start of every rank's buffer (the N-split all-gather without a
+        collective, overlapped with the product)."""
+        from .ops import _TORCH_DT
+        m, k = x.shape
+        esz = x.element_size()
+        if m * n_total * esz > self.nbytes:
+            raise ValueError("the gathered matrix does not fit in the shared buffer")
+        outs = [self.peer_bufs[self.rank] + col0 * esz] + [p + col0 * esz for r, p in enumerate(self.peer_bufs) if r != self.rank]
+        self.ctx.qmm_multi(w.data_ptr(), scales.data_ptr(), biases.data_ptr(), x.data_ptr(), outs, n_total, m, w.shape[0], k,
+                           bits, group_size, _TORCH_DT[x.dtype], stream=stream)
+
     def barrier(self, stream: int):
         self.ctx.peer_barrier(self.peer_flags, self.rank, self.flags, self.flags + 128, stream=stream)
 
@@ -250,6 +267,8 @@ class ExpertParallelMoE:
 
     def _experts(self, x_sorted, offsets):
         be, sh = self.backend, self.shard
+        if hasattr(be, "experts"):
+            return be.experts(x_sorted, sh.gate, sh.up, sh.down, sh.bits, sh.group_size, offsets)
         g = be.gather_qmm(x_sorted, *sh.gate, sh.bits, sh.group_size, offsets)
         u = be.gather_qmm(x_sorted, *sh.up, sh.bits, sh.group_size, offsets)
         a = be.swiglu(g, u)

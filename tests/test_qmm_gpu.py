@@ -238,3 +238,34 @@ def test_wide_items_equal_single_chunk_items(ctx, m, n, k, bits, gs, dt):
     for (r0, r1) in ((0, 64), (m - 40, m)):                  # the oracle on the first and the last rows
         ref = oracle.qmm(w, s, b, x[r0:r1], r1 - r0, n, k, bits, gs)
         assert rel_err(wide[r0:r1].float().cpu().numpy(), ref) <= TOL[dt]
+
+
+def test_qmm_multi_writes_column_blocks_of_wider_matrices(ctx):
+    """mtc_qmm_multi: the [M, N] result lands as a column block (row stride ld) in every destination - the form the
+    sharded prefill uses to gather through peer stores.  Same values as mtc_qmm, nothing outside the block is touched."""
+    import torch
+    from metaltile_b200 import MetalTileError
+    from metaltile_b200.ops import _TORCH_DT
+    m, n, k, bits, gs, dt = 300, 200, 512, 4, 64, "bf16"
+    w, s, b, x = dense_case(m, n, k, bits, gs, dt, seed=23)
+    wd, sd, bd, xd = to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt)
+    from metaltile_b200 import ops
+    ref = ops.qmm(wd, sd, bd, xd, bits, gs, ctx=ctx)
+    ld, col0 = 520, 136
+    dests = [torch.full((m, ld), 7.0, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    st = torch.cuda.current_stream().cuda_stream
+    ctx.qmm_multi(wd.data_ptr(), sd.data_ptr(), bd.data_ptr(), xd.data_ptr(), [d.data_ptr() + col0 * 2 for d in dests], ld, m, n, k,
+                  bits, gs, _TORCH_DT[xd.dtype], stream=st)
+    torch.cuda.synchronize()
+    assert ctx.status_word() == 0
+    for d in dests:
+        assert torch.equal(d[:, col0:col0 + n], ref)
+        assert bool((d[:, :col0] == 7.0).all()) and bool((d[:, col0 + n:] == 7.0).all())
+    with pytest.raises(MetalTileError) as ei:               # a row stride narrower than the block
+        ctx.qmm_multi(wd.data_ptr(), sd.data_ptr(), bd.data_ptr(), xd.data_ptr(), [dests[0].data_ptr()], n - 1, m, n, k, bits, gs,
+                      _TORCH_DT[xd.dtype], stream=st)
+    assert ei.value.variant == "Invalid"
+    with pytest.raises(MetalTileError) as ei:               # M <= 16 belongs to the decode kernels
+        ctx.qmm_multi(wd.data_ptr(), sd.data_ptr(), bd.data_ptr(), xd.data_ptr(), [dests[0].data_ptr()], ld, 8, n, k, bits, gs,
+                      _TORCH_DT[xd.dtype], stream=st)
+    assert ei.value.variant == "Unsupported"
