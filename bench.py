@@ -827,7 +827,9 @@ def extra_measurements(ctx, dev, hbm_peak, tf_peak, local_rank=0, layers=None):
         us, clk = with_clocks(lambda: time_rot([step8], 10))
         nbytes = step_bytes(m8, len(layers))
         out["c2_decode_set_m8"] = {"ms": us / 1e3, "GB/s": nbytes / us / 1e3, "frac_of_hbm_peak": nbytes / us / 1e3 / hbm_peak,
-                                   "launches": len(groups), "clocks": clk}
+                                   "launches": len(groups) if ctx.qmm_route(m8, 4096, 4096, BITS, GROUP, "bf16") == "qmv_stream"
+                                   else sum(len(g) for g in groups),
+                                   "route": ctx.qmm_route(m8, 4096, 4096, BITS, GROUP, "bf16"), "clocks": clk}
     return out
 
 

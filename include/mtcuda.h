@@ -198,8 +198,10 @@ int mtc_peer_barrier(mtc_ctx *ctx, void *stream, void *const *peer_flags, int n_
  *                      activation stage (dense qmm only; default 0)
  *   "qmm_wide"         0: a dense work item of the tensor-core kernel never covers two 256-row token chunks
  *                      (default 1 for M > 256: one dequantised weight stage meets two activation chunks; same results)
- *   "qmv_stream"       0: M <= 8 decode shapes never take the streaming kernel (default 1: 4-bit, f16 / bf16,
- *                      K % 512 == 0, group 64 or 128, 16-byte aligned pointers do)
+ *   "qmv_stream"       the streaming decode kernel (4-bit, f16 / bf16, K % 512 == 0, group 64 or 128, 16-byte aligned
+ *                      pointers): 1 (default) takes M = 1; 2 takes every M <= 8 (slower than the register-ring kernel
+ *                      there); 0 never.  mtc_qmv_batched fuses its projections into one launch where this kernel
+ *                      takes them and launches them one by one otherwise
  *   "qmv_tc"           1: those shapes run on the tensor-memory decode kernel instead (slower today; default 0)
  *   "gather_stream"    0: grouped products never take the weight-streaming kernel (default 1: the CSR form with
  *                      4-bit codes, f16 / bf16, k_in % 256 == 0, group 64 or 128 and m_total <= 64 n_experts does)

@@ -136,6 +136,11 @@ constexpr size_t kTcCounterBytes = 1u << 20;       // (tile, quarter) counters o
 
 // Partial-sum planes of the tcgen05 decode kernel.  Grow-only; an outgrown block is kept until mtc_destroy, so a CUDA
 // graph captured earlier never reads freed memory.  Growing allocates: not during stream capture.
+// Option "qmv_stream": 1 (default) = the streaming decode kernel takes M = 1, where it is the fastest kernel of the
+// library; 2 = every M <= 8 it supports (at 2 <= M <= 8 the register-ring kernel of qmv_mma.cu is faster: measured
+// 13.3 against 21.7 us on 14336 x 4096 at M = 8); 0 = never.
+inline bool stream_takes(const Ctx *ctx, int M) { return ctx->qmv_stream == 2 ? M <= 8 : (ctx->qmv_stream == 1 && M == 1); }
+
 int ensure_tc_scratch(Ctx *ctx, size_t bytes, cudaStream_t st) {
     if (bytes <= ctx->tc_scratch_bytes) return MTC_OK;
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
@@ -391,7 +396,7 @@ int mtc_qmv(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
         const int t = try_qmv_tc(ctx, stream, w, scales, biases, x, outs1, 1, M, N, K, bits, group_size, dtype);
         if (t <= 0) return t;
     }
-    if (ctx->qmv_stream && mtc::qmv_stream_supported(M, N, K, bits, group_size, dtype, w, scales, biases, x)) {
+    if (stream_takes(ctx, M) && mtc::qmv_stream_supported(M, N, K, bits, group_size, dtype, w, scales, biases, x)) {
         mtc_qmv_desc d{};
         d.w = w; d.scales = scales; d.biases = biases; d.x = x;
         d.outs[0] = out; d.n_outs = 1;
@@ -428,7 +433,7 @@ int mtc_qmv_multi(mtc_ctx *ctx, void *stream, const void *w, const void *scales,
         const int t = try_qmv_tc(ctx, stream, w, scales, biases, x, outs, n_outs, M, N, K, bits, group_size, dtype);
         if (t <= 0) return t;
     }
-    if (ctx->qmv_stream && M > 0 && N > 0 && mtc::qmv_stream_supported(M, N, K, bits, group_size, dtype, w, scales, biases, x)) {
+    if (stream_takes(ctx, M) && M > 0 && N > 0 && mtc::qmv_stream_supported(M, N, K, bits, group_size, dtype, w, scales, biases, x)) {
         mtc_qmv_desc d{};
         d.w = w; d.scales = scales; d.biases = biases; d.x = x;
         for (int i = 0; i < n_outs; ++i) d.outs[i] = outs[i];
@@ -459,7 +464,7 @@ int mtc_qmv_batched(mtc_ctx *ctx, void *stream, const mtc_qmv_desc *descs, int n
     if (!ctx) return MTC_ERR_INVALID;
     MTC_ENTER(ctx);
     if (!descs || n < 1 || n > 4) return fail(ctx, MTC_ERR_INVALID, "qmv_batched: 1 to 4 projections");
-    bool fused = ctx->qmv_stream != 0;
+    bool fused = stream_takes(ctx, descs[0].M);
     for (int i = 0; i < n; ++i) {
         int rc = check_desc(ctx, descs[i], "qmv_batched");
         if (rc != MTC_OK) return rc;
@@ -496,7 +501,7 @@ int mtc_qmv_batched_sync(mtc_ctx *ctx, void *stream, const mtc_qmv_desc *descs, 
         const mtc_qmv_desc &d = descs[i];
         if (d.x != descs[0].x || d.M != descs[0].M || d.K != descs[0].K || d.dtype != descs[0].dtype || d.group_size != descs[0].group_size)
             return fail(ctx, MTC_ERR_INVALID, "qmv_batched_sync: the projections must share x, M, K, dtype and group size");
-        if (!ctx->qmv_stream || !mtc::qmv_stream_supported(d.M, d.N, d.K, d.bits, d.group_size, d.dtype, d.w, d.scales, d.biases, d.x))
+        if (ctx->qmv_stream == 0 || !mtc::qmv_stream_supported(d.M, d.N, d.K, d.bits, d.group_size, d.dtype, d.w, d.scales, d.biases, d.x))
             return fail(ctx, MTC_ERR_UNSUPPORTED, "qmv_batched_sync: only shapes of the streaming kernel (4-bit, f16 / bf16, M <= 8, "
                                                   "K % 512 == 0, group 64 or 128, 16-byte aligned pointers)");
     }
@@ -623,8 +628,8 @@ static bool mma_chunks_preferred(int enabled, int sms, int M, int N, int K, int 
 }
 
 const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dtype) {
-    if (M >= 1 && M <= 8 && mtc::qmv_stream_supported(M, N, K, bits, group_size, dtype, nullptr, nullptr, nullptr, nullptr))
-        return "qmv_stream";
+    if (M == 1 && mtc::qmv_stream_supported(M, N, K, bits, group_size, dtype, nullptr, nullptr, nullptr, nullptr))
+        return "qmv_stream";      // option "qmv_stream" = 2 extends it to M <= 8
     if (mma_chunks_preferred(1, 148, M, N, K, bits, group_size, dtype, nullptr, nullptr)) return "qmv_mma_sync";
     if (M > 16 && mtc::qmm_tcgen05_supported(M, N, K, bits, group_size, dtype, nullptr, nullptr, nullptr))
         return "qmm_tcgen05";
@@ -724,7 +729,7 @@ int mtc_set_option(mtc_ctx *ctx, const char *name, int value) {
         return MTC_OK;
     }
     if (std::strcmp(name, "qmv_stream") == 0) {
-        ctx->qmv_stream = value ? 1 : 0;
+        ctx->qmv_stream = value < 0 ? 0 : (value > 2 ? 2 : value);
         return MTC_OK;
     }
     if (std::strcmp(name, "pdl_early_weights") == 0) {

@@ -25,7 +25,7 @@ def run_qmm(w, s, b, x, bits, gs, dt):
 def test_routing_follows_m_and_dtype(ctx):
     """The selector (mt_qmm_for, crates/metaltile-std/src/mlx/quantized.rs:5040-5065,5127-5199) in this back end."""
     assert ctx.qmm_route(1, 4096, 4096, 4, 64, "bf16") == "qmv_stream"
-    assert ctx.qmm_route(8, 4096, 4096, 4, 128, "f16") == "qmv_stream"
+    assert ctx.qmm_route(8, 4096, 4096, 4, 128, "f16") == "qmv_mma_sync"          # the streaming kernel takes M = 1 by default
     assert ctx.qmm_route(1, 4096, 4096, 4, 64, "f32") == "qmv_cuda_core"
     assert ctx.qmm_route(1, 4096, 4096, 3, 64, "bf16") == "qmv_cuda_core"
     assert ctx.qmm_route(16, 4096, 4096, 4, 64, "bf16") == "qmv_mma_sync"

@@ -11,8 +11,13 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(scope="module")
 def ctx():
+    """The context with the streaming kernel taking every M <= 8 it supports (option value 2; the default routes only
+    M = 1 to it), so that the multi-token cases below exercise that kernel."""
     from metaltile_b200 import ops
-    return ops.context(0)
+    c = ops.context(0)
+    c.set_option("qmv_stream", 2)
+    yield c
+    c.set_option("qmv_stream", 1)
 
 
 def _bands(n, width=32):
@@ -45,7 +50,7 @@ def test_stream_matches_oracle(ctx, m, n, k, gs, dt, engine):
     import torch
     from metaltile_b200 import ops
     w, s, b, x = dense_case(m, n, k, 4, gs, dt, seed=2, salt=m + n % 7)
-    assert ctx.qmm_route(m, n, k, 4, gs, dt) == "qmv_stream"
+    assert ctx.qmm_route(1, n, k, 4, gs, dt) == "qmv_stream"
     ctx.set_option("qmv_tc", 1 if engine == "tcgen05" else 0)
     try:
         got = ops.qmv(to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt), 4, gs, ctx=ctx)
@@ -107,7 +112,7 @@ def test_stream_equals_the_cuda_core_kernel_within_rounding(ctx):
     try:
         c = ops.qmv(*args, ctx=ctx)                # the CUDA-core kernel
     finally:
-        ctx.set_option("qmv_stream", 1)
+        ctx.set_option("qmv_stream", 2)
     assert torch.mean((a == t2).float()).item() > 0.98
     torch.cuda.synchronize()
     assert rel_err(a.float().cpu().numpy(), c.float().cpu().numpy()) <= 1e-2
