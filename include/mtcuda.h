@@ -194,8 +194,6 @@ int mtc_peer_barrier(mtc_ctx *ctx, void *stream, void *const *peer_flags, int n_
  *                      shapes run as 16-row chunks of the small-M tensor-core qmv when that fills the GPU better)
  *   "qmm_raw"          0: the dequant warps of the tensor-core kernel load packed words straight from global
  *                      memory instead of through the shared-memory staging buffers (default 1)
- *   "qmm_pair"         1: a work item covers two adjacent weight-row tiles that share every
- *                      activation stage (dense qmm only; default 0)
  *   "qmm_wide"         0: a dense work item of the tensor-core kernel never covers two 256-row token chunks
  *                      (default 1 for M > 256: one dequantised weight stage meets two activation chunks; same results)
  *   "qmv_stream"       the streaming decode kernel (4-bit, f16 / bf16, K % 512 == 0, group 64 or 128, 16-byte aligned

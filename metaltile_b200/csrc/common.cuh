@@ -30,7 +30,6 @@ struct Ctx {
     int qmm_wait_hint_ns = 5000;      // option "qmm_wait_hint_ns": base suspend-time hint of the kernel's mbarrier waits
     int qmm_mma_chunks = 1;        // option "qmm_mma_chunks": 0 = 17 <= M <= 64 always on the tcgen05 kernel
     int qmm_raw = 1;               // option "qmm_raw": 0 = dequant warps load their packed words straight from global memory
-    int qmm_pair = 0;              // option "qmm_pair": 1 = give a work item two adjacent weight-row tiles
     int qmm_wide = 1;              // option "qmm_wide": 0 = a dense work item never covers two token chunks (one W stage, two X chunks)
     uint32_t peer_poll_limit = 1u << 22;   // option "peer_poll_limit": polls of mtc_peer_barrier before it gives up on a peer
     int qmv_tc = 0;                // option "qmv_tc": 1 = M <= 8 decode shapes run on the tcgen05 decode kernel (qmv_tc.cu; slower than the stream kernel today)

@@ -79,8 +79,6 @@ struct QmmParams {
     int wide_items;              // wide: items [0, wide_items) cover two token chunks, each later pair of items one such unit
     int wide;                    // 1: a dense item covers up to 2 TN token rows: one dequantised W stage meets two X chunks, both
                                  //    accumulators belong to the item (the dequant work per flop halves; no epilogue overlap)
-    int pair;                    // 1: an item covers two adjacent weight-row tiles that share every X stage
-    int pair_items;              // dense + pair: items [0, pair_items) are pairs, the rest single tiles
     int n_tiles;                 // dense: weight-row tiles
     uint32_t idesc;
 };
@@ -346,15 +344,15 @@ __device__ __forceinline__ void dequant_half(const uint32_t (&w)[BITS], float s,
 }
 
 struct Item {
-    int n_tile, expert, row0, rows, nt;     // nt: weight-row tiles covered (1 or 2)
-    int nc;                                 // token chunks of TN rows covered (1 or 2); nt * nc <= 2 accumulators
+    int n_tile, expert, row0, rows;
+    int nc;                                 // token chunks of TN rows covered (1 or 2): one accumulator each
 };
 
 __device__ __forceinline__ Item get_item(const QmmParams &p, int i) {
     Item it;
     if (p.items) {
         const int4 v = __ldg(p.items + i);
-        it.n_tile = v.x; it.expert = v.y & 0xFFFFFF; it.nt = 1 + ((v.y >> 24) & 1); it.row0 = v.z; it.rows = v.w;
+        it.n_tile = v.x; it.expert = v.y & 0xFFFFFF; it.row0 = v.z; it.rows = v.w;
         it.nc = 1;
     } else if (p.wide) {
         // dense, wide: m_chunks items of up to 2 TN token rows per weight-row tile, adjacent so that CTAs running at
@@ -366,27 +364,16 @@ __device__ __forceinline__ Item get_item(const QmmParams &p, int i) {
         const int unit = u / p.m_chunks, chunk = u - unit * p.m_chunks;
         it.expert = 0;
         it.n_tile = unit;
-        it.nt = 1;
         it.row0 = chunk * 2 * p.TN + half * p.TN;
         it.rows = i < p.wide_items ? min(2 * p.TN, p.M - it.row0) : min(p.TN, p.M - it.row0);
         it.nc = it.rows > p.TN ? 2 : 1;
     } else {
+        // dense: the token chunks of one weight-row tile are adjacent, so CTAs running at the same time share its
+        // packed words in L2
+        const int unit = i / p.m_chunks, chunk = i - unit * p.m_chunks;
         it.nc = 1;
-        // dense: the token chunks of one weight-row tile (pair) are adjacent, so CTAs running at the same time
-        // share its packed words in L2.  Pairs first; what does not fill a whole wave of pairs runs as single
-        // tiles so that the last wave is short.
-        int unit, chunk;
         it.expert = 0;
-        if (i < p.pair_items) {
-            unit = i / p.m_chunks; chunk = i - unit * p.m_chunks;
-            it.n_tile = unit * (p.pair ? 2 : 1);
-            it.nt = (p.pair && it.n_tile + 1 < p.n_tiles) ? 2 : 1;
-        } else {
-            const int j = i - p.pair_items;
-            unit = j / p.m_chunks; chunk = j - unit * p.m_chunks;
-            it.n_tile = (p.pair_items / p.m_chunks) * 2 + unit;
-            it.nt = 1;
-        }
+        it.n_tile = unit;
         it.row0 = chunk * p.TN;
         it.rows = min(p.TN, p.M - it.row0);
     }
@@ -399,7 +386,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     const int nst = p.nst;
-    const uint32_t w_stage = (p.pair ? 2 : 1) * A_BYTES;                // one or two dequantised W tiles per stage
+    const uint32_t w_stage = A_BYTES;                                   // one dequantised W tile per stage
     const uint32_t x_stage = static_cast<uint32_t>(p.TN) * BK * 2;      // one X chunk; multiple of 2 KB
     const uint32_t x_slot = (p.wide ? 2 : 1) * x_stage;                 // one or two X chunks per stage
     uint8_t *sW = smem;                                  // nst x w_stage: dequantised weights (A operand)
@@ -474,9 +461,9 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
             const uint32_t a_step = w_stage >> 4, b_step = x_slot >> 4;       // descriptor address units per stage
             for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x, ++tile_i) {
                 const Item item = get_item(p, i);
-                // pairs: both 256-column accumulators belong to one item (no double buffering);
-                // single tiles: the two accumulators alternate so the epilogue overlaps the next item
-                const bool both = p.pair || p.wide;
+                // wide items: both 256-column accumulators belong to one item (no double buffering);
+                // otherwise the two accumulators alternate so that the epilogue overlaps the next item
+                const bool both = p.wide != 0;
                 const int buf = both ? 0 : (tile_i & 1);
                 const uint32_t acc_ph = (both ? tile_i : (tile_i >> 1)) & 1;
                 if (!(ok = mbar_wait_warp(&ctl->acc_empty[buf], acc_ph ^ 1, ctl, p.status, 0x201, 0))) break;
@@ -487,14 +474,12 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                     tc_fence_after();
                     if (leader) {
                         const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * b_step);
-                        for (int t = 0; t < item.nt; ++t) {
-                            const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * a_step + t * (A_BYTES >> 4));
-                            for (int c = 0; c < item.nc; ++c) {      // nt * nc <= 2: accumulator half t + c
-                                const uint64_t bd = bdesc + static_cast<uint64_t>(c * (x_stage >> 4));
+                        const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * a_step);
+                        for (int c = 0; c < item.nc; ++c) {          // token chunk c accumulates in TMEM half c
+                            const uint64_t bd = bdesc + static_cast<uint64_t>(c * (x_stage >> 4));
 #pragma unroll
-                                for (int k = 0; k < BK / 16; ++k)   // 16 elements = 32 bytes further along the swizzled row
-                                    umma_f16(tmem_d + (t + c) * TN_MAX, adesc + 2 * k, bd + 2 * k, p.idesc, (kb | k) ? 1u : 0u);
-                            }
+                            for (int k = 0; k < BK / 16; ++k)       // 16 elements = 32 bytes further along the swizzled row
+                                umma_f16(tmem_d + c * TN_MAX, adesc + 2 * k, bd + 2 * k, p.idesc, (kb | k) ? 1u : 0u);
                         }
                         umma_commit(&ctl->empty[s]);         // frees the stage when these MMAs have read it
                     }
@@ -514,17 +499,16 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
         uint32_t tile_i = 0;
         bool ok = true;
         for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x, ++tile_i) {
-            const bool both = p.pair || p.wide;
+            const bool both = p.wide != 0;
             const int buf = both ? 0 : (tile_i & 1);
             const uint32_t acc_ph = (both ? tile_i : (tile_i >> 1)) & 1;
             const Item item = get_item(p, i);
             if (!(ok = mbar_wait_warp(&ctl->acc_full[buf], acc_ph, ctl, p.status, 0x301, p.hint_ns))) break;
             tc_fence_after();
-            const int halves = item.nt * item.nc;               // accumulators of this item: 1 or 2
-            for (int hh = 0; hh < halves; ++hh) {
-                const int t = item.nt == 2 ? hh : 0, c = item.nc == 2 ? hh : 0;
-                const int n = (item.n_tile + t) * BMW + q * 32 + lane;     // output column owned by this thread
-                const bool n_ok = n < p.N;
+            const int n = item.n_tile * BMW + q * 32 + lane;     // output column owned by this thread
+            const bool n_ok = n < p.N;
+            for (int hh = 0; hh < item.nc; ++hh) {               // accumulators of this item: 1 or 2
+                const int c = hh;
                 const int row_base = item.row0 + c * p.TN;
                 const int rows_h = item.nc == 2 ? min(p.TN, item.rows - c * p.TN) : item.rows;
                 const int cols = (rows_h + 15) & ~15;
@@ -578,30 +562,28 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
             // buffers, one super-block ahead and across items, and read their pieces back from shared memory.
             constexpr int ROW_BYTES = 32 * BITS, PITCH = ROW_BYTES + 16, CPR = 2 * BITS;   // padded rows: conflict-free reads
             const uint32_t raw0 = smem_u32(smem) + p.raw_off;
-            const uint32_t buf_bytes = (p.pair ? 2u : 1u) * p.raw_tile;
+            const uint32_t buf_bytes = p.raw_tile;
             const int num_sb = num_kb / SB_PER_RAW;
             const int sb_bytes = (2 * SB_PER_RAW * BK) >> p.gs_shift;       // scale bytes of a row per super-block: 16, 8 or 4
             const int srow = t & (BMW - 1), sarr = t >> 7;                  // this thread copies scales (0) or biases (1) of a row
             auto issue = [&](const Item &im, int sbk, int buf) {
-                for (int tt = 0; tt < im.nt; ++tt) {
-                    const uint32_t dstt = raw0 + buf * buf_bytes + tt * p.raw_tile;
-                    const int n0 = (im.n_tile + tt) * BMW;
-                    const size_t erow = static_cast<size_t>(im.expert) * p.N;
+                const uint32_t dstt = raw0 + buf * buf_bytes;
+                const int n0 = im.n_tile * BMW;
+                const size_t erow = static_cast<size_t>(im.expert) * p.N;
 #pragma unroll
-                    for (int c = 0; c < BITS; ++c) {
-                        const int ch = c * DEQ_THREADS + t, row = ch / CPR, col = ch - row * CPR;
-                        const size_t grow = erow + min(n0 + row, p.N - 1);          // rows past N copy the last row; never stored
-                        cp_async_16(dstt + row * PITCH + col * 16,
-                                    reinterpret_cast<const char *>(p.w + grow * p.wpr) + static_cast<size_t>(sbk) * ROW_BYTES + col * 16);
-                    }
-                    const size_t grow = erow + min(n0 + srow, p.N - 1);
-                    const char *src = static_cast<const char *>(sarr ? p.biases : p.scales) + (grow * p.gpr) * 2 +
-                                      static_cast<size_t>(sbk) * sb_bytes;
-                    const uint32_t d = dstt + BMW * PITCH + sarr * (BMW * 16) + srow * 16;
-                    if (sb_bytes == 16) cp_async_16(d, src);
-                    else if (sb_bytes == 8) cp_async_small<8>(d, src);
-                    else cp_async_small<4>(d, src);
+                for (int c = 0; c < BITS; ++c) {
+                    const int ch = c * DEQ_THREADS + t, row = ch / CPR, col = ch - row * CPR;
+                    const size_t grow = erow + min(n0 + row, p.N - 1);          // rows past N copy the last row; never stored
+                    cp_async_16(dstt + row * PITCH + col * 16,
+                                reinterpret_cast<const char *>(p.w + grow * p.wpr) + static_cast<size_t>(sbk) * ROW_BYTES + col * 16);
                 }
+                const size_t grow = erow + min(n0 + srow, p.N - 1);
+                const char *src = static_cast<const char *>(sarr ? p.biases : p.scales) + (grow * p.gpr) * 2 +
+                                  static_cast<size_t>(sbk) * sb_bytes;
+                const uint32_t d = dstt + BMW * PITCH + sarr * (BMW * 16) + srow * 16;
+                if (sb_bytes == 16) cp_async_16(d, src);
+                else if (sb_bytes == 8) cp_async_small<8>(d, src);
+                else cp_async_small<4>(d, src);
             };
             // request stream: (item, super-block) pairs in processing order
             int i_n = blockIdx.x, sb_n = 0;
@@ -634,25 +616,22 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                     for (int j = 0; j < SB_PER_RAW; ++j) {
                         if (!(ok = mbar_wait_warp(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x401, 0))) break;
                         const int g = (j * BK + h * 32) >> p.gs_shift;       // group within the super-block
-#pragma unroll
-                        for (int tt = 0; tt < 2; ++tt) {
-                            if (tt < item.nt) {
-                                const uint32_t base = raw0 + buf * buf_bytes + tt * p.raw_tile;
-                                uint32_t wv[BITS];
-                                lds_words<BITS>(base + r * PITCH + (2 * j + h) * (4 * BITS), wv);
-                                unsigned short sr, br;
-                                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sr) : "r"(base + BMW * PITCH + r * 16 + g * 2));
-                                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(br) : "r"(base + BMW * PITCH + BMW * 16 + r * 16 + g * 2));
-                                float sc, bi;
-                                if (p.sb_dt == MTC_F16) {
-                                    sc = __half2float(__ushort_as_half(sr));
-                                    bi = __half2float(__ushort_as_half(br));
-                                } else {
-                                    sc = __uint_as_float(static_cast<uint32_t>(sr) << 16);
-                                    bi = __uint_as_float(static_cast<uint32_t>(br) << 16);
-                                }
-                                dequant_half<BITS>(wv, sc, bi, dst, s * w_stage + tt * A_BYTES);
+                        {
+                            const uint32_t base = raw0 + buf * buf_bytes;
+                            uint32_t wv[BITS];
+                            lds_words<BITS>(base + r * PITCH + (2 * j + h) * (4 * BITS), wv);
+                            unsigned short sr, br;
+                            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sr) : "r"(base + BMW * PITCH + r * 16 + g * 2));
+                            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(br) : "r"(base + BMW * PITCH + BMW * 16 + r * 16 + g * 2));
+                            float sc, bi;
+                            if (p.sb_dt == MTC_F16) {
+                                sc = __half2float(__ushort_as_half(sr));
+                                bi = __half2float(__ushort_as_half(br));
+                            } else {
+                                sc = __uint_as_float(static_cast<uint32_t>(sr) << 16);
+                                bi = __uint_as_float(static_cast<uint32_t>(br) << 16);
                             }
+                            dequant_half<BITS>(wv, sc, bi, dst, s * w_stage);
                         }
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> async proxy (MMA)
                         __syncwarp();
@@ -668,60 +647,40 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
         } else
         for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x) {
             const Item item = get_item(p, i);
-            bool valid[2];
-            const uint32_t *wrow[2];
-            const unsigned short *sc16[2], *bi16[2];
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {
-                const int n = (item.n_tile + t) * BMW + r;
-                valid[t] = t < item.nt && n < p.N;
-                const size_t grow = static_cast<size_t>(item.expert) * p.N + (valid[t] ? n : 0);
-                wrow[t] = p.w + grow * p.wpr + h * BITS;
-                sc16[t] = static_cast<const unsigned short *>(p.scales) + grow * p.gpr;
-                bi16[t] = static_cast<const unsigned short *>(p.biases) + grow * p.gpr;
-            }
-            uint32_t wnext[2][BITS];
-            uint32_t sn[2] = {0, 0}, bn[2] = {0, 0};       // raw 16-bit scale / bias, converted when used
+            const int n = item.n_tile * BMW + r;
+            const bool valid = n < p.N;
+            const size_t grow = static_cast<size_t>(item.expert) * p.N + (valid ? n : 0);
+            const uint32_t *wrow = p.w + grow * p.wpr + h * BITS;
+            const unsigned short *sc16 = static_cast<const unsigned short *>(p.scales) + grow * p.gpr;
+            const unsigned short *bi16 = static_cast<const unsigned short *>(p.biases) + grow * p.gpr;
+            uint32_t wnext[BITS];
+            uint32_t sn = 0, bn = 0;                       // raw 16-bit scale / bias, converted when used
             auto request = [&](int kb) {
-#pragma unroll
-                for (int t = 0; t < 2; ++t) {
-                    if (t < item.nt) {
-                        load_half_words<BITS>(wrow[t] + static_cast<size_t>(kb) * (2 * BITS), wnext[t], valid[t]);
-                        if (valid[t]) {
-                            const int g = (kb * BK + h * 32) >> p.gs_shift;
-                            sn[t] = __ldg(sc16[t] + g);
-                            bn[t] = __ldg(bi16[t] + g);
-                        }
-                    }
+                load_half_words<BITS>(wrow + static_cast<size_t>(kb) * (2 * BITS), wnext, valid);
+                if (valid) {
+                    const int g = (kb * BK + h * 32) >> p.gs_shift;
+                    sn = __ldg(sc16 + g);
+                    bn = __ldg(bi16 + g);
                 }
             };
             request(0);
             for (int kb = 0; kb < num_kb; ++kb) {
-                uint32_t wcur[2][BITS];
-                uint32_t sr[2], br[2];
+                uint32_t wcur[BITS];
 #pragma unroll
-                for (int t = 0; t < 2; ++t) {
-#pragma unroll
-                    for (int j = 0; j < BITS; ++j) wcur[t][j] = wnext[t][j];
-                    sr[t] = sn[t]; br[t] = bn[t];
-                }
+                for (int j = 0; j < BITS; ++j) wcur[j] = wnext[j];
+                const uint32_t sr = sn, br = bn;
                 if (kb + 1 < num_kb) request(kb + 1);      // the next k block is requested before this one is converted
                 // the stage is free once empty[s] has completed (the producer waits on the same barrier)
                 if (!(ok = mbar_wait_warp(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x401, 0))) break;
-#pragma unroll
-                for (int t = 0; t < 2; ++t) {
-                    if (t < item.nt) {
-                        float sc, bi;
-                        if (p.sb_dt == MTC_F16) {
-                            sc = __half2float(__ushort_as_half(static_cast<unsigned short>(sr[t])));
-                            bi = __half2float(__ushort_as_half(static_cast<unsigned short>(br[t])));
-                        } else {
-                            sc = __uint_as_float(sr[t] << 16);
-                            bi = __uint_as_float(br[t] << 16);
-                        }
-                        dequant_half<BITS>(wcur[t], sc, bi, dst, s * w_stage + t * A_BYTES);
-                    }
+                float sc, bi;
+                if (p.sb_dt == MTC_F16) {
+                    sc = __half2float(__ushort_as_half(static_cast<unsigned short>(sr)));
+                    bi = __half2float(__ushort_as_half(static_cast<unsigned short>(br)));
+                } else {
+                    sc = __uint_as_float(sr << 16);
+                    bi = __uint_as_float(br << 16);
                 }
+                dequant_half<BITS>(wcur, sc, bi, dst, s * w_stage);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> async proxy (MMA)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ctl->full[s]);
@@ -896,15 +855,15 @@ cudaError_t make_x_map(CUtensorMap *tmap, const void *x, int rows, int K, int TN
     return cudaSuccess;
 }
 
-// Ring depth and raw staging buffers for p.TN / p.pair.  The raw path needs whole super-blocks (K % 256 == 0), 4 to 16
+// Ring depth and raw staging buffers for p.TN / p.wide.  The raw path needs whole super-blocks (K % 256 == 0), 4 to 16
 // bytes of scales per row and super-block (group 32, 64 or 128) and 16-byte aligned scale / bias arrays; it takes
 // two buffers per weight tile out of the ring, which costs nothing: measured, a ring deeper than 2 stages does not
 // change the time of any shape.
 void plan_smem(QmmParams &p, Ctx *ctx, int bits) {
-    const int stage = (p.pair ? 2 : 1) * A_BYTES + (p.wide ? 2 : 1) * p.TN * BK * 2;
+    const int stage = A_BYTES + (p.wide ? 2 : 1) * p.TN * BK * 2;
     const auto al16 = [](const void *ptr) { return reinterpret_cast<uintptr_t>(ptr) % 16 == 0; };
     p.raw_tile = static_cast<uint32_t>(BMW * (32 * bits + 16) + RAW_SB_BYTES);
-    const int raw_total = 2 * (p.pair ? 2 : 1) * static_cast<int>(p.raw_tile);
+    const int raw_total = 2 * static_cast<int>(p.raw_tile);
     p.raw = ctx->qmm_raw != 0 && p.K % (SB_PER_RAW * BK) == 0 && p.gs_shift >= 5 && p.gs_shift <= 7 && al16(p.scales) &&
             al16(p.biases) && (RING_BYTES - raw_total) / stage >= 2;
     p.nst = (RING_BYTES - (p.raw ? raw_total : 0)) / stage;
@@ -932,7 +891,6 @@ void fill_common(QmmParams &p, Ctx *ctx, const void *w, const void *scales, cons
     p.wpr = K * bits / 32;
     p.gpr = K / group_size;
     p.TN = TN;
-    p.pair = 0;
     p.wide = 0;
     plan_smem(p, ctx, bits);
     p.hint_ns = static_cast<uint32_t>(ctx->qmm_wait_hint_ns);
@@ -995,22 +953,7 @@ cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const v
     p.m_chunks = (M + TN - 1) / TN;
     p.n_tiles = (N + BMW - 1) / BMW;
     const int sms = ctx->sm_count;
-    // Two adjacent weight-row tiles per item halve the activation traffic from L2 (one X stage feeds both) at
-    // the price of a 3-deep ring and no epilogue overlap; measured slower on B200 for the prefill shapes, so it
-    // is off unless asked for.
-    p.pair = (ctx->qmm_pair > 0 && p.n_tiles >= 2) ? 1 : 0;
-    if (p.pair) {
-        plan_smem(p, ctx, bits);
-        const int pairs = (p.n_tiles + 1) / 2;
-        const int pair_units = pairs * p.m_chunks;
-        // whole waves of pairs; the rest as single tiles (whole pair rows of m_chunks items stay together)
-        int full_units = (pair_units / sms) * sms;
-        full_units = (full_units / p.m_chunks) * p.m_chunks;
-        p.pair_items = full_units;
-        const int tiles_done = (full_units / p.m_chunks) * 2;
-        const int tiles_left = p.n_tiles > tiles_done ? p.n_tiles - tiles_done : 0;
-        p.dense_items = full_units + tiles_left * p.m_chunks;
-    } else {
+    {
         // Two token chunks per item: the dequantised W stage, which sets the pace of a k block, is built once per
         // 2 TN token rows instead of once per TN.
         if (ctx->qmm_wide && TN == TN_MAX && M > TN_MAX) {
@@ -1023,8 +966,7 @@ cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const v
                 p.m_chunks = (M + 2 * TN - 1) / (2 * TN);
             }
         }
-        p.pair_items = p.n_tiles * p.m_chunks;
-        p.dense_items = p.pair_items;
+        p.dense_items = p.n_tiles * p.m_chunks;
         if (p.wide) {
             // a k block costs the same whatever the token count, so the leftover of the last round is cheaper as
             // single-chunk items on twice as many SMs - when those still fit in one round and every unit has two halves

@@ -744,10 +744,6 @@ int mtc_set_option(mtc_ctx *ctx, const char *name, int value) {
         ctx->qmm_wide = value ? 1 : 0;
         return MTC_OK;
     }
-    if (std::strcmp(name, "qmm_pair") == 0) {
-        ctx->qmm_pair = value ? 1 : 0;
-        return MTC_OK;
-    }
     return fail(ctx, MTC_ERR_UNSUPPORTED, std::string("unknown option: ") + name);
 }
 
