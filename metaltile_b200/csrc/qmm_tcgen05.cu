@@ -343,6 +343,15 @@ __device__ __forceinline__ void dequant_half(const uint32_t (&w)[BITS], float s,
     }
 }
 
+// 16-bit scale (or bias) of k block j (0..3) of a super-block for the thread's 32-code half h, out of the row's line:
+// group 32: entry 2j + h; group 64: entry j; group 128: entry j / 2.  j is a compile-time constant where this is used.
+__device__ __forceinline__ uint32_t sb_half(const uint4 &v, int j, int h, int gs_shift) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    if (gs_shift == 5) return (w[j] >> (16 * h)) & 0xFFFFu;
+    if (gs_shift == 6) return (w[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
+    return (w[0] >> (16 * ((j >> 1) & 1))) & 0xFFFFu;
+}
+
 struct Item {
     int n_tile, expert, row0, rows;
     int nc;                                 // token chunks of TN rows covered (1 or 2): one accumulator each
@@ -612,17 +621,22 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                     }
                     if (i_n < num_items) issue(item_n, sb_n, buf ^ 1);
                     asm volatile("cp.async.commit_group;" ::: "memory");
+                    // the row's scales and biases of the whole super-block: one 16-byte load each (4, 8 or 16 bytes are in use)
+                    uint4 sline, bline;
+                    {
+                        const uint32_t sb_addr = raw0 + buf * buf_bytes + BMW * PITCH + r * 16;
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(sline.x), "=r"(sline.y), "=r"(sline.z), "=r"(sline.w) : "r"(sb_addr));
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(bline.x), "=r"(bline.y), "=r"(bline.z), "=r"(bline.w) : "r"(sb_addr + BMW * 16));
+                    }
 #pragma unroll
                     for (int j = 0; j < SB_PER_RAW; ++j) {
                         if (!(ok = mbar_wait_warp(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x401, 0))) break;
-                        const int g = (j * BK + h * 32) >> p.gs_shift;       // group within the super-block
                         {
                             const uint32_t base = raw0 + buf * buf_bytes;
                             uint32_t wv[BITS];
                             lds_words<BITS>(base + r * PITCH + (2 * j + h) * (4 * BITS), wv);
-                            unsigned short sr, br;
-                            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(sr) : "r"(base + BMW * PITCH + r * 16 + g * 2));
-                            asm volatile("ld.shared.u16 %0, [%1];" : "=h"(br) : "r"(base + BMW * PITCH + BMW * 16 + r * 16 + g * 2));
+                            const unsigned short sr = static_cast<unsigned short>(sb_half(sline, j, h, p.gs_shift));
+                            const unsigned short br = static_cast<unsigned short>(sb_half(bline, j, h, p.gs_shift));
                             float sc, bi;
                             if (p.sb_dt == MTC_F16) {
                                 sc = __half2float(__ushort_as_half(sr));
