@@ -166,6 +166,15 @@ int mtc_chain_is_fused(const mtc_chain *chain);
  * 0x601 + the rank that never arrived and the kernel returns. */
 int mtc_qmv_multi(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x,
                   void *const *outs, int n_outs, int M, int N, int K, int bits, int group_size, int dtype);
+/* ffai_rms_norm_qgemv / _fast (crates/metaltile-std/src/ffai/rms_norm_qgemv.rs:51-107,131-146): the decode projection
+ * of the RMS-normalised activation in one launch,
+ *     out[n] = sum_k w(n, k) * (x[k] * norm_weight[k] * inv_rms),   inv_rms = 1 / sqrt(mean(x^2) + eps),
+ * x, norm_weight T[K]; the normalised activation stays in f32 (it is staged in shared memory, never rounded to T and
+ * never written to global memory), as in the reference.  Shapes the fused kernel does not take (unaligned pointers,
+ * groups that are not a power of two, K too long for one shared-memory stage) are normalised into a row of type T
+ * first and then run through mtc_qmv. */
+int mtc_rms_norm_qmv(mtc_ctx *ctx, void *stream, const void *x, const void *norm_weight, float eps, const void *w,
+                     const void *scales, const void *biases, void *out, int N, int K, int bits, int group_size, int dtype);
 /* mtc_qmm whose [M, N] result is a column block of wider row-major matrices, written to 1 to 8 destinations (no
  * counterpart in the reference): outs[i] points at row 0 of the block inside destination i, ld = elements between
  * consecutive rows of a destination (>= N).  With the peers' mappings of one [M, N_total] buffer per rank (mtc_ipc_*) as

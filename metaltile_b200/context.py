@@ -184,6 +184,10 @@ class Context:
         self._check(self._lib.mtc_qmv_multi(self._h, stream, w, scales, biases, x, arr, len(outs), M, N, K, bits,
                                             group_size, _dt(dtype)))
 
+    def rms_norm_qmv(self, x, norm_weight, eps, w, scales, biases, out, N, K, bits, group_size, dtype, stream: int = 0):
+        self._check(self._lib.mtc_rms_norm_qmv(self._h, stream, x, norm_weight, float(eps), w, scales, biases, out, N, K, bits,
+                                               group_size, _dt(dtype)))
+
     def qmm_multi(self, w, scales, biases, x, outs, ld, M, N, K, bits, group_size, dtype, stream: int = 0):
         """qmm whose [M, N] result is a column block (row stride ``ld`` elements) of every destination in ``outs``."""
         arr = (ctypes.c_void_p * len(outs))(*[int(o) for o in outs])

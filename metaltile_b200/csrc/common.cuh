@@ -46,6 +46,8 @@ struct Ctx {
     void *d_gfrag = nullptr;       // streaming gather: activations in fragment order, their sums, the table of passes (grow-only)
     size_t gfrag_bytes = 0;
     int gather_stream = 1;         // option "gather_stream": 0 = grouped products never take the streaming kernel (gather_stream.cu)
+    void *d_norm = nullptr;        // mtc_rms_norm_qmv on shapes the fused kernel does not take: the normalised row (grow-only)
+    size_t norm_bytes = 0;
     void *d_moe = nullptr;         // mtc_moe_experts: gate and up outputs (and permuted rows on the composed path) (grow-only)
     size_t moe_bytes = 0;
 };
@@ -128,7 +130,9 @@ __device__ __forceinline__ uint32_t code_at(const uint32_t *row, uint32_t k, int
 // Launchers implemented per .cu file; all return cudaError_t from the launch.
 cudaError_t launch_qmv(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases,
                        const void *x, void *out, int M, int N, int K, int bits, int group_size, int dt,
-                       std::string *why, void *const *extra_outs = nullptr, int n_extra = 0);
+                       std::string *why, void *const *extra_outs = nullptr, int n_extra = 0, const void *norm_w = nullptr,
+                       float eps = 0.0f);
+cudaError_t launch_rms_norm_row(cudaStream_t st, const void *x, const void *norm_w, void *out, int K, float eps, int dt);
 // all ranks have stored: one flag per peer, written with system-scope release, awaited with a bounded poll
 cudaError_t launch_peer_barrier(Ctx *ctx, cudaStream_t st, uint32_t *const *peer_flags, int n_peers, int rank,
                                 uint32_t *local_flags, uint32_t *epoch);

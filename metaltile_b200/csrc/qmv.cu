@@ -56,6 +56,10 @@ struct QmvArgs {
     int ksplit;        // warps sharing one row group
     int groups, iters; // row groups (ceil(N/R)), row-group iterations per CTA slot
     int gpc;           // consecutive row groups owned by one CTA (its weights are one contiguous range)
+    // fused RMSNorm (ffai_rms_norm_qgemv, crates/metaltile-std/src/ffai/rms_norm_qgemv.rs:51-107; M = 1): the staged
+    // activation is x[k] * norm_w[k] * inv_rms in f32, inv_rms = rsqrt(mean(x^2) + eps); null = plain x
+    const void *norm_w;
+    float eps;
 };
 
 // Further copies of the output tile (peer GPUs' buffers: the all-gather is the store).  A second kernel parameter of
@@ -93,8 +97,39 @@ __device__ __forceinline__ float comp(const float4 &v, int i) {
 //          ((jb * V + vv) * (CODES*MT/4) + (i*MT+m)/4) * 32 + ln, component (i*MT+m)%4,
 //          value x[m, k] * 2^(kPreExp - (i % CPW) * BITS);
 //   xsum : plain sum of the base chunk's x values, at ((jb*32 + ln) * V + vv) * MT + m.
+// CODES consecutive elements of a T array (f32, f16 or bf16; 16-byte aligned position) as f32.
+template <int CODES>
+__device__ __forceinline__ void load_vals(const void *src, size_t base, int dt, float (&v)[CODES]) {
+    if (dt == MTC_F32) {
+        const float4 *p = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(src) + base);
+#pragma unroll
+        for (int q = 0; q < CODES / 4; ++q) {
+            float4 t = __ldg(p + q);
+            v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
+        }
+    } else {
+        const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(src) + base);
+#pragma unroll
+        for (int q = 0; q < CODES / 8; ++q) {
+            uint4 t = __ldg(p + q);
+            uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                if (dt == MTC_BF16) {
+                    v[8 * q + 2 * h] = __uint_as_float(u[h] << 16);
+                    v[8 * q + 2 * h + 1] = __uint_as_float(u[h] & 0xFFFF0000u);
+                } else {
+                    float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&u[h]));
+                    v[8 * q + 2 * h] = f.x;
+                    v[8 * q + 2 * h + 1] = f.y;
+                }
+            }
+        }
+    }
+}
+
 template <int BITS, int MT, int V>
-__device__ __forceinline__ void stage_x(const QmvArgs &a, float *xs, float *xsum, int chunk0, int nch) {
+__device__ __forceinline__ void stage_x(const QmvArgs &a, float *xs, float *xsum, int chunk0, int nch, float inv_rms = 1.0f) {
     using P = Pack<BITS>;
     constexpr int E4 = P::CODES * MT / 4;   // float4 per base chunk
     for (int t = threadIdx.x; t < nch * MT; t += blockDim.x) {
@@ -106,32 +141,12 @@ __device__ __forceinline__ void stage_x(const QmvArgs &a, float *xs, float *xsum
         {
             float v[P::CODES];
             if (m < a.M) {
-                const size_t base = static_cast<size_t>(m) * a.K + k0;
-                if (a.dt == MTC_F32) {
-                    const float4 *p = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(a.x) + base);
+                load_vals<P::CODES>(a.x, static_cast<size_t>(m) * a.K + k0, a.dt, v);
+                if (a.norm_w) {
+                    float nw[P::CODES];
+                    load_vals<P::CODES>(a.norm_w, k0, a.dt, nw);
 #pragma unroll
-                    for (int q = 0; q < P::CODES / 4; ++q) {
-                        float4 t = __ldg(p + q);
-                        v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
-                    }
-                } else {
-                    const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(a.x) + base);
-#pragma unroll
-                    for (int q = 0; q < P::CODES / 8; ++q) {
-                        uint4 t = __ldg(p + q);
-                        uint32_t u[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-                        for (int h = 0; h < 4; ++h) {
-                            if (a.dt == MTC_BF16) {
-                                v[8 * q + 2 * h] = __uint_as_float(u[h] << 16);
-                                v[8 * q + 2 * h + 1] = __uint_as_float(u[h] & 0xFFFF0000u);
-                            } else {
-                                float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&u[h]));
-                                v[8 * q + 2 * h] = f.x;
-                                v[8 * q + 2 * h + 1] = f.y;
-                            }
-                        }
-                    }
+                    for (int i = 0; i < P::CODES; ++i) v[i] = v[i] * nw[i] * inv_rms;
                 }
             } else {
 #pragma unroll
@@ -347,7 +362,24 @@ __global__ void __launch_bounds__(256, (MT <= 2 ? 2 : 1)) qmv_pipe_kernel(const 
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    stage_x<BITS, MT, V>(a, xs, xsum, 0, a.nchunks);
+    float inv_rms = 1.0f;
+    if (a.norm_w) {
+        // sum of squares of the (single) activation row over the CTA, then every thread holds inv_rms
+        float ssq = 0.0f;
+        for (int k = threadIdx.x; k < a.K; k += blockDim.x) {
+            const float v = ld_as_f32(a.x, static_cast<size_t>(k), a.dt);
+            ssq = fmaf(v, v, ssq);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+        if (lane == 0) red[warp] = ssq;
+        __syncthreads();
+        float tot = 0.0f;
+        for (int wi = 0; wi < nwarps; ++wi) tot += red[wi];
+        inv_rms = 1.0f / sqrtf(tot / static_cast<float>(a.K) + a.eps);
+        __syncthreads();                 // `red` is free again before the row-group sums use it
+    }
+    stage_x<BITS, MT, V>(a, xs, xsum, 0, a.nchunks, inv_rms);
     __syncthreads();
 
     float acc[R][MT], accb[R][MT];
@@ -572,6 +604,7 @@ cudaError_t launch_tile(Ctx *ctx, cudaStream_t st, QmvArgs a, const QmvTail<true
     const size_t per_jb = (static_cast<size_t>(32) * P::CODES * MT + 32 * MT) * sizeof(float);  // per 32 base chunks
     const size_t red_bytes = static_cast<size_t>(kWarps) * kRows * MT * sizeof(float);
     const size_t whole_k = per_jb * ((a.nchunks + 31) / 32 + 1) + red_bytes;
+    if (a.norm_w && (MT != 1 || whole_k > kSmemPipe)) return cudaErrorNotSupported;   // fused RMSNorm: M = 1, whole K staged
     if (whole_k <= kSmemPipe) {
         if (V > 1 && a.nchunks % V == 0 && a.gs >= V * P::CODES) return launch_pipe<BITS, MT, V>(ctx, st, a, per_jb, red_bytes, tail);
         return launch_pipe<BITS, MT, 1>(ctx, st, a, per_jb, red_bytes, tail);
@@ -637,7 +670,7 @@ cudaError_t qmv_init_device() {
 
 cudaError_t launch_qmv(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases,
                        const void *x, void *out, int M, int N, int K, int bits, int group_size, int dt,
-                       std::string *why, void *const *extra_outs, int n_extra) {
+                       std::string *why, void *const *extra_outs, int n_extra, const void *norm_w, float eps) {
     if (n_extra < 0 || n_extra > kMaxPeers - 1 || (n_extra > 0 && !extra_outs)) {
         if (why) *why = "qmv: at most 8 output copies";
         return cudaErrorInvalidValue;
@@ -660,6 +693,7 @@ cudaError_t launch_qmv(Ctx *ctx, cudaStream_t st, const void *w, const void *sca
         if (why) *why = "qmv with several outputs needs the vectorised path (power-of-two group, aligned pointers)";
         return cudaErrorInvalidValue;
     }
+    if (norm_w && (!fast || M != 1 || !aligned(norm_w, 16))) return cudaErrorNotSupported;   // the caller normalises separately
     if (!fast) {
         const int wpb = 8;
         qmv_generic_kernel<<<(N + wpb - 1) / wpb, wpb * 32, 0, st>>>(
@@ -686,6 +720,8 @@ cudaError_t launch_qmv(Ctx *ctx, cudaStream_t st, const void *w, const void *sca
         a.dt = dt;
         a.wpr = K * bits / 32;
         a.gpr = K / group_size;
+        a.norm_w = norm_w;
+        a.eps = eps;
         cudaError_t e;
         switch (bits) {
             case 2: e = launch_bits<2>(ctx, st, a, tp); break;
@@ -695,11 +731,37 @@ cudaError_t launch_qmv(Ctx *ctx, cudaStream_t st, const void *w, const void *sca
             case 6: e = launch_bits<6>(ctx, st, a, tp); break;
             default: e = launch_bits<8>(ctx, st, a, tp); break;
         }
+        if (e == cudaErrorNotSupported && norm_w) return e;
         if (e == cudaErrorNotSupported && why) *why = "qmv with several outputs: M = 1 with the whole K staged in shared memory only";
         if (e == cudaErrorNotSupported) return cudaErrorInvalidValue;
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;
+}
+
+// x * norm_w * inv_rms of one row, rounded to the activation type: the unfused form for shapes the fused kernel does not take
+__global__ void __launch_bounds__(256) rms_norm_row_kernel(const void *x, const void *norm_w, void *out, int K, float eps, int dt) {
+    __shared__ float red[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float ssq = 0.0f;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+        const float v = ld_as_f32(x, static_cast<size_t>(k), dt);
+        ssq = fmaf(v, v, ssq);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+    if (lane == 0) red[warp] = ssq;
+    __syncthreads();
+    float tot = 0.0f;
+    for (int wi = 0; wi < 8; ++wi) tot += red[wi];
+    const float inv_rms = 1.0f / sqrtf(tot / static_cast<float>(K) + eps);
+    for (int k = threadIdx.x; k < K; k += blockDim.x)
+        st_from_f32(out, static_cast<size_t>(k), ld_as_f32(x, static_cast<size_t>(k), dt) * ld_as_f32(norm_w, static_cast<size_t>(k), dt) * inv_rms, dt);
+}
+
+cudaError_t launch_rms_norm_row(cudaStream_t st, const void *x, const void *norm_w, void *out, int K, float eps, int dt) {
+    rms_norm_row_kernel<<<1, 256, 0, st>>>(x, norm_w, out, K, eps, dt);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_unpack_codes(cudaStream_t st, const void *w, void *codes, int N, int K, int bits) {

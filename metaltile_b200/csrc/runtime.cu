@@ -46,7 +46,7 @@ bool dtype_ok(int dt) { return dt == MTC_F32 || dt == MTC_F16 || dt == MTC_BF16;
 // "gs_per_row" (hand-tuned int4/int8/mma kernels: group_size = k / gs_per_row) or
 // "group_size" (generic _b* family).  has_n: whether an `n` constexpr is bound
 // (mt_qmv / mt_qmv_int8_fast take N from the size of `out`).
-enum Family { DENSE_QMV, DENSE_QMM, GATHER_CSR, GATHER_IDX, ROUTER_TOPK, MOE_PERMUTE, MOE_UNPERMUTE, SWIGLU, BATCHED_QKV, BATCHED_4 };
+enum Family { DENSE_QMV, DENSE_QMM, GATHER_CSR, GATHER_IDX, ROUTER_TOPK, MOE_PERMUTE, MOE_UNPERMUTE, SWIGLU, BATCHED_QKV, BATCHED_4, RMS_QMV };
 struct KernelRow {
     const char *name;
     Family family;
@@ -89,6 +89,9 @@ const KernelRow kKernels[] = {
     {"ffai_batched_qkv_qgemv", BATCHED_QKV, 4, "group_size", false},
     {"ffai_batched_qkv_qgemv_fast", BATCHED_QKV, 4, "group_size", false},
     {"ffai_batched_4_qgemv_fast", BATCHED_4, 4, "group_size", false},
+    // RMSNorm fused into the decode projection: crates/metaltile-std/src/ffai/rms_norm_qgemv.rs:51-107,131-146
+    {"ffai_rms_norm_qgemv", RMS_QMV, 4, "group_size", false},
+    {"ffai_rms_norm_qgemv_fast", RMS_QMV, 4, "group_size", false},
     // MoE: crates/metaltile-std/src/ffai/moe.rs:65,222,283 (routing), :358,602-605,634,900,1363 (CSR gather),
     // :2256,2832-2835,2857,3231 (per-row-index gather); crates/metaltile-std/src/mlx/swiglu.rs:45
     {"mt_moe_router_topk", ROUTER_TOPK, -1, "", false},
@@ -242,6 +245,7 @@ int mtc_destroy(mtc_ctx *ctx) {
     if (ctx->d_xconv) cudaFree(ctx->d_xconv);
     if (ctx->d_gfrag) cudaFree(ctx->d_gfrag);
     if (ctx->d_moe) cudaFree(ctx->d_moe);
+    if (ctx->d_norm) cudaFree(ctx->d_norm);
     if (ctx->d_tc_scratch) cudaFree(ctx->d_tc_scratch);
     if (ctx->d_tc_counters) cudaFree(ctx->d_tc_counters);
     for (void *p : ctx->retired) cudaFree(p);
@@ -667,6 +671,29 @@ int mtc_qmm(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
     return mtc_qmv(ctx, stream, w, scales, biases, x, out, M, N, K, bits, group_size, dtype);
 }
 
+int mtc_rms_norm_qmv(mtc_ctx *ctx, void *stream, const void *x, const void *norm_weight, float eps, const void *w,
+                     const void *scales, const void *biases, void *out, int N, int K, int bits, int group_size, int dtype) {
+    if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "rms_norm_qmv: dtype must be f32, f16 or bf16");
+    if (N < 0 || K <= 0) return fail(ctx, MTC_ERR_INVALID, "rms_norm_qmv: sizes must be positive");
+    if (N == 0) return MTC_OK;
+    if (!x || !norm_weight || !w || !scales || !biases || !out) return fail(ctx, MTC_ERR_INVALID, "rms_norm_qmv: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    std::string why;
+    cudaError_t e = mtc::launch_qmv(ctx, st, w, scales, biases, x, out, 1, N, K, bits, group_size, dtype, &why, nullptr, 0, norm_weight, eps);
+    if (e == cudaSuccess) return MTC_OK;
+    if (e != cudaErrorNotSupported)
+        return fail(ctx, e == cudaErrorInvalidValue ? MTC_ERR_UNSUPPORTED : MTC_ERR_DISPATCH,
+                    "rms_norm_qmv launch: " + (why.empty() ? std::string(cudaGetErrorString(e)) : why));
+    // shapes the fused kernel does not take (unaligned pointers, odd groups, K too long for one stage): normalise into a
+    // row of the activation type, then the plain product
+    e = mtc::grow_block(ctx, st, &ctx->d_norm, &ctx->norm_bytes, static_cast<size_t>(K) * mtc::dtype_size(dtype), &why);
+    if (e != cudaSuccess) return fail(ctx, MTC_ERR_BUFFER, "rms_norm_qmv staging: " + (why.empty() ? std::string(cudaGetErrorString(e)) : why));
+    MTC_CUDA(ctx, mtc::launch_rms_norm_row(st, x, norm_weight, ctx->d_norm, K, eps, dtype), MTC_ERR_DISPATCH);
+    return mtc_qmv(ctx, stream, w, scales, biases, ctx->d_norm, out, 1, N, K, bits, group_size, dtype);
+}
+
 int mtc_qmm_multi(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x,
                   void *const *outs, int n_outs, long long ld, int M, int N, int K, int bits, int group_size, int dtype) {
     if (!ctx) return MTC_ERR_INVALID;
@@ -1002,6 +1029,7 @@ int dispatch_pass(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_bu
         if (!read_const(bufs, n_bufs, name, v) && err.empty()) err = kn + ": constexpr " + name + " missing";
     };
     st_bufs.reserve(20);
+    float rms_eps = 0.0f;
     int nb = 0;                          // fused decode projections: count, rows of each, buffer names of each
     uint32_t b_out[4] = {0, 0, 0, 0};
     std::string b_names[4][4];
@@ -1081,6 +1109,23 @@ int dispatch_pass(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_bu
                 sum += b_out[i];
             }
             if (qkv) need_buf("out", sum * esz);
+            break;
+        }
+        case RMS_QMV: {
+            need_const("in_dim", &k);
+            need_const("group_size", &gs);
+            if (!err.empty()) break;
+            mtc_named_buf *bo = find_buf(bufs, n_bufs, "output"), *be = find_buf(bufs, n_bufs, "eps_buf");
+            if (!bo || !be || !be->data || be->bytes < 4) { err = kn + ": buffers x, norm_weight, weight, scales, biases, output, eps_buf must be bound"; break; }
+            if (k == 0 || gs == 0 || k % gs != 0 || k % 8 != 0) return fail(ctx, MTC_ERR_UNSUPPORTED, kn + ": need group_size | in_dim and in_dim % 8 == 0");
+            n = static_cast<uint32_t>(bo->bytes / esz);
+            std::memcpy(&rms_eps, be->data, 4);
+            need_buf("x", static_cast<size_t>(k) * esz);
+            need_buf("norm_weight", static_cast<size_t>(k) * esz);
+            need_buf("weight", static_cast<size_t>(n) * k / 2);
+            need_buf("scales", static_cast<size_t>(n) * (k / gs) * esz);
+            need_buf("biases", static_cast<size_t>(n) * (k / gs) * esz);
+            need_buf("output", static_cast<size_t>(n) * esz);
             break;
         }
         case ROUTER_TOPK: {
@@ -1223,6 +1268,10 @@ int dispatch_pass(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_bu
             rc = mtc_qmv_batched(ctx, st, ds, nb);
             break;
         }
+        case RMS_QMV:
+            rc = mtc_rms_norm_qmv(ctx, st, dev("x"), dev("norm_weight"), rms_eps, dev("weight"), dev("scales"), dev("biases"), dev("output"),
+                                  static_cast<int>(n), static_cast<int>(k), 4, static_cast<int>(gs), dtype);
+            break;
         case ROUTER_TOPK:
             rc = mtc_moe_router_topk(ctx, st, dev("router_logits"), dev("indices_out"), dev("weights_out"), static_cast<int>(rows),
                                      static_cast<int>(n_exp), static_cast<int>(topk), static_cast<int>(norm), dtype);

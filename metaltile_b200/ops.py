@@ -227,3 +227,20 @@ def moe_experts(x, gate, up, down, bits: int, group_size: int, expert_offsets, s
                     ptr(down), expert_offsets.data_ptr(), out.data_ptr(), m_total, hidden, inter, n_experts, bits, group_size,
                     _TORCH_DT[x.dtype], stream=_stream())
     return out
+
+
+def rms_norm_qmv(w, scales, biases, x, norm_weight, eps: float, bits: int, group_size: int, out=None, ctx: Context = None):
+    """``qmv(rms_norm(x) * norm_weight)`` in one launch (``ffai_rms_norm_qgemv``,
+    crates/metaltile-std/src/ffai/rms_norm_qgemv.rs:51-107): x and norm_weight are vectors of length K, out [1, N]."""
+    k = x.numel()
+    n = w.shape[0]
+    if norm_weight.numel() != k or w.shape[1] * 32 != k * bits:
+        raise ValueError("x and norm_weight must have K elements and w must be [N, K*bits/32]")
+    if out is None:
+        out = torch.empty((1, n), dtype=x.dtype, device=x.device)
+    else:
+        _check_out(out, 1, n, x)
+    ctx = ctx or context(x.device)
+    ctx.rms_norm_qmv(x.data_ptr(), norm_weight.data_ptr(), eps, w.data_ptr(), scales.data_ptr(), biases.data_ptr(), out.data_ptr(),
+                     n, k, bits, group_size, _TORCH_DT[x.dtype], stream=_stream())
+    return out

@@ -184,5 +184,18 @@ def swiglu(gate, up) -> np.ndarray:
     return out
 
 
+def rms_normed(x, norm_weight, eps: float) -> np.ndarray:
+    """``x * norm_weight * inv_rms`` in f32 (crates/metaltile-std/tests/rms_norm_qgemv_gpu_correctness.rs:59-72)."""
+    xv, nw = _f32(x).reshape(-1), _f32(norm_weight).reshape(-1)
+    out = np.empty_like(xv)
+    lib().mto_rms_normed(_p(xv), _p(nw), _p(out), _sz(xv.size), ctypes.c_float(eps))
+    return out
+
+
+def rms_norm_qmv(w, scales, biases, x, norm_weight, eps, n, k, bits, group_size) -> np.ndarray:
+    """ffai_rms_norm_qgemv: the quantized product of the normalised activation, f32 accumulator [1, n]."""
+    return qmm(w, scales, biases, rms_normed(x, norm_weight, eps).reshape(1, k), 1, n, k, bits, group_size)
+
+
 def max_threads() -> int:
     return int(lib().mto_max_threads())

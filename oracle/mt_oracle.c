@@ -358,6 +358,18 @@ void mto_swiglu(const float *gate, const float *up, float *out, size_t n) {
     }
 }
 
+/* The normalised activation of ffai_rms_norm_qgemv, crates/metaltile-std/src/ffai/rms_norm_qgemv.rs:51-107, with the
+ * arithmetic of the reference's own CPU check (crates/metaltile-std/tests/rms_norm_qgemv_gpu_correctness.rs:59-90):
+ *   ssq = sum x[d]^2 (one f32 accumulator, d ascending);  inv_rms = 1 / sqrt(ssq / K + eps);
+ *   normed[d] = (x[d] * norm_weight[d]) * inv_rms      - f32, never rounded to the activation type.
+ * The fused product is then mto_qmm_rows on `normed` as a one-row x. */
+void mto_rms_normed(const float *x, const float *norm_weight, float *normed, size_t k, float eps) {
+    float ssq = 0.0f;
+    for (size_t d = 0; d < k; d++) ssq += x[d] * x[d];
+    float inv_rms = 1.0f / sqrtf(ssq / (float)k + eps);
+    for (size_t d = 0; d < k; d++) normed[d] = x[d] * norm_weight[d] * inv_rms;
+}
+
 int mto_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

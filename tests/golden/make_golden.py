@@ -25,6 +25,7 @@ Reference sources restated here
   swiglu setup ............... crates/metaltile-std/src/mlx/swiglu.rs:65-72
   batched q/k/v decode ....... crates/metaltile-std/tests/batched_qkv_qgemv_gpu_correctness.rs:30-127,167-181,312-321
   batched 4-way decode ....... crates/metaltile-std/src/ffai/batched_4_qgemv.rs:342-440
+  fused RMSNorm + decode ..... crates/metaltile-std/tests/rms_norm_qgemv_gpu_correctness.rs:35-177,232-294
 """
 from __future__ import annotations
 
@@ -272,6 +273,22 @@ def batched_case(dt, in_dim, gs, outs, seeds):
     return d
 
 
+def rms_norm_case(dt, in_dim, gs, out_dim, eps=1e-5):
+    """run_case / run_case_fast of crates/metaltile-std/tests/rms_norm_qgemv_gpu_correctness.rs:138-177,232-276 with the
+    CPU check `naive` (:59-90): normed = x * norm_weight * inv_rms in f32, inv_rms = 1 / sqrt(ssq / K + eps)."""
+    x = round_dt(xorshift_source(in_dim, 0xA1, 2.0, 0.1), dt)
+    nw = round_dt(xorshift_source(in_dim, 0xB2, 0.4, 1.0), dt)
+    codes, sc, bi = quantize_int4_matrix(xorshift_source(out_dim * in_dim, 0xC3, 3.0, 0.0), out_dim, in_dim, gs)
+    ssq = f32(0.0)
+    for v in x:
+        ssq = f32(ssq + f32(v * v))
+    inv_rms = f32(f32(1.0) / f32(np.sqrt(f32(f32(ssq / f32(in_dim)) + f32(eps)))))
+    normed = ((x * nw).astype(f32) * inv_rms).astype(f32)
+    acc = qmm_ref(codes, round_dt(sc, dt), round_dt(bi, dt), normed.reshape(1, in_dim), gs)
+    return dict(x=x, norm_weight=nw, w=pack_rows(codes, 4), scales=sc, biases=bi, normed=normed, acc=acc.reshape(-1),
+                eps=np.array([eps], dtype=np.float32), meta=np.array([in_dim, gs, out_dim]))
+
+
 def save_new(path, **arrays):
     """Write a fixture unless the file already holds exactly these arrays (keeps unchanged fixtures byte-stable)."""
     if os.path.exists(path):
@@ -289,6 +306,9 @@ def main():
                                    ("bf16", 512, 64, 16, 8)):
         save_new(os.path.join(HERE, f"batched_qkv_k{in_dim}_g{gs}_q{oq}_kv{ok}_{dt}.npz"),
                  **batched_case(dt, in_dim, gs, (oq, ok, ok), (0x22, 0x33, 0x44)))
+    for dt, in_dim, gs, od in (("f32", 256, 64, 8), ("f32", 512, 128, 6), ("f16", 256, 64, 8), ("bf16", 256, 64, 8),
+                               ("f32", 512, 64, 16), ("f16", 512, 64, 16), ("bf16", 512, 64, 16), ("f32", 1024, 64, 32)):
+        save_new(os.path.join(HERE, f"rms_norm_qgemv_k{in_dim}_g{gs}_n{od}_{dt}.npz"), **rms_norm_case(dt, in_dim, gs, od))
     for dt in ("f32", "f16", "bf16"):
         save_new(os.path.join(HERE, f"test_batched_4_qgemv_fast_{dt}.npz"),
                  **batched_case(dt, 512, 64, (16, 8, 8, 8), (0x22, 0x33, 0x44, 0x55)))

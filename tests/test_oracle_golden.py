@@ -173,3 +173,20 @@ def test_batched_decode_fixtures(path):
         assert codes.max() <= 15 and fx[f"w{i}"].shape == (n, in_dim // 8)
         acc = oracle.qmm(fx[f"w{i}"], s, b, fx["x"], 1, n, in_dim, 4, gs)
         assert np.array_equal(_bits(acc.reshape(-1)), _bits(fx[f"acc{i}"]))
+
+
+RMS = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "rms_norm_qgemv_*.npz")))
+
+
+@pytest.mark.parametrize("path", RMS, ids=[os.path.basename(p)[:-4] for p in RMS])
+def test_rms_norm_qgemv_fixtures(path):
+    """Fused RMSNorm + decode projection (rms_norm_qgemv_gpu_correctness.rs:59-90,138-177): the C oracle reproduces the
+    normalised activation and the accumulator bit for bit."""
+    fx = _load(path)
+    dt = DT[os.path.basename(path)[:-4].rsplit("_", 1)[1]]
+    in_dim, gs, n = (int(v) for v in fx["meta"])
+    eps = float(fx["eps"][0])
+    assert np.array_equal(_bits(oracle.rms_normed(fx["x"], fx["norm_weight"], eps)), _bits(fx["normed"]))
+    s, b = oracle.round_through(fx["scales"], dt), oracle.round_through(fx["biases"], dt)
+    acc = oracle.rms_norm_qmv(fx["w"], s, b, fx["x"], fx["norm_weight"], eps, n, in_dim, 4, gs)
+    assert np.array_equal(_bits(acc.reshape(-1)), _bits(fx["acc"]))

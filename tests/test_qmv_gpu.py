@@ -329,3 +329,42 @@ def test_error_behaviour(ctx):
         ctx.qmv(1, 1, 1, 1, 1, 1, 8, 64, 7, 64, "f32")
     assert ei.value.variant == "Unsupported"
     assert ctx.status_word() == 0
+
+
+RMS_CASES = [("ffai_rms_norm_qgemv", 256, 64, 8, "f32"), ("ffai_rms_norm_qgemv", 512, 128, 6, "f32"), ("ffai_rms_norm_qgemv", 256, 64, 8, "f16"),
+             ("ffai_rms_norm_qgemv", 256, 64, 8, "bf16"), ("ffai_rms_norm_qgemv_fast", 512, 64, 16, "f32"),
+             ("ffai_rms_norm_qgemv_fast", 512, 64, 16, "f16"), ("ffai_rms_norm_qgemv_fast", 512, 64, 16, "bf16"),
+             ("ffai_rms_norm_qgemv_fast", 1024, 64, 32, "f32")]
+
+
+@pytest.mark.parametrize("kernel,in_dim,gs,n,dt", RMS_CASES)
+def test_rms_norm_qgemv_via_dispatch(ctx, kernel, in_dim, gs, n, dt):
+    """The reference's own cases of the fused RMSNorm + decode projection under its kernel and buffer names
+    (crates/metaltile-std/tests/rms_norm_qgemv_gpu_correctness.rs:93-124,179-294), with its tolerances and this build's."""
+    fx = dict(np.load(os.path.join(GOLDEN, f"rms_norm_qgemv_k{in_dim}_g{gs}_n{n}_{dt}.npz")))
+    bufs = {"x": dt_bytes(fx["x"], dt), "norm_weight": dt_bytes(fx["norm_weight"], dt), "weight": fx["w"].tobytes(),
+            "scales": dt_bytes(fx["scales"], dt), "biases": dt_bytes(fx["biases"], dt), "output": bytes(n * (4 if dt == "f32" else 2)),
+            "eps_buf": fx["eps"].astype(np.float32).tobytes()}
+    res = ctx.dispatch_with_grid(kernel, bufs, {"in_dim": in_dim, "group_size": gs}, (n, 1, 1), (128, 1, 1), dtype=dt, outputs=("output",))
+    got = bytes_to_f32(res.outputs["output"], dt)
+    exp = fx["acc"]
+    assert np.any(got != 0.0)
+    ref_tol = {"f32": 5e-3, "f16": 2e-2, "bf16": 5e-2}[dt]
+    assert float(np.max(np.abs(got - exp) / np.maximum(np.abs(exp), 1e-3))) <= ref_tol
+    assert rel_err(got.reshape(1, -1), exp.reshape(1, -1)) <= TOL[dt]
+
+
+@pytest.mark.parametrize("n,k,gs,dt", [(4096, 4096, 64, "bf16"), (1024, 4096, 128, "f16"), (300, 2048, 64, "f32"), (64, 480, 96, "bf16")])
+def test_rms_norm_qmv_typed(ctx, n, k, gs, dt):
+    """mtc_rms_norm_qmv at decode sizes against the oracle (the normalised activation stays f32); the last case has a group
+    that is not a power of two: the unfused form (normalise into a row of the activation type, then the plain product)."""
+    import torch
+    from metaltile_b200 import ops, synth
+    w, s, b, x = dense_case(1, n, k, 4, gs, dt, seed=31)
+    nw = oracle.round_through(1.0 + 0.2 * synth.activations(1, k, seed=32), {"f32": oracle.F32, "f16": oracle.F16, "bf16": oracle.BF16}[dt])
+    eps = 1e-5
+    got = ops.rms_norm_qmv(to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt).reshape(-1), to_dev(nw, dt).reshape(-1), eps, 4, gs, ctx=ctx)
+    torch.cuda.synchronize()
+    ref = oracle.rms_norm_qmv(w, s, b, x.reshape(-1), nw.reshape(-1), eps, n, k, 4, gs)
+    assert ctx.status_word() == 0
+    assert rel_err(got.float().cpu().numpy(), ref) <= TOL[dt]
