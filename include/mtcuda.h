@@ -166,6 +166,18 @@ int mtc_chain_is_fused(const mtc_chain *chain);
  * 0x601 + the rank that never arrived and the kernel returns. */
 int mtc_qmv_multi(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x,
                   void *const *outs, int n_outs, int M, int N, int K, int bits, int group_size, int dtype);
+/* mt_affine_quantize_int{2,3,4,5,6,8} / mt_affine_dequantize_int{2,3,4,5,6,8} (crates/metaltile-std/src/mlx/quantized.rs:
+ * 3575-4214): the producer and the inverse of the packed format the matmuls read.
+ *   quantize:   w T[n_elem] -> out u32[n_elem * bits / 32] (LSB-first bit-stream, one per group), scales / biases T[n_elem / G]:
+ *               scale = (max - min) / (2^bits - 1) (1 when below 1e-7), bias = min,
+ *               q = trunc(clamp((v - bias) * (1 / scale) + 0.5, 0, 2^bits - 1))
+ *   dequantize: out T[n_elem] = scale * q + bias
+ * Every float operation is rounded to f32 on its own (no fused multiply-add): codes and values equal the scalar CPU
+ * formula bit for bit.  Whole groups only, group_size * bits % 32 == 0. */
+int mtc_affine_quantize(mtc_ctx *ctx, void *stream, const void *w, void *out, void *scales, void *biases, size_t n_elem, int bits,
+                        int group_size, int dtype);
+int mtc_affine_dequantize(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, void *out,
+                          size_t n_elem, int bits, int group_size, int dtype);
 /* ffai_rms_norm_qgemv / _fast (crates/metaltile-std/src/ffai/rms_norm_qgemv.rs:51-107,131-146): the decode projection
  * of the RMS-normalised activation in one launch,
  *     out[n] = sum_k w(n, k) * (x[k] * norm_weight[k] * inv_rms),   inv_rms = 1 / sqrt(mean(x^2) + eps),

@@ -71,6 +71,8 @@ SIGNATURES = {
     "mtc_qmm": (_i, _DENSE),
     "mtc_qmm_route": (ctypes.c_char_p, [_i, _i, _i, _i, _i, _i]),
     "mtc_qmv_multi": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i]),
+    "mtc_affine_quantize": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_size_t, _i, _i, _i]),
+    "mtc_affine_dequantize": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_size_t, _i, _i, _i]),
     "mtc_rms_norm_qmv": (_i, [_vp, _vp, _vp, _vp, ctypes.c_float, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i]),
     "mtc_qmm_multi": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_vp), _i, ctypes.c_longlong, _i, _i, _i, _i, _i, _i]),
     "mtc_qmv_batched": (_i, [_vp, _vp, ctypes.POINTER(QmvDesc), _i]),

@@ -184,6 +184,12 @@ class Context:
         self._check(self._lib.mtc_qmv_multi(self._h, stream, w, scales, biases, x, arr, len(outs), M, N, K, bits,
                                             group_size, _dt(dtype)))
 
+    def affine_quantize(self, w, out, scales, biases, n_elem, bits, group_size, dtype, stream: int = 0):
+        self._check(self._lib.mtc_affine_quantize(self._h, stream, w, out, scales, biases, n_elem, bits, group_size, _dt(dtype)))
+
+    def affine_dequantize(self, w, scales, biases, out, n_elem, bits, group_size, dtype, stream: int = 0):
+        self._check(self._lib.mtc_affine_dequantize(self._h, stream, w, scales, biases, out, n_elem, bits, group_size, _dt(dtype)))
+
     def rms_norm_qmv(self, x, norm_weight, eps, w, scales, biases, out, N, K, bits, group_size, dtype, stream: int = 0):
         self._check(self._lib.mtc_rms_norm_qmv(self._h, stream, x, norm_weight, float(eps), w, scales, biases, out, N, K, bits,
                                                group_size, _dt(dtype)))

@@ -190,6 +190,10 @@ struct GatherMats {
 cudaError_t launch_gather_stream(Ctx *ctx, cudaStream_t st, const void *x, const void *x2, const uint32_t *row_src, int n_src_rows,
                                  const GatherMats *mats, int n_mats, const uint32_t *expert_offsets, int m_total, int n_out, int K,
                                  int n_experts, int group_size, int dtype, void *scratch);
+cudaError_t launch_affine_dequantize(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases, void *out,
+                                     size_t n_elem, int bits, int group_size, int dt);
+cudaError_t launch_affine_quantize(Ctx *ctx, cudaStream_t st, const void *w, void *out, void *scales, void *biases, size_t n_groups,
+                                   int bits, int group_size, int dt);
 cudaError_t launch_gather_generic(cudaStream_t st, const void *x, const void *w, const void *scales, const void *biases,
                                   const uint32_t *offsets, const uint32_t *indices, void *out, int t_rows, int k_in, int n_out,
                                   int n_experts, int bits, int gs, int dt);

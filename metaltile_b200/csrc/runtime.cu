@@ -46,7 +46,7 @@ bool dtype_ok(int dt) { return dt == MTC_F32 || dt == MTC_F16 || dt == MTC_BF16;
 // "gs_per_row" (hand-tuned int4/int8/mma kernels: group_size = k / gs_per_row) or
 // "group_size" (generic _b* family).  has_n: whether an `n` constexpr is bound
 // (mt_qmv / mt_qmv_int8_fast take N from the size of `out`).
-enum Family { DENSE_QMV, DENSE_QMM, GATHER_CSR, GATHER_IDX, ROUTER_TOPK, MOE_PERMUTE, MOE_UNPERMUTE, SWIGLU, BATCHED_QKV, BATCHED_4, RMS_QMV };
+enum Family { DENSE_QMV, DENSE_QMM, GATHER_CSR, GATHER_IDX, ROUTER_TOPK, MOE_PERMUTE, MOE_UNPERMUTE, SWIGLU, BATCHED_QKV, BATCHED_4, RMS_QMV, AFFINE_Q, AFFINE_DQ };
 struct KernelRow {
     const char *name;
     Family family;
@@ -92,6 +92,19 @@ const KernelRow kKernels[] = {
     // RMSNorm fused into the decode projection: crates/metaltile-std/src/ffai/rms_norm_qgemv.rs:51-107,131-146
     {"ffai_rms_norm_qgemv", RMS_QMV, 4, "group_size", false},
     {"ffai_rms_norm_qgemv_fast", RMS_QMV, 4, "group_size", false},
+    // the codec: crates/metaltile-std/src/mlx/quantized.rs:3575-4214
+    {"mt_affine_quantize_int2", AFFINE_Q, 2, "group_size", false},
+    {"mt_affine_quantize_int3", AFFINE_Q, 3, "group_size", false},
+    {"mt_affine_quantize_int4", AFFINE_Q, 4, "group_size", false},
+    {"mt_affine_quantize_int5", AFFINE_Q, 5, "group_size", false},
+    {"mt_affine_quantize_int6", AFFINE_Q, 6, "group_size", false},
+    {"mt_affine_quantize_int8", AFFINE_Q, 8, "group_size", false},
+    {"mt_affine_dequantize_int2", AFFINE_DQ, 2, "group_size", false},
+    {"mt_affine_dequantize_int3", AFFINE_DQ, 3, "group_size", false},
+    {"mt_affine_dequantize_int4", AFFINE_DQ, 4, "group_size", false},
+    {"mt_affine_dequantize_int5", AFFINE_DQ, 5, "group_size", false},
+    {"mt_affine_dequantize_int6", AFFINE_DQ, 6, "group_size", false},
+    {"mt_affine_dequantize_int8", AFFINE_DQ, 8, "group_size", false},
     // MoE: crates/metaltile-std/src/ffai/moe.rs:65,222,283 (routing), :358,602-605,634,900,1363 (CSR gather),
     // :2256,2832-2835,2857,3231 (per-row-index gather); crates/metaltile-std/src/mlx/swiglu.rs:45
     {"mt_moe_router_topk", ROUTER_TOPK, -1, "", false},
@@ -671,6 +684,40 @@ int mtc_qmm(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
     return mtc_qmv(ctx, stream, w, scales, biases, x, out, M, N, K, bits, group_size, dtype);
 }
 
+static int affine_args_ok(mtc_ctx *ctx, const char *who, size_t n_elem, int bits, int group_size, int dtype) {
+    if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, std::string(who) + ": dtype must be f32, f16 or bf16");
+    const bool bits_ok = bits == 2 || bits == 3 || bits == 4 || bits == 5 || bits == 6 || bits == 8;
+    if (!bits_ok || group_size <= 0 || (static_cast<long long>(group_size) * bits) % 32 != 0 || n_elem % static_cast<size_t>(group_size) != 0)
+        return fail(ctx, MTC_ERR_UNSUPPORTED, std::string(who) + ": need bits in {2,3,4,5,6,8}, whole groups, group_size * bits % 32 == 0");
+    return MTC_OK;
+}
+
+int mtc_affine_quantize(mtc_ctx *ctx, void *stream, const void *w, void *out, void *scales, void *biases, size_t n_elem, int bits,
+                        int group_size, int dtype) {
+    if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    int rc = affine_args_ok(ctx, "affine_quantize", n_elem, bits, group_size, dtype);
+    if (rc != MTC_OK) return rc;
+    if (n_elem == 0) return MTC_OK;
+    if (!w || !out || !scales || !biases) return fail(ctx, MTC_ERR_INVALID, "affine_quantize: null pointer");
+    MTC_CUDA(ctx, mtc::launch_affine_quantize(ctx, static_cast<cudaStream_t>(stream), w, out, scales, biases, n_elem / group_size, bits,
+                                              group_size, dtype), MTC_ERR_DISPATCH);
+    return MTC_OK;
+}
+
+int mtc_affine_dequantize(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, void *out, size_t n_elem,
+                          int bits, int group_size, int dtype) {
+    if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    int rc = affine_args_ok(ctx, "affine_dequantize", n_elem, bits, group_size, dtype);
+    if (rc != MTC_OK) return rc;
+    if (n_elem == 0) return MTC_OK;
+    if (!w || !out || !scales || !biases) return fail(ctx, MTC_ERR_INVALID, "affine_dequantize: null pointer");
+    MTC_CUDA(ctx, mtc::launch_affine_dequantize(ctx, static_cast<cudaStream_t>(stream), w, scales, biases, out, n_elem, bits, group_size,
+                                                dtype), MTC_ERR_DISPATCH);
+    return MTC_OK;
+}
+
 int mtc_rms_norm_qmv(mtc_ctx *ctx, void *stream, const void *x, const void *norm_weight, float eps, const void *w,
                      const void *scales, const void *biases, void *out, int N, int K, int bits, int group_size, int dtype) {
     if (!ctx) return MTC_ERR_INVALID;
@@ -1111,6 +1158,23 @@ int dispatch_pass(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_bu
             if (qkv) need_buf("out", sum * esz);
             break;
         }
+        case AFFINE_Q:
+        case AFFINE_DQ: {
+            need_const("group_size", &gs);
+            if (!err.empty()) break;
+            const bool quant = row->family == AFFINE_Q;
+            mtc_named_buf *bw = find_buf(bufs, n_bufs, "w");
+            if (!bw) { err = kn + ": buffers w, out, scales, biases must be bound"; break; }
+            if (gs == 0 || (static_cast<unsigned long long>(gs) * row->bits) % 32 != 0)
+                return fail(ctx, MTC_ERR_UNSUPPORTED, kn + ": group_size * bits must be a multiple of 32");
+            rows = quant ? bw->bytes / esz : (bw->bytes / 4) * 32 / row->bits;      // elements
+            rows -= rows % gs;
+            need_buf("w", quant ? rows * esz : rows * row->bits / 8);
+            need_buf("out", quant ? rows * row->bits / 8 : rows * esz);
+            need_buf("scales", rows / gs * esz);
+            need_buf("biases", rows / gs * esz);
+            break;
+        }
         case RMS_QMV: {
             need_const("in_dim", &k);
             need_const("group_size", &gs);
@@ -1268,6 +1332,12 @@ int dispatch_pass(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_bu
             rc = mtc_qmv_batched(ctx, st, ds, nb);
             break;
         }
+        case AFFINE_Q:
+            rc = mtc_affine_quantize(ctx, st, dev("w"), dev("out"), dev("scales"), dev("biases"), rows, row->bits, static_cast<int>(gs), dtype);
+            break;
+        case AFFINE_DQ:
+            rc = mtc_affine_dequantize(ctx, st, dev("w"), dev("scales"), dev("biases"), dev("out"), rows, row->bits, static_cast<int>(gs), dtype);
+            break;
         case RMS_QMV:
             rc = mtc_rms_norm_qmv(ctx, st, dev("x"), dev("norm_weight"), rms_eps, dev("weight"), dev("scales"), dev("biases"), dev("output"),
                                   static_cast<int>(n), static_cast<int>(k), 4, static_cast<int>(gs), dtype);

@@ -244,3 +244,35 @@ def rms_norm_qmv(w, scales, biases, x, norm_weight, eps: float, bits: int, group
     ctx.rms_norm_qmv(x.data_ptr(), norm_weight.data_ptr(), eps, w.data_ptr(), scales.data_ptr(), biases.data_ptr(), out.data_ptr(),
                      n, k, bits, group_size, _TORCH_DT[x.dtype], stream=_stream())
     return out
+
+
+def affine_quantize(w, bits: int, group_size: int, ctx: Context = None):
+    """Float tensor ``w [..., K]`` (K a multiple of the group size) -> (packed int32 ``[..., K*bits/32]``, scales, biases
+    ``[..., K/group_size]``) in the layout the quantized matmuls read (``mt_affine_quantize_int*``,
+    crates/metaltile-std/src/mlx/quantized.rs:3629-3667)."""
+    if not w.is_contiguous():
+        raise ValueError("w must be contiguous")
+    k = w.shape[-1]
+    if k % group_size or (group_size * bits) % 32:
+        raise ValueError("the last dimension must hold whole groups and group_size * bits must be a multiple of 32")
+    lead = tuple(w.shape[:-1])
+    out = torch.empty(lead + (k * bits // 32,), dtype=torch.int32, device=w.device)
+    scales = torch.empty(lead + (k // group_size,), dtype=w.dtype, device=w.device)
+    biases = torch.empty_like(scales)
+    ctx = ctx or context(w.device)
+    ctx.affine_quantize(w.data_ptr(), out.data_ptr(), scales.data_ptr(), biases.data_ptr(), w.numel(), bits, group_size,
+                        _TORCH_DT[w.dtype], stream=_stream())
+    return out, scales, biases
+
+
+def affine_dequantize(w, scales, biases, bits: int, group_size: int, ctx: Context = None):
+    """The inverse of ``affine_quantize``: ``scale * q + bias`` in the type of ``scales`` (``mt_affine_dequantize_int*``)."""
+    for t in (w, scales, biases):
+        if not t.is_contiguous():
+            raise ValueError("operands must be contiguous")
+    k = w.shape[-1] * 32 // bits
+    out = torch.empty(tuple(w.shape[:-1]) + (k,), dtype=scales.dtype, device=w.device)
+    ctx = ctx or context(w.device)
+    ctx.affine_dequantize(w.data_ptr(), scales.data_ptr(), biases.data_ptr(), out.data_ptr(), out.numel(), bits, group_size,
+                          _TORCH_DT[scales.dtype], stream=_stream())
+    return out

@@ -197,5 +197,26 @@ def rms_norm_qmv(w, scales, biases, x, norm_weight, eps, n, k, bits, group_size)
     return qmm(w, scales, biases, rms_normed(x, norm_weight, eps).reshape(1, k), 1, n, k, bits, group_size)
 
 
+def affine_quantize(w, bits: int, group_size: int):
+    """(packed u32 [n_groups * group_size * bits / 32], scales f32 [n_groups], biases f32 [n_groups]) of
+    ``mt_affine_quantize_int*`` (crates/metaltile-std/src/mlx/quantized.rs:3629-3667)."""
+    v = _f32(w).reshape(-1)
+    if v.size % group_size or (group_size * bits) % 32:
+        raise ValueError("whole groups of whole words only")
+    ng = v.size // group_size
+    out = np.zeros(ng * group_size * bits // 32, dtype=np.uint32)
+    sc, bi = np.empty(ng, dtype=np.float32), np.empty(ng, dtype=np.float32)
+    lib().mto_affine_quantize(_p(v), _p(out), _p(sc), _p(bi), _sz(ng), _sz(group_size), ctypes.c_uint32(bits))
+    return out, sc, bi
+
+
+def affine_dequantize(w, scales, biases, n_elem: int, bits: int, group_size: int) -> np.ndarray:
+    """f32 [n_elem] of ``mt_affine_dequantize_int*`` (quantized.rs:3575-3604); scales / biases already rounded through T."""
+    ww, sc, bi = _u32(w).reshape(-1), _f32(scales).reshape(-1), _f32(biases).reshape(-1)
+    out = np.empty(n_elem, dtype=np.float32)
+    lib().mto_affine_dequantize(_p(ww), _p(sc), _p(bi), _p(out), _sz(n_elem), _sz(group_size), ctypes.c_uint32(bits))
+    return out
+
+
 def max_threads() -> int:
     return int(lib().mto_max_threads())

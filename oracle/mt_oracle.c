@@ -370,6 +370,59 @@ void mto_rms_normed(const float *x, const float *norm_weight, float *normed, siz
     for (size_t d = 0; d < k; d++) normed[d] = x[d] * norm_weight[d] * inv_rms;
 }
 
+/* mt_affine_quantize_int{2,3,4,5,6,8}, crates/metaltile-std/src/mlx/quantized.rs:3629-3667,3707-3750,3793-3860,3871-4070
+ * (one template, checked by :5268-5339 and tests/affine_int356_quantize_gpu_correctness.rs): per group of `group_size`
+ * values  scale = (max - min) / (2^bits - 1), 1 when that is below 1e-7;  bias = min;
+ *         q = trunc(clamp((v - bias) * (1 / scale) + 0.5, 0, 2^bits - 1))      - every operation rounded to f32, no FMA;
+ * codes packed LSB-first as one bit-stream per group (group_size * bits is a multiple of 32); scales and biases are
+ * returned in f32 (the kernels store them rounded to the activation type). */
+void mto_affine_quantize(const float *w, uint32_t *out, float *scales, float *biases, size_t n_groups, size_t group_size,
+                         uint32_t bits) {
+    const float n_bins = (float)((1u << bits) - 1u);
+    const size_t wpg = group_size * bits / 32;
+    for (size_t g = 0; g < n_groups; g++) {
+        const float *v = w + g * group_size;
+        float mn = INFINITY, mx = -INFINITY;
+        for (size_t i = 0; i < group_size; i++) {
+            if (v[i] < mn) mn = v[i];
+            if (v[i] > mx) mx = v[i];
+        }
+        float raw = (mx - mn) / n_bins;
+        float scale = raw < 1.0e-7f ? 1.0f : raw;
+        float inv = 1.0f / scale;
+        scales[g] = scale;
+        biases[g] = mn;
+        uint32_t *o = out + g * wpg;
+        for (size_t i = 0; i < wpg; i++) o[i] = 0u;
+        for (size_t i = 0; i < group_size; i++) {
+            float t = v[i] - mn;
+            float qf = t * inv;
+            qf = qf + 0.5f;
+            if (qf > n_bins) qf = n_bins;
+            if (qf < 0.0f) qf = 0.0f;
+            uint32_t q = (uint32_t)qf;
+            size_t bit = i * bits;
+            o[bit >> 5] |= q << (bit & 31u);
+            if ((bit & 31u) + bits > 32u) o[(bit >> 5) + 1] |= q >> (32u - (bit & 31u));
+        }
+    }
+}
+
+/* mt_affine_dequantize_int{2,3,4,5,6,8}, quantized.rs:3575-3604,3681-3705,3762-3791,4081-4214 (expected values of
+ * :5216-5251): out[i] = scale[i / group_size] * q_i + bias[i / group_size] in f32, codes read from the LSB-first stream. */
+void mto_affine_dequantize(const uint32_t *w, const float *scales, const float *biases, float *out, size_t n_elem,
+                           size_t group_size, uint32_t bits) {
+    const uint32_t mask = (1u << bits) - 1u;
+    for (size_t i = 0; i < n_elem; i++) {
+        size_t bit = i * bits;
+        uint32_t q = w[bit >> 5] >> (bit & 31u);
+        if ((bit & 31u) + bits > 32u) q |= w[(bit >> 5) + 1] << (32u - (bit & 31u));
+        q &= mask;
+        float prod = scales[i / group_size] * (float)q;
+        out[i] = prod + biases[i / group_size];
+    }
+}
+
 int mto_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

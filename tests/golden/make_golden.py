@@ -25,6 +25,7 @@ Reference sources restated here
   swiglu setup ............... crates/metaltile-std/src/mlx/swiglu.rs:65-72
   batched q/k/v decode ....... crates/metaltile-std/tests/batched_qkv_qgemv_gpu_correctness.rs:30-127,167-181,312-321
   batched 4-way decode ....... crates/metaltile-std/src/ffai/batched_4_qgemv.rs:342-440
+  affine quantize / dequantize crates/metaltile-std/src/mlx/quantized.rs:3629-3667,5216-5330
   fused RMSNorm + decode ..... crates/metaltile-std/tests/rms_norm_qgemv_gpu_correctness.rs:35-177,232-294
 """
 from __future__ import annotations
@@ -289,6 +290,37 @@ def rms_norm_case(dt, in_dim, gs, out_dim, eps=1e-5):
                 eps=np.array([eps], dtype=np.float32), meta=np.array([in_dim, gs, out_dim]))
 
 
+def affine_dequant_case(bits, gs, n_groups, dt):
+    """dequant_setup of crates/metaltile-std/src/mlx/quantized.rs:5216-5251."""
+    pf = 32 // bits
+    n_elem = n_groups * gs
+    w = ((np.arange(n_elem // pf, dtype=np.uint64) * 2654435761) & 0xFFFFFFFF).astype(np.uint32)
+    scales = (f32(0.05) + np.arange(n_groups).astype(f32) * f32(0.01)).astype(f32)
+    biases = (f32(-0.2) + np.arange(n_groups).astype(f32) * f32(0.03)).astype(f32)
+    sd, bd = round_dt(scales, dt), round_dt(biases, dt)
+    q = unpack_rows(w.reshape(1, -1), n_elem, bits).reshape(-1).astype(f32)
+    g = np.arange(n_elem) // gs
+    expected = ((sd[g] * q).astype(f32) + bd[g]).astype(f32)
+    return dict(w=w, scales=scales, biases=biases, expected=expected, meta=np.array([bits, gs, n_groups]))
+
+
+def affine_quant_case(bits, gs, n_groups, dt):
+    """quantize_setup of quantized.rs:5268-5305 (scales and biases are what the reference pins); the codes follow the
+    kernels' formula (:3657-3664) with every operation rounded to f32: trunc(clamp((v - min) * (1 / scale) + 0.5))."""
+    n_bins = f32((1 << bits) - 1)
+    n_elem = n_groups * gs
+    w = (((np.arange(n_elem) % 37).astype(f32) - f32(18.0)) * f32(0.05)).astype(f32)
+    wd = round_dt(w, dt).reshape(n_groups, gs)
+    mn, mx = wd.min(axis=1), wd.max(axis=1)
+    raw = ((mx - mn).astype(f32) / n_bins).astype(f32)
+    scales = np.where(raw < f32(1.0e-7), f32(1.0), raw).astype(f32)
+    inv = (f32(1.0) / scales).astype(f32)
+    qf = (((wd - mn[:, None]).astype(f32) * inv[:, None]).astype(f32) + f32(0.5)).astype(f32)
+    codes = np.clip(qf, f32(0.0), n_bins).astype(np.uint32)
+    words = pack_rows(codes, bits).reshape(-1)
+    return dict(w=w, scales=scales, biases=mn.astype(f32), codes=codes.astype(np.uint8), words=words, meta=np.array([bits, gs, n_groups]))
+
+
 def save_new(path, **arrays):
     """Write a fixture unless the file already holds exactly these arrays (keeps unchanged fixtures byte-stable)."""
     if os.path.exists(path):
@@ -309,6 +341,11 @@ def main():
     for dt, in_dim, gs, od in (("f32", 256, 64, 8), ("f32", 512, 128, 6), ("f16", 256, 64, 8), ("bf16", 256, 64, 8),
                                ("f32", 512, 64, 16), ("f16", 512, 64, 16), ("bf16", 512, 64, 16), ("f32", 1024, 64, 32)):
         save_new(os.path.join(HERE, f"rms_norm_qgemv_k{in_dim}_g{gs}_n{od}_{dt}.npz"), **rms_norm_case(dt, in_dim, gs, od))
+    for dt in ("f32", "f16", "bf16"):
+        for bits, gs, ng in ((4, 64, 8), (8, 64, 4), (2, 64, 16)):                     # quantized.rs:5253-5265
+            save_new(os.path.join(HERE, f"test_affine_dequantize_int{bits}_{dt}.npz"), **affine_dequant_case(bits, gs, ng, dt))
+        for bits, gs in ((2, 64), (3, 32), (4, 64), (5, 32), (6, 32), (8, 64)):          # quantized.rs:5307-5330
+            save_new(os.path.join(HERE, f"test_affine_quantize_int{bits}_{dt}.npz"), **affine_quant_case(bits, gs, 8, dt))
     for dt in ("f32", "f16", "bf16"):
         save_new(os.path.join(HERE, f"test_batched_4_qgemv_fast_{dt}.npz"),
                  **batched_case(dt, 512, 64, (16, 8, 8, 8), (0x22, 0x33, 0x44, 0x55)))

@@ -1,0 +1,94 @@
+"""The codec either side of the quantized matmuls on the GPU: mt_affine_quantize_int* / mt_affine_dequantize_int*
+(crates/metaltile-std/src/mlx/quantized.rs:3575-4214) against the reference's own cases and against the oracle.
+Integer codes, scales, biases and dequantized values are compared for equality."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from helpers import ODT, TOL, bytes_to_f32, dt_bytes, rel_err, to_dev
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    from metaltile_b200 import ops
+    return ops.context(0)
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("bits", [2, 4, 8])
+def test_reference_dequantize_cases(ctx, bits, dt):
+    """test_affine_dequantize_int{2,4,8} (quantized.rs:5216-5265) under the reference's kernel and buffer names."""
+    fx = dict(np.load(os.path.join(GOLDEN, f"test_affine_dequantize_int{bits}_{dt}.npz")))
+    _, gs, ng = (int(v) for v in fx["meta"])
+    n = ng * gs
+    bufs = {"w": fx["w"].tobytes(), "scales": dt_bytes(fx["scales"], dt), "biases": dt_bytes(fx["biases"], dt),
+            "out": bytes(n * (4 if dt == "f32" else 2))}
+    res = ctx.dispatch_with_grid(f"mt_affine_dequantize_int{bits}", bufs, {"group_size": gs}, (n * bits // 32, 1, 1), (64, 1, 1), dtype=dt)
+    got = bytes_to_f32(res.outputs["out"], dt)
+    assert np.array_equal(got, oracle.round_through(fx["expected"], ODT[dt]))
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("bits", [2, 3, 4, 5, 6, 8])
+def test_reference_quantize_cases(ctx, bits, dt):
+    """test_affine_quantize_int{2,3,4,5,6,8} (quantized.rs:5268-5330): the scales and biases the reference pins, and the
+    packed codes of its formula, all for equality."""
+    fx = dict(np.load(os.path.join(GOLDEN, f"test_affine_quantize_int{bits}_{dt}.npz")))
+    _, gs, ng = (int(v) for v in fx["meta"])
+    n, esz = ng * gs, (4 if dt == "f32" else 2)
+    bufs = {"w": dt_bytes(fx["w"], dt), "out": bytes(n * bits // 8), "scales": bytes(ng * esz), "biases": bytes(ng * esz)}
+    res = ctx.dispatch_with_grid(f"mt_affine_quantize_int{bits}", bufs, {"group_size": gs}, (ng, 1, 1), (32, 1, 1), dtype=dt,
+                                 outputs=("out", "scales", "biases"))
+    assert np.array_equal(bytes_to_f32(res.outputs["scales"], dt), oracle.round_through(fx["scales"], ODT[dt]))
+    assert np.array_equal(bytes_to_f32(res.outputs["biases"], dt), oracle.round_through(fx["biases"], ODT[dt]))
+    assert np.array_equal(np.frombuffer(res.outputs["out"], dtype=np.uint32), fx["words"])
+
+
+@pytest.mark.parametrize("bits,gs,dt", [(4, 64, "bf16"), (3, 32, "f16"), (8, 128, "bf16"), (5, 32, "f32"), (6, 64, "bf16"), (2, 64, "f16"),
+                                        (2, 48, "bf16"), (4, 8, "f32")])
+def test_quantize_then_matmul_on_device(ctx, bits, gs, dt):
+    """Real float weights packed on the device: codes, scales and biases equal the oracle's, the inverse equals the
+    oracle's, and the decode product of the packed matrix matches the oracle's product (the last two shapes have groups
+    that are not a multiple of 32: the one-thread-per-group form)."""
+    import torch
+    from metaltile_b200 import ops, synth
+    n, k = 512, 1536
+    wf = oracle.round_through(0.05 * synth.activations(n, k, seed=40 + bits), ODT[dt])
+    wd = to_dev(wf, dt)
+    q, s, b = ops.affine_quantize(wd, bits, gs, ctx=ctx)
+    back = ops.affine_dequantize(q, s, b, bits, gs, ctx=ctx)
+    torch.cuda.synchronize()
+    oq, osc, obi = oracle.affine_quantize(wf, bits, gs)
+    assert np.array_equal(q.cpu().numpy().view(np.uint32).reshape(-1), oq)
+    s_h, b_h = s.float().cpu().numpy().reshape(-1), b.float().cpu().numpy().reshape(-1)
+    assert np.array_equal(s_h, oracle.round_through(osc, ODT[dt])) and np.array_equal(b_h, oracle.round_through(obi, ODT[dt]))
+    ref_back = oracle.round_through(oracle.affine_dequantize(oq, s_h, b_h, n * k, bits, gs), ODT[dt])
+    assert np.array_equal(back.float().cpu().numpy().reshape(-1), ref_back)
+    # half a quantization step (plus the rounding of scale and bias to the activation type)
+    assert np.all(np.abs(back.float().cpu().numpy() - wf) <= (0.5 * np.repeat(s_h, gs).reshape(n, k) * 1.02 + 2e-3))
+    if k % gs == 0 and gs >= 32:
+        x = oracle.round_through(synth.activations(1, k, seed=3), ODT[dt])
+        got = ops.qmv(q, s, b, to_dev(x, dt), bits, gs, ctx=ctx)
+        torch.cuda.synchronize()
+        ref = oracle.qmm(oq.reshape(n, -1), s_h.reshape(n, -1), b_h.reshape(n, -1), x, 1, n, k, bits, gs)
+        assert rel_err(got.float().cpu().numpy(), ref) <= TOL[dt]
+    assert ctx.status_word() == 0
+
+
+def test_codec_refuses_partial_groups(ctx):
+    import torch
+    from metaltile_b200 import MetalTileError
+    w = torch.zeros(100, dtype=torch.float32, device="cuda")
+    out = torch.zeros(64, dtype=torch.int32, device="cuda")
+    sb = torch.zeros(8, dtype=torch.float32, device="cuda")
+    with pytest.raises(MetalTileError) as ei:               # 100 is not a whole number of groups of 64
+        ctx.affine_quantize(w.data_ptr(), out.data_ptr(), sb.data_ptr(), sb.data_ptr(), 100, 4, 64, "f32")
+    assert ei.value.variant == "Unsupported"
+    with pytest.raises(MetalTileError) as ei:               # 3-bit groups of 8 are not whole words
+        ctx.affine_dequantize(out.data_ptr(), sb.data_ptr(), sb.data_ptr(), w.data_ptr(), 64, 3, 8, "f32")
+    assert ei.value.variant == "Unsupported"

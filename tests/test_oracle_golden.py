@@ -190,3 +190,33 @@ def test_rms_norm_qgemv_fixtures(path):
     s, b = oracle.round_through(fx["scales"], dt), oracle.round_through(fx["biases"], dt)
     acc = oracle.rms_norm_qmv(fx["w"], s, b, fx["x"], fx["norm_weight"], eps, n, in_dim, 4, gs)
     assert np.array_equal(_bits(acc.reshape(-1)), _bits(fx["acc"]))
+
+
+AFFINE_DQ = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "test_affine_dequantize_*.npz")))
+AFFINE_Q = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "test_affine_quantize_*.npz")))
+
+
+@pytest.mark.parametrize("path", AFFINE_DQ, ids=[os.path.basename(p)[:-4] for p in AFFINE_DQ])
+def test_affine_dequantize_fixtures(path):
+    """test_affine_dequantize_int{2,4,8} (crates/metaltile-std/src/mlx/quantized.rs:5216-5265): expected values bit for bit."""
+    fx = _load(path)
+    dt = DT[os.path.basename(path)[:-4].rsplit("_", 1)[1]]
+    bits, gs, ng = (int(v) for v in fx["meta"])
+    got = oracle.affine_dequantize(fx["w"], oracle.round_through(fx["scales"], dt), oracle.round_through(fx["biases"], dt), ng * gs, bits, gs)
+    assert np.array_equal(_bits(got), _bits(fx["expected"]))
+
+
+@pytest.mark.parametrize("path", AFFINE_Q, ids=[os.path.basename(p)[:-4] for p in AFFINE_Q])
+def test_affine_quantize_fixtures(path):
+    """test_affine_quantize_int{2,3,4,5,6,8} (quantized.rs:5268-5330): scales and biases (what the reference pins) and the
+    packed codes of the kernels' formula, bit for bit; and the quantize -> dequantize round trip stays within half a step."""
+    fx = _load(path)
+    dt = DT[os.path.basename(path)[:-4].rsplit("_", 1)[1]]
+    bits, gs, ng = (int(v) for v in fx["meta"])
+    wd = oracle.round_through(fx["w"], dt)
+    words, sc, bi = oracle.affine_quantize(wd, bits, gs)
+    assert np.array_equal(_bits(sc), _bits(fx["scales"])) and np.array_equal(_bits(bi), _bits(fx["biases"]))
+    assert np.array_equal(words, fx["words"])
+    assert np.array_equal(oracle.unpack_matrix(words.reshape(ng, -1), gs, bits), fx["codes"])
+    back = oracle.affine_dequantize(words, sc, bi, ng * gs, bits, gs).reshape(ng, gs)
+    assert np.all(np.abs(back - wd.reshape(ng, gs)) <= 0.5 * sc[:, None] * (1 + 1e-5))
