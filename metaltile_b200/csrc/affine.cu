@@ -127,6 +127,82 @@ __global__ void __launch_bounds__(256) affine_quantize_kernel(const void *w, uin
     }
 }
 
+// One thread per 32 consecutive values = BITS whole output words; the group_size / 32 threads of a group (a power of two,
+// adjacent lanes) share min and max through xor-shuffles.  One pass: the values stay in registers between the reduction
+// and the packing.  `w` 16-byte aligned.
+template <int BITS>
+__global__ void __launch_bounds__(256) affine_quantize32_kernel(const void *w, uint32_t *out, void *scales, void *biases, size_t n_chunks,
+                                                                int tpg /* threads per group */, int dt) {
+    const float n_bins = static_cast<float>((1u << BITS) - 1u);
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    // whole warps stay in the loop (the shuffles need every lane); lanes past the end work on chunk 0 and store nothing
+    for (size_t c0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x - (threadIdx.x & 31); c0 < n_chunks; c0 += stride) {
+        const size_t c = c0 + (threadIdx.x & 31);
+        const bool on = c < n_chunks;
+        const size_t cc = on ? c : 0;
+        float v[32];
+        if (dt == MTC_F32) {
+            const float4 *p = reinterpret_cast<const float4 *>(static_cast<const float *>(w) + cc * 32);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const float4 t = __ldg(p + q);
+                v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
+            }
+        } else {
+            const uint4 *p = reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(w) + cc * 32);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint4 t = __ldg(p + q);
+                const uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    if (dt == MTC_BF16) {
+                        v[8 * q + 2 * h] = __uint_as_float(u[h] << 16);
+                        v[8 * q + 2 * h + 1] = __uint_as_float(u[h] & 0xFFFF0000u);
+                    } else {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&u[h]));
+                        v[8 * q + 2 * h] = f.x;
+                        v[8 * q + 2 * h + 1] = f.y;
+                    }
+                }
+            }
+        }
+        float mn = v[0], mx = v[0];
+#pragma unroll
+        for (int k = 1; k < 32; ++k) {
+            mn = fminf(mn, v[k]);
+            mx = fmaxf(mx, v[k]);
+        }
+        for (int o = 1; o < tpg; o <<= 1) {
+            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        }
+        const float raw = __fdiv_rn(__fsub_rn(mx, mn), n_bins);
+        const float scale = raw < 1.0e-7f ? 1.0f : raw;
+        const float inv = __fdiv_rn(1.0f, scale);
+        uint32_t words[BITS];
+#pragma unroll
+        for (int j = 0; j < BITS; ++j) words[j] = 0u;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+            float qf = __fadd_rn(__fmul_rn(__fsub_rn(v[k], mn), inv), 0.5f);
+            qf = qf > n_bins ? n_bins : (qf < 0.0f ? 0.0f : qf);
+            const uint32_t q = static_cast<uint32_t>(qf);
+            const int bit = k * BITS, word = bit >> 5, sh = bit & 31;       // compile-time after unrolling
+            words[word] |= q << sh;
+            if (sh + BITS > 32) words[word + 1] |= q >> (32 - sh);
+        }
+        if (on) {
+#pragma unroll
+            for (int j = 0; j < BITS; ++j) out[c * BITS + j] = words[j];
+            if ((c & (tpg - 1)) == 0) {
+                st_from_f32(scales, c / tpg, scale, dt);
+                st_from_f32(biases, c / tpg, mn, dt);
+            }
+        }
+    }
+}
+
 // any group size, any alignment: one thread per element (dequantize) / one thread per group (quantize)
 __global__ void __launch_bounds__(256) affine_dequantize_generic(const uint32_t *w, const void *scales, const void *biases, void *out,
                                                                  size_t n_elem, int group_size, int bits, int dt) {
@@ -211,6 +287,20 @@ cudaError_t launch_affine_quantize(Ctx *ctx, cudaStream_t st, const void *w, voi
     uint32_t *oo = static_cast<uint32_t *>(out);
     if (group_size % 32 != 0) {
         affine_quantize_generic<<<grid_for(n_groups, 128, ctx->sm_count), 128, 0, st>>>(w, oo, scales, biases, n_groups, group_size, bits, dt);
+        return cudaGetLastError();
+    }
+    const int tpg = group_size / 32;
+    if ((tpg & (tpg - 1)) == 0 && tpg <= 32 && reinterpret_cast<uintptr_t>(w) % 16 == 0) {
+        const size_t chunks = n_groups * tpg;
+        const int g32 = grid_for(chunks, 256, ctx->sm_count);
+        switch (bits) {
+            case 2: affine_quantize32_kernel<2><<<g32, 256, 0, st>>>(w, oo, scales, biases, chunks, tpg, dt); break;
+            case 3: affine_quantize32_kernel<3><<<g32, 256, 0, st>>>(w, oo, scales, biases, chunks, tpg, dt); break;
+            case 4: affine_quantize32_kernel<4><<<g32, 256, 0, st>>>(w, oo, scales, biases, chunks, tpg, dt); break;
+            case 5: affine_quantize32_kernel<5><<<g32, 256, 0, st>>>(w, oo, scales, biases, chunks, tpg, dt); break;
+            case 6: affine_quantize32_kernel<6><<<g32, 256, 0, st>>>(w, oo, scales, biases, chunks, tpg, dt); break;
+            default: affine_quantize32_kernel<8><<<g32, 256, 0, st>>>(w, oo, scales, biases, chunks, tpg, dt); break;
+        }
         return cudaGetLastError();
     }
     const int grid = grid_for(n_groups, 8, ctx->sm_count);
