@@ -178,6 +178,12 @@ int mtc_affine_quantize(mtc_ctx *ctx, void *stream, const void *w, void *out, vo
                         int group_size, int dtype);
 int mtc_affine_dequantize(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, void *out,
                           size_t n_elem, int bits, int group_size, int dtype);
+/* dequant_gather_int{2,3,4,5,6,8} (crates/metaltile-std/src/ffai/dequant_gather.rs:44-101): rows indices[t] (u32) of a
+ * quantized table weight u32[vocab, hidden*bits/32], scales / biases T[vocab, hidden/G], dequantized into
+ * out T[n_tokens, hidden] = q * scale + bias (separately rounded f32 operations).  An index outside the table reads
+ * row 0 and is reported through the status word (0x904). */
+int mtc_dequant_gather(mtc_ctx *ctx, void *stream, const void *weight, const void *scales, const void *biases, const void *indices,
+                       void *out, size_t n_tokens, int hidden, int vocab, int bits, int group_size, int dtype);
 /* ffai_rms_norm_qgemv / _fast (crates/metaltile-std/src/ffai/rms_norm_qgemv.rs:51-107,131-146): the decode projection
  * of the RMS-normalised activation in one launch,
  *     out[n] = sum_k w(n, k) * (x[k] * norm_weight[k] * inv_rms),   inv_rms = 1 / sqrt(mean(x^2) + eps),

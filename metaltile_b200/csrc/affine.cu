@@ -203,6 +203,85 @@ __global__ void __launch_bounds__(256) affine_quantize32_kernel(const void *w, u
     }
 }
 
+// dequant_gather_int* (crates/metaltile-std/src/ffai/dequant_gather.rs:44-94): rows indices[t] of a quantized table
+// [vocab, hidden], dequantized into out [n_tokens, hidden].  One thread per 32 values of an output row (hidden and the
+// group size are multiples of 32); an index outside the table reads row 0 and is reported (status 0x904).
+template <int BITS>
+__global__ void __launch_bounds__(256) dequant_gather_kernel(const uint32_t *w, const void *scales, const void *biases,
+                                                             const uint32_t *indices, void *out, size_t n_tokens, int hidden,
+                                                             int group_size, int vocab, int dt, int vec_ok, uint32_t *status) {
+    const int cpr = hidden >> 5;                                   // chunks per row
+    const size_t n_chunks = n_tokens * cpr;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n_chunks;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t tok = i / cpr;
+        const int c = static_cast<int>(i - tok * cpr);
+        uint32_t row = __ldg(indices + tok);
+        if (row >= static_cast<uint32_t>(vocab)) {
+            atomicCAS(status, 0u, 0x904u);
+            row = 0;
+        }
+        const uint32_t *rw = w + (static_cast<size_t>(row) * cpr + c) * BITS;
+        uint32_t words[BITS];
+#pragma unroll
+        for (int j = 0; j < BITS; ++j) words[j] = __ldg(rw + j);
+        const size_t g = static_cast<size_t>(row) * (hidden / group_size) + (c * 32) / group_size;
+        const float s = ld_as_f32(scales, g, dt), b = ld_as_f32(biases, g, dt);
+        float v[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) v[k] = __fadd_rn(__fmul_rn(static_cast<float>(code_of<BITS>(words, k)), s), b);
+        const size_t o = tok * hidden + c * 32;
+        if (dt == MTC_F32) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) static_cast<float *>(out)[o + k] = v[k];
+        } else {
+            uint32_t h[16];
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+                if (dt == MTC_BF16) {
+                    const __nv_bfloat162 p2 = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
+                    h[q] = *reinterpret_cast<const uint32_t *>(&p2);
+                } else {
+                    const __half2 p2 = __floats2half2_rn(v[2 * q], v[2 * q + 1]);
+                    h[q] = *reinterpret_cast<const uint32_t *>(&p2);
+                }
+            }
+            if (vec_ok) {
+                uint4 *p = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(out) + o);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) p[q] = make_uint4(h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]);
+            } else {
+                uint16_t *p = static_cast<uint16_t *>(out) + o;
+#pragma unroll
+                for (int q = 0; q < 16; ++q) {
+                    p[2 * q] = static_cast<uint16_t>(h[q] & 0xFFFFu);
+                    p[2 * q + 1] = static_cast<uint16_t>(h[q] >> 16);
+                }
+            }
+        }
+    }
+}
+
+// any hidden / group size: one thread per output element
+__global__ void __launch_bounds__(256) dequant_gather_generic(const uint32_t *w, const void *scales, const void *biases,
+                                                              const uint32_t *indices, void *out, size_t n_tokens, int hidden,
+                                                              int group_size, int vocab, int bits, int dt, uint32_t *status) {
+    const size_t n = n_tokens * hidden;
+    const size_t wpr = static_cast<size_t>(hidden) * bits / 32;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t tok = i / hidden;
+        const uint32_t d = static_cast<uint32_t>(i - tok * hidden);
+        uint32_t row = __ldg(indices + tok);
+        if (row >= static_cast<uint32_t>(vocab)) {
+            atomicCAS(status, 0u, 0x904u);
+            row = 0;
+        }
+        const float q = static_cast<float>(code_at(w + row * wpr, d, bits));
+        const size_t g = static_cast<size_t>(row) * (hidden / group_size) + d / group_size;
+        st_from_f32(out, i, __fadd_rn(__fmul_rn(q, ld_as_f32(scales, g, dt)), ld_as_f32(biases, g, dt)), dt);
+    }
+}
+
 // any group size, any alignment: one thread per element (dequantize) / one thread per group (quantize)
 __global__ void __launch_bounds__(256) affine_dequantize_generic(const uint32_t *w, const void *scales, const void *biases, void *out,
                                                                  size_t n_elem, int group_size, int bits, int dt) {
@@ -278,6 +357,30 @@ cudaError_t launch_affine_dequantize(Ctx *ctx, cudaStream_t st, const void *w, c
         case 6: affine_dequantize_kernel<6><<<grid, 256, 0, st>>>(ww, scales, biases, out, chunks, group_size, dt, vec_ok); break;
         default: affine_dequantize_kernel<8><<<grid, 256, 0, st>>>(ww, scales, biases, out, chunks, group_size, dt, vec_ok); break;
     }
+    return cudaGetLastError();
+}
+
+cudaError_t launch_dequant_gather(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases, const void *indices,
+                                  void *out, size_t n_tokens, int hidden, int vocab, int bits, int group_size, int dt) {
+    if (n_tokens == 0 || hidden == 0) return cudaSuccess;
+    const uint32_t *ww = static_cast<const uint32_t *>(w), *ix = static_cast<const uint32_t *>(indices);
+    if (hidden % 32 != 0 || group_size % 32 != 0) {
+        dequant_gather_generic<<<grid_for(n_tokens * hidden, 256, ctx->sm_count), 256, 0, st>>>(ww, scales, biases, ix, out, n_tokens, hidden,
+                                                                                              group_size, vocab, bits, dt, ctx->d_status);
+        return cudaGetLastError();
+    }
+    const int vec_ok = reinterpret_cast<uintptr_t>(out) % 16 == 0 ? 1 : 0;
+    const int grid = grid_for(n_tokens * (hidden / 32), 256, ctx->sm_count);
+#define MTC_DG(B) dequant_gather_kernel<B><<<grid, 256, 0, st>>>(ww, scales, biases, ix, out, n_tokens, hidden, group_size, vocab, dt, vec_ok, ctx->d_status)
+    switch (bits) {
+        case 2: MTC_DG(2); break;
+        case 3: MTC_DG(3); break;
+        case 4: MTC_DG(4); break;
+        case 5: MTC_DG(5); break;
+        case 6: MTC_DG(6); break;
+        default: MTC_DG(8); break;
+    }
+#undef MTC_DG
     return cudaGetLastError();
 }
 

@@ -192,6 +192,8 @@ cudaError_t launch_gather_stream(Ctx *ctx, cudaStream_t st, const void *x, const
                                  int n_experts, int group_size, int dtype, void *scratch);
 cudaError_t launch_affine_dequantize(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases, void *out,
                                      size_t n_elem, int bits, int group_size, int dt);
+cudaError_t launch_dequant_gather(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases, const void *indices,
+                                  void *out, size_t n_tokens, int hidden, int vocab, int bits, int group_size, int dt);
 cudaError_t launch_affine_quantize(Ctx *ctx, cudaStream_t st, const void *w, void *out, void *scales, void *biases, size_t n_groups,
                                    int bits, int group_size, int dt);
 cudaError_t launch_gather_generic(cudaStream_t st, const void *x, const void *w, const void *scales, const void *biases,

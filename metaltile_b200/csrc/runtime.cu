@@ -46,7 +46,7 @@ bool dtype_ok(int dt) { return dt == MTC_F32 || dt == MTC_F16 || dt == MTC_BF16;
 // "gs_per_row" (hand-tuned int4/int8/mma kernels: group_size = k / gs_per_row) or
 // "group_size" (generic _b* family).  has_n: whether an `n` constexpr is bound
 // (mt_qmv / mt_qmv_int8_fast take N from the size of `out`).
-enum Family { DENSE_QMV, DENSE_QMM, GATHER_CSR, GATHER_IDX, ROUTER_TOPK, MOE_PERMUTE, MOE_UNPERMUTE, SWIGLU, BATCHED_QKV, BATCHED_4, RMS_QMV, AFFINE_Q, AFFINE_DQ };
+enum Family { DENSE_QMV, DENSE_QMM, GATHER_CSR, GATHER_IDX, ROUTER_TOPK, MOE_PERMUTE, MOE_UNPERMUTE, SWIGLU, BATCHED_QKV, BATCHED_4, RMS_QMV, AFFINE_Q, AFFINE_DQ, DQ_GATHER };
 struct KernelRow {
     const char *name;
     Family family;
@@ -105,6 +105,13 @@ const KernelRow kKernels[] = {
     {"mt_affine_dequantize_int5", AFFINE_DQ, 5, "group_size", false},
     {"mt_affine_dequantize_int6", AFFINE_DQ, 6, "group_size", false},
     {"mt_affine_dequantize_int8", AFFINE_DQ, 8, "group_size", false},
+    // quantized embedding tables: crates/metaltile-std/src/ffai/dequant_gather.rs:44-101
+    {"dequant_gather_int2", DQ_GATHER, 2, "group_size", false},
+    {"dequant_gather_int3", DQ_GATHER, 3, "group_size", false},
+    {"dequant_gather_int4", DQ_GATHER, 4, "group_size", false},
+    {"dequant_gather_int5", DQ_GATHER, 5, "group_size", false},
+    {"dequant_gather_int6", DQ_GATHER, 6, "group_size", false},
+    {"dequant_gather_int8", DQ_GATHER, 8, "group_size", false},
     // MoE: crates/metaltile-std/src/ffai/moe.rs:65,222,283 (routing), :358,602-605,634,900,1363 (CSR gather),
     // :2256,2832-2835,2857,3231 (per-row-index gather); crates/metaltile-std/src/mlx/swiglu.rs:45
     {"mt_moe_router_topk", ROUTER_TOPK, -1, "", false},
@@ -718,6 +725,21 @@ int mtc_affine_dequantize(mtc_ctx *ctx, void *stream, const void *w, const void 
     return MTC_OK;
 }
 
+int mtc_dequant_gather(mtc_ctx *ctx, void *stream, const void *weight, const void *scales, const void *biases, const void *indices,
+                       void *out, size_t n_tokens, int hidden, int vocab, int bits, int group_size, int dtype) {
+    if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "dequant_gather: dtype must be f32, f16 or bf16");
+    const bool bits_ok = bits == 2 || bits == 3 || bits == 4 || bits == 5 || bits == 6 || bits == 8;
+    if (!bits_ok || hidden <= 0 || vocab <= 0 || group_size <= 0 || hidden % group_size != 0 || (static_cast<long long>(hidden) * bits) % 32 != 0)
+        return fail(ctx, MTC_ERR_UNSUPPORTED, "dequant_gather: need bits in {2,3,4,5,6,8}, group_size | hidden, hidden * bits % 32 == 0");
+    if (n_tokens == 0) return MTC_OK;
+    if (!weight || !scales || !biases || !indices || !out) return fail(ctx, MTC_ERR_INVALID, "dequant_gather: null pointer");
+    MTC_CUDA(ctx, mtc::launch_dequant_gather(ctx, static_cast<cudaStream_t>(stream), weight, scales, biases, indices, out, n_tokens, hidden,
+                                             vocab, bits, group_size, dtype), MTC_ERR_DISPATCH);
+    return MTC_OK;
+}
+
 int mtc_rms_norm_qmv(mtc_ctx *ctx, void *stream, const void *x, const void *norm_weight, float eps, const void *w,
                      const void *scales, const void *biases, void *out, int N, int K, int bits, int group_size, int dtype) {
     if (!ctx) return MTC_ERR_INVALID;
@@ -1175,6 +1197,24 @@ int dispatch_pass(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_bu
             need_buf("biases", rows / gs * esz);
             break;
         }
+        case DQ_GATHER: {
+            need_const("hidden", &hidden);
+            need_const("group_size", &gs);
+            if (!err.empty()) break;
+            mtc_named_buf *bw = find_buf(bufs, n_bufs, "weight"), *bi = find_buf(bufs, n_bufs, "indices");
+            if (!bw || !bi) { err = kn + ": buffers weight, scales, biases, indices, out must be bound"; break; }
+            if (hidden == 0 || gs == 0 || hidden % gs != 0 || (static_cast<unsigned long long>(hidden) * row->bits) % 32 != 0)
+                return fail(ctx, MTC_ERR_UNSUPPORTED, kn + ": need group_size | hidden and hidden * bits % 32 == 0");
+            rows = bi->bytes / 4;                                                  // tokens
+            n_exp = static_cast<uint32_t>(bw->bytes / (static_cast<size_t>(hidden) * row->bits / 8));    // vocab
+            if (n_exp == 0) return fail(ctx, MTC_ERR_BUFFER_SIZE, kn + ": weight holds less than one row");
+            need_buf("weight", static_cast<size_t>(n_exp) * hidden * row->bits / 8);
+            need_buf("scales", static_cast<size_t>(n_exp) * (hidden / gs) * esz);
+            need_buf("biases", static_cast<size_t>(n_exp) * (hidden / gs) * esz);
+            need_buf("indices", rows * 4);
+            need_buf("out", rows * hidden * esz);
+            break;
+        }
         case RMS_QMV: {
             need_const("in_dim", &k);
             need_const("group_size", &gs);
@@ -1337,6 +1377,10 @@ int dispatch_pass(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_bu
             break;
         case AFFINE_DQ:
             rc = mtc_affine_dequantize(ctx, st, dev("w"), dev("scales"), dev("biases"), dev("out"), rows, row->bits, static_cast<int>(gs), dtype);
+            break;
+        case DQ_GATHER:
+            rc = mtc_dequant_gather(ctx, st, dev("weight"), dev("scales"), dev("biases"), dev("indices"), dev("out"), rows,
+                                    static_cast<int>(hidden), static_cast<int>(n_exp), row->bits, static_cast<int>(gs), dtype);
             break;
         case RMS_QMV:
             rc = mtc_rms_norm_qmv(ctx, st, dev("x"), dev("norm_weight"), rms_eps, dev("weight"), dev("scales"), dev("biases"), dev("output"),

@@ -276,3 +276,18 @@ def affine_dequantize(w, scales, biases, bits: int, group_size: int, ctx: Contex
     ctx.affine_dequantize(w.data_ptr(), scales.data_ptr(), biases.data_ptr(), out.data_ptr(), out.numel(), bits, group_size,
                           _TORCH_DT[scales.dtype], stream=_stream())
     return out
+
+
+def dequant_gather(weight, scales, biases, indices, bits: int, group_size: int, ctx: Context = None):
+    """Rows ``indices`` (int32) of a quantized table ``weight [vocab, hidden*bits/32]`` dequantized: ``[n_tokens, hidden]``
+    in the type of ``scales`` (``dequant_gather_int*``, crates/metaltile-std/src/ffai/dequant_gather.rs:44-101)."""
+    for t in (weight, scales, biases, indices):
+        if not t.is_contiguous():
+            raise ValueError("operands must be contiguous")
+    vocab, hidden = weight.shape[0], weight.shape[1] * 32 // bits
+    n_tokens = indices.numel()
+    out = torch.empty((n_tokens, hidden), dtype=scales.dtype, device=weight.device)
+    ctx = ctx or context(weight.device)
+    ctx.dequant_gather(weight.data_ptr(), scales.data_ptr(), biases.data_ptr(), indices.data_ptr(), out.data_ptr(), n_tokens, hidden,
+                       vocab, bits, group_size, _TORCH_DT[scales.dtype], stream=_stream())
+    return out

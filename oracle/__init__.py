@@ -218,5 +218,13 @@ def affine_dequantize(w, scales, biases, n_elem: int, bits: int, group_size: int
     return out
 
 
+def dequant_gather(weight, scales, biases, indices, hidden: int, bits: int, group_size: int) -> np.ndarray:
+    """f32 [n_tokens, hidden] of ``dequant_gather_int*`` (crates/metaltile-std/src/ffai/dequant_gather.rs:44-94)."""
+    ww, sc, bi, ix = _u32(weight).reshape(-1), _f32(scales).reshape(-1), _f32(biases).reshape(-1), _u32(indices).reshape(-1)
+    out = np.empty((ix.size, hidden), dtype=np.float32)
+    lib().mto_dequant_gather(_p(ww), _p(sc), _p(bi), _p(ix), _p(out), _sz(ix.size), _sz(hidden), _sz(group_size), ctypes.c_uint32(bits))
+    return out
+
+
 def max_threads() -> int:
     return int(lib().mto_max_threads())

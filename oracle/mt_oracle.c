@@ -423,6 +423,26 @@ void mto_affine_dequantize(const uint32_t *w, const float *scales, const float *
     }
 }
 
+/* dequant_gather_int{2,3,4,5,6,8}, crates/metaltile-std/src/ffai/dequant_gather.rs:44-94 (CPU check :150-190): row
+ * indices[t] of a quantized table, dequantized: out[t, d] = q * scale[row, d / G] + bias[row, d / G] in f32. */
+void mto_dequant_gather(const uint32_t *weight, const float *scales, const float *biases, const uint32_t *indices, float *out,
+                        size_t n_tokens, size_t hidden, size_t group_size, uint32_t bits) {
+    const size_t wpr = hidden * bits / 32, gpr = hidden / group_size;
+    const uint32_t mask = (1u << bits) - 1u;
+    for (size_t t = 0; t < n_tokens; t++) {
+        const size_t row = indices[t];
+        const uint32_t *rw = weight + row * wpr;
+        for (size_t d = 0; d < hidden; d++) {
+            size_t bit = d * bits;
+            uint32_t q = rw[bit >> 5] >> (bit & 31u);
+            if ((bit & 31u) + bits > 32u) q |= rw[(bit >> 5) + 1] << (32u - (bit & 31u));
+            q &= mask;
+            float prod = (float)q * scales[row * gpr + d / group_size];
+            out[t * hidden + d] = prod + biases[row * gpr + d / group_size];
+        }
+    }
+}
+
 int mto_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

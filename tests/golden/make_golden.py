@@ -26,6 +26,7 @@ Reference sources restated here
   batched q/k/v decode ....... crates/metaltile-std/tests/batched_qkv_qgemv_gpu_correctness.rs:30-127,167-181,312-321
   batched 4-way decode ....... crates/metaltile-std/src/ffai/batched_4_qgemv.rs:342-440
   affine quantize / dequantize crates/metaltile-std/src/mlx/quantized.rs:3629-3667,5216-5330
+  dequantizing gather ........ crates/metaltile-std/src/ffai/dequant_gather.rs:119-243
   fused RMSNorm + decode ..... crates/metaltile-std/tests/rms_norm_qgemv_gpu_correctness.rs:35-177,232-294
 """
 from __future__ import annotations
@@ -321,6 +322,22 @@ def affine_quant_case(bits, gs, n_groups, dt):
     return dict(w=w, scales=scales, biases=mn.astype(f32), codes=codes.astype(np.uint8), words=words, meta=np.array([bits, gs, n_groups]))
 
 
+def dequant_gather_case(bits, hidden, gs, dt):
+    """gather_setup of crates/metaltile-std/src/ffai/dequant_gather.rs:119-215."""
+    vocab, ng = 8, hidden // gs
+    r, d = np.meshgrid(np.arange(vocab, dtype=np.uint64), np.arange(hidden, dtype=np.uint64), indexing="ij")
+    codes = ((((r * hidden + d) & 0xFFFFFFFF) * 2654435761 + d) & 0xFFFFFFFF).astype(np.uint32) & np.uint32((1 << bits) - 1)
+    w = pack_rows(codes, bits)
+    i = np.arange(vocab * ng)
+    scales = (f32(0.02) + (i % 7).astype(f32) * f32(0.01)).astype(f32).reshape(vocab, ng)
+    biases = (((i % 5).astype(f32) - f32(2.0)) * f32(0.05)).astype(f32).reshape(vocab, ng)
+    idx = np.array([3, 0, 7, 1, 4, 4], dtype=np.uint32)
+    s, b = round_dt(scales, dt), round_dt(biases, dt)
+    g = np.arange(hidden) // gs
+    expected = np.stack([((codes[t].astype(f32) * s[t][g]).astype(f32) + b[t][g]).astype(f32) for t in idx])
+    return dict(weight=w, scales=scales, biases=biases, indices=idx, expected=expected, meta=np.array([bits, hidden, gs, vocab]))
+
+
 def save_new(path, **arrays):
     """Write a fixture unless the file already holds exactly these arrays (keeps unchanged fixtures byte-stable)."""
     if os.path.exists(path):
@@ -344,6 +361,8 @@ def main():
     for dt in ("f32", "f16", "bf16"):
         for bits, gs, ng in ((4, 64, 8), (8, 64, 4), (2, 64, 16)):                     # quantized.rs:5253-5265
             save_new(os.path.join(HERE, f"test_affine_dequantize_int{bits}_{dt}.npz"), **affine_dequant_case(bits, gs, ng, dt))
+        for bits, hidden, gs in ((2, 256, 64), (4, 256, 64), (8, 256, 64), (3, 64, 32), (5, 64, 32), (6, 64, 32)):   # dequant_gather.rs:217-243
+            save_new(os.path.join(HERE, f"test_dequant_gather_int{bits}_{dt}.npz"), **dequant_gather_case(bits, hidden, gs, dt))
         for bits, gs in ((2, 64), (3, 32), (4, 64), (5, 32), (6, 32), (8, 64)):          # quantized.rs:5307-5330
             save_new(os.path.join(HERE, f"test_affine_quantize_int{bits}_{dt}.npz"), **affine_quant_case(bits, gs, 8, dt))
     for dt in ("f32", "f16", "bf16"):

@@ -92,3 +92,52 @@ def test_codec_refuses_partial_groups(ctx):
     with pytest.raises(MetalTileError) as ei:               # 3-bit groups of 8 are not whole words
         ctx.affine_dequantize(out.data_ptr(), sb.data_ptr(), sb.data_ptr(), w.data_ptr(), 64, 3, 8, "f32")
     assert ei.value.variant == "Unsupported"
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("bits,hidden,gs", [(2, 256, 64), (4, 256, 64), (8, 256, 64), (3, 64, 32), (5, 64, 32), (6, 64, 32)])
+def test_reference_dequant_gather_cases(ctx, bits, hidden, gs, dt):
+    """test_dequant_gather_int{2,3,4,5,6,8} (crates/metaltile-std/src/ffai/dequant_gather.rs:119-243) under the reference's
+    kernel and buffer names: a non-monotonic gather that repeats a row."""
+    fx = dict(np.load(os.path.join(GOLDEN, f"test_dequant_gather_int{bits}_{dt}.npz")))
+    n_tok = fx["indices"].size
+    bufs = {"weight": fx["weight"].tobytes(), "scales": dt_bytes(fx["scales"], dt), "biases": dt_bytes(fx["biases"], dt),
+            "indices": fx["indices"].astype(np.uint32).tobytes(), "out": bytes(n_tok * hidden * (4 if dt == "f32" else 2))}
+    res = ctx.dispatch_with_grid(f"dequant_gather_int{bits}", bufs, {"hidden": hidden, "group_size": gs}, (n_tok * hidden // 256 + 1, 1, 1),
+                                 (256, 1, 1), dtype=dt)
+    got = bytes_to_f32(res.outputs["out"], dt).reshape(n_tok, hidden)
+    assert np.array_equal(got, oracle.round_through(fx["expected"], ODT[dt]))
+
+
+@pytest.mark.parametrize("bits,hidden,gs,dt", [(4, 4096, 64, "bf16"), (3, 1024, 32, "f16"), (8, 2048, 128, "f32"), (4, 72, 24, "bf16")])
+def test_embedding_gather_at_size(ctx, bits, hidden, gs, dt):
+    """A quantized embedding table with 1000 rows, 777 lookups (repeats, first and last row); the last shape has a hidden
+    size and a group that are not multiples of 32: the one-thread-per-element form.  Equal to the oracle."""
+    import torch
+    from metaltile_b200 import ops, synth
+    vocab, n_tok = 1000, 777
+    w, s, b = synth.quantized_matrix(vocab, hidden, bits, gs, seed=50 + bits)
+    s, b = oracle.round_through(s, ODT[dt]), oracle.round_through(b, ODT[dt])
+    rng = np.random.default_rng(bits)
+    idx = rng.integers(0, vocab, n_tok).astype(np.uint32)
+    idx[:3] = (0, vocab - 1, vocab - 1)
+    got = ops.dequant_gather(to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(idx), bits, gs, ctx=ctx)
+    torch.cuda.synchronize()
+    ref = oracle.round_through(oracle.dequant_gather(w, s, b, idx, hidden, bits, gs), ODT[dt])
+    assert ctx.status_word() == 0
+    assert np.array_equal(got.float().cpu().numpy(), ref)
+
+
+def test_embedding_gather_reports_a_bad_index(ctx):
+    import torch
+    from metaltile_b200 import MetalTileError, ops, synth
+    w, s, b = synth.quantized_matrix(16, 256, 4, 64, seed=1)
+    idx = np.array([1, 99, 2], dtype=np.uint32)             # 99 is outside the table: row 0 is read, 0x904 reported
+    try:
+        got = ops.dequant_gather(to_dev(w), to_dev(s, "bf16"), to_dev(b, "bf16"), to_dev(idx), 4, 64, ctx=ctx)
+        with pytest.raises(MetalTileError):
+            ctx.sync(torch.cuda.current_stream().cuda_stream)
+        assert ctx.status_word() == 0x904
+    finally:
+        ctx.status_clear()
+    assert torch.equal(got[1], ops.dequant_gather(to_dev(w), to_dev(s, "bf16"), to_dev(b, "bf16"), to_dev(np.array([0], dtype=np.uint32)), 4, 64, ctx=ctx)[0])

@@ -220,3 +220,17 @@ def test_affine_quantize_fixtures(path):
     assert np.array_equal(oracle.unpack_matrix(words.reshape(ng, -1), gs, bits), fx["codes"])
     back = oracle.affine_dequantize(words, sc, bi, ng * gs, bits, gs).reshape(ng, gs)
     assert np.all(np.abs(back - wd.reshape(ng, gs)) <= 0.5 * sc[:, None] * (1 + 1e-5))
+
+
+DQ_GATHER = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "test_dequant_gather_*.npz")))
+
+
+@pytest.mark.parametrize("path", DQ_GATHER, ids=[os.path.basename(p)[:-4] for p in DQ_GATHER])
+def test_dequant_gather_fixtures(path):
+    """test_dequant_gather_int{2,3,4,5,6,8} (crates/metaltile-std/src/ffai/dequant_gather.rs:119-243): bit for bit."""
+    fx = _load(path)
+    dt = DT[os.path.basename(path)[:-4].rsplit("_", 1)[1]]
+    bits, hidden, gs, _ = (int(v) for v in fx["meta"])
+    got = oracle.dequant_gather(fx["weight"], oracle.round_through(fx["scales"], dt), oracle.round_through(fx["biases"], dt),
+                                fx["indices"], hidden, bits, gs)
+    assert np.array_equal(_bits(got), _bits(fx["expected"]))
