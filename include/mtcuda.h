@@ -178,6 +178,13 @@ int mtc_affine_quantize(mtc_ctx *ctx, void *stream, const void *w, void *out, vo
                         int group_size, int dtype);
 int mtc_affine_dequantize(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, void *out,
                           size_t n_elem, int bits, int group_size, int dtype);
+/* mt_qvm_b{3,4,5,6,8} / mt_qvm_int4_fast (crates/metaltile-std/src/mlx/quantized.rs:4397-4530,4582-4700): the quantized
+ * vector-matrix product, y = x W with W stored transposed: w u32[K, N*bits/32] (row d = LSB-first bit-stream of N codes),
+ * scales / biases T[K/G, N] (groups along K), x T[M, K], out T[M, N]:
+ *     out[m, c] = sum_d (q(d, c) * scale[d/G, c] + bias[d/G, c]) * x[m, d]        (f32 accumulation).
+ * K is split over CTAs; the partial sums live in a grow-only block of the context and are added in a fixed order. */
+int mtc_qvm(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x, void *out, int M, int N,
+            int K, int bits, int group_size, int dtype);
 /* dequant_gather_int{2,3,4,5,6,8} (crates/metaltile-std/src/ffai/dequant_gather.rs:44-101): rows indices[t] (u32) of a
  * quantized table weight u32[vocab, hidden*bits/32], scales / biases T[vocab, hidden/G], dequantized into
  * out T[n_tokens, hidden] = q * scale + bias (separately rounded f32 operations).  An index outside the table reads

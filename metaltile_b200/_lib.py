@@ -73,6 +73,7 @@ SIGNATURES = {
     "mtc_qmv_multi": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i]),
     "mtc_affine_quantize": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_size_t, _i, _i, _i]),
     "mtc_affine_dequantize": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_size_t, _i, _i, _i]),
+    "mtc_qvm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i]),
     "mtc_dequant_gather": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_size_t, _i, _i, _i, _i, _i]),
     "mtc_rms_norm_qmv": (_i, [_vp, _vp, _vp, _vp, ctypes.c_float, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i]),
     "mtc_qmm_multi": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_vp), _i, ctypes.c_longlong, _i, _i, _i, _i, _i, _i]),

@@ -190,6 +190,9 @@ class Context:
     def affine_dequantize(self, w, scales, biases, out, n_elem, bits, group_size, dtype, stream: int = 0):
         self._check(self._lib.mtc_affine_dequantize(self._h, stream, w, scales, biases, out, n_elem, bits, group_size, _dt(dtype)))
 
+    def qvm(self, w, scales, biases, x, out, M, N, K, bits, group_size, dtype, stream: int = 0):
+        self._check(self._lib.mtc_qvm(self._h, stream, w, scales, biases, x, out, M, N, K, bits, group_size, _dt(dtype)))
+
     def dequant_gather(self, weight, scales, biases, indices, out, n_tokens, hidden, vocab, bits, group_size, dtype, stream: int = 0):
         self._check(self._lib.mtc_dequant_gather(self._h, stream, weight, scales, biases, indices, out, n_tokens, hidden, vocab, bits,
                                                  group_size, _dt(dtype)))

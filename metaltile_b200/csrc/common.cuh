@@ -46,6 +46,8 @@ struct Ctx {
     void *d_gfrag = nullptr;       // streaming gather: activations in fragment order, their sums, the table of passes (grow-only)
     size_t gfrag_bytes = 0;
     int gather_stream = 1;         // option "gather_stream": 0 = grouped products never take the streaming kernel (gather_stream.cu)
+    void *d_qvm = nullptr;         // mtc_qvm: partial sums of the K chunks (grow-only)
+    size_t qvm_bytes = 0;
     void *d_norm = nullptr;        // mtc_rms_norm_qmv on shapes the fused kernel does not take: the normalised row (grow-only)
     size_t norm_bytes = 0;
     void *d_moe = nullptr;         // mtc_moe_experts: gate and up outputs (and permuted rows on the composed path) (grow-only)
@@ -192,6 +194,10 @@ cudaError_t launch_gather_stream(Ctx *ctx, cudaStream_t st, const void *x, const
                                  int n_experts, int group_size, int dtype, void *scratch);
 cudaError_t launch_affine_dequantize(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases, void *out,
                                      size_t n_elem, int bits, int group_size, int dt);
+int qvm_k_chunks(int sms, int N, int K, int bits, int group_size);
+bool qvm_fast_supported(int N, int K, int bits, int group_size);
+cudaError_t launch_qvm(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases, const void *x, void *out,
+                       int M, int N, int K, int bits, int group_size, int dt, float *partial, int KC);
 cudaError_t launch_dequant_gather(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases, const void *indices,
                                   void *out, size_t n_tokens, int hidden, int vocab, int bits, int group_size, int dt);
 cudaError_t launch_affine_quantize(Ctx *ctx, cudaStream_t st, const void *w, void *out, void *scales, void *biases, size_t n_groups,

@@ -46,7 +46,7 @@ bool dtype_ok(int dt) { return dt == MTC_F32 || dt == MTC_F16 || dt == MTC_BF16;
 // "gs_per_row" (hand-tuned int4/int8/mma kernels: group_size = k / gs_per_row) or
 // "group_size" (generic _b* family).  has_n: whether an `n` constexpr is bound
 // (mt_qmv / mt_qmv_int8_fast take N from the size of `out`).
-enum Family { DENSE_QMV, DENSE_QMM, GATHER_CSR, GATHER_IDX, ROUTER_TOPK, MOE_PERMUTE, MOE_UNPERMUTE, SWIGLU, BATCHED_QKV, BATCHED_4, RMS_QMV, AFFINE_Q, AFFINE_DQ, DQ_GATHER };
+enum Family { DENSE_QMV, DENSE_QMM, GATHER_CSR, GATHER_IDX, ROUTER_TOPK, MOE_PERMUTE, MOE_UNPERMUTE, SWIGLU, BATCHED_QKV, BATCHED_4, RMS_QMV, AFFINE_Q, AFFINE_DQ, DQ_GATHER, QVM };
 struct KernelRow {
     const char *name;
     Family family;
@@ -105,6 +105,13 @@ const KernelRow kKernels[] = {
     {"mt_affine_dequantize_int5", AFFINE_DQ, 5, "group_size", false},
     {"mt_affine_dequantize_int6", AFFINE_DQ, 6, "group_size", false},
     {"mt_affine_dequantize_int8", AFFINE_DQ, 8, "group_size", false},
+    // vecmat, transposed weights: crates/metaltile-std/src/mlx/quantized.rs:4397-4530,4582-4700
+    {"mt_qvm_b3", QVM, 3, "group_size", true},
+    {"mt_qvm_b4", QVM, 4, "group_size", true},
+    {"mt_qvm_b5", QVM, 5, "group_size", true},
+    {"mt_qvm_b6", QVM, 6, "group_size", true},
+    {"mt_qvm_b8", QVM, 8, "group_size", true},
+    {"mt_qvm_int4_fast", QVM, 4, "gs_per_col", true},
     // quantized embedding tables: crates/metaltile-std/src/ffai/dequant_gather.rs:44-101
     {"dequant_gather_int2", DQ_GATHER, 2, "group_size", false},
     {"dequant_gather_int3", DQ_GATHER, 3, "group_size", false},
@@ -266,6 +273,7 @@ int mtc_destroy(mtc_ctx *ctx) {
     if (ctx->d_gfrag) cudaFree(ctx->d_gfrag);
     if (ctx->d_moe) cudaFree(ctx->d_moe);
     if (ctx->d_norm) cudaFree(ctx->d_norm);
+    if (ctx->d_qvm) cudaFree(ctx->d_qvm);
     if (ctx->d_tc_scratch) cudaFree(ctx->d_tc_scratch);
     if (ctx->d_tc_counters) cudaFree(ctx->d_tc_counters);
     for (void *p : ctx->retired) cudaFree(p);
@@ -740,6 +748,31 @@ int mtc_dequant_gather(mtc_ctx *ctx, void *stream, const void *weight, const voi
     return MTC_OK;
 }
 
+int mtc_qvm(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x, void *out, int M, int N,
+            int K, int bits, int group_size, int dtype) {
+    if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "qvm: dtype must be f32, f16 or bf16");
+    const bool bits_ok = bits == 2 || bits == 3 || bits == 4 || bits == 5 || bits == 6 || bits == 8;
+    if (!bits_ok || M < 0 || N < 0 || K <= 0 || group_size <= 0 || K % group_size != 0 || (static_cast<long long>(N) * bits) % 32 != 0)
+        return fail(ctx, MTC_ERR_UNSUPPORTED, "qvm: need bits in {2,3,4,5,6,8}, group_size | K, N * bits % 32 == 0");
+    if (M == 0 || N == 0) return MTC_OK;
+    if (!w || !scales || !biases || !x || !out) return fail(ctx, MTC_ERR_INVALID, "qvm: null pointer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int kc = 1;
+    if (mtc::qvm_fast_supported(N, K, bits, group_size)) {
+        kc = mtc::qvm_k_chunks(ctx->sm_count, N, K, bits, group_size);
+        if (kc > 1) {
+            std::string why;
+            cudaError_t e = mtc::grow_block(ctx, st, &ctx->d_qvm, &ctx->qvm_bytes, static_cast<size_t>(kc) * M * N * sizeof(float), &why);
+            if (e != cudaSuccess) return fail(ctx, MTC_ERR_BUFFER, "qvm partial sums: " + (why.empty() ? std::string(cudaGetErrorString(e)) : why));
+        }
+    }
+    MTC_CUDA(ctx, mtc::launch_qvm(ctx, st, w, scales, biases, x, out, M, N, K, bits, group_size, dtype, static_cast<float *>(ctx->d_qvm), kc),
+             MTC_ERR_DISPATCH);
+    return MTC_OK;
+}
+
 int mtc_rms_norm_qmv(mtc_ctx *ctx, void *stream, const void *x, const void *norm_weight, float eps, const void *w,
                      const void *scales, const void *biases, void *out, int N, int K, int bits, int group_size, int dtype) {
     if (!ctx) return MTC_ERR_INVALID;
@@ -1197,6 +1230,26 @@ int dispatch_pass(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_bu
             need_buf("biases", rows / gs * esz);
             break;
         }
+        case QVM: {
+            need_const("k", &k);
+            need_const("n", &n);
+            need_const(row->gs_const, &gsc);
+            if (!err.empty()) break;
+            mtc_named_buf *bx = find_buf(bufs, n_bufs, "x");
+            if (!bx) { err = kn + ": buffers w, scales, biases, x, out must be bound"; break; }
+            if (k == 0 || n == 0 || gsc == 0) { err = kn + ": k, n and the group constexpr must be positive"; break; }
+            gs = std::strcmp(row->gs_const, "gs_per_col") == 0 ? k / gsc : gsc;
+            if (gs == 0 || k % gs != 0 || (static_cast<unsigned long long>(n) * row->bits) % 32 != 0)
+                return fail(ctx, MTC_ERR_UNSUPPORTED, kn + ": group size must divide k and n * bits must be a multiple of 32");
+            m = bx->bytes / (static_cast<size_t>(k) * esz);
+            if (m == 0) return fail(ctx, MTC_ERR_BUFFER_SIZE, kn + ": x holds less than one row of k");
+            need_buf("w", static_cast<size_t>(k) * n * row->bits / 8);
+            need_buf("scales", static_cast<size_t>(k / gs) * n * esz);
+            need_buf("biases", static_cast<size_t>(k / gs) * n * esz);
+            need_buf("x", m * k * esz);
+            need_buf("out", m * n * esz);
+            break;
+        }
         case DQ_GATHER: {
             need_const("hidden", &hidden);
             need_const("group_size", &gs);
@@ -1377,6 +1430,10 @@ int dispatch_pass(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_bu
             break;
         case AFFINE_DQ:
             rc = mtc_affine_dequantize(ctx, st, dev("w"), dev("scales"), dev("biases"), dev("out"), rows, row->bits, static_cast<int>(gs), dtype);
+            break;
+        case QVM:
+            rc = mtc_qvm(ctx, st, dev("w"), dev("scales"), dev("biases"), dev("x"), dev("out"), static_cast<int>(m), static_cast<int>(n),
+                         static_cast<int>(k), row->bits, static_cast<int>(gs), dtype);
             break;
         case DQ_GATHER:
             rc = mtc_dequant_gather(ctx, st, dev("weight"), dev("scales"), dev("biases"), dev("indices"), dev("out"), rows,

@@ -291,3 +291,24 @@ def dequant_gather(weight, scales, biases, indices, bits: int, group_size: int, 
     ctx.dequant_gather(weight.data_ptr(), scales.data_ptr(), biases.data_ptr(), indices.data_ptr(), out.data_ptr(), n_tokens, hidden,
                        vocab, bits, group_size, _TORCH_DT[scales.dtype], stream=_stream())
     return out
+
+
+def qvm(w, scales, biases, x, bits: int, group_size: int, out=None, ctx: Context = None):
+    """``x @ W`` with W stored transposed and quantized along K: w [K, N*bits/32], scales / biases [K/group_size, N],
+    x [M, K] -> out [M, N] (``mt_qvm_*``, crates/metaltile-std/src/mlx/quantized.rs:4397-4530)."""
+    for t in (w, scales, biases, x):
+        if not t.is_contiguous():
+            raise ValueError("operands must be contiguous")
+    x2 = x.reshape(-1, x.shape[-1])
+    m, k = x2.shape
+    n = w.shape[1] * 32 // bits
+    if w.shape[0] != k or scales.shape != (k // group_size, n) or biases.shape != scales.shape:
+        raise ValueError("w must be [K, N*bits/32] and scales / biases [K/group_size, N]")
+    if out is None:
+        out = torch.empty((m, n), dtype=x.dtype, device=x.device)
+    else:
+        _check_out(out, m, n, x)
+    ctx = ctx or context(x.device)
+    ctx.qvm(w.data_ptr(), scales.data_ptr(), biases.data_ptr(), x2.data_ptr(), out.data_ptr(), m, n, k, bits, group_size,
+            _TORCH_DT[x.dtype], stream=_stream())
+    return out

@@ -226,5 +226,14 @@ def dequant_gather(weight, scales, biases, indices, hidden: int, bits: int, grou
     return out
 
 
+def qvm(w, scales, biases, x, m: int, n: int, k: int, bits: int, group_size: int) -> np.ndarray:
+    """f32 accumulator [m, n] of ``mt_qvm_*``: w [k, n*bits/32], scales / biases [k/group_size, n], x [m, k]
+    (crates/metaltile-std/src/mlx/quantized.rs:5613-5635)."""
+    ww, sc, bi, xv = _u32(w).reshape(-1), _f32(scales).reshape(-1), _f32(biases).reshape(-1), _f32(x).reshape(-1)
+    out = np.empty((m, n), dtype=np.float32)
+    lib().mto_qvm(_p(ww), _p(sc), _p(bi), _p(xv), _p(out), _sz(m), _sz(n), _sz(k), ctypes.c_uint32(bits), _sz(group_size))
+    return out
+
+
 def max_threads() -> int:
     return int(lib().mto_max_threads())

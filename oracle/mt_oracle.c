@@ -443,6 +443,35 @@ void mto_dequant_gather(const uint32_t *weight, const float *scales, const float
     }
 }
 
+/* mt_qvm_b{3,4,5,6,8} / mt_qvm_int4_fast, crates/metaltile-std/src/mlx/quantized.rs:4397-4530 with the CPU check
+ * qvm_oracle (:5613-5635) generalised to every width: the weight matrix is [K, N], row d an LSB-first bit-stream of N codes,
+ * scales / biases [K / G, N] (groups along K):
+ *     out[m, c] = sum_d (q(d, c) * scale[d / G, c] + bias[d / G, c]) * x[m, d]     (one f32 accumulator, d ascending). */
+void mto_qvm(const uint32_t *w, const float *scales, const float *biases, const float *x, float *out, size_t m, size_t n, size_t k,
+             uint32_t bits, size_t group_size) {
+    const size_t wpr = n * bits / 32;
+    const uint32_t mask = (1u << bits) - 1u;
+#pragma omp parallel for schedule(static)
+    for (size_t c = 0; c < n; c++) {
+        for (size_t mr = 0; mr < m; mr++) {
+            float acc = 0.0f;
+            for (size_t d = 0; d < k; d++) {
+                const uint32_t *rw = w + d * wpr;
+                size_t bit = c * bits;
+                uint32_t q = rw[bit >> 5] >> (bit & 31u);
+                if ((bit & 31u) + bits > 32u) q |= rw[(bit >> 5) + 1] << (32u - (bit & 31u));
+                q &= mask;
+                size_t g = d / group_size;
+                float wv = (float)q * scales[g * n + c];
+                wv = wv + biases[g * n + c];
+                float p = wv * x[mr * k + d];
+                acc = acc + p;
+            }
+            out[mr * n + c] = acc;
+        }
+    }
+}
+
 int mto_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -338,6 +338,23 @@ def dequant_gather_case(bits, hidden, gs, dt):
     return dict(weight=w, scales=scales, biases=biases, indices=idx, expected=expected, meta=np.array([bits, hidden, gs, vocab]))
 
 
+def qvm_case(dt):
+    """test_qvm_int4_fast of crates/metaltile-std/src/mlx/quantized.rs:5637-5663 with qvm_oracle (:5613-5635)."""
+    n, k, gs = 32, 512, 64
+    w = synth_packed_w(k, n, 4)                       # [K, N] transposed: K rows of N codes
+    i = np.arange((k // gs) * n)
+    scales = (f32(0.004) + (i % 7).astype(f32) * f32(0.0008)).astype(f32).reshape(k // gs, n)
+    biases = (((i % 5).astype(f32) - f32(2.0)) * f32(0.0009)).astype(f32).reshape(k // gs, n)
+    x = (((np.arange(k) % 11).astype(f32) - f32(5.0)) * f32(0.01)).astype(f32)
+    s, b, xr = round_dt(scales, dt), round_dt(biases, dt), round_dt(x, dt)
+    codes = unpack_rows(w, n, 4).astype(f32)          # [K, N]
+    acc = np.zeros(n, dtype=np.float32)
+    for d in range(k):
+        wv = ((codes[d] * s[d // gs]).astype(f32) + b[d // gs]).astype(f32)
+        acc = (acc + (wv * xr[d]).astype(f32)).astype(f32)
+    return dict(w=w, scales=scales, biases=biases, x=x.reshape(1, k), acc=acc, meta=np.array([n, k, gs]))
+
+
 def save_new(path, **arrays):
     """Write a fixture unless the file already holds exactly these arrays (keeps unchanged fixtures byte-stable)."""
     if os.path.exists(path):
@@ -361,6 +378,7 @@ def main():
     for dt in ("f32", "f16", "bf16"):
         for bits, gs, ng in ((4, 64, 8), (8, 64, 4), (2, 64, 16)):                     # quantized.rs:5253-5265
             save_new(os.path.join(HERE, f"test_affine_dequantize_int{bits}_{dt}.npz"), **affine_dequant_case(bits, gs, ng, dt))
+        save_new(os.path.join(HERE, f"qvm_int4_fast_{dt}.npz"), **qvm_case(dt))
         for bits, hidden, gs in ((2, 256, 64), (4, 256, 64), (8, 256, 64), (3, 64, 32), (5, 64, 32), (6, 64, 32)):   # dequant_gather.rs:217-243
             save_new(os.path.join(HERE, f"test_dequant_gather_int{bits}_{dt}.npz"), **dequant_gather_case(bits, hidden, gs, dt))
         for bits, gs in ((2, 64), (3, 32), (4, 64), (5, 32), (6, 32), (8, 64)):          # quantized.rs:5307-5330

@@ -141,3 +141,41 @@ def test_embedding_gather_reports_a_bad_index(ctx):
     finally:
         ctx.status_clear()
     assert torch.equal(got[1], ops.dequant_gather(to_dev(w), to_dev(s, "bf16"), to_dev(b, "bf16"), to_dev(np.array([0], dtype=np.uint32)), 4, 64, ctx=ctx)[0])
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+def test_reference_qvm_case(ctx, dt):
+    """test_qvm_int4_fast (crates/metaltile-std/src/mlx/quantized.rs:5637-5663) under the reference's names, with its
+    tolerances (5e-3 / 5e-2 / 2e-1) and this build's."""
+    fx = dict(np.load(os.path.join(GOLDEN, f"qvm_int4_fast_{dt}.npz")))
+    n, k, gs = (int(v) for v in fx["meta"])
+    bufs = {"w": fx["w"].tobytes(), "scales": dt_bytes(fx["scales"], dt), "biases": dt_bytes(fx["biases"], dt), "x": dt_bytes(fx["x"], dt),
+            "out": bytes(n * (4 if dt == "f32" else 2))}
+    for kernel, consts in (("mt_qvm_int4_fast", {"k": k, "n": n, "gs_per_col": k // gs}), ("mt_qvm_b4", {"k": k, "n": n, "group_size": gs})):
+        res = ctx.dispatch_with_grid(kernel, bufs, consts, (n // 8, 1, 1), (64, 1, 1), dtype=dt)
+        got = bytes_to_f32(res.outputs["out"], dt)
+        assert np.any(got != 0.0)
+        assert rel_err(got.reshape(1, -1), fx["acc"].reshape(1, -1)) <= TOL[dt]
+        assert float(np.max(np.abs(got - fx["acc"]))) <= {"f32": 5e-3, "f16": 5e-2, "bf16": 2e-1}[dt]
+
+
+@pytest.mark.parametrize("m,n,k,bits,gs,dt", [
+    (1, 4096, 4096, 4, 64, "bf16"), (1, 1024, 2048, 8, 64, "f16"), (2, 512, 1024, 3, 32, "bf16"), (1, 320, 768, 5, 128, "f32"),
+    (3, 96, 256, 6, 64, "bf16"), (1, 4096, 512, 2, 64, "f16"), (1, 40, 192, 4, 48, "f32"), (1, 24, 128, 4, 64, "bf16"),
+])
+def test_qvm_matches_oracle(ctx, m, n, k, bits, gs, dt):
+    """The vector-matrix product over transposed weights against the oracle: every width, several token rows, K split over
+    CTAs and not, a column count that leaves lanes idle (40, 24), a group that is not a power of two; twice for equality."""
+    import torch
+    from metaltile_b200 import ops, synth
+    w = synth.words(k * n * bits // 32, seed=60 + bits).reshape(k, -1)                          # [K, N] codes packed along N
+    sc = oracle.round_through(0.002 + 0.018 * np.random.default_rng(bits).random((k // gs, n), dtype=np.float32), ODT[dt])
+    bi = oracle.round_through(-8.0 * sc, ODT[dt])
+    x = oracle.round_through(synth.activations(m, k, seed=7), ODT[dt])
+    got = ops.qvm(to_dev(w), to_dev(sc, dt), to_dev(bi, dt), to_dev(x, dt), bits, gs, ctx=ctx)
+    again = ops.qvm(to_dev(w), to_dev(sc, dt), to_dev(bi, dt), to_dev(x, dt), bits, gs, ctx=ctx)
+    torch.cuda.synchronize()
+    ref = oracle.qvm(w, sc, bi, x, m, n, k, bits, gs)
+    assert ctx.status_word() == 0
+    assert torch.equal(got, again)
+    assert rel_err(got.float().cpu().numpy(), ref) <= TOL[dt]

@@ -234,3 +234,14 @@ def test_dequant_gather_fixtures(path):
     got = oracle.dequant_gather(fx["weight"], oracle.round_through(fx["scales"], dt), oracle.round_through(fx["biases"], dt),
                                 fx["indices"], hidden, bits, gs)
     assert np.array_equal(_bits(got), _bits(fx["expected"]))
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+def test_qvm_fixture(golden_dir, dt):
+    """test_qvm_int4_fast (crates/metaltile-std/src/mlx/quantized.rs:5607-5663): the transposed-weight product bit for bit."""
+    fx = _load(os.path.join(golden_dir, f"qvm_int4_fast_{dt}.npz"))
+    n, k, gs = (int(v) for v in fx["meta"])
+    d = DT[dt]
+    acc = oracle.qvm(fx["w"], oracle.round_through(fx["scales"], d), oracle.round_through(fx["biases"], d), oracle.round_through(fx["x"], d),
+                     1, n, k, 4, gs)
+    assert np.array_equal(_bits(acc.reshape(-1)), _bits(fx["acc"]))
