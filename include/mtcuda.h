@@ -178,6 +178,20 @@ int mtc_affine_quantize(mtc_ctx *ctx, void *stream, const void *w, void *out, vo
                         int group_size, int dtype);
 int mtc_affine_dequantize(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, void *out,
                           size_t n_elem, int bits, int group_size, int dtype);
+/* The M = 1 tail of a mixture-of-experts layer with the expert ids read on the device (4-bit stacked weights
+ * w u32[E, out_dim, in_dim/8], scales / biases T[E, out_dim, in_dim/G], expert_indices u32[n_slots], 1 <= n_slots <= 8):
+ *   mtc_moe_down_swiglu_accum - ffai_moe_down_swiglu_accum_int4_chain8 (crates/metaltile-std/src/ffai/moe_down_swiglu_accum.rs:
+ *       158-318): out[row] = sum_k slot_weights[k] * sum_d w(e_k, row, d) * silu(gates[k][d]) * ups[k][d]; gates[k], ups[k] T[in_dim];
+ *       the inner activations stay in f32 (shared memory), as in the reference;
+ *   mtc_qmv_expert_indexed    - dequant_gemv_int4_expert_indexed (ffai/dequant_gemv_expert_indexed.rs:56-103), for n_slots
+ *       inputs at once: out[k][row] = sum_d w(e_k, row, d) * xs[k][d]; out T[n_slots, out_dim].
+ * An expert id outside the stack reads expert 0 and is reported through the status word (0x905). */
+int mtc_moe_down_swiglu_accum(mtc_ctx *ctx, void *stream, const void *const *gates, const void *const *ups, int n_slots,
+                              const void *expert_indices, const void *slot_weights, const void *w, const void *scales,
+                              const void *biases, void *out, int in_dim, int out_dim, int n_experts, int group_size, int dtype);
+int mtc_qmv_expert_indexed(mtc_ctx *ctx, void *stream, const void *const *xs, int n_slots, const void *expert_indices, const void *w,
+                           const void *scales, const void *biases, void *out, int in_dim, int out_dim, int n_experts, int group_size,
+                           int dtype);
 /* mt_qvm_b{3,4,5,6,8} / mt_qvm_int4_fast (crates/metaltile-std/src/mlx/quantized.rs:4397-4530,4582-4700): the quantized
  * vector-matrix product, y = x W with W stored transposed: w u32[K, N*bits/32] (row d = LSB-first bit-stream of N codes),
  * scales / biases T[K/G, N] (groups along K), x T[M, K], out T[M, N]:

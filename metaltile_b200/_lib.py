@@ -73,6 +73,8 @@ SIGNATURES = {
     "mtc_qmv_multi": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, ctypes.POINTER(_vp), _i, _i, _i, _i, _i, _i, _i]),
     "mtc_affine_quantize": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_size_t, _i, _i, _i]),
     "mtc_affine_dequantize": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_size_t, _i, _i, _i]),
+    "mtc_moe_down_swiglu_accum": (_i, [_vp, _vp, ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i]),
+    "mtc_qmv_expert_indexed": (_i, [_vp, _vp, ctypes.POINTER(_vp), _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i]),
     "mtc_qvm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i]),
     "mtc_dequant_gather": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, ctypes.c_size_t, _i, _i, _i, _i, _i]),
     "mtc_rms_norm_qmv": (_i, [_vp, _vp, _vp, _vp, ctypes.c_float, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i]),

@@ -190,6 +190,18 @@ class Context:
     def affine_dequantize(self, w, scales, biases, out, n_elem, bits, group_size, dtype, stream: int = 0):
         self._check(self._lib.mtc_affine_dequantize(self._h, stream, w, scales, biases, out, n_elem, bits, group_size, _dt(dtype)))
 
+    def moe_down_swiglu_accum(self, gates, ups, expert_indices, slot_weights, w, scales, biases, out, in_dim, out_dim, n_experts,
+                              group_size, dtype, stream: int = 0):
+        ga = (ctypes.c_void_p * len(gates))(*[int(p) for p in gates])
+        ua = (ctypes.c_void_p * len(ups))(*[int(p) for p in ups])
+        self._check(self._lib.mtc_moe_down_swiglu_accum(self._h, stream, ga, ua, len(gates), expert_indices, slot_weights, w, scales,
+                                                        biases, out, in_dim, out_dim, n_experts, group_size, _dt(dtype)))
+
+    def qmv_expert_indexed(self, xs, expert_indices, w, scales, biases, out, in_dim, out_dim, n_experts, group_size, dtype, stream: int = 0):
+        xa = (ctypes.c_void_p * len(xs))(*[int(p) for p in xs])
+        self._check(self._lib.mtc_qmv_expert_indexed(self._h, stream, xa, len(xs), expert_indices, w, scales, biases, out, in_dim, out_dim,
+                                                     n_experts, group_size, _dt(dtype)))
+
     def qvm(self, w, scales, biases, x, out, M, N, K, bits, group_size, dtype, stream: int = 0):
         self._check(self._lib.mtc_qvm(self._h, stream, w, scales, biases, x, out, M, N, K, bits, group_size, _dt(dtype)))
 

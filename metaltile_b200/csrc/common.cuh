@@ -46,6 +46,8 @@ struct Ctx {
     void *d_gfrag = nullptr;       // streaming gather: activations in fragment order, their sums, the table of passes (grow-only)
     size_t gfrag_bytes = 0;
     int gather_stream = 1;         // option "gather_stream": 0 = grouped products never take the streaming kernel (gather_stream.cu)
+    void *d_tail = nullptr;        // MoE decode tail: the staged inner activations of a call (grow-only)
+    size_t tail_bytes = 0;
     void *d_qvm = nullptr;         // mtc_qvm: partial sums of the K chunks (grow-only)
     size_t qvm_bytes = 0;
     void *d_norm = nullptr;        // mtc_rms_norm_qmv on shapes the fused kernel does not take: the normalised row (grow-only)
@@ -194,6 +196,10 @@ cudaError_t launch_gather_stream(Ctx *ctx, cudaStream_t st, const void *x, const
                                  int n_experts, int group_size, int dtype, void *scratch);
 cudaError_t launch_affine_dequantize(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases, void *out,
                                      size_t n_elem, int bits, int group_size, int dt);
+size_t moe_decode_smem_bytes(int n_slots, int in_dim);
+cudaError_t launch_moe_decode(Ctx *ctx, cudaStream_t st, const void *const *gate, const void *const *up, const void *experts,
+                              const void *slot_w, const void *w, const void *scales, const void *biases, void *out, int n_slots, int in_dim,
+                              int out_dim, int n_experts, int group_size, int dt, int fused, float *staged);
 int qvm_k_chunks(int sms, int N, int K, int bits, int group_size);
 bool qvm_fast_supported(int N, int K, int bits, int group_size);
 cudaError_t launch_qvm(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases, const void *x, void *out,

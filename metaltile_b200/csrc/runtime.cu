@@ -46,7 +46,7 @@ bool dtype_ok(int dt) { return dt == MTC_F32 || dt == MTC_F16 || dt == MTC_BF16;
 // "gs_per_row" (hand-tuned int4/int8/mma kernels: group_size = k / gs_per_row) or
 // "group_size" (generic _b* family).  has_n: whether an `n` constexpr is bound
 // (mt_qmv / mt_qmv_int8_fast take N from the size of `out`).
-enum Family { DENSE_QMV, DENSE_QMM, GATHER_CSR, GATHER_IDX, ROUTER_TOPK, MOE_PERMUTE, MOE_UNPERMUTE, SWIGLU, BATCHED_QKV, BATCHED_4, RMS_QMV, AFFINE_Q, AFFINE_DQ, DQ_GATHER, QVM };
+enum Family { DENSE_QMV, DENSE_QMM, GATHER_CSR, GATHER_IDX, ROUTER_TOPK, MOE_PERMUTE, MOE_UNPERMUTE, SWIGLU, BATCHED_QKV, BATCHED_4, RMS_QMV, AFFINE_Q, AFFINE_DQ, DQ_GATHER, QVM, MOE_TAIL, EXPERT_QMV };
 struct KernelRow {
     const char *name;
     Family family;
@@ -105,6 +105,9 @@ const KernelRow kKernels[] = {
     {"mt_affine_dequantize_int5", AFFINE_DQ, 5, "group_size", false},
     {"mt_affine_dequantize_int6", AFFINE_DQ, 6, "group_size", false},
     {"mt_affine_dequantize_int8", AFFINE_DQ, 8, "group_size", false},
+    // M = 1 MoE decode tail: crates/metaltile-std/src/ffai/moe_down_swiglu_accum.rs:158-318, ffai/dequant_gemv_expert_indexed.rs:56-103
+    {"ffai_moe_down_swiglu_accum_int4_chain8", MOE_TAIL, 4, "group_size", false},
+    {"dequant_gemv_int4_expert_indexed", EXPERT_QMV, 4, "group_size", false},
     // vecmat, transposed weights: crates/metaltile-std/src/mlx/quantized.rs:4397-4530,4582-4700
     {"mt_qvm_b3", QVM, 3, "group_size", true},
     {"mt_qvm_b4", QVM, 4, "group_size", true},
@@ -274,6 +277,7 @@ int mtc_destroy(mtc_ctx *ctx) {
     if (ctx->d_moe) cudaFree(ctx->d_moe);
     if (ctx->d_norm) cudaFree(ctx->d_norm);
     if (ctx->d_qvm) cudaFree(ctx->d_qvm);
+    if (ctx->d_tail) cudaFree(ctx->d_tail);
     if (ctx->d_tc_scratch) cudaFree(ctx->d_tc_scratch);
     if (ctx->d_tc_counters) cudaFree(ctx->d_tc_counters);
     for (void *p : ctx->retired) cudaFree(p);
@@ -748,6 +752,58 @@ int mtc_dequant_gather(mtc_ctx *ctx, void *stream, const void *weight, const voi
     return MTC_OK;
 }
 
+static int moe_decode_args_ok(mtc_ctx *ctx, const char *who, int n_slots, int in_dim, int out_dim, int n_experts, int group_size, int dtype) {
+    if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, std::string(who) + ": dtype must be f32, f16 or bf16");
+    if (n_slots < 1 || n_slots > 8 || in_dim <= 0 || out_dim < 0 || n_experts <= 0 || group_size <= 0 || in_dim % group_size != 0 ||
+        group_size < 8 || (group_size & (group_size - 1)) != 0 || mtc::moe_decode_smem_bytes(n_slots, in_dim) > 200 * 1024)
+        return fail(ctx, MTC_ERR_UNSUPPORTED, std::string(who) + ": need 1..8 slots, 4-bit weights, a power-of-two group_size >= 8 that divides in_dim, "
+                                              "n_slots * in_dim * 4.5 bytes of shared memory <= 200 KB");
+    return MTC_OK;
+}
+
+static int moe_decode_stage(mtc_ctx *ctx, cudaStream_t st, int n_slots, int in_dim) {
+    std::string why;
+    cudaError_t e = mtc::grow_block(ctx, st, &ctx->d_tail, &ctx->tail_bytes, mtc::moe_decode_smem_bytes(n_slots, in_dim), &why);
+    if (e != cudaSuccess) return fail(ctx, MTC_ERR_BUFFER, "moe decode tail staging: " + (why.empty() ? std::string(cudaGetErrorString(e)) : why));
+    return MTC_OK;
+}
+
+int mtc_moe_down_swiglu_accum(mtc_ctx *ctx, void *stream, const void *const *gates, const void *const *ups, int n_slots,
+                              const void *expert_indices, const void *slot_weights, const void *w, const void *scales,
+                              const void *biases, void *out, int in_dim, int out_dim, int n_experts, int group_size, int dtype) {
+    if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    int rc = moe_decode_args_ok(ctx, "moe_down_swiglu_accum", n_slots, in_dim, out_dim, n_experts, group_size, dtype);
+    if (rc != MTC_OK) return rc;
+    if (out_dim == 0) return MTC_OK;
+    if (!gates || !ups || !expert_indices || !slot_weights || !w || !scales || !biases || !out) return fail(ctx, MTC_ERR_INVALID, "moe_down_swiglu_accum: null pointer");
+    for (int k = 0; k < n_slots; ++k)
+        if (!gates[k] || !ups[k]) return fail(ctx, MTC_ERR_INVALID, "moe_down_swiglu_accum: null gate / up");
+    rc = moe_decode_stage(ctx, static_cast<cudaStream_t>(stream), n_slots, in_dim);
+    if (rc != MTC_OK) return rc;
+    MTC_CUDA(ctx, mtc::launch_moe_decode(ctx, static_cast<cudaStream_t>(stream), gates, ups, expert_indices, slot_weights, w, scales, biases, out,
+                                         n_slots, in_dim, out_dim, n_experts, group_size, dtype, 1, static_cast<float *>(ctx->d_tail)), MTC_ERR_DISPATCH);
+    return MTC_OK;
+}
+
+int mtc_qmv_expert_indexed(mtc_ctx *ctx, void *stream, const void *const *xs, int n_slots, const void *expert_indices, const void *w,
+                           const void *scales, const void *biases, void *out, int in_dim, int out_dim, int n_experts, int group_size,
+                           int dtype) {
+    if (!ctx) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    int rc = moe_decode_args_ok(ctx, "qmv_expert_indexed", n_slots, in_dim, out_dim, n_experts, group_size, dtype);
+    if (rc != MTC_OK) return rc;
+    if (out_dim == 0) return MTC_OK;
+    if (!xs || !expert_indices || !w || !scales || !biases || !out) return fail(ctx, MTC_ERR_INVALID, "qmv_expert_indexed: null pointer");
+    for (int k = 0; k < n_slots; ++k)
+        if (!xs[k]) return fail(ctx, MTC_ERR_INVALID, "qmv_expert_indexed: null input");
+    rc = moe_decode_stage(ctx, static_cast<cudaStream_t>(stream), n_slots, in_dim);
+    if (rc != MTC_OK) return rc;
+    MTC_CUDA(ctx, mtc::launch_moe_decode(ctx, static_cast<cudaStream_t>(stream), xs, nullptr, expert_indices, nullptr, w, scales, biases, out,
+                                         n_slots, in_dim, out_dim, n_experts, group_size, dtype, 0, static_cast<float *>(ctx->d_tail)), MTC_ERR_DISPATCH);
+    return MTC_OK;
+}
+
 int mtc_qvm(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x, void *out, int M, int N,
             int K, int bits, int group_size, int dtype) {
     if (!ctx) return MTC_ERR_INVALID;
@@ -1130,7 +1186,7 @@ int dispatch_pass(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_bu
     auto need_const = [&](const char *name, uint32_t *v) {
         if (!read_const(bufs, n_bufs, name, v) && err.empty()) err = kn + ": constexpr " + name + " missing";
     };
-    st_bufs.reserve(20);
+    st_bufs.reserve(32);
     float rms_eps = 0.0f;
     int nb = 0;                          // fused decode projections: count, rows of each, buffer names of each
     uint32_t b_out[4] = {0, 0, 0, 0};
@@ -1228,6 +1284,36 @@ int dispatch_pass(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_bu
             need_buf("out", quant ? rows * row->bits / 8 : rows * esz);
             need_buf("scales", rows / gs * esz);
             need_buf("biases", rows / gs * esz);
+            break;
+        }
+        case MOE_TAIL:
+        case EXPERT_QMV: {
+            need_const("in_dim", &k);
+            need_const("out_dim", &n);
+            need_const("group_size", &gs);
+            if (!err.empty()) break;
+            mtc_named_buf *bw = find_buf(bufs, n_bufs, "weights_stacked");
+            if (!bw) { err = kn + ": buffer 'weights_stacked' must be bound"; break; }
+            if (k == 0 || n == 0 || gs == 0 || k % gs != 0 || k % 8 != 0) return fail(ctx, MTC_ERR_UNSUPPORTED, kn + ": need group_size | in_dim and in_dim % 8 == 0");
+            n_exp = static_cast<uint32_t>(bw->bytes / (static_cast<size_t>(n) * k / 2));
+            if (n_exp == 0) return fail(ctx, MTC_ERR_BUFFER_SIZE, kn + ": weights hold less than one expert");
+            need_buf("weights_stacked", static_cast<size_t>(n_exp) * n * k / 2);
+            need_buf("scales_stacked", static_cast<size_t>(n_exp) * n * (k / gs) * esz);
+            need_buf("biases_stacked", static_cast<size_t>(n_exp) * n * (k / gs) * esz);
+            need_buf("output", static_cast<size_t>(n) * esz);
+            if (row->family == MOE_TAIL) {
+                for (int i = 0; i < 8; ++i) {
+                    b_names[i / 4][i % 4] = "gate_" + std::to_string(i);      // 16 names in the two name tables
+                    b_names[2 + i / 4][i % 4] = "up_" + std::to_string(i);
+                    need_buf(b_names[i / 4][i % 4].c_str(), static_cast<size_t>(k) * esz);
+                    need_buf(b_names[2 + i / 4][i % 4].c_str(), static_cast<size_t>(k) * esz);
+                }
+                need_buf("expert_indices", 8 * 4);
+                need_buf("slot_weights", 8 * esz);
+            } else {
+                need_buf("input", static_cast<size_t>(k) * esz);
+                need_buf("expert_index", 4);
+            }
             break;
         }
         case QVM: {
@@ -1431,6 +1517,23 @@ int dispatch_pass(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_bu
         case AFFINE_DQ:
             rc = mtc_affine_dequantize(ctx, st, dev("w"), dev("scales"), dev("biases"), dev("out"), rows, row->bits, static_cast<int>(gs), dtype);
             break;
+        case MOE_TAIL: {
+            const void *gs8[8], *us8[8];
+            for (int i = 0; i < 8; ++i) {
+                gs8[i] = dev(b_names[i / 4][i % 4].c_str());
+                us8[i] = dev(b_names[2 + i / 4][i % 4].c_str());
+            }
+            rc = mtc_moe_down_swiglu_accum(ctx, st, gs8, us8, 8, dev("expert_indices"), dev("slot_weights"), dev("weights_stacked"),
+                                           dev("scales_stacked"), dev("biases_stacked"), dev("output"), static_cast<int>(k), static_cast<int>(n),
+                                           static_cast<int>(n_exp), static_cast<int>(gs), dtype);
+            break;
+        }
+        case EXPERT_QMV: {
+            const void *xs1[1] = {dev("input")};
+            rc = mtc_qmv_expert_indexed(ctx, st, xs1, 1, dev("expert_index"), dev("weights_stacked"), dev("scales_stacked"), dev("biases_stacked"),
+                                        dev("output"), static_cast<int>(k), static_cast<int>(n), static_cast<int>(n_exp), static_cast<int>(gs), dtype);
+            break;
+        }
         case QVM:
             rc = mtc_qvm(ctx, st, dev("w"), dev("scales"), dev("biases"), dev("x"), dev("out"), static_cast<int>(m), static_cast<int>(n),
                          static_cast<int>(k), row->bits, static_cast<int>(gs), dtype);

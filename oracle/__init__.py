@@ -235,5 +235,17 @@ def qvm(w, scales, biases, x, m: int, n: int, k: int, bits: int, group_size: int
     return out
 
 
+def moe_down_swiglu_accum(gates, ups, experts, slot_weights, w, scales, biases, in_dim: int, out_dim: int, group_size: int) -> np.ndarray:
+    """f32 [out_dim] of ``ffai_moe_down_swiglu_accum_int4_chain8`` (crates/metaltile-std/src/ffai/moe_down_swiglu_accum.rs:
+    355-402): gates / ups [n_slots, in_dim], stacked int4 weights [E, out_dim, in_dim/8], scales / biases [E, out_dim, in_dim/G]."""
+    g, u = _f32(gates).reshape(-1), _f32(ups).reshape(-1)
+    ex, sw = _u32(experts).reshape(-1), _f32(slot_weights).reshape(-1)
+    ww, sc, bi = _u32(w).reshape(-1), _f32(scales).reshape(-1), _f32(biases).reshape(-1)
+    out = np.empty(out_dim, dtype=np.float32)
+    lib().mto_moe_down_swiglu_accum(_p(g), _p(u), _p(ex), _p(sw), _p(ww), _p(sc), _p(bi), _p(out), _sz(ex.size), _sz(in_dim), _sz(out_dim),
+                                    _sz(group_size))
+    return out
+
+
 def max_threads() -> int:
     return int(lib().mto_max_threads())

@@ -472,6 +472,40 @@ void mto_qvm(const uint32_t *w, const float *scales, const float *biases, const 
     }
 }
 
+/* ffai_moe_down_swiglu_accum_int4_chain8, crates/metaltile-std/src/ffai/moe_down_swiglu_accum.rs:158-318 with the CPU check
+ * `oracle` (:355-402): the M = 1 MoE decode tail for n_slots routed experts,
+ *     out[row] = sum_k sum_d (sw[k] * (q(e_k, row, d) * scale + bias)) * inner_k[d],   inner_k[d] = silu(gate_k[d]) * up_k[d],
+ * one f32 accumulator, slots, packs and nibbles ascending; gates / ups are [n_slots, in_dim]. */
+void mto_moe_down_swiglu_accum(const float *gates, const float *ups, const uint32_t *experts, const float *slot_w, const uint32_t *w,
+                               const float *scales, const float *biases, float *out, size_t n_slots, size_t in_dim, size_t out_dim,
+                               size_t group_size) {
+    const size_t ppr = in_dim / 8, gpr = in_dim / group_size;
+    float *inner = (float *)malloc(n_slots * in_dim * sizeof(float));
+    for (size_t i = 0; i < n_slots * in_dim; i++) {
+        float g = gates[i];
+        float silu = g / (1.0f + expf(-g));
+        inner[i] = silu * ups[i];
+    }
+    for (size_t row = 0; row < out_dim; row++) {
+        float acc = 0.0f;
+        for (size_t k = 0; k < n_slots; k++) {
+            const size_t e = experts[k];
+            const uint32_t *rw = w + (e * out_dim + row) * ppr;
+            const float *rs = scales + (e * out_dim + row) * gpr, *rb = biases + (e * out_dim + row) * gpr;
+            for (size_t d = 0; d < in_dim; d++) {
+                float q = (float)((rw[d >> 3] >> ((d & 7u) * 4u)) & 0xFu);
+                float dq = q * rs[d / group_size];
+                dq = dq + rb[d / group_size];
+                float t = slot_w[k] * dq;
+                t = t * inner[k * in_dim + d];
+                acc = acc + t;
+            }
+        }
+        out[row] = acc;
+    }
+    free(inner);
+}
+
 int mto_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

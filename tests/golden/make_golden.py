@@ -355,6 +355,53 @@ def qvm_case(dt):
     return dict(w=w, scales=scales, biases=biases, x=x.reshape(1, k), acc=acc, meta=np.array([n, k, gs]))
 
 
+def expert_indexed_case(dt):
+    """test_dequant_gemv_int4_expert_indexed of crates/metaltile-std/src/ffai/dequant_gemv_expert_indexed.rs:129-208."""
+    ne, od, idim, gs, expert = 4, 4, 256, 64, 2
+    idx = np.arange(ne * od * idim, dtype=np.uint64)
+    codes = (((idx & 0xFFFFFFFF) * 2654435761) & 0xFFFFFFFF).astype(np.uint32) & np.uint32(15)
+    w = pack_rows(codes.reshape(ne * od, idim), 4)
+    i = np.arange(ne * od * (idim // gs))
+    scales = (f32(0.004) + (i % 7).astype(f32) * f32(0.0008)).astype(f32)
+    biases = (((i % 5).astype(f32) - f32(2.0)) * f32(0.0009)).astype(f32)
+    x = (((np.arange(idim) % 11).astype(f32) - f32(5.0)) * f32(0.01)).astype(f32)
+    s, b, xr = round_dt(scales, dt).reshape(ne * od, -1), round_dt(biases, dt).reshape(ne * od, -1), round_dt(x, dt)
+    sl = slice(expert * od, (expert + 1) * od)
+    acc = qmm_ref(codes.reshape(ne * od, idim)[sl], s[sl], b[sl], xr.reshape(1, idim), gs).reshape(-1)
+    return dict(w=w, scales=scales, biases=biases, x=x, acc=acc, meta=np.array([ne, od, idim, gs, expert]))
+
+
+def moe_decode_tail_case(dt):
+    """test_moe_down_swiglu_accum_int4_chain8 of crates/metaltile-std/src/ffai/moe_down_swiglu_accum.rs:355-487 (setup(4, 64, 8, 32))."""
+    ne, idim, od, gs, ns = 4, 64, 8, 32, 8
+    kd = np.arange(ns * idim).astype(f32)
+    gates = (np.sin((kd * f32(0.017)).astype(f32)).astype(f32) * f32(0.5)).astype(f32).reshape(ns, idim)
+    ups = (np.cos((kd * f32(0.021)).astype(f32)).astype(f32) * f32(0.5)).astype(f32).reshape(ns, idim)
+    experts = (np.arange(ns) % ne).astype(np.uint32)
+    sw = (f32(0.1) + np.arange(ns).astype(f32) * f32(0.05)).astype(f32)
+    codes = ((np.arange(ne * od * idim, dtype=np.uint64) * 7 + 3) & 15).astype(np.uint32).reshape(ne * od, idim)
+    w = pack_rows(codes, 4)
+    i = np.arange(ne * od * (idim // gs)).astype(f32)
+    scales = (f32(0.005) + (f32(0.001) * np.sin((i * f32(0.03)).astype(f32)).astype(f32)).astype(f32)).astype(f32)
+    biases = (f32(-0.02) + (f32(0.005) * np.cos((i * f32(0.07)).astype(f32)).astype(f32)).astype(f32)).astype(f32)
+    g_r, u_r, sw_r = round_dt(gates, dt), round_dt(ups, dt), round_dt(sw, dt)
+    s_r, b_r = round_dt(scales, dt).reshape(ne * od, -1), round_dt(biases, dt).reshape(ne * od, -1)
+    silu = (g_r / (f32(1.0) + np.exp(-g_r).astype(f32)).astype(f32)).astype(f32)
+    inner = (silu * u_r).astype(f32)
+    out = np.zeros(od, dtype=np.float32)
+    cf = codes.astype(f32)
+    for row in range(od):
+        acc = f32(0.0)
+        for k in range(ns):
+            r = int(experts[k]) * od + row
+            for d in range(idim):
+                dq = f32(f32(cf[r, d] * s_r[r, d // gs]) + b_r[r, d // gs])
+                acc = f32(acc + f32(f32(sw_r[k] * dq) * inner[k, d]))
+        out[row] = acc
+    return dict(gates=gates, ups=ups, experts=experts, slot_weights=sw, w=w, scales=scales, biases=biases, acc=out,
+                meta=np.array([ne, idim, od, gs, ns]))
+
+
 def save_new(path, **arrays):
     """Write a fixture unless the file already holds exactly these arrays (keeps unchanged fixtures byte-stable)."""
     if os.path.exists(path):
@@ -379,6 +426,8 @@ def main():
         for bits, gs, ng in ((4, 64, 8), (8, 64, 4), (2, 64, 16)):                     # quantized.rs:5253-5265
             save_new(os.path.join(HERE, f"test_affine_dequantize_int{bits}_{dt}.npz"), **affine_dequant_case(bits, gs, ng, dt))
         save_new(os.path.join(HERE, f"qvm_int4_fast_{dt}.npz"), **qvm_case(dt))
+        save_new(os.path.join(HERE, f"expert_indexed_gemv_{dt}.npz"), **expert_indexed_case(dt))
+        save_new(os.path.join(HERE, f"moe_down_swiglu_accum_{dt}.npz"), **moe_decode_tail_case(dt))
         for bits, hidden, gs in ((2, 256, 64), (4, 256, 64), (8, 256, 64), (3, 64, 32), (5, 64, 32), (6, 64, 32)):   # dequant_gather.rs:217-243
             save_new(os.path.join(HERE, f"test_dequant_gather_int{bits}_{dt}.npz"), **dequant_gather_case(bits, hidden, gs, dt))
         for bits, gs in ((2, 64), (3, 32), (4, 64), (5, 32), (6, 32), (8, 64)):          # quantized.rs:5307-5330

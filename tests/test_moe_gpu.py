@@ -348,3 +348,93 @@ def test_moe_experts_reports_a_bad_row_index(ctx):
         assert ctx.status_word() == 0x903
     finally:
         ctx.status_clear()
+
+
+@pytest.mark.parametrize("dt", DT_NAMES)
+def test_reference_decode_tail_cases(ctx, dt):
+    """test_dequant_gemv_int4_expert_indexed (ffai/dequant_gemv_expert_indexed.rs:129-208) and
+    test_moe_down_swiglu_accum_int4_chain8 (ffai/moe_down_swiglu_accum.rs:405-487) under the reference's names, with its
+    tolerances (5e-3 / 5e-2 / 2e-1) and this build's."""
+    ref_tol = {"f32": 5e-3, "f16": 5e-2, "bf16": 2e-1}[dt]
+    esz = 4 if dt == "f32" else 2
+    fx = dict(np.load(os.path.join(GOLDEN, f"expert_indexed_gemv_{dt}.npz")))
+    ne, od, idim, gs, e = (int(v) for v in fx["meta"])
+    bufs = {"weights_stacked": fx["w"].tobytes(), "scales_stacked": dt_bytes(fx["scales"], dt), "biases_stacked": dt_bytes(fx["biases"], dt),
+            "input": dt_bytes(fx["x"], dt), "expert_index": np.array([e], dtype=np.uint32).tobytes(), "output": bytes(od * esz)}
+    res = ctx.dispatch_with_grid("dequant_gemv_int4_expert_indexed", bufs, {"in_dim": idim, "out_dim": od, "group_size": gs}, (od, 1, 1),
+                                 (64, 1, 1), dtype=dt, outputs=("output",))
+    got = bytes_to_f32(res.outputs["output"], dt)
+    assert np.any(got != 0.0) and float(np.max(np.abs(got - fx["acc"]))) <= ref_tol
+    assert rel_err(got.reshape(1, -1), fx["acc"].reshape(1, -1)) <= TOL[dt]
+    fx = dict(np.load(os.path.join(GOLDEN, f"moe_down_swiglu_accum_{dt}.npz")))
+    ne, idim, od, gs, ns = (int(v) for v in fx["meta"])
+    bufs = {"weights_stacked": fx["w"].tobytes(), "scales_stacked": dt_bytes(fx["scales"], dt), "biases_stacked": dt_bytes(fx["biases"], dt),
+            "expert_indices": fx["experts"].astype(np.uint32).tobytes(), "slot_weights": dt_bytes(fx["slot_weights"], dt), "output": bytes(od * esz)}
+    for k in range(ns):
+        bufs[f"gate_{k}"], bufs[f"up_{k}"] = dt_bytes(fx["gates"][k], dt), dt_bytes(fx["ups"][k], dt)
+    res = ctx.dispatch_with_grid("ffai_moe_down_swiglu_accum_int4_chain8", bufs, {"in_dim": idim, "out_dim": od, "group_size": gs},
+                                 (od, 1, 1), (64, 1, 1), dtype=dt, outputs=("output",))
+    got = bytes_to_f32(res.outputs["output"], dt)
+    assert np.any(got != 0.0) and float(np.max(np.abs(got - fx["acc"]))) <= ref_tol
+    assert rel_err(got.reshape(1, -1), fx["acc"].reshape(1, -1)) <= TOL[dt]
+
+
+@pytest.mark.parametrize("dt,n_slots,in_dim,out_dim,gs", [("bf16", 8, 768, 2048, 64), ("f16", 4, 512, 300, 128), ("f32", 8, 64, 40, 32),
+                                                          ("bf16", 2, 2048, 72, 64)])      # the last: more than 4 words per lane
+def test_moe_decode_tail_at_size(ctx, dt, n_slots, in_dim, out_dim, gs):
+    """The fused M = 1 tail (SwiGLU, expert-indexed down projection, weighted sum over the routed slots) against the oracle,
+    and against its unfused composition: mt_swiglu per slot, the expert-indexed product of all slots in one launch, the sum."""
+    import torch
+    from metaltile_b200 import ops, synth
+    from metaltile_b200.ops import _TORCH_DT
+    E = 16
+    w, s, b = synth.quantized_matrix(E * out_dim, in_dim, 4, gs, seed=70)
+    rt = lambda a: oracle.round_through(a, ODT[dt])
+    s, b = rt(s), rt(b)
+    gates, ups = rt(synth.activations(n_slots, in_dim, seed=71)), rt(synth.activations(n_slots, in_dim, seed=72))
+    experts = np.array([(5 * k + 3) % E for k in range(n_slots)], dtype=np.uint32)
+    sw = rt((0.05 + 0.03 * np.arange(n_slots)).astype(np.float32))
+    wd, sd, bd = to_dev(w), to_dev(s, dt), to_dev(b, dt)
+    gd, ud, ed, swd = to_dev(gates, dt), to_dev(ups, dt), to_dev(experts), to_dev(sw, dt)
+    out = torch.zeros(out_dim, dtype=gd.dtype, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    esz = gd.element_size()
+    ctx.moe_down_swiglu_accum([gd.data_ptr() + k * in_dim * esz for k in range(n_slots)], [ud.data_ptr() + k * in_dim * esz for k in range(n_slots)],
+                              ed.data_ptr(), swd.data_ptr(), wd.data_ptr(), sd.data_ptr(), bd.data_ptr(), out.data_ptr(), in_dim, out_dim, E, gs,
+                              _TORCH_DT[gd.dtype], stream=st)
+    torch.cuda.synchronize()
+    ref = oracle.moe_down_swiglu_accum(gates, ups, experts, sw, w, s, b, in_dim, out_dim, gs)
+    assert ctx.status_word() == 0
+    assert rel_err(out.float().cpu().numpy().reshape(1, -1), ref.reshape(1, -1)) <= TOL[dt]
+    # unfused: swiglu (rounded to T, as the stand-alone kernel stores it), expert-indexed products, weighted sum on the host
+    act = ops.swiglu(gd, ud, ctx=ctx)
+    per = torch.zeros((n_slots, out_dim), dtype=gd.dtype, device="cuda")
+    ctx.qmv_expert_indexed([act.data_ptr() + k * in_dim * esz for k in range(n_slots)], ed.data_ptr(), wd.data_ptr(), sd.data_ptr(), bd.data_ptr(),
+                           per.data_ptr(), in_dim, out_dim, E, gs, _TORCH_DT[gd.dtype], stream=st)
+    torch.cuda.synchronize()
+    act_h = act.float().cpu().numpy()
+    for k in (0, n_slots - 1):
+        e = int(experts[k])
+        sl = slice(e * out_dim, (e + 1) * out_dim)
+        assert rel_err(per[k].float().cpu().numpy().reshape(1, -1), oracle.qmm(w[sl], s[sl], b[sl], act_h[k:k + 1], 1, out_dim, in_dim, 4, gs)) <= TOL[dt]
+    comp = (per.float().cpu().numpy() * sw[:, None]).sum(axis=0)
+    assert rel_err(out.float().cpu().numpy().reshape(1, -1), comp.reshape(1, -1)) <= 3 * TOL[dt]
+
+
+def test_moe_decode_tail_reports_a_bad_expert(ctx):
+    import torch
+    from metaltile_b200 import MetalTileError, synth
+    from metaltile_b200.ops import _TORCH_DT
+    E, in_dim, out_dim = 4, 64, 16
+    w, s, b = synth.quantized_matrix(E * out_dim, in_dim, 4, 32, seed=73)
+    x = to_dev(synth.activations(1, in_dim, seed=74), "bf16")
+    out = torch.zeros((1, out_dim), dtype=torch.bfloat16, device="cuda")
+    bad = to_dev(np.array([77], dtype=np.uint32))
+    try:
+        ctx.qmv_expert_indexed([x.data_ptr()], bad.data_ptr(), to_dev(w).data_ptr(), to_dev(s, "bf16").data_ptr(), to_dev(b, "bf16").data_ptr(),
+                               out.data_ptr(), in_dim, out_dim, E, 32, _TORCH_DT[x.dtype], stream=torch.cuda.current_stream().cuda_stream)
+        with pytest.raises(MetalTileError):
+            ctx.sync(torch.cuda.current_stream().cuda_stream)
+        assert ctx.status_word() == 0x905
+    finally:
+        ctx.status_clear()

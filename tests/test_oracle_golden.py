@@ -245,3 +245,24 @@ def test_qvm_fixture(golden_dir, dt):
     acc = oracle.qvm(fx["w"], oracle.round_through(fx["scales"], d), oracle.round_through(fx["biases"], d), oracle.round_through(fx["x"], d),
                      1, n, k, 4, gs)
     assert np.array_equal(_bits(acc.reshape(-1)), _bits(fx["acc"]))
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+def test_moe_decode_tail_fixtures(golden_dir, dt):
+    """test_dequant_gemv_int4_expert_indexed (ffai/dequant_gemv_expert_indexed.rs:129-208) and
+    test_moe_down_swiglu_accum_int4_chain8 (ffai/moe_down_swiglu_accum.rs:355-487).  The expert-indexed product is the plain
+    product on the chosen expert's slab, bit for bit; the fused tail agrees with the numpy restatement to within the last
+    bits of expf (numpy's float32 exp and libm's expf are not the same function)."""
+    d = DT[dt]
+    fx = _load(os.path.join(golden_dir, f"expert_indexed_gemv_{dt}.npz"))
+    ne, od, idim, gs, e = (int(v) for v in fx["meta"])
+    s, b = oracle.round_through(fx["scales"], d).reshape(ne * od, -1), oracle.round_through(fx["biases"], d).reshape(ne * od, -1)
+    sl = slice(e * od, (e + 1) * od)
+    acc = oracle.qmm(fx["w"][sl], s[sl], b[sl], oracle.round_through(fx["x"], d).reshape(1, idim), 1, od, idim, 4, gs)
+    assert np.array_equal(_bits(acc.reshape(-1)), _bits(fx["acc"]))
+    fx = _load(os.path.join(golden_dir, f"moe_down_swiglu_accum_{dt}.npz"))
+    ne, idim, od, gs, ns = (int(v) for v in fx["meta"])
+    rt = lambda a: oracle.round_through(a, d)
+    got = oracle.moe_down_swiglu_accum(rt(fx["gates"]), rt(fx["ups"]), fx["experts"], rt(fx["slot_weights"]), fx["w"], rt(fx["scales"]),
+                                       rt(fx["biases"]), idim, od, gs)
+    assert np.max(np.abs(got - fx["acc"])) <= 1e-6 * max(1.0, float(np.max(np.abs(fx["acc"]))))
