@@ -242,8 +242,9 @@ int mtc_peer_barrier(mtc_ctx *ctx, void *stream, void *const *peer_flags, int n_
  *                      shapes run as 16-row chunks of the small-M tensor-core qmv when that fills the GPU better)
  *   "qmm_raw"          0: the dequant warps of the tensor-core kernel load packed words straight from global
  *                      memory instead of through the shared-memory staging buffers (default 1)
- *   "qmm_wide"         0: a dense work item of the tensor-core kernel never covers two 256-row token chunks
- *                      (default 1 for M > 256: one dequantised weight stage meets two activation chunks; same results)
+ *   "qmm_wide"         a dense work item of the tensor-core kernel covers two 256-row token chunks (one dequantised
+ *                      weight stage meets two activation chunks; same results): 0 never, 1 (default) when that saves
+ *                      rounds of the grid (M > 256), 2 whenever M > 256
  *   "qmv_stream"       the streaming decode kernel (4-bit, f16 / bf16, K % 512 == 0, group 64 or 128, 16-byte aligned
  *                      pointers): 1 (default) takes M = 1; 2 takes every M <= 8 (slower than the register-ring kernel
  *                      there); 0 never.  mtc_qmv_batched fuses its projections into one launch where this kernel

@@ -970,7 +970,20 @@ cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const v
     {
         // Two token chunks per item: the dequantised W stage, which sets the pace of a k block, is built once per
         // 2 TN token rows instead of once per TN.
+        // Worth it when it saves rounds of the grid: a k block of a wide item costs ~1.55 x one of a single-chunk item
+        // (measured), so 7 rounds of single chunks against 3 wide rounds + a short one is a win, one round against one
+        // wide round on half the SMs is not.
+        bool wide_pays = false;
         if (ctx->qmm_wide && TN == TN_MAX && M > TN_MAX) {
+            const int single = p.n_tiles * p.m_chunks, units = p.n_tiles * ((M + 2 * TN - 1) / (2 * TN));
+            const double cost_single = static_cast<double>((single + sms - 1) / sms);
+            const int left = units % sms;
+            const bool two_halves = M % (2 * TN) == 0 || M % (2 * TN) > TN;
+            const bool split_tail = units > sms && left > 0 && 2 * left <= sms && two_halves;
+            const double cost_wide = 1.55 * (units / sms) + (left == 0 ? 0.0 : (split_tail ? 1.0 : 1.55));
+            wide_pays = cost_wide < cost_single || ctx->qmm_wide == 2;      // 2: whenever the shape allows (tests)
+        }
+        if (wide_pays) {
             p.wide = 1;
             plan_smem(p, ctx, bits);
             if (p.nst < 2) {

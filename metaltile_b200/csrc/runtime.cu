@@ -926,7 +926,7 @@ int mtc_set_option(mtc_ctx *ctx, const char *name, int value) {
         return MTC_OK;
     }
     if (std::strcmp(name, "qmm_wide") == 0) {
-        ctx->qmm_wide = value ? 1 : 0;
+        ctx->qmm_wide = value < 0 ? 0 : (value > 2 ? 2 : value);
         return MTC_OK;
     }
     return fail(ctx, MTC_ERR_UNSUPPORTED, std::string("unknown option: ") + name);

@@ -208,16 +208,17 @@ def test_k_not_a_multiple_of_256(ctx):
     (1024, 9600, 256, 4, 64, "f16"),       # the same with two units per weight tile
 ])
 def test_wide_items_equal_single_chunk_items(ctx, m, n, k, bits, gs, dt):
-    """"qmm_wide" (default 1): a dense work item covers two 256-row token chunks that share every dequantised weight
+    """"qmm_wide": a dense work item covers two 256-row token chunks that share every dequantised weight
     stage.  Every output is the same sum in the same order as with one chunk per item: bit-identical."""
     import torch
     from metaltile_b200 import ops
     w, s, b, x = dense_case(m, n, k, bits, gs, dt, seed=21, salt=m)
     args = (to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt), bits, gs)
-    wide = ops.qmm(*args)
-    again = ops.qmm(*args)
-    ctx.set_option("qmm_wide", 0)
+    ctx.set_option("qmm_wide", 2)              # whenever the shape allows (the default takes them only when they save rounds)
     try:
+        wide = ops.qmm(*args)
+        again = ops.qmm(*args)
+        ctx.set_option("qmm_wide", 0)
         single = ops.qmm(*args)
         torch.cuda.synchronize()
     finally:
