@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(256) gather_prep_kernel(const void *x, const v
             const int rows = hi - lo, np = (rows + TB - 1) / TB;
             const int full = rows / TB, rem = rows - full * TB;
             const int c = full * (2 + (TB + 7) / 8) + (rem ? 2 + (rem + 7) / 8 : 0);
-            int pp = np, pc = c;                       // inclusive scans over the 32 experts of this round
+            int pp = np, pc = c;                       // inclusive scans over these 32 experts
             for (int d = 1; d < 32; d <<= 1) {
                 const int up = __shfl_up_sync(0xffffffffu, pp, d), uc = __shfl_up_sync(0xffffffffu, pc, d);
                 if (lane >= d) {

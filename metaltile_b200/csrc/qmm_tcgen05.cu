@@ -829,7 +829,7 @@ template <int BITS>
 cudaError_t launch_bits(cudaStream_t st, const CUtensorMap &tmap, const QmmParams &p, int grid) {
     auto kern = qmm_tcgen05_kernel<BITS>;
     constexpr size_t smem = qmm_smem_bytes<BITS>();
-    static_assert(smem <= 227 * 1024, "shared memory budget");
+    static_assert(smem <= 227 * 1024, "shared memory per CTA");
     static PerDeviceAttr attr;
     cudaError_t e = attr.set(kern, smem);
     if (e != cudaSuccess) return e;
