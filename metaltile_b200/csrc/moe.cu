@@ -82,9 +82,11 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const void *logits, ui
 // ---- MoE sort ------------------------------------------------------------------------------------
 // The reference leaves the sort to its caller (moe.rs:253-271 states the contract only).  Definition
 // used here: stable sort of the flat slots f = token*k + slot by (expert[f], f).  One CTA of 1024
-// threads: (1) histogram + exclusive scan -> expert_offsets, (2) 1024-slot chunks in order; inside a
-// chunk a warp ranks its lanes per expert with __match_any_sync, per-warp counts are prefix-summed
-// per expert over the 32 warps, and a running cursor per expert carries over to the next chunk.
+// threads; warp w owns the contiguous slots [w * per, (w + 1) * per) and walks them 32 at a time:
+// (1) per-warp, per-expert counts (lanes of a sub-chunk are grouped per expert with __match_any_sync; no
+// atomics: a warp only writes its own row), (2) per expert a prefix over the 32 warps and the expert
+// totals, scanned into expert_offsets, (3) the same walk again, now placing: position = first row of the
+// expert + slots of earlier warps + slots of earlier sub-chunks of this warp + rank inside the sub-chunk.
 constexpr int kSortThreads = 1024;
 
 __global__ void __launch_bounds__(kSortThreads) moe_sort_kernel(const uint32_t *topk_idx, int total, int k, int n_experts,
@@ -92,16 +94,35 @@ __global__ void __launch_bounds__(kSortThreads) moe_sort_kernel(const uint32_t *
                                                                 uint32_t *expert_offsets, uint32_t *row_expert,
                                                                 uint32_t *status) {
     extern __shared__ uint32_t sm[];
-    uint32_t *cursor = sm;                         // [n_experts + 1]
-    uint32_t *wcnt = sm + n_experts + 1;           // [32][n_experts] per-warp counts, then bases
+    uint32_t *cursor = sm;                         // [n_experts + 1] first row of every expert
+    uint32_t *wcnt = sm + n_experts + 1;           // [32][n_experts] per-warp counts, then running positions
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    for (int e = tid; e <= n_experts; e += kSortThreads) cursor[e] = 0;
+    const int per = ((total + 32 * 32 - 1) / (32 * 32)) * 32;          // slots per warp, whole sub-chunks
+    const int f0 = warp * per, f1 = min(f0 + per, total);
+    for (int i = tid; i < 32 * n_experts; i += kSortThreads) wcnt[i] = 0;
     __syncthreads();
-    for (int f = tid; f < total; f += kSortThreads) {
-        const uint32_t e = topk_idx[f];
-        if (e < static_cast<uint32_t>(n_experts)) atomicAdd(&cursor[e + 1], 1u);
-        else atomicCAS(status, 0u, 0x501u);        // expert id out of range: recorded, slot skipped
+    uint32_t *mine = wcnt + warp * n_experts;
+    for (int c = f0; c < f1; c += 32) {
+        const int f = c + lane;
+        const bool have = f < f1;
+        const uint32_t e = have ? topk_idx[f] : 0xFFFFFFFFu;
+        const bool ok = have && e < static_cast<uint32_t>(n_experts);
+        if (have && !ok) atomicCAS(status, 0u, 0x501u);        // expert id out of range: recorded, slot skipped
+        const uint32_t peers = __match_any_sync(0xffffffffu, ok ? e : 0xFFFFFFFFu);
+        if (ok && __popc(peers & ((1u << lane) - 1u)) == 0) mine[e] += __popc(peers);
+        __syncwarp();
     }
+    __syncthreads();
+    for (int ee = tid; ee < n_experts; ee += kSortThreads) {   // per expert: exclusive prefix over the warps, total
+        uint32_t run = 0;
+        for (int w = 0; w < 32; ++w) {
+            const uint32_t c = wcnt[w * n_experts + ee];
+            wcnt[w * n_experts + ee] = run;
+            run += c;
+        }
+        cursor[ee + 1] = run;
+    }
+    if (tid == 0) cursor[0] = 0;
     __syncthreads();
     if (warp == 0) {                               // inclusive scan of cursor[1..E] by one warp
         uint32_t carry = 0;
@@ -119,37 +140,24 @@ __global__ void __launch_bounds__(kSortThreads) moe_sort_kernel(const uint32_t *
     }
     __syncthreads();
     for (int e = tid; e <= n_experts; e += kSortThreads) expert_offsets[e] = cursor[e];
-    __syncthreads();
-    // cursor[e] now = first row of expert e; it advances as chunks are placed
-    for (int c0 = 0; c0 < total; c0 += kSortThreads) {
-        for (int i = tid; i < 32 * n_experts; i += kSortThreads) wcnt[i] = 0;
-        __syncthreads();
-        const int f = c0 + tid;
-        const bool have = f < total;
-        uint32_t e = have ? topk_idx[f] : 0xFFFFFFFFu;
+    for (int c = f0; c < f1; c += 32) {
+        const int f = c + lane;
+        const bool have = f < f1;
+        const uint32_t e = have ? topk_idx[f] : 0xFFFFFFFFu;
         const bool ok = have && e < static_cast<uint32_t>(n_experts);
-        const uint32_t key = ok ? e : 0xFFFFFFFFu;
-        const uint32_t peers = __match_any_sync(0xffffffffu, key);
+        const uint32_t peers = __match_any_sync(0xffffffffu, ok ? e : 0xFFFFFFFFu);
         const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
-        if (ok && rank == 0) wcnt[warp * n_experts + e] = __popc(peers);
-        __syncthreads();
-        for (int ee = tid; ee < n_experts; ee += kSortThreads) {   // per expert: prefix over warps, advance cursor
-            uint32_t run = cursor[ee];
-            for (int w = 0; w < 32; ++w) {
-                const uint32_t c = wcnt[w * n_experts + ee];
-                wcnt[w * n_experts + ee] = run;
-                run += c;
-            }
-            cursor[ee] = run;
-        }
-        __syncthreads();
+        uint32_t before = 0;
+        if (ok) before = mine[e];                  // slots of this expert in earlier warps and earlier sub-chunks
+        __syncwarp();
+        if (ok && rank == 0) mine[e] = before + __popc(peers);
+        __syncwarp();
         if (ok) {
-            const uint32_t pos = wcnt[warp * n_experts + e] + rank;
+            const uint32_t pos = cursor[e] + before + rank;
             sort_token_idx[pos] = static_cast<uint32_t>(f / k);
             inv_perm[f] = pos;
             if (row_expert) row_expert[pos] = e;
         }
-        __syncthreads();
     }
 }
 
