@@ -377,6 +377,22 @@ typedef struct {
     int n_bufs;
 } mtc_dispatch_spec;
 int mtc_dispatch_chain(mtc_ctx *ctx, const mtc_dispatch_spec *specs, int n_specs, float *elapsed_us);
+
+/* Timed repetitions of one kernel - GpuRunner::measure / GpuRunner::bench / bench_gbps
+ * (crates/metaltile-std/src/runner.rs:413-442,638-650) with the summary of BenchStats::from_samples
+ * (crates/metaltile-std/src/stats.rs:5-47).  The buffers are bound by name as for mtc_dispatch and staged on the
+ * device ONCE by an untimed first launch; then `warmup` untimed and `iters` timed launches run, each timed launch
+ * between its own pair of events (device time of the kernel alone, no copies).  cold_l2 != 0 rewrites a 256 MiB block
+ * (twice the L2) before every launch, outside the timed pair - the counterpart of GpuRunner::flush_slc
+ * (runner.rs:444-458).  samples_us (may be NULL) receives the `iters` samples in launch order; stats (may be NULL) the
+ * summary: sorted samples, median = s[n/2], p95 = s[n*95/100], p99 = s[n*99/100], population standard deviation,
+ * cv_pct = stddev / mean * 100.  Buffers flagged is_output hold the last launch's result when the call returns. */
+typedef struct {
+    double min_us, mean_us, median_us, p95_us, p99_us, stddev_us, cv_pct;
+    int iters;
+} mtc_bench_stats;
+int mtc_measure(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_buf *bufs, int n_bufs, int warmup, int iters,
+                int cold_l2, double *samples_us, mtc_bench_stats *stats);
 /* Number of kernel names mtc_dispatch knows, and the i-th name (registry walk:
  * all_kernels(), crates/metaltile-core/src/toolchain/registry.rs:56-78). */
 int mtc_kernel_count(void);

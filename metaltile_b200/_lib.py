@@ -39,6 +39,12 @@ class DispatchSpec(ctypes.Structure):
     _fields_ = [("kernel_name", ctypes.c_char_p), ("dtype", ctypes.c_int), ("bufs", ctypes.c_void_p), ("n_bufs", ctypes.c_int)]
 
 
+class BenchStatsC(ctypes.Structure):
+    """mtc_bench_stats: the summary mtc_measure fills."""
+    _fields_ = [(n, ctypes.c_double) for n in ("min_us", "mean_us", "median_us", "p95_us", "p99_us", "stddev_us", "cv_pct")] + \
+               [("iters", ctypes.c_int)]
+
+
 class QMat(ctypes.Structure):
     """mtc_qmat: packed words, scales and biases of one stacked expert matrix."""
     _fields_ = [("w", ctypes.c_void_p), ("scales", ctypes.c_void_p), ("biases", ctypes.c_void_p)]
@@ -102,6 +108,8 @@ SIGNATURES = {
     "mtc_swiglu": (_i, [_vp] * 5 + [_sz, _i]),
     "mtc_set_option": (_i, [_vp, ctypes.c_char_p, _i]),
     "mtc_unpack_codes": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i]),
+    "mtc_measure": (_i, [_vp, ctypes.c_char_p, _i, ctypes.POINTER(NamedBuf), _i, _i, _i, _i, ctypes.POINTER(ctypes.c_double),
+                         ctypes.POINTER(BenchStatsC)]),
     "mtc_dispatch": (_i, [_vp, ctypes.c_char_p, _i, ctypes.POINTER(NamedBuf), _i,
                           ctypes.POINTER(ctypes.c_uint32), ctypes.POINTER(ctypes.c_uint32),
                           ctypes.POINTER(ctypes.c_float)]),

@@ -17,7 +17,7 @@ from dataclasses import dataclass, field
 from typing import Dict, Mapping, Optional, Sequence
 
 from . import _lib
-from ._lib import BF16, F16, F32, DispatchSpec, NamedBuf, PeerSync, QMat, QmvDesc
+from ._lib import BF16, F16, F32, BenchStatsC, DispatchSpec, NamedBuf, PeerSync, QMat, QmvDesc
 
 DTYPES = {"f32": F32, "f16": F16, "bf16": BF16}
 
@@ -36,6 +36,21 @@ class DispatchResult:
     """crates/metaltile-runtime/src/context.rs:49-56."""
     outputs: Dict[str, bytes] = field(default_factory=dict)
     elapsed_us: float = 0.0
+
+
+@dataclass
+class BenchStats:
+    """crates/metaltile-std/src/stats.rs:5-22: summary of a set of device timings, microseconds."""
+    min_us: float
+    mean_us: float
+    median_us: float
+    p95_us: float
+    p99_us: float
+    stddev_us: float
+    cv_pct: float
+
+    def is_valid(self) -> bool:
+        return self.mean_us > 0.0
 
 
 def _dt(dtype) -> int:
@@ -129,6 +144,37 @@ class Context:
             if arr[i].is_output:
                 res.outputs[name] = keep[i].raw
         return res
+
+    def bench(self, kernel: str, buffers: Mapping[str, bytes], fn_consts: Optional[Mapping[str, int]] = None,
+              dtype="f32", outputs: Sequence[str] = ("out",), warmup: int = 15, iters: int = 10, cold_l2: bool = True):
+        """``GpuRunner::bench`` (crates/metaltile-std/src/runner.rs:432-442) with the reference's defaults of 15 warm-up and
+        10 timed launches (runner.rs:635-636): the buffers are staged once, every timed launch sits between its own pair
+        of events, ``cold_l2`` rewrites a block larger than L2 before every launch (``flush_slc``, runner.rs:444-458).
+        Returns ``(BenchStats, samples_us, outputs)``; the outputs are the last launch's."""
+        items = dict(buffers)
+        for k, v in (fn_consts or {}).items():
+            items[k] = int(v).to_bytes(4, "little")
+        keep = []
+        arr = (NamedBuf * len(items))()
+        for i, (name, data) in enumerate(items.items()):
+            raw = ctypes.create_string_buffer(bytes(data), len(data))
+            keep.append(raw)
+            arr[i].name = name.encode()
+            arr[i].data = ctypes.cast(raw, ctypes.c_void_p)
+            arr[i].bytes = len(data)
+            arr[i].is_output = 1 if name in outputs else 0
+        samples = (ctypes.c_double * int(iters))()
+        st = BenchStatsC()
+        self._check(self._lib.mtc_measure(self._h, kernel.encode(), _dt(dtype), arr, len(items), int(warmup), int(iters),
+                                          1 if cold_l2 else 0, samples, ctypes.byref(st)))
+        stats = BenchStats(**{n: getattr(st, n) for n in ("min_us", "mean_us", "median_us", "p95_us", "p99_us", "stddev_us", "cv_pct")})
+        outs = {name: keep[i].raw for i, name in enumerate(items) if arr[i].is_output}
+        return stats, list(samples), outs
+
+    def bench_gbps(self, kernel: str, buffers: Mapping[str, bytes], nbytes: float, **kw):
+        """``bench_gbps`` (crates/metaltile-std/src/runner.rs:638-650): GB/s of ``nbytes`` over the minimum sample."""
+        stats, _, _ = self.bench(kernel, buffers, **kw)
+        return (nbytes / (stats.min_us * 1e-6) / 1e9 if stats.is_valid() else None), stats
 
     def dispatch_chain(self, passes) -> list:
         """``Context::dispatch_chain`` (context.rs:347-395): ``passes`` is a list of

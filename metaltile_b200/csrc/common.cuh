@@ -52,6 +52,8 @@ struct Ctx {
     size_t qvm_bytes = 0;
     void *d_norm = nullptr;        // mtc_rms_norm_qmv on shapes the fused kernel does not take: the normalised row (grow-only)
     size_t norm_bytes = 0;
+    void *d_flush = nullptr;       // mtc_measure with cold_l2: a block larger than L2 that a memset rewrites between timed launches
+    size_t flush_bytes = 0;
     void *d_moe = nullptr;         // mtc_moe_experts: gate and up outputs (and permuted rows on the composed path) (grow-only)
     size_t moe_bytes = 0;
 };

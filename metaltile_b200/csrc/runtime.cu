@@ -1,7 +1,9 @@
 // Runtime behind include/mtcuda.h: context, device memory, the typed entry points and
 // the name-keyed host-buffer dispatch that mirrors Context::dispatch_with_grid
 // (crates/metaltile-runtime/src/context.rs:269-284).
+#include <algorithm>
 #include <chrono>
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <map>
@@ -278,6 +280,7 @@ int mtc_destroy(mtc_ctx *ctx) {
     if (ctx->d_norm) cudaFree(ctx->d_norm);
     if (ctx->d_qvm) cudaFree(ctx->d_qvm);
     if (ctx->d_tail) cudaFree(ctx->d_tail);
+    if (ctx->d_flush) cudaFree(ctx->d_flush);
     if (ctx->d_tc_scratch) cudaFree(ctx->d_tc_scratch);
     if (ctx->d_tc_counters) cudaFree(ctx->d_tc_counters);
     for (void *p : ctx->retired) cudaFree(p);
@@ -1159,6 +1162,7 @@ struct Produced {
 };
 struct ChainCtx {
     bool measure = true;             // first walk: only the bytes every pass stages
+    bool skip_upload = false;        // mtc_measure after its first launch: the inputs are already where this walk puts them
     size_t offset = 0;               // scratch bytes taken by the passes walked so far
     std::vector<Produced> produced;
 };
@@ -1454,7 +1458,7 @@ int dispatch_pass(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_bu
                                                          " bytes by an earlier pass, this pass needs " + std::to_string(sb.need));
             sb.dev = from->dev;
             from->consumed = true;
-        } else if (sb.need) {
+        } else if (sb.need && !(cc && cc->skip_upload)) {
             MTC_CUDA(ctx, cudaMemcpyAsync(sb.dev, sb.buf->data, sb.need, cudaMemcpyHostToDevice, st), MTC_ERR_BUFFER);
         }
     }
@@ -1642,6 +1646,83 @@ int mtc_dispatch_chain(mtc_ctx *ctx, const mtc_dispatch_spec *specs, int n_specs
         cudaEventDestroy(e1);
     }
     return rc;
+}
+
+int mtc_measure(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_buf *bufs, int n_bufs, int warmup, int iters,
+                int cold_l2, double *samples_us, mtc_bench_stats *stats) {
+    if (!ctx || !kernel_name || (!bufs && n_bufs > 0)) return MTC_ERR_INVALID;
+    MTC_ENTER(ctx);
+    if (warmup < 0 || iters < 1 || iters > (1 << 20)) return fail(ctx, MTC_ERR_INVALID, "measure: need warmup >= 0 and 1 <= iters <= 2^20");
+    ChainCtx cc;
+    int rc = dispatch_pass(ctx, kernel_name, dtype, bufs, n_bufs, nullptr, &cc);       // checks and sizes, enqueues nothing
+    if (rc != MTC_OK) return rc;
+    rc = ensure_scratch(ctx, cc.offset);
+    if (rc != MTC_OK) return rc;
+    cudaStream_t st = nullptr;
+    constexpr size_t kFlushBytes = 256u << 20;                                         // twice the 126 MB L2
+    if (cold_l2) {
+        std::string why;
+        cudaError_t e = mtc::grow_block(ctx, st, &ctx->d_flush, &ctx->flush_bytes, kFlushBytes, &why);
+        if (e != cudaSuccess) return fail(ctx, MTC_ERR_BUFFER, std::string("measure: flush block: ") + cudaGetErrorString(e));
+    }
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    MTC_CUDA(ctx, cudaEventCreate(&e0), MTC_ERR_DISPATCH);
+    MTC_CUDA(ctx, cudaEventCreate(&e1), MTC_ERR_DISPATCH);
+    cc.measure = false;
+    std::vector<double> samples;
+    samples.reserve(iters);
+    // One untimed launch stages the inputs (the only host-to-device copies of the call); every later walk finds them in place.
+    rc = dispatch_pass(ctx, kernel_name, dtype, bufs, n_bufs, nullptr, &cc);
+    cc.skip_upload = true;
+    if (rc == MTC_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = fail(ctx, MTC_ERR_DISPATCH, "measure: the first launch failed");
+    for (int pass = 0; pass < warmup + iters && rc == MTC_OK; ++pass) {
+        cc.offset = 0;
+        cc.produced.clear();
+        if (cold_l2) cudaMemsetAsync(ctx->d_flush, pass & 0xff, kFlushBytes, st);        // outside the timed pair of events
+        cudaEventRecord(e0, st);
+        rc = dispatch_pass(ctx, kernel_name, dtype, bufs, n_bufs, nullptr, &cc);
+        cudaEventRecord(e1, st);
+        if (rc != MTC_OK) break;
+        cudaError_t e = cudaEventSynchronize(e1);
+        float ms = 0.f;
+        if (e != cudaSuccess || cudaEventElapsedTime(&ms, e0, e1) != cudaSuccess) {
+            rc = fail(ctx, MTC_ERR_DISPATCH, std::string("measure: ") + cudaGetErrorString(e));
+            break;
+        }
+        if (pass >= warmup) samples.push_back(static_cast<double>(ms) * 1000.0);
+    }
+    if (rc == MTC_OK) {
+        for (Produced &pr : cc.produced)                                               // the last launch's outputs go back once
+            if (pr.bytes) cudaMemcpyAsync(pr.host->data, pr.dev, pr.bytes, cudaMemcpyDeviceToHost, st);
+    }
+    cudaError_t e = cudaStreamSynchronize(st);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (rc != MTC_OK) return rc;
+    if (e != cudaSuccess) return fail(ctx, MTC_ERR_DISPATCH, std::string("measure: ") + cudaGetErrorString(e));
+    rc = check_status(ctx, "measure");
+    if (rc != MTC_OK) return rc;
+    if (samples_us) std::copy(samples.begin(), samples.end(), samples_us);
+    if (stats) {
+        // the summary the reference prints (crates/metaltile-std/src/stats.rs:24-47): sorted samples, n/2, n*95/100, n*99/100
+        std::vector<double> s(samples);
+        std::sort(s.begin(), s.end());
+        const size_t n = s.size();
+        double mean = 0.0, var = 0.0;
+        for (double v : s) mean += v;
+        mean /= static_cast<double>(n);
+        for (double v : s) var += (v - mean) * (v - mean);
+        var /= static_cast<double>(n);
+        stats->min_us = s[0];
+        stats->mean_us = mean;
+        stats->median_us = s[n / 2];
+        stats->p95_us = s[std::min(n * 95 / 100, n - 1)];
+        stats->p99_us = s[std::min(n * 99 / 100, n - 1)];
+        stats->stddev_us = std::sqrt(var);
+        stats->cv_pct = mean > 0.0 ? stats->stddev_us / mean * 100.0 : 0.0;
+        stats->iters = static_cast<int>(n);
+    }
+    return MTC_OK;
 }
 
 }  // extern "C"

@@ -158,3 +158,54 @@ def test_hand_off_wait_for_an_absent_rank_expires():
         bad = dict(desc, group_size=32)
         ctx.qmv_batched_sync([bad], [f], 0, f, f + 128, f + 192, stream=st)
     assert ei.value.variant in ("Unsupported", "Invalid")
+
+
+# ---- mtc_measure: GpuRunner::measure / bench / bench_gbps (crates/metaltile-std/src/runner.rs:413-442,638-650) ----
+def _measure_case(dt="bf16", n=2048, k=2048, gs=64):
+    from helpers import dt_bytes
+    w, s, b, x = dense_case(1, n, k, 4, gs, dt, seed=11)
+    bufs = {"w": w.tobytes(), "scales": dt_bytes(s, dt), "biases": dt_bytes(b, dt), "x": dt_bytes(x, dt),
+            "out": bytes(n * (4 if dt == "f32" else 2))}
+    return bufs, {"k": k, "gs_per_row": k // gs}, (w, s, b, x)
+
+
+@pytest.mark.parametrize("cold", [False, True])
+def test_measure_matches_dispatch_and_summarises_like_the_reference(cold):
+    from helpers import bytes_to_f32
+    from metaltile_b200 import ops
+    ctx = ops.context(0)
+    bufs, consts, (w, s, b, x) = _measure_case()
+    one = ctx.dispatch_with_grid("mt_qmv", bufs, consts, (256, 1, 1), (64, 1, 1), dtype="bf16")
+    stats, samples, outs = ctx.bench("mt_qmv", bufs, consts, dtype="bf16", warmup=3, iters=21, cold_l2=cold)
+    assert outs["out"] == one.outputs["out"]                       # the last timed launch computed the same bytes
+    ref = oracle.qmm(w, s, b, x, 1, 2048, 2048, 4, 64)
+    assert rel_err(bytes_to_f32(outs["out"], "bf16").reshape(1, -1), ref) <= TOL["bf16"]
+    assert len(samples) == 21 and all(v > 0.0 for v in samples)
+    srt = sorted(samples)                                          # BenchStats::from_samples, stats.rs:24-47
+    mean = sum(srt) / 21
+    std = (sum((v - mean) ** 2 for v in srt) / 21) ** 0.5
+    assert stats.min_us == srt[0] and stats.median_us == srt[10] and stats.p95_us == srt[19] and stats.p99_us == srt[20]
+    assert abs(stats.mean_us - mean) <= 1e-9 * mean and abs(stats.stddev_us - std) <= 1e-6 * max(std, 1e-9) + 1e-12
+    assert abs(stats.cv_pct - std / mean * 100.0) <= 1e-6
+    assert stats.is_valid() and ctx.status_word() == 0
+
+
+def test_measure_gbps_and_errors():
+    from metaltile_b200 import MetalTileError, ops
+    ctx = ops.context(0)
+    bufs, consts, _ = _measure_case("f32", n=1024, k=1024)
+    nbytes = 1024 * 1024 // 2 + 2 * 1024 * 16 * 4 + 1024 * 4 + 1024 * 4
+    gbps, stats = ctx.bench_gbps("mt_qmv", bufs, nbytes, fn_consts=consts, dtype="f32", warmup=2, iters=5)
+    assert gbps is not None and gbps > 0.0 and abs(gbps - nbytes / (stats.min_us * 1e-6) / 1e9) <= 1e-6 * gbps
+    with pytest.raises(MetalTileError) as ei:
+        ctx.bench("mt_no_such_kernel", bufs, consts, dtype="f32", warmup=0, iters=1)
+    assert ei.value.variant == "FunctionNotFound"
+    with pytest.raises(MetalTileError) as ei:
+        ctx.bench("mt_qmv", bufs, consts, dtype="f32", warmup=0, iters=0)
+    assert ei.value.variant == "Invalid"
+    short = dict(bufs, w=bufs["w"][:-4])
+    with pytest.raises(MetalTileError) as ei:
+        ctx.bench("mt_qmv", short, consts, dtype="f32", warmup=0, iters=1)
+    assert ei.value.variant == "BufferSize"
+    stats, samples, _ = ctx.bench("mt_qmv", bufs, consts, dtype="f32", warmup=0, iters=1, cold_l2=False)
+    assert len(samples) == 1 and stats.min_us == stats.p99_us == samples[0]
