@@ -70,7 +70,8 @@ constexpr int kMaxInline = 4;
 struct SArgs {
     SProj inl[kMaxInline];   // a launch of 1-4 projections that share their activations carries them here
     int n_inl;
-    int rows_q, rows_r;      // inline launch: total rows = rows_q * gridDim.x + rows_r
+    int rows_q, rows_r;      // inline launch: total units = rows_q * gridDim.x + rows_r, a unit being 1 << unit_sh rows
+    int unit_sh;             // 4 when a CTA has more than one row tile: shares end on tile boundaries, so no CTA pays a pass for a sliver
     const SProj *projs;      // chain: device array, nullptr for an inline launch
     const int4 *pieces;      // chain: [gridDim.x][max_pieces] {projection, row0, row1, flags}; projection < 0 ends a list
     int max_pieces;
@@ -333,7 +334,8 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_stream_kernel(const __grid_co
         // first r CTAs one more); piece j is this CTA's part of projection j (possibly empty)
         if (j >= a.n_inl) return false;
         const int b = blockIdx.x;
-        const int lo_all = b * a.rows_q + min(b, a.rows_r), hi_all = lo_all + a.rows_q + (b < a.rows_r ? 1 : 0);
+        const int lo_u = b * a.rows_q + min(b, a.rows_r);
+        const int lo_all = lo_u << a.unit_sh, hi_all = (lo_u + a.rows_q + (b < a.rows_r ? 1 : 0)) << a.unit_sh;
         int before = 0;
         for (int q = 0; q < j; ++q) before += a.inl[q].N;
         const int n = a.inl[j].N;
@@ -751,8 +753,12 @@ cudaError_t launch_qmv_stream(Ctx *ctx, cudaStream_t st, const mtc_qmv_desc *d, 
     long long grid = static_cast<long long>(ctx->sm_count) * plan.per_sm;
     if (grid > (rows + 7) / 8) grid = (rows + 7) / 8;
     if (grid < 1) grid = 1;
-    a.rows_q = static_cast<int>(rows / grid);
-    a.rows_r = static_cast<int>(rows % grid);
+    // Shares in whole row tiles once a CTA has more than one: 14336 + 14336 rows over 296 CTAs are 96.9 rows each, which
+    // dealt by rows is seven passes (the last for one row) on 255 CTAs and dealt by tiles is six on 280 and seven on 16.
+    a.unit_sh = rows / grid >= 16 ? 4 : 0;
+    const long long units = (rows + (1 << a.unit_sh) - 1) >> a.unit_sh;
+    a.rows_q = static_cast<int>(units / grid);
+    a.rows_r = static_cast<int>(units % grid);
     return launch_stream_kernel(st, a, pick_kernel(d[0].dtype == MTC_BF16, d[0].group_size == 64 ? 0 : 1, M == 1, plan.depth),
                                 static_cast<int>(grid), plan.smem);
 }

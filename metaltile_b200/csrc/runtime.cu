@@ -1669,6 +1669,7 @@ int mtc_measure(mtc_ctx *ctx, const char *kernel_name, int dtype, mtc_named_buf 
     MTC_CUDA(ctx, cudaEventCreate(&e0), MTC_ERR_DISPATCH);
     MTC_CUDA(ctx, cudaEventCreate(&e1), MTC_ERR_DISPATCH);
     cc.measure = false;
+    cc.offset = 0;
     std::vector<double> samples;
     samples.reserve(iters);
     // One untimed launch stages the inputs (the only host-to-device copies of the call); every later walk finds them in place.
