@@ -262,14 +262,11 @@ __device__ __forceinline__ void consume_segment(const unsigned char *slot_lo, co
     constexpr int gi = P >> GSH;                 // group of this segment within the run
     constexpr int hf = gi & 1;
     const float s_lo = f32_of_half<BF16, hf>(word_of(sl, gi >> 1)), s_hi = f32_of_half<BF16, hf>(word_of(sh, gi >> 1));
-    const float b_lo = f32_of_half<BF16, hf>(word_of(bl, gi >> 1)), b_hi = f32_of_half<BF16, hf>(word_of(bh, gi >> 1));
     if (M1) {
-        const float x_sum = xs[P];
-        as[0] = fmaf(s_lo, d[0], as[0]);
+        as[0] = fmaf(s_lo, d[0], as[0]);         // the bias term of a one-token run is added per run (consume_run)
         as[2] = fmaf(s_hi, d[2], as[2]);
-        ab[0] = fmaf(b_lo, x_sum, ab[0]);
-        ab[2] = fmaf(b_hi, x_sum, ab[2]);
     } else {
+        const float b_lo = f32_of_half<BF16, hf>(word_of(bl, gi >> 1)), b_hi = f32_of_half<BF16, hf>(word_of(bh, gi >> 1));
         const float2 x_sum = *reinterpret_cast<const float2 *>(xs + P * 8);
         as[0] = fmaf(s_lo, d[0], as[0]);
         as[1] = fmaf(s_lo, d[1], as[1]);
@@ -290,7 +287,29 @@ __device__ __forceinline__ void consume_run(const unsigned char *slot, uint32_t 
                                             float (&ab)[4]) {
     const unsigned char *slot_lo = slot + a_lo, *slot_hi = slot_lo + 8 * kRowPitch;
     const uint4 sl = *reinterpret_cast<const uint4 *>(slot + kSlotW + ra16), sh = *reinterpret_cast<const uint4 *>(slot + kSlotW + ra16 + 128);
-    const uint4 bl = *reinterpret_cast<const uint4 *>(slot + kSlotW + 256 + ra16), bh = *reinterpret_cast<const uint4 *>(slot + kSlotW + 256 + ra16 + 128);
+    uint4 bl = make_uint4(0u, 0u, 0u, 0u), bh = bl;
+    if (M1) {
+        // One token: the four lanes of a quad hold the same sums, so each adds the bias term of two of the run's eight
+        // segments (2t, 2t + 1) and the quad's parts meet once per row tile (tile_bias_sum).
+        const int t = (threadIdx.x & 3);
+        const float2 x_sum = *reinterpret_cast<const float2 *>(xs + 2 * t);
+        if (GSH == 0) {                          // a group per segment: the pair of biases is one word
+            const uint32_t wl = *reinterpret_cast<const uint32_t *>(slot + kSlotW + 256 + ra16 + 4 * t);
+            const uint32_t wh = *reinterpret_cast<const uint32_t *>(slot + kSlotW + 256 + ra16 + 128 + 4 * t);
+            ab[0] = fmaf(f32_of_half<BF16, 0>(wl), x_sum.x, ab[0]);
+            ab[0] = fmaf(f32_of_half<BF16, 1>(wl), x_sum.y, ab[0]);
+            ab[2] = fmaf(f32_of_half<BF16, 0>(wh), x_sum.x, ab[2]);
+            ab[2] = fmaf(f32_of_half<BF16, 1>(wh), x_sum.y, ab[2]);
+        } else {                                 // a group per two segments: one bias for both
+            const uint32_t wl = *reinterpret_cast<const uint16_t *>(slot + kSlotW + 256 + ra16 + 2 * t);
+            const uint32_t wh = *reinterpret_cast<const uint16_t *>(slot + kSlotW + 256 + ra16 + 128 + 2 * t);
+            ab[0] = fmaf(f32_of_half<BF16, 0>(wl), x_sum.x + x_sum.y, ab[0]);
+            ab[2] = fmaf(f32_of_half<BF16, 0>(wh), x_sum.x + x_sum.y, ab[2]);
+        }
+    } else {
+        bl = *reinterpret_cast<const uint4 *>(slot + kSlotW + 256 + ra16);
+        bh = *reinterpret_cast<const uint4 *>(slot + kSlotW + 256 + ra16 + 128);
+    }
     consume_segment<BF16, GSH, M1, 0>(slot_lo, slot_hi, sl, sh, bl, bh, xa, xb, xstride, xs, as, ab);
     consume_segment<BF16, GSH, M1, 1>(slot_lo, slot_hi, sl, sh, bl, bh, xa, xb, xstride, xs, as, ab);
     consume_segment<BF16, GSH, M1, 2>(slot_lo, slot_hi, sl, sh, bl, bh, xa, xb, xstride, xs, as, ab);
@@ -397,9 +416,11 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_stream_kernel(const __grid_co
 
     if (!a.early_weights) asm volatile("griddepcontrol.wait;" ::: "memory");
     copy_enter();
+    // the whole ring is requested before anything waits: the copies run while the previous kernel of the stream drains
+    // and while this CTA stages its activations
 #pragma unroll 1
-    for (int p = 0; p < DEPTH - 1; ++p) copy_next(ring + p * kSlotBytes);
-    int islot = DEPTH - 1, cslot = 0;
+    for (int p = 0; p < DEPTH; ++p) copy_next(ring + p * kSlotBytes);
+    int cslot = 0;
     // the weights do not depend on the previous kernel of the stream; the activations and every store do
     if (a.early_weights) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (a.n_peers > 0) {
@@ -482,16 +503,15 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_stream_kernel(const __grid_co
             float as[4] = {0.f, 0.f, 0.f, 0.f}, ab[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
             for (int run = rb; run < re; ++run) {
-                __syncwarp();                                    // every lane is done with the slot about to be refilled
-                copy_next(ring + islot * kSlotBytes);
                 cp_wait_oldest<DEPTH>();                         // this run has landed (this lane's copies)
                 __syncwarp();                                    // ... and every other lane's
                 const unsigned char *slot = ring_p + cslot * kSlotBytes;
                 const uint32_t so = run * kRunSegs;              // first segment of the run
                 consume_run<BF16, GSH, M1>(slot, a_lo, ra16, x0 + so * xstride, x1 + so * xstride, xstride,
                                            xs0 + (M1 ? so : so * 8), as, ab);
+                __syncwarp();                                    // every lane is done with the slot: refill it
+                copy_next(ring + cslot * kSlotBytes);
                 if (++cslot == DEPTH) cslot = 0;
-                if (++islot == DEPTH) islot = 0;
             }
 
             // ---- add up the warps that share this tile; the last one to arrive stores ----
@@ -516,6 +536,12 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_stream_kernel(const __grid_co
                 __syncwarp();
                 ok = ctl->abort == 0u;
                 if (!ok) break;                                  // this warp stops computing but still meets the CTA's barriers
+            }
+            if (M1) {                                            // the quad's parts of the bias term (consume_run)
+                ab[0] += __shfl_xor_sync(0xffffffffu, ab[0], 1);
+                ab[2] += __shfl_xor_sync(0xffffffffu, ab[2], 1);
+                ab[0] += __shfl_xor_sync(0xffffffffu, ab[0], 2);
+                ab[2] += __shfl_xor_sync(0xffffffffu, ab[2], 2);
             }
             // c * 2^(pre-scale) leaves once per output: f16 codes are q * 2^-24; bf16 codes q * 2^-133 against x * 2^64
             const float post = BF16 ? 5.9029581035870565e20f /* 2^69 */ : 16777216.0f /* 2^24 */;
