@@ -228,10 +228,20 @@ __device__ __forceinline__ void issue_run(const CopyIt &c, uint32_t slot, int la
     const int crow = lane >> 4, cch = lane & 15;
     const char *src = c.w + static_cast<size_t>(c.run) * 256 + cch * 16;
     const uint32_t dst = slot + crow * kRowPitch + cch * 16;
+    if (r0 + 15 <= last) {                       // a whole tile (the usual case): one pointer walks the rows
+        const char *p = src + static_cast<size_t>(r0 + crow) * c.rowbytes;
+        const size_t step = static_cast<size_t>(2 * c.rowbytes);
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {
-        const int row = min(r0 + crow + 2 * q, last);
-        cp16(dst + q * 2 * kRowPitch, src + static_cast<size_t>(row) * c.rowbytes);
+        for (int q = 0; q < 8; ++q) {
+            cp16(dst + q * 2 * kRowPitch, p);
+            p += step;
+        }
+    } else {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int row = min(r0 + crow + 2 * q, last);
+            cp16(dst + q * 2 * kRowPitch, src + static_cast<size_t>(row) * c.rowbytes);
+        }
     }
     const int srow = min(r0 + (lane & 15), last);
     const uint32_t sdst = slot + kSlotW + (lane >> 4) * 256 + (lane & 15) * 16;
