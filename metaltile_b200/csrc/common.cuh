@@ -48,7 +48,7 @@ struct Ctx {
     int gather_stream = 1;         // option "gather_stream": 0 = grouped products never take the streaming kernel (gather_stream.cu)
     void *d_tail = nullptr;        // MoE decode tail: the staged inner activations of a call (grow-only)
     size_t tail_bytes = 0;
-    void *d_qvm = nullptr;         // mtc_qvm: partial sums of the K chunks (grow-only)
+    void *d_qvm = nullptr;         // mtc_qvm: arrival counters (zero between launches), then the partial sums of the K chunks (grow-only)
     size_t qvm_bytes = 0;
     void *d_norm = nullptr;        // mtc_rms_norm_qmv on shapes the fused kernel does not take: the normalised row (grow-only)
     size_t norm_bytes = 0;
@@ -205,7 +205,8 @@ cudaError_t launch_moe_decode(Ctx *ctx, cudaStream_t st, const void *const *gate
 int qvm_k_chunks(int sms, int N, int K, int bits, int group_size);
 bool qvm_fast_supported(int N, int K, int bits, int group_size);
 cudaError_t launch_qvm(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases, const void *x, void *out,
-                       int M, int N, int K, int bits, int group_size, int dt, float *partial, int KC);
+                       int M, int N, int K, int bits, int group_size, int dt, void *scratch, int KC);
+size_t qvm_scratch_bytes(int M, int N, int KC);
 cudaError_t launch_dequant_gather(Ctx *ctx, cudaStream_t st, const void *w, const void *scales, const void *biases, const void *indices,
                                   void *out, size_t n_tokens, int hidden, int vocab, int bits, int group_size, int dt);
 cudaError_t launch_affine_quantize(Ctx *ctx, cudaStream_t st, const void *w, void *out, void *scales, void *biases, size_t n_groups,

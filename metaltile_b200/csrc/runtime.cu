@@ -823,11 +823,14 @@ int mtc_qvm(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
         kc = mtc::qvm_k_chunks(ctx->sm_count, N, K, bits, group_size);
         if (kc > 1) {
             std::string why;
-            cudaError_t e = mtc::grow_block(ctx, st, &ctx->d_qvm, &ctx->qvm_bytes, static_cast<size_t>(kc) * M * N * sizeof(float), &why);
+            void *before = ctx->d_qvm;
+            cudaError_t e = mtc::grow_block(ctx, st, &ctx->d_qvm, &ctx->qvm_bytes, mtc::qvm_scratch_bytes(M, N, kc), &why);
             if (e != cudaSuccess) return fail(ctx, MTC_ERR_BUFFER, "qvm partial sums: " + (why.empty() ? std::string(cudaGetErrorString(e)) : why));
+            // a new block starts with its arrival counters at zero; every launch leaves them there
+            if (ctx->d_qvm != before) MTC_CUDA(ctx, cudaMemsetAsync(ctx->d_qvm, 0, mtc::qvm_scratch_bytes(1, 0, 2), st), MTC_ERR_BUFFER);
         }
     }
-    MTC_CUDA(ctx, mtc::launch_qvm(ctx, st, w, scales, biases, x, out, M, N, K, bits, group_size, dtype, static_cast<float *>(ctx->d_qvm), kc),
+    MTC_CUDA(ctx, mtc::launch_qvm(ctx, st, w, scales, biases, x, out, M, N, K, bits, group_size, dtype, ctx->d_qvm, kc),
              MTC_ERR_DISPATCH);
     return MTC_OK;
 }

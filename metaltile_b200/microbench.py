@@ -2,9 +2,10 @@
 
     python -m metaltile_b200.microbench qmv --m 1 --n 14336 --k 4096 --bits 4 --copies 8
     python -m metaltile_b200.microbench qmm --m 2048 --n 2304 --k 4096 --dtype bf16
+    python -m metaltile_b200.microbench qvm --m 1 --n 4096 --k 14336 --bits 4 --copies 8
     python -m metaltile_b200.microbench moe --tokens 512 --hidden 2048 --inter 768 --experts 128 --top-k 8
 
-`qmv` cycles through `--copies` independent weight sets so that consecutive launches do not find
+`qmv` and `qvm` cycle through `--copies` independent weight sets so that consecutive launches do not find
 their weights in L2 (pick copies * bytes > 126 MB for DRAM figures); `qmm` and `moe` reuse one set,
 as a prefill does.  Prints one line per repetition: microseconds per launch (qmv, qmm) or per
 layer (moe).  Counterpart of the reference's `tile bench --kernel NAME` for a single shape
@@ -40,7 +41,7 @@ def _timed(fn, reps, per):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("family", choices=["qmv", "qmm", "moe"])
+    ap.add_argument("family", choices=["qmv", "qvm", "qmm", "moe"])
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -64,12 +65,19 @@ def main(argv=None):
         ctx.set_option(name, int(value))
     dt = _DT[a.dtype]
 
-    if a.family in ("qmv", "qmm"):
-        copies = a.copies if a.family == "qmv" else 1
-        sets = [_weights((), a.n, a.k, a.bits, a.group, dt, dev) for _ in range(copies)]
+    if a.family in ("qmv", "qvm", "qmm"):
+        copies = a.copies if a.family != "qmm" else 1
+        if a.family == "qvm":                # transposed storage: w [K, N*bits/32], scales / biases [K/group, N]
+            sets = []
+            for _ in range(copies):
+                w = torch.randint(-2 ** 31, 2 ** 31 - 1, (a.k, a.n * a.bits // 32), dtype=torch.int32, device=dev)
+                sc = (0.002 + 0.018 * torch.rand((a.k // a.group, a.n), device=dev)).to(dt)
+                sets.append((w, sc, (-8.0 * sc.float()).to(dt)))
+        else:
+            sets = [_weights((), a.n, a.k, a.bits, a.group, dt, dev) for _ in range(copies)]
         x = torch.randn((a.m, a.k), device=dev).to(dt)
         out = torch.empty((a.m, a.n), dtype=dt, device=dev)
-        op = ops.qmv if a.family == "qmv" else ops.qmm
+        op = {"qmv": ops.qmv, "qvm": ops.qvm, "qmm": ops.qmm}[a.family]
 
         def body():
             for w, sc, bi in sets:
