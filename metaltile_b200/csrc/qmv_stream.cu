@@ -149,6 +149,36 @@ __device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) { return i ==
 //   the odd fragments (j = 1, 3) hold x / 16: their codes arrive as 16 q (exact for bf16, whose staged values carry
 //   2^64; for f16 exact unless |x| < 2^-10, where the quotient is a subnormal f16: absolute error below 2^-25);
 //   xsum: sum of the 64 activations of (segment s, token m), unscaled, f32 - M = 1: xsum[s]; else xsum[s*8 + m], 0 for m >= M.
+// The 16 activations x[16t .. 16t + 15] of a segment as this lane's two fragment units, and their sum.
+template <bool BF16>
+__device__ __forceinline__ void stage_item(const uint4 &v0, const uint4 &v1, uint4 &f01, uint4 &f23, float &sum) {
+    const uint32_t u[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};   // word q holds (h[2q], h[2q+1])
+    uint32_t e[8], o[8];              // as staged for the even fragments; / 16 for the odd ones
+    sum = 0.0f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        if (BF16) {
+            const float lo = __uint_as_float(u[q] << 16), hi = __uint_as_float(u[q] & 0xFFFF0000u);
+            sum += lo + hi;
+            // times 2^64 (2^60): an exact change of exponent (inf beyond 2^63)
+            e[q] = (__float_as_uint(lo * 18446744073709551616.0f) >> 16) | (__float_as_uint(hi * 18446744073709551616.0f) & 0xFFFF0000u);
+            o[q] = (__float_as_uint(lo * 1152921504606846976.0f) >> 16) | (__float_as_uint(hi * 1152921504606846976.0f) & 0xFFFF0000u);
+        } else {
+            const __half2 h2 = *reinterpret_cast<const __half2 *>(&u[q]);
+            const float2 f = __half22float2(h2);
+            sum += f.x + f.y;
+            e[q] = u[q];
+            const __half2 sc = __hmul2(h2, __float2half2_rn(0.0625f));
+            o[q] = *reinterpret_cast<const uint32_t *>(&sc);
+        }
+    }
+    // fragment j: .x = (h[j], h[j+4]) of the first 8 values, .y = the same of the second 8
+    f01 = make_uint4(__byte_perm(e[0], e[2], 0x5410), __byte_perm(e[4], e[6], 0x5410), __byte_perm(o[0], o[2], 0x7632),
+                     __byte_perm(o[4], o[6], 0x7632));
+    f23 = make_uint4(__byte_perm(e[1], e[3], 0x5410), __byte_perm(e[5], e[7], 0x5410), __byte_perm(o[1], o[3], 0x7632),
+                     __byte_perm(o[5], o[7], 0x7632));
+}
+
 template <bool BF16, bool M1>
 __device__ __forceinline__ void stage_x(const void *x, int K, int M, unsigned char *sm, uint32_t off_xsum) {
     const int nseg = K >> 6;
@@ -167,41 +197,58 @@ __device__ __forceinline__ void stage_x(const void *x, int K, int M, unsigned ch
             if (on) {
                 const uint4 *p = reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(x) + static_cast<size_t>(m) * K +
                                                                  static_cast<size_t>(s) * 64 + 16 * t);
-                v0 = __ldg(p);        // x[16t + 0..7]: word q holds (h[2q], h[2q+1])
+                v0 = __ldg(p);        // x[16t + 0..7]
                 v1 = __ldg(p + 1);    // x[16t + 8..15]
             }
-            const uint32_t u[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-            uint32_t e[8], o[8];              // as staged for the even fragments; / 16 for the odd ones
-            float sum = 0.0f;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                if (BF16) {
-                    const float lo = __uint_as_float(u[q] << 16), hi = __uint_as_float(u[q] & 0xFFFF0000u);
-                    sum += lo + hi;
-                    // times 2^64 (2^60): an exact change of exponent (inf beyond 2^63)
-                    e[q] = (__float_as_uint(lo * 18446744073709551616.0f) >> 16) | (__float_as_uint(hi * 18446744073709551616.0f) & 0xFFFF0000u);
-                    o[q] = (__float_as_uint(lo * 1152921504606846976.0f) >> 16) | (__float_as_uint(hi * 1152921504606846976.0f) & 0xFFFF0000u);
-                } else {
-                    const __half2 h2 = *reinterpret_cast<const __half2 *>(&u[q]);
-                    const float2 f = __half22float2(h2);
-                    sum += f.x + f.y;
-                    e[q] = u[q];
-                    const __half2 sc = __hmul2(h2, __float2half2_rn(0.0625f));
-                    o[q] = *reinterpret_cast<const uint32_t *>(&sc);
-                }
-            }
+            uint4 f01, f23;
+            float sum;
+            stage_item<BF16>(v0, v1, f01, f23, sum);
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);
             sum += __shfl_xor_sync(0xffffffffu, sum, 2);
             if (on) {
-                // fragment j: .x = (h[j], h[j+4]) of the first 8 values, .y = the same of the second 8
-                const uint4 f01 = make_uint4(__byte_perm(e[0], e[2], 0x5410), __byte_perm(e[4], e[6], 0x5410),
-                                             __byte_perm(o[0], o[2], 0x7632), __byte_perm(o[4], o[6], 0x7632));
-                const uint4 f23 = make_uint4(__byte_perm(e[1], e[3], 0x5410), __byte_perm(e[5], e[7], 0x5410),
-                                             __byte_perm(o[1], o[3], 0x7632), __byte_perm(o[5], o[7], 0x7632));
                 const int unit = ((s * M + m) * 4 + t) * 2;
                 xb[unit + (m & 1)] = f01;
                 xb[unit + ((m & 1) ^ 1)] = f23;
                 if (t == 0) xsum[M1 ? s : s * 8 + m] = sum;
+            }
+        }
+    }
+}
+
+// One token, a warp stages only the segments [seg0, seg1) that its own runs read: no warp waits for another.  All of a
+// round's loads are issued before the first is converted.
+template <bool BF16>
+__device__ __forceinline__ void stage_x_warp(const void *x, int seg0, int seg1, unsigned char *sm, uint32_t off_xsum, int lane) {
+    float *xsum = reinterpret_cast<float *>(sm + off_xsum);
+    uint4 *xb = reinterpret_cast<uint4 *>(sm + kOffX);
+    const int t = lane & 3, nitems = (seg1 - seg0) * 4;
+    constexpr int U = 4;
+    for (int base = 0; base < nitems; base += 32 * U) {
+        uint4 v0[U], v1[U];
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+            const int it = base + 32 * i + lane;
+            v0[i] = v1[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (it < nitems) {
+                const uint4 *p = reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(x) + static_cast<size_t>(seg0 + (it >> 2)) * 64 + 16 * t);
+                v0[i] = __ldg(p);
+                v1[i] = __ldg(p + 1);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < U; ++i) {
+            const int it = base + 32 * i + lane;
+            if (base + 32 * i >= nitems) break;                              // warp-uniform
+            uint4 f01, f23;
+            float sum;
+            stage_item<BF16>(v0[i], v1[i], f01, f23, sum);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            if (it < nitems) {
+                const int s = seg0 + (it >> 2);
+                xb[(s * 4 + t) * 2] = f01;
+                xb[(s * 4 + t) * 2 + 1] = f23;
+                if (t == 0) xsum[s] = sum;
             }
         }
     }
@@ -495,8 +542,14 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_stream_kernel(const __grid_co
         }
         if (pc.w & F_STAGE) {
             __syncthreads();                                     // every warp is done with the previous activations
-            stage_x<BF16, M1>(I.x, I.K, I.M, sm, a.off_xsum);
-            __syncthreads();
+            if (M1 && (1 << I.ksh) == kNW) {
+                // the warps of a CTA split K eight ways: each stages what its own runs read and goes on alone
+                stage_x_warp<BF16>(I.x, ((warp * I.rpt) >> I.ksh) * kRunSegs, (((warp + 1) * I.rpt) >> I.ksh) * kRunSegs, sm, a.off_xsum, lane);
+                __syncwarp();
+            } else {
+                stage_x<BF16, M1>(I.x, I.K, I.M, sm, a.off_xsum);
+                __syncthreads();
+            }
         }
         const int M = M1 ? 1 : I.M, Mp = (M + 1) & ~1;
         const int ksh = I.ksh, KS = 1 << ksh, slots = kNW >> ksh, ks = warp & (KS - 1);
