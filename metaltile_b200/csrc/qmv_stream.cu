@@ -160,9 +160,9 @@ __device__ __forceinline__ void stage_item(const uint4 &v0, const uint4 &v1, uin
         if (BF16) {
             const float lo = __uint_as_float(u[q] << 16), hi = __uint_as_float(u[q] & 0xFFFF0000u);
             sum += lo + hi;
-            // times 2^64 (2^60): an exact change of exponent (inf beyond 2^63)
-            e[q] = (__float_as_uint(lo * 18446744073709551616.0f) >> 16) | (__float_as_uint(hi * 18446744073709551616.0f) & 0xFFFF0000u);
-            o[q] = (__float_as_uint(lo * 1152921504606846976.0f) >> 16) | (__float_as_uint(hi * 1152921504606846976.0f) & 0xFFFF0000u);
+            // times 2^64 (2^60) on both halves at once: an exact change of exponent, subnormals included (inf beyond 2^63)
+            asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(e[q]) : "r"(u[q]), "r"(0x5F805F80u));
+            asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(o[q]) : "r"(u[q]), "r"(0x5D805D80u));
         } else {
             const __half2 h2 = *reinterpret_cast<const __half2 *>(&u[q]);
             const float2 f = __half22float2(h2);

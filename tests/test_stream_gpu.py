@@ -96,6 +96,34 @@ def test_stream_is_exact_before_rounding(ctx):
     assert np.mean(got.float().cpu().numpy() == exp) > 0.99
 
 
+def bits_of(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+@pytest.mark.parametrize("m", [1, 3])
+def test_stream_staging_of_special_activations(ctx, m):
+    """The activations are staged times 2^64 (bf16): zeros of both signs, bf16 subnormals, tiny and large magnitudes must
+    come through exactly - the result is compared with the oracle on an x made of such values."""
+    import torch
+    from metaltile_b200 import ops
+    n, k = 64, 4096
+    w, s, b, x = dense_case(m, n, k, 4, 64, "bf16", seed=4)
+    special = np.array([0x0000, 0x8000, 0x0001, 0x8001, 0x007F, 0x0080, 0x8080, 0x0100, 0x1F80, 0x5D80, 0xDD80, 0x3F80],
+                       dtype=np.uint32)                       # +-0, smallest / largest subnormal, smallest normals, 2^-64, +-2^60, 1
+    bits = (special[np.arange(m * k) % len(special)] << 16).astype(np.uint32).reshape(m, k)
+    x = bits.view(np.float32).copy()
+    x[:, 7::13] = oracle.round_through(np.random.default_rng(5).standard_normal(x[:, 7::13].shape).astype(np.float32), oracle.BF16)
+    ref = oracle.qmm(w, s, b, x, m, n, k, 4, 64)
+    xd = torch.from_numpy((bits_of(x) >> 16).astype(np.int16)).cuda().view(torch.bfloat16)      # the exact bit patterns
+    got = ops.qmv(to_dev(w), to_dev(s, "bf16"), to_dev(b, "bf16"), xd, 4, 64, ctx=ctx)
+    torch.cuda.synchronize()
+    assert ctx.status_word() == 0
+    got = got.float().cpu().numpy()
+    assert np.all(np.isfinite(got)) and rel_err(got, ref) <= TOL["bf16"]
+    exp = oracle.round_through(ref, oracle.BF16)
+    assert np.mean(got == exp) > 0.98
+
+
 def test_stream_equals_the_cuda_core_kernel_within_rounding(ctx):
     import torch
     from metaltile_b200 import ops
