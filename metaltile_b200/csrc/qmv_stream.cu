@@ -541,7 +541,7 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_stream_kernel(const __grid_co
             if (ctl->abort) break;                               // uniform: every thread reads the flag after the barrier
         }
         if (pc.w & F_STAGE) {
-            __syncthreads();                                     // every warp is done with the previous activations
+            if (j > 0) __syncthreads();                          // every warp is done with the previous activations
             if (M1 && (1 << I.ksh) == kNW) {
                 // the warps of a CTA split K eight ways: each stages what its own runs read and goes on alone
                 stage_x_warp<BF16>(I.x, ((warp * I.rpt) >> I.ksh) * kRunSegs, (((warp + 1) * I.rpt) >> I.ksh) * kRunSegs, sm, a.off_xsum, lane);
@@ -626,8 +626,12 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_stream_kernel(const __grid_co
                 const int r0 = pc.y + tile * 16;
                 const int dt = BF16 ? MTC_BF16 : MTC_F16;
                 for (int idx = lane; idx < 16 * Mp; idx += 32) {
-                    float v = 0.0f;
-                    for (int q = 0; q < KS; ++q) v += first[q * 16 * Mp + idx];
+                    float pv[kNW];                               // all partial sums in flight, then added in warp order
+#pragma unroll
+                    for (int q = 0; q < kNW; ++q) pv[q] = q < KS ? first[q * 16 * Mp + idx] : 0.0f;
+                    float v = pv[0];
+#pragma unroll
+                    for (int q = 1; q < kNW; ++q) v += pv[q];
                     const int row = (idx * I.inv_mp) >> 16, tok = idx - row * Mp;      // idx / Mp for idx < 128
                     const int n = r0 + row;
                     if (tok < M && n < pc.z) {
