@@ -245,6 +245,14 @@ int mtc_peer_barrier(mtc_ctx *ctx, void *stream, void *const *peer_flags, int n_
  *   "qmm_wide"         a dense work item of the tensor-core kernel covers two 256-row token chunks (one dequantised
  *                      weight stage meets two activation chunks; same results): 0 never, 1 (default) when that saves
  *                      rounds of the grid (M > 256), 2 whenever M > 256
+ *   "qmm_ksplit"       0: a dense launch of the tensor-core kernel never cuts K into slices (default 1: with one token
+ *                      chunk (M <= 256) and weight-row tiles for less than half of the SMs, K is cut into up to 16
+ *                      slices that run as work items of their own; f32 partial sums in a context scratch block are
+ *                      added in slice order by a second kernel - deterministic, same products)
+ *   "qmv_small_m_tc"   2 <= M <= 16 on shapes the warp-level kernels do not take (other widths than 4-bit, group 32):
+ *                      1 (default) 9 <= M <= 16, and 5 <= M <= 8 on matrices of 32 Mi codes or more, run on the
+ *                      tensor-core kernel (f16 / bf16, K % 64 == 0, power-of-two group >= 32) instead of one FFMA per
+ *                      (code, token) on CUDA cores; 0 never; 2 whenever that kernel takes the shape
  *   "qmv_stream"       the streaming decode kernel (4-bit, f16 / bf16, K % 512 == 0, group 64 or 128, 16-byte aligned
  *                      pointers): 1 (default) takes M = 1; 2 takes every M <= 8 (slower than the register-ring kernel
  *                      there); 0 never.  mtc_qmv_batched fuses its projections into one launch where this kernel

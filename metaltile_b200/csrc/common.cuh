@@ -52,6 +52,10 @@ struct Ctx {
     size_t qvm_bytes = 0;
     void *d_norm = nullptr;        // mtc_rms_norm_qmv on shapes the fused kernel does not take: the normalised row (grow-only)
     size_t norm_bytes = 0;
+    void *d_ksplit = nullptr;      // tcgen05 qmm with K slices: the f32 partial sums of a launch (grow-only)
+    size_t ksplit_bytes = 0;
+    int qmm_ksplit = 1;            // option "qmm_ksplit": 0 = a dense launch with few weight-row tiles never cuts K into slices
+    int qmv_small_m_tc = 1;        // option "qmv_small_m_tc": 0 = M <= 16 never takes the tcgen05 kernel; 2 = whenever it supports the shape (M >= 2)
     void *d_flush = nullptr;       // mtc_measure with cold_l2: a block larger than L2 that a memset rewrites between timed launches
     size_t flush_bytes = 0;
     void *d_moe = nullptr;         // mtc_moe_experts: gate and up outputs (and permuted rows on the composed path) (grow-only)

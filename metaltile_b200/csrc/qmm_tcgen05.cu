@@ -80,6 +80,9 @@ struct QmmParams {
     int wide;                    // 1: a dense item covers up to 2 TN token rows: one dequantised W stage meets two X chunks, both
                                  //    accumulators belong to the item (the dequant work per flop halves; no epilogue overlap)
     int n_tiles;                 // dense: weight-row tiles
+    int ksplit;                  // dense, one token chunk: K slices per weight-row tile (each an item of its own); 1 = none
+    int kb_per;                  // k blocks per item (K / BK / ksplit)
+    float *partial;              // ksplit > 1: f32 partial sums [ksplit][M][N], added by ksplit_sum_kernel
     uint32_t idesc;
 };
 
@@ -355,10 +358,13 @@ __device__ __forceinline__ uint32_t sb_half(const uint4 &v, int j, int h, int gs
 struct Item {
     int n_tile, expert, row0, rows;
     int nc;                                 // token chunks of TN rows covered (1 or 2): one accumulator each
+    int kb0, ks;                            // first k block and index of the K slice (0, 0 unless the launch splits K)
 };
 
 __device__ __forceinline__ Item get_item(const QmmParams &p, int i) {
     Item it;
+    it.kb0 = 0;
+    it.ks = 0;
     if (p.items) {
         const int4 v = __ldg(p.items + i);
         it.n_tile = v.x; it.expert = v.y & 0xFFFFFF; it.row0 = v.z; it.rows = v.w;
@@ -379,7 +385,11 @@ __device__ __forceinline__ Item get_item(const QmmParams &p, int i) {
     } else {
         // dense: the token chunks of one weight-row tile are adjacent, so CTAs running at the same time share its
         // packed words in L2
-        const int unit = i / p.m_chunks, chunk = i - unit * p.m_chunks;
+        // K slices of one tile are adjacent items too
+        const int b = p.ksplit > 1 ? i / p.ksplit : i;
+        it.ks = i - b * (p.ksplit > 1 ? p.ksplit : 1);
+        it.kb0 = it.ks * p.kb_per;
+        const int unit = b / p.m_chunks, chunk = b - unit * p.m_chunks;
         it.nc = 1;
         it.expert = 0;
         it.n_tile = unit;
@@ -403,7 +413,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
     SmemCtrl *ctl = reinterpret_cast<SmemCtrl *>(smem + RING_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_kb = p.K / BK;
+    const int num_kb = p.kb_per;                           // k blocks per item
     const int num_items = p.items ? __ldg(p.item_count) : p.dense_items;
     const uint32_t x_bytes = static_cast<uint32_t>(p.TN) * BK * 2;
 
@@ -441,7 +451,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                     if (!(ok = mbar_wait(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x101, p.hint_ns))) break;
                     mbar_expect_tx(&ctl->full[s], x_bytes * item.nc);
                     for (int c = 0; c < item.nc; ++c)
-                        tma_load_2d(sX + s * x_slot + c * x_stage, &tmap_x, kb * BK, item.row0 + c * p.TN, &ctl->full[s]);
+                        tma_load_2d(sX + s * x_slot + c * x_stage, &tmap_x, (item.kb0 + kb) * BK, item.row0 + c * p.TN, &ctl->full[s]);
                     if (++s == nst) {
                         s = 0;
                         ph ^= 1;
@@ -528,7 +538,13 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                         ts[j] = (p.tok_scale && c0 + j < rows_h) ? __ldg(p.tok_scale + row_base + c0 + j) : 1.0f;
                     uint32_t v[16];
                     tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (buf + hh) * TN_MAX + c0, v);
-                    if (n_ok) {
+                    if (n_ok && p.ksplit > 1) {
+                        // a K slice: f32 partial sums, 128-byte segments per warp and token row
+                        float *o = p.partial + (static_cast<size_t>(item.ks) * p.M + row_base + c0) * p.N + n;
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (c0 + j < rows_h) o[static_cast<size_t>(j) * p.N] = __uint_as_float(v[j]) * ts[j];
+                    } else if (n_ok) {
                         // lanes of a warp hold 32 consecutive columns of the same output row: 64-byte segments
                         unsigned short hv[16];
 #pragma unroll
@@ -575,7 +591,8 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
             const int num_sb = num_kb / SB_PER_RAW;
             const int sb_bytes = (2 * SB_PER_RAW * BK) >> p.gs_shift;       // scale bytes of a row per super-block: 16, 8 or 4
             const int srow = t & (BMW - 1), sarr = t >> 7;                  // this thread copies scales (0) or biases (1) of a row
-            auto issue = [&](const Item &im, int sbk, int buf) {
+            auto issue = [&](const Item &im, int sb_rel, int buf) {
+                const int sbk = im.kb0 / SB_PER_RAW + sb_rel;                     // super-block of the row
                 const uint32_t dstt = raw0 + buf * buf_bytes;
                 const int n0 = im.n_tile * BMW;
                 const size_t erow = static_cast<size_t>(im.expert) * p.N;
@@ -677,13 +694,13 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                     bn = __ldg(bi16 + g);
                 }
             };
-            request(0);
+            request(item.kb0);
             for (int kb = 0; kb < num_kb; ++kb) {
                 uint32_t wcur[BITS];
 #pragma unroll
                 for (int j = 0; j < BITS; ++j) wcur[j] = wnext[j];
                 const uint32_t sr = sn, br = bn;
-                if (kb + 1 < num_kb) request(kb + 1);      // the next k block is requested before this one is converted
+                if (kb + 1 < num_kb) request(item.kb0 + kb + 1);      // the next k block is requested before this one is converted
                 // the stage is free once empty[s] has completed (the producer waits on the same barrier)
                 if (!(ok = mbar_wait_warp(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x401, 0))) break;
                 float sc, bi;
@@ -906,6 +923,9 @@ void fill_common(QmmParams &p, Ctx *ctx, const void *w, const void *scales, cons
     p.gpr = K / group_size;
     p.TN = TN;
     p.wide = 0;
+    p.ksplit = 1;
+    p.kb_per = K / BK;
+    p.partial = nullptr;
     plan_smem(p, ctx, bits);
     p.hint_ns = static_cast<uint32_t>(ctx->qmm_wait_hint_ns);
     const uint32_t fmt = p.op_f16 ? 0u : 1u;           // both operands carry the same 16-bit format
@@ -930,6 +950,19 @@ cudaError_t stage_x(Ctx *ctx, cudaStream_t st, const void *x, int rows, int K, i
     *x_op = y;
     *tok_scale = scale;
     return cudaSuccess;
+}
+
+// out[i] = sum over the K slices of partial[s][i], in slice order
+__global__ void __launch_bounds__(256) ksplit_sum_kernel(const float *partial, void *out, size_t mn, int S, int dt) {
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < mn; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float pv[16];
+#pragma unroll
+        for (int q = 0; q < 16; ++q) pv[q] = q < S ? partial[static_cast<size_t>(q) * mn + i] : 0.0f;
+        float v = pv[0];
+#pragma unroll
+        for (int q = 1; q < 16; ++q) v += pv[q];
+        st_from_f32(out, i, v, dt);
+    }
 }
 
 }  // namespace
@@ -1006,8 +1039,30 @@ cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const v
             }
         }
     }
+    // Few weight-row tiles and one token chunk: the tiles alone would leave most SMs idle, so K is cut into slices that
+    // run as items of their own (f32 partial sums, added in slice order by a second small kernel).
+    if (ctx->qmm_ksplit && !p.wide && p.m_chunks == 1 && !outs && 2 * p.n_tiles <= sms) {
+        const int nkb = K / BK, unit = p.raw ? SB_PER_RAW : 1;
+        int S = sms / p.n_tiles;
+        if (S > 16) S = 16;
+        while (S > 1 && (nkb % (S * unit) != 0 || nkb / S < 4)) --S;
+        if (S > 1) {
+            cudaError_t ge = grow_block(ctx, st, &ctx->d_ksplit, &ctx->ksplit_bytes, static_cast<size_t>(S) * M * N * sizeof(float), why);
+            if (ge != cudaSuccess) return ge;
+            p.ksplit = S;
+            p.kb_per = nkb / S;
+            p.partial = static_cast<float *>(ctx->d_ksplit);
+            p.dense_items *= S;
+        }
+    }
     const int grid = p.dense_items < sms ? p.dense_items : sms;
-    return launch_any(bits, st, tmap, p, grid);
+    e = launch_any(bits, st, tmap, p, grid);
+    if (e != cudaSuccess || p.ksplit == 1) return e;
+    const size_t mn = static_cast<size_t>(M) * N;
+    size_t sgrid = (mn + 255) / 256;
+    if (sgrid > static_cast<size_t>(sms) * 8) sgrid = static_cast<size_t>(sms) * 8;
+    ksplit_sum_kernel<<<static_cast<int>(sgrid), 256, 0, st>>>(p.partial, out, mn, p.ksplit, dt);
+    return cudaGetLastError();
 }
 
 // scratch bytes the gather work list needs for these sizes

@@ -281,6 +281,7 @@ int mtc_destroy(mtc_ctx *ctx) {
     if (ctx->d_qvm) cudaFree(ctx->d_qvm);
     if (ctx->d_tail) cudaFree(ctx->d_tail);
     if (ctx->d_flush) cudaFree(ctx->d_flush);
+    if (ctx->d_ksplit) cudaFree(ctx->d_ksplit);
     if (ctx->d_tc_scratch) cudaFree(ctx->d_tc_scratch);
     if (ctx->d_tc_counters) cudaFree(ctx->d_tc_counters);
     for (void *p : ctx->retired) cudaFree(p);
@@ -409,6 +410,25 @@ int mtc_status_clear(mtc_ctx *ctx) {
     return MTC_OK;
 }
 
+// 2 <= M <= 16 on a shape only the CUDA-core kernel would take otherwise: the tensor-memory qmm kernel is preferred when
+// option qmv_small_m_tc says so.
+// Measured on B200 (2 / 3 / 6 / 8-bit and group 32, bf16, square matrices of 2048 - 8192): the CUDA-core kernel costs one
+// FFMA per (code, token) in row tiles of 4, 8 or 16 tokens (4096 x 4096: 10-14 / 17-20 / 35-49 us; 8192 x 8192: 32-47 /
+// 84-139 / 125-186 us), the tensor-memory kernel with K slices ~12 / 21 / 54 us whatever the token count.
+static bool small_m_tc_rule(int mode, int M, int N, int K) {
+    if (!mode || M < 2 || M > 16) return false;
+    if (mode == 2) return true;
+    const long long codes = static_cast<long long>(N) * K;
+    if (M >= 9) return codes >= (2ll << 20);
+    if (M >= 5) return codes >= (32ll << 20);
+    return false;
+}
+
+static bool small_m_tc_preferred(mtc_ctx *ctx, int M, int N, int K, int bits, int group_size, int dtype, const void *w, const void *x,
+                                 const void *out) {
+    return small_m_tc_rule(ctx->qmv_small_m_tc, M, N, K) && mtc::qmm_tcgen05_supported(M, N, K, bits, group_size, dtype, w, x, out);
+}
+
 // The tcgen05 decode kernel, when it takes the shape: 0 = launched, 1 = not its shape, < 0 = error.
 static int try_qmv_tc(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const void *biases, const void *x,
                       void *const *outs, int n_outs, int M, int N, int K, int bits, int group_size, int dtype) {
@@ -449,6 +469,15 @@ int mtc_qmv(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
         cudaError_t e2 = mtc::launch_qmv_mma(ctx, static_cast<cudaStream_t>(stream), w, scales, biases, x, out, M, N, K,
                                              group_size, dtype);
         if (e2 != cudaSuccess) return fail(ctx, MTC_ERR_DISPATCH, std::string("qmv (mma) launch: ") + cudaGetErrorString(e2));
+        return MTC_OK;
+    }
+    if (small_m_tc_preferred(ctx, M, N, K, bits, group_size, dtype, w, x, out)) {
+        // a few token rows on a width or group the warp-level kernels do not take: one FFMA per (code, token) on CUDA
+        // cores against the tensor-memory kernel with K cut into slices
+        cudaError_t e3 = mtc::launch_qmm_tcgen05(ctx, static_cast<cudaStream_t>(stream), w, scales, biases, x, out, M, N, K, bits,
+                                                 group_size, dtype, &why);
+        if (e3 != cudaSuccess)
+            return fail(ctx, MTC_ERR_DISPATCH, "qmv (tcgen05 qmm) launch: " + (why.empty() ? std::string(cudaGetErrorString(e3)) : why));
         return MTC_OK;
     }
     cudaError_t e = mtc::launch_qmv(ctx, static_cast<cudaStream_t>(stream), w, scales, biases, x, out, M, N, K, bits,
@@ -674,6 +703,8 @@ const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dty
         return "qmm_tcgen05";
     // alignment is a run-time property of the pointers; the route names the kernel an aligned call gets
     if (mtc::qmv_mma_supported(M, N, K, bits, group_size, dtype, nullptr, nullptr)) return "qmv_mma_sync";
+    if (small_m_tc_rule(1, M, N, K) && mtc::qmm_tcgen05_supported(M, N, K, bits, group_size, dtype, nullptr, nullptr, nullptr))
+        return "qmm_tcgen05";     // a few token rows on a width or group the warp-level kernels do not take (option "qmv_small_m_tc")
     return "qmv_cuda_core";
 }
 
@@ -933,6 +964,14 @@ int mtc_set_option(mtc_ctx *ctx, const char *name, int value) {
     }
     if (std::strcmp(name, "qmm_wide") == 0) {
         ctx->qmm_wide = value < 0 ? 0 : (value > 2 ? 2 : value);
+        return MTC_OK;
+    }
+    if (std::strcmp(name, "qmm_ksplit") == 0) {
+        ctx->qmm_ksplit = value ? 1 : 0;
+        return MTC_OK;
+    }
+    if (std::strcmp(name, "qmv_small_m_tc") == 0) {
+        ctx->qmv_small_m_tc = value < 0 ? 0 : (value > 2 ? 2 : value);
         return MTC_OK;
     }
     return fail(ctx, MTC_ERR_UNSUPPORTED, std::string("unknown option: ") + name);

@@ -3,6 +3,7 @@
     python -m metaltile_b200.microbench qmv --m 1 --n 14336 --k 4096 --bits 4 --copies 8
     python -m metaltile_b200.microbench qmm --m 2048 --n 2304 --k 4096 --dtype bf16
     python -m metaltile_b200.microbench qvm --m 1 --n 4096 --k 14336 --bits 4 --copies 8
+    python -m metaltile_b200.microbench sweep --dtype bf16       # bits x group x M x K = N grid, one line per cell
     python -m metaltile_b200.microbench moe --tokens 512 --hidden 2048 --inter 768 --experts 128 --top-k 8
 
 `qmv` and `qvm` cycle through `--copies` independent weight sets so that consecutive launches do not find
@@ -41,7 +42,7 @@ def _timed(fn, reps, per):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("family", choices=["qmv", "qvm", "qmm", "moe"])
+    ap.add_argument("family", choices=["qmv", "qvm", "qmm", "moe", "sweep"])
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -65,7 +66,49 @@ def main(argv=None):
         ctx.set_option(name, int(value))
     dt = _DT[a.dtype]
 
-    if a.family in ("qmv", "qvm", "qmm"):
+    if a.family == "sweep":
+        # the sweep grid of the qmv family: every cell cycles enough weight copies to exceed L2 twice over
+        hbm = 6552.3
+        print("bits group M KN us GB/s frac_of_6552", flush=True)
+        for kn in (2048, 4096, 8192):
+            for bits in (2, 3, 4, 6, 8):
+                for group in (32, 64, 128):
+                    nbytes = kn * kn * bits // 8 + 2 * kn * (kn // group) * dt.itemsize
+                    copies = max(2, min(256, -(-2 * 132_000_000 // nbytes)))
+                    scale = 16.0 / 2 ** bits
+                    sets = []
+                    for _ in range(copies):
+                        w = torch.randint(-2 ** 31, 2 ** 31 - 1, (kn, kn * bits // 32), dtype=torch.int32, device=dev)
+                        sc = (scale * (0.002 + 0.018 * torch.rand((kn, kn // group), device=dev))).to(dt)
+                        sets.append((w, sc, (-(2 ** (bits - 1)) * sc.float()).to(dt)))
+                    for m in (1, 4, 8, 16):
+                        x = torch.randn((m, kn), device=dev).to(dt)
+                        out = torch.empty((m, kn), dtype=dt, device=dev)
+
+                        def body():
+                            for w, sc, bi in sets:
+                                ops.qmv(w, sc, bi, x, bits, group, out=out, ctx=ctx)
+
+                        body()
+                        torch.cuda.synchronize()
+                        graph = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(graph):
+                            body()
+                        graph.replay()
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        torch.cuda.synchronize()
+                        e0.record()
+                        for _ in range(a.reps):
+                            graph.replay()
+                        e1.record()
+                        torch.cuda.synchronize()
+                        us = e0.elapsed_time(e1) * 1e3 / (a.reps * copies)
+                        tot = nbytes + 2 * m * kn * dt.itemsize
+                        print(f"{bits} {group} {m} {kn} {us:.2f} {tot / us / 1e3:.0f} {tot / us / 1e3 / hbm:.3f}", flush=True)
+                        del graph
+                    del sets
+                    torch.cuda.empty_cache()
+    elif a.family in ("qmv", "qvm", "qmm"):
         copies = a.copies if a.family != "qmm" else 1
         if a.family == "qvm":                # transposed storage: w [K, N*bits/32], scales / biases [K/group, N]
             sets = []

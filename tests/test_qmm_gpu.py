@@ -31,8 +31,14 @@ def test_routing_follows_m_and_dtype(ctx):
     assert ctx.qmm_route(16, 4096, 4096, 4, 64, "bf16") == "qmv_mma_sync"
     assert ctx.qmm_route(9, 4096, 4096, 4, 128, "f16") == "qmv_mma_sync"
     assert ctx.qmm_route(2, 4096, 4160, 4, 64, "f16") == "qmv_mma_sync"           # K % 256 != 0: not the streaming kernel
-    assert ctx.qmm_route(16, 4096, 4096, 4, 32, "bf16") == "qmv_cuda_core"        # group < 64
-    assert ctx.qmm_route(16, 4096, 4096, 8, 64, "bf16") == "qmv_cuda_core"        # 4-bit codes only
+    # group < 64 or other widths: no warp-level kernel; 9..16 token rows (and 5..8 on large matrices) take the
+    # tensor-memory kernel with K slices, fewer stay on CUDA cores
+    assert ctx.qmm_route(16, 4096, 4096, 4, 32, "bf16") == "qmm_tcgen05"
+    assert ctx.qmm_route(16, 4096, 4096, 8, 64, "bf16") == "qmm_tcgen05"
+    assert ctx.qmm_route(8, 4096, 4096, 8, 64, "bf16") == "qmv_cuda_core"
+    assert ctx.qmm_route(8, 8192, 8192, 3, 64, "f16") == "qmm_tcgen05"
+    assert ctx.qmm_route(4, 8192, 8192, 8, 64, "bf16") == "qmv_cuda_core"
+    assert ctx.qmm_route(16, 512, 512, 8, 64, "bf16") == "qmv_cuda_core"          # too small to pay three launches
     assert ctx.qmm_route(16, 4096, 4096, 4, 64, "f32") == "qmv_cuda_core"
     assert ctx.qmm_route(17, 4096, 4096, 4, 64, "bf16") == "qmv_mma_sync"      # few rows: 16-row chunks of the small-M kernel
     assert ctx.qmm_route(64, 4096, 4096, 4, 64, "bf16") == "qmv_mma_sync"      # 32 weight tiles would fill a fifth of the SMs
@@ -259,3 +265,51 @@ def test_qmm_multi_writes_column_blocks_of_wider_matrices(ctx):
         ctx.qmm_multi(wd.data_ptr(), sd.data_ptr(), bd.data_ptr(), xd.data_ptr(), [dests[0].data_ptr()], ld, 8, n, k, bits, gs,
                       _TORCH_DT[xd.dtype], stream=st)
     assert ei.value.variant == "Unsupported"
+
+
+@pytest.mark.parametrize("m,n,k,bits,gs,dt", [
+    (16, 4096, 4096, 8, 64, "bf16"), (9, 2048, 2048, 3, 32, "f16"), (12, 1024, 4096, 6, 128, "bf16"), (16, 2048, 2048, 2, 64, "bf16"),
+    (40, 4096, 4096, 8, 64, "bf16"), (200, 1024, 8192, 5, 64, "f16"), (256, 640, 2048, 4, 32, "bf16"), (130, 288, 512, 6, 128, "bf16"),
+    (24, 1000, 1344, 8, 64, "f16"),                                # 21 k blocks, K % 256 != 0: three slices of 7 on the direct loader
+    (24, 1000, 1280, 8, 64, "f16"),                                # 20 k blocks: five slices of one super-block each
+])
+def test_k_slices_match_oracle_and_the_unsliced_kernel(ctx, m, n, k, bits, gs, dt):
+    """Few weight-row tiles and one token chunk: K is cut into slices that run as work items of their own, f32 partial
+    sums added in slice order by a second kernel.  Checked against the oracle and against the same kernel without slices
+    (option `qmm_ksplit` 0); M <= 16 reaches the kernel through mtc_qmv (option `qmv_small_m_tc`)."""
+    import torch
+    from metaltile_b200 import ops
+    w, s, b, x = dense_case(m, n, k, bits, gs, dt, seed=6, salt=m + n)
+    band = (n // 2, min(n, n // 2 + 64))
+    ref = oracle.qmm(w, s, b, x, m, n, k, bits, gs, rows=band)[:, band[0]:band[1]]
+    dev = [to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt)]
+    outs = {}
+    for ks in (1, 0):
+        ctx.set_option("qmm_ksplit", ks)
+        ctx.set_option("qmv_small_m_tc", 2)
+        ctx.set_option("qmm_mma_chunks", 0)
+        try:
+            got = (ops.qmv if m <= 16 else ops.qmm)(*dev, bits, gs, ctx=ctx)
+            torch.cuda.synchronize()
+        finally:
+            ctx.set_option("qmm_ksplit", 1)
+            ctx.set_option("qmv_small_m_tc", 1)
+            ctx.set_option("qmm_mma_chunks", 1)
+        outs[ks] = got.float().cpu().numpy()
+        assert ctx.status_word() == 0
+        assert rel_err(outs[ks][:, band[0]:band[1]], ref) <= TOL[dt], ks
+    # the same products, summed per slice first: equal up to the rounding of the output type
+    assert rel_err(outs[1], outs[0]) <= (2.0 ** -7 if dt == "bf16" else 2.0 ** -10)
+
+
+def test_small_m_default_route_is_within_tolerance(ctx):
+    """M = 16, 8-bit: the default route (tensor-memory kernel) through mtc_qmv against the oracle."""
+    import torch
+    from metaltile_b200 import ops
+    m, n, k = 16, 2048, 4096
+    assert ctx.qmm_route(m, n, k, 8, 64, "bf16") == "qmm_tcgen05"
+    w, s, b, x = dense_case(m, n, k, 8, 64, "bf16", seed=8)
+    got = ops.qmv(to_dev(w), to_dev(s, "bf16"), to_dev(b, "bf16"), to_dev(x, "bf16"), 8, 64, ctx=ctx)
+    torch.cuda.synchronize()
+    ref = oracle.qmm(w, s, b, x, m, n, k, 8, 64, rows=(512, 576))[:, 512:576]
+    assert rel_err(got.float().cpu().numpy()[:, 512:576], ref) <= TOL["bf16"] and ctx.status_word() == 0
