@@ -688,17 +688,19 @@ int mtc_peer_barrier(mtc_ctx *ctx, void *stream, void *const *peer_flags, int n_
 // 4096 x 4096: 54 us on 32 SMs).  The small-M tensor-core qmv in 16-row chunks streams the weights once per chunk
 // on every SM instead (2 x 9.3 us for that case).  Taken for M <= 32 always, up to 64 while the tcgen05 grid would
 // cover less than half of the SMs.
-static bool mma_chunks_preferred(int enabled, int sms, int M, int N, int K, int bits, int group_size, int dtype,
+// With K slices (option "qmm_ksplit") the tcgen05 kernel fills the SMs on exactly those shapes, and wins from M = 33 on
+// (4096 x 4096: 27 us against 30 / 34 / 42 us at M = 33 / 48 / 64), so the chunks keep 17 <= M <= 32 only.
+static bool mma_chunks_preferred(int enabled, int ksplit, int sms, int M, int N, int K, int bits, int group_size, int dtype,
                                  const void *w, const void *x) {
     if (!enabled || M <= 16 || M > 64) return false;
     if (!mtc::qmv_mma_supported(16, N, K, bits, group_size, dtype, w, x)) return false;
-    return M <= 32 || ((N + 127) / 128) * 2 <= sms;
+    return M <= 32 || (!ksplit && ((N + 127) / 128) * 2 <= sms);
 }
 
 const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dtype) {
     if (M == 1 && mtc::qmv_stream_supported(M, N, K, bits, group_size, dtype, nullptr, nullptr, nullptr, nullptr))
         return "qmv_stream";      // option "qmv_stream" = 2 extends it to M <= 8
-    if (mma_chunks_preferred(1, 148, M, N, K, bits, group_size, dtype, nullptr, nullptr)) return "qmv_mma_sync";
+    if (mma_chunks_preferred(1, 1, 148, M, N, K, bits, group_size, dtype, nullptr, nullptr)) return "qmv_mma_sync";
     if (M > 16 && mtc::qmm_tcgen05_supported(M, N, K, bits, group_size, dtype, nullptr, nullptr, nullptr))
         return "qmm_tcgen05";
     // alignment is a run-time property of the pointers; the route names the kernel an aligned call gets
@@ -714,7 +716,7 @@ int mtc_qmm(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
     MTC_ENTER(ctx);
     if (!dtype_ok(dtype)) return fail(ctx, MTC_ERR_UNSUPPORTED, "qmm: dtype must be f32, f16 or bf16");
     if (w && scales && biases && x && out &&
-        mma_chunks_preferred(ctx->qmm_mma_chunks && ctx->qmv_small_m_mma, ctx->sm_count, M, N, K, bits, group_size, dtype, w, x)) {
+        mma_chunks_preferred(ctx->qmm_mma_chunks && ctx->qmv_small_m_mma, ctx->qmm_ksplit, ctx->sm_count, M, N, K, bits, group_size, dtype, w, x)) {
         const size_t esz = 2;      // f16 / bf16 only on this path
         for (int m0 = 0; m0 < M; m0 += 16) {
             const int mc = M - m0 < 16 ? M - m0 : 16;

@@ -41,7 +41,8 @@ def test_routing_follows_m_and_dtype(ctx):
     assert ctx.qmm_route(16, 512, 512, 8, 64, "bf16") == "qmv_cuda_core"          # too small to pay three launches
     assert ctx.qmm_route(16, 4096, 4096, 4, 64, "f32") == "qmv_cuda_core"
     assert ctx.qmm_route(17, 4096, 4096, 4, 64, "bf16") == "qmv_mma_sync"      # few rows: 16-row chunks of the small-M kernel
-    assert ctx.qmm_route(64, 4096, 4096, 4, 64, "bf16") == "qmv_mma_sync"      # 32 weight tiles would fill a fifth of the SMs
+    assert ctx.qmm_route(32, 4096, 4096, 4, 64, "bf16") == "qmv_mma_sync"
+    assert ctx.qmm_route(64, 4096, 4096, 4, 64, "bf16") == "qmm_tcgen05"       # 32 weight tiles x 4 K slices fill the SMs
     assert ctx.qmm_route(64, 14336, 4096, 4, 64, "bf16") == "qmm_tcgen05"
     assert ctx.qmm_route(65, 4096, 4096, 4, 64, "bf16") == "qmm_tcgen05"
     assert ctx.qmm_route(17, 4096, 4096, 8, 64, "bf16") == "qmm_tcgen05"
@@ -82,12 +83,16 @@ def test_qmm_matches_oracle(ctx, m, n, k, bits, gs, dt):
 @pytest.mark.parametrize("m,n,k,gs,dt", [(17, 4096, 4096, 64, "bf16"), (32, 1000, 512, 128, "f16"), (50, 2048, 2048, 64, "bf16"),
                                          (64, 272, 1024, 64, "f16")])
 def test_few_rows_run_as_chunks_of_the_small_m_kernel(ctx, m, n, k, gs, dt):
-    """17 <= M <= 64 on a matrix too small to fill the GPU with 128-row tiles: 16-row chunks of the tensor-core qmv;
-    same oracle, and within round-off of the tcgen05 kernel."""
-    assert ctx.qmm_route(m, n, k, 4, gs, dt) == "qmv_mma_sync"
+    """17 <= M <= 32 (up to 64 when the tcgen05 kernel may not cut K into slices) on a matrix too small to fill the GPU
+    with 128-row tiles: 16-row chunks of the tensor-core qmv; same oracle, and within round-off of the tcgen05 kernel."""
+    assert ctx.qmm_route(m, n, k, 4, gs, dt) == ("qmv_mma_sync" if m <= 32 else "qmm_tcgen05")
     w, s, b, x = dense_case(m, n, k, 4, gs, dt, seed=16, salt=m)
     ref = oracle.qmm(w, s, b, x, m, n, k, 4, gs)
-    got = run_qmm(w, s, b, x, 4, gs, dt)
+    ctx.set_option("qmm_ksplit", 1 if m <= 32 else 0)
+    try:
+        got = run_qmm(w, s, b, x, 4, gs, dt)
+    finally:
+        ctx.set_option("qmm_ksplit", 1)
     assert got.shape == (m, n)
     assert rel_err(got, ref) <= TOL[dt]
     ctx.set_option("qmm_mma_chunks", 0)
