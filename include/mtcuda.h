@@ -254,8 +254,9 @@ int mtc_peer_barrier(mtc_ctx *ctx, void *stream, void *const *peer_flags, int n_
  *                      tensor-core kernel (f16 / bf16, K % 64 == 0, power-of-two group >= 32) instead of one FFMA per
  *                      (code, token) on CUDA cores; 0 never; 2 whenever that kernel takes the shape
  *   "qmv_stream"       the streaming decode kernel (4-bit, f16 / bf16, K % 512 == 0, group 64 or 128, 16-byte aligned
- *                      pointers): 1 (default) takes M = 1; 2 takes every M <= 8 (slower than the register-ring kernel
- *                      there); 0 never.  mtc_qmv_batched fuses its projections into one launch where this kernel
+ *                      pointers): 1 (default) takes M = 1 - a single projection from 8 Mi codes on (below that the
+ *                      CUDA-core kernel is faster), fused projections at any size; 2 takes every M <= 8 at any size
+ *                      (slower than the register-ring kernel at M >= 2); 0 never.  mtc_qmv_batched fuses its projections into one launch where this kernel
  *                      takes them and launches them one by one otherwise
  *   "qmv_tc"           1: those shapes run on the tensor-memory decode kernel instead (slower today; default 0)
  *   "gather_stream"    0: grouped products never take the weight-streaming kernel (default 1: the CSR form with

@@ -175,6 +175,12 @@ constexpr size_t kTcCounterBytes = 1u << 20;       // (tile, quarter) counters o
 // library; 2 = every M <= 8 it supports (at 2 <= M <= 8 the register-ring kernel of qmv_mma.cu is faster: measured
 // 13.3 against 21.7 us on 14336 x 4096 at M = 8); 0 = never.
 inline bool stream_takes(const Ctx *ctx, int M) { return ctx->qmv_stream == 2 ? M <= 8 : (ctx->qmv_stream == 1 && M == 1); }
+// A single projection on its own launch: below 8 Mi codes the CUDA-core kernel is the faster one (measured at M = 1:
+// 1024 x 4096 3.4 against 3.9 us, 2048 x 2048 2.8 against 3.8, 4096 x 4096 5.5 = 5.4, 14336 x 4096 12.5 against 10.7).
+constexpr long long kStreamMinCodes = 8ll << 20;
+inline bool stream_takes_single(const Ctx *ctx, int M, int N, int K) {
+    return stream_takes(ctx, M) && (ctx->qmv_stream == 2 || static_cast<long long>(N) * K >= kStreamMinCodes);
+}
 
 int ensure_tc_scratch(Ctx *ctx, size_t bytes, cudaStream_t st) {
     if (bytes <= ctx->tc_scratch_bytes) return MTC_OK;
@@ -455,7 +461,7 @@ int mtc_qmv(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
         const int t = try_qmv_tc(ctx, stream, w, scales, biases, x, outs1, 1, M, N, K, bits, group_size, dtype);
         if (t <= 0) return t;
     }
-    if (stream_takes(ctx, M) && mtc::qmv_stream_supported(M, N, K, bits, group_size, dtype, w, scales, biases, x)) {
+    if (stream_takes_single(ctx, M, N, K) && mtc::qmv_stream_supported(M, N, K, bits, group_size, dtype, w, scales, biases, x)) {
         mtc_qmv_desc d{};
         d.w = w; d.scales = scales; d.biases = biases; d.x = x;
         d.outs[0] = out; d.n_outs = 1;
@@ -698,8 +704,9 @@ static bool mma_chunks_preferred(int enabled, int ksplit, int sms, int M, int N,
 }
 
 const char *mtc_qmm_route(int M, int N, int K, int bits, int group_size, int dtype) {
-    if (M == 1 && mtc::qmv_stream_supported(M, N, K, bits, group_size, dtype, nullptr, nullptr, nullptr, nullptr))
-        return "qmv_stream";      // option "qmv_stream" = 2 extends it to M <= 8
+    if (M == 1 && static_cast<long long>(N) * K >= kStreamMinCodes &&
+        mtc::qmv_stream_supported(M, N, K, bits, group_size, dtype, nullptr, nullptr, nullptr, nullptr))
+        return "qmv_stream";      // option "qmv_stream" = 2 extends it to M <= 8 and to small matrices; fused launches take it at any size
     if (mma_chunks_preferred(1, 1, 148, M, N, K, bits, group_size, dtype, nullptr, nullptr)) return "qmv_mma_sync";
     if (M > 16 && mtc::qmm_tcgen05_supported(M, N, K, bits, group_size, dtype, nullptr, nullptr, nullptr))
         return "qmm_tcgen05";
