@@ -361,6 +361,7 @@ struct Item {
     int kb0, ks;                            // first k block and index of the K slice (0, 0 unless the launch splits K)
 };
 
+template <bool KSPLIT>
 __device__ __forceinline__ Item get_item(const QmmParams &p, int i) {
     Item it;
     it.kb0 = 0;
@@ -386,9 +387,11 @@ __device__ __forceinline__ Item get_item(const QmmParams &p, int i) {
         // dense: the token chunks of one weight-row tile are adjacent, so CTAs running at the same time share its
         // packed words in L2
         // K slices of one tile are adjacent items too
-        const int b = p.ksplit > 1 ? i / p.ksplit : i;
-        it.ks = i - b * (p.ksplit > 1 ? p.ksplit : 1);
-        it.kb0 = it.ks * p.kb_per;
+        const int b = KSPLIT ? i / p.ksplit : i;
+        if (KSPLIT) {
+            it.ks = i - b * p.ksplit;
+            it.kb0 = it.ks * p.kb_per;
+        }
         const int unit = b / p.m_chunks, chunk = b - unit * p.m_chunks;
         it.nc = 1;
         it.expert = 0;
@@ -399,7 +402,9 @@ __device__ __forceinline__ Item get_item(const QmmParams &p, int i) {
     return it;
 }
 
-template <int BITS>
+// KSPLIT: the launch cuts K into slices (items carry a first k block, the epilogue writes f32 partial sums); a
+// separate instantiation, so that the code of every other launch is what it was without the feature.
+template <int BITS, bool KSPLIT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -413,7 +418,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
     SmemCtrl *ctl = reinterpret_cast<SmemCtrl *>(smem + RING_BYTES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_kb = p.kb_per;                           // k blocks per item
+    const int num_kb = KSPLIT ? p.kb_per : p.K / BK;       // k blocks per item
     const int num_items = p.items ? __ldg(p.item_count) : p.dense_items;
     const uint32_t x_bytes = static_cast<uint32_t>(p.TN) * BK * 2;
 
@@ -446,12 +451,12 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
             uint32_t ph = 0;                              // stage and ring-pass parity, advanced without a division
             bool ok = true;
             for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x) {
-                const Item item = get_item(p, i);
+                const Item item = get_item<KSPLIT>(p, i);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!(ok = mbar_wait(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x101, p.hint_ns))) break;
                     mbar_expect_tx(&ctl->full[s], x_bytes * item.nc);
                     for (int c = 0; c < item.nc; ++c)
-                        tma_load_2d(sX + s * x_slot + c * x_stage, &tmap_x, (item.kb0 + kb) * BK, item.row0 + c * p.TN, &ctl->full[s]);
+                        tma_load_2d(sX + s * x_slot + c * x_stage, &tmap_x, ((KSPLIT ? item.kb0 : 0) + kb) * BK, item.row0 + c * p.TN, &ctl->full[s]);
                     if (++s == nst) {
                         s = 0;
                         ph ^= 1;
@@ -479,7 +484,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
             const uint64_t adesc0 = make_desc_sw128(smem_u32(sW)), bdesc0 = make_desc_sw128(smem_u32(sX));
             const uint32_t a_step = w_stage >> 4, b_step = x_slot >> 4;       // descriptor address units per stage
             for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x, ++tile_i) {
-                const Item item = get_item(p, i);
+                const Item item = get_item<KSPLIT>(p, i);
                 // wide items: both 256-column accumulators belong to one item (no double buffering);
                 // otherwise the two accumulators alternate so that the epilogue overlaps the next item
                 const bool both = p.wide != 0;
@@ -521,7 +526,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
             const bool both = p.wide != 0;
             const int buf = both ? 0 : (tile_i & 1);
             const uint32_t acc_ph = (both ? tile_i : (tile_i >> 1)) & 1;
-            const Item item = get_item(p, i);
+            const Item item = get_item<KSPLIT>(p, i);
             if (!(ok = mbar_wait_warp(&ctl->acc_full[buf], acc_ph, ctl, p.status, 0x301, p.hint_ns))) break;
             tc_fence_after();
             const int n = item.n_tile * BMW + q * 32 + lane;     // output column owned by this thread
@@ -538,7 +543,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                         ts[j] = (p.tok_scale && c0 + j < rows_h) ? __ldg(p.tok_scale + row_base + c0 + j) : 1.0f;
                     uint32_t v[16];
                     tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + (buf + hh) * TN_MAX + c0, v);
-                    if (n_ok && p.ksplit > 1) {
+                    if (KSPLIT && n_ok) {
                         // a K slice: f32 partial sums, 128-byte segments per warp and token row
                         float *o = p.partial + (static_cast<size_t>(item.ks) * p.M + row_base + c0) * p.N + n;
 #pragma unroll
@@ -592,7 +597,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
             const int sb_bytes = (2 * SB_PER_RAW * BK) >> p.gs_shift;       // scale bytes of a row per super-block: 16, 8 or 4
             const int srow = t & (BMW - 1), sarr = t >> 7;                  // this thread copies scales (0) or biases (1) of a row
             auto issue = [&](const Item &im, int sb_rel, int buf) {
-                const int sbk = im.kb0 / SB_PER_RAW + sb_rel;                     // super-block of the row
+                const int sbk = (KSPLIT ? im.kb0 / SB_PER_RAW : 0) + sb_rel;      // super-block of the row
                 const uint32_t dstt = raw0 + buf * buf_bytes;
                 const int n0 = im.n_tile * BMW;
                 const size_t erow = static_cast<size_t>(im.expert) * p.N;
@@ -615,13 +620,13 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
             int i_n = blockIdx.x, sb_n = 0;
             Item item_n{};
             if (i_n < num_items) {
-                item_n = get_item(p, i_n);
+                item_n = get_item<KSPLIT>(p, i_n);
                 issue(item_n, 0, 0);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
             uint32_t q = 0;
             for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x) {
-                const Item item = get_item(p, i);
+                const Item item = get_item<KSPLIT>(p, i);
                 for (int sbk = 0; sbk < num_sb && ok; ++sbk, ++q) {
                     const int buf = q & 1;
                     // this super-block has landed: my copies, then every warp's (which also says that every warp is
@@ -634,7 +639,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                     if (++sb_n == num_sb) {
                         sb_n = 0;
                         i_n += gridDim.x;
-                        if (i_n < num_items) item_n = get_item(p, i_n);
+                        if (i_n < num_items) item_n = get_item<KSPLIT>(p, i_n);
                     }
                     if (i_n < num_items) issue(item_n, sb_n, buf ^ 1);
                     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -677,7 +682,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         } else
         for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x) {
-            const Item item = get_item(p, i);
+            const Item item = get_item<KSPLIT>(p, i);
             const int n = item.n_tile * BMW + r;
             const bool valid = n < p.N;
             const size_t grow = static_cast<size_t>(item.expert) * p.N + (valid ? n : 0);
@@ -694,13 +699,14 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
                     bn = __ldg(bi16 + g);
                 }
             };
-            request(item.kb0);
+            const int kb0 = KSPLIT ? item.kb0 : 0;
+            request(kb0);
             for (int kb = 0; kb < num_kb; ++kb) {
                 uint32_t wcur[BITS];
 #pragma unroll
                 for (int j = 0; j < BITS; ++j) wcur[j] = wnext[j];
                 const uint32_t sr = sn, br = bn;
-                if (kb + 1 < num_kb) request(item.kb0 + kb + 1);      // the next k block is requested before this one is converted
+                if (kb + 1 < num_kb) request(kb0 + kb + 1);      // the next k block is requested before this one is converted
                 // the stage is free once empty[s] has completed (the producer waits on the same barrier)
                 if (!(ok = mbar_wait_warp(&ctl->empty[s], ph ^ 1, ctl, p.status, 0x401, 0))) break;
                 float sc, bi;
@@ -844,9 +850,17 @@ constexpr size_t qmm_smem_bytes() {
 
 template <int BITS>
 cudaError_t launch_bits(cudaStream_t st, const CUtensorMap &tmap, const QmmParams &p, int grid) {
-    auto kern = qmm_tcgen05_kernel<BITS>;
     constexpr size_t smem = qmm_smem_bytes<BITS>();
     static_assert(smem <= 227 * 1024, "shared memory per CTA");
+    if (p.ksplit > 1) {
+        auto kern = qmm_tcgen05_kernel<BITS, true>;
+        static PerDeviceAttr attr;
+        cudaError_t e = attr.set(kern, smem);
+        if (e != cudaSuccess) return e;
+        kern<<<grid, NUM_THREADS, smem, st>>>(tmap, p);
+        return cudaGetLastError();
+    }
+    auto kern = qmm_tcgen05_kernel<BITS, false>;
     static PerDeviceAttr attr;
     cudaError_t e = attr.set(kern, smem);
     if (e != cudaSuccess) return e;
