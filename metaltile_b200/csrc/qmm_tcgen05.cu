@@ -83,6 +83,9 @@ struct QmmParams {
     int ksplit;                  // dense, one token chunk: K slices per weight-row tile (each an item of its own); 1 = none
     int kb_per;                  // k blocks per item (K / BK / ksplit)
     float *partial;              // ksplit > 1: f32 partial sums [ksplit][M][N], added by ksplit_sum_kernel
+    int pdl_roles;               // programmatic dependent launch: 1 = only the roles that touch what an earlier kernel of the
+                                 //    stream may have written (producer: x; epilogue: token factors, out) wait for it, the
+                                 //    dequant warps start on the weights at once; 0 = every thread waits first
     uint32_t idesc;
 };
 
@@ -443,6 +446,8 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
+    asm volatile("griddepcontrol.launch_dependents;");
+    if (!p.pdl_roles) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         // ---------------- producer: TMA loads of the X chunk ----------------
@@ -450,6 +455,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
             int s = 0;
             uint32_t ph = 0;                              // stage and ring-pass parity, advanced without a division
             bool ok = true;
+            if (p.pdl_roles) asm volatile("griddepcontrol.wait;" ::: "memory");      // x may come from the previous kernel
             for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x) {
                 const Item item = get_item<KSPLIT>(p, i);
                 for (int kb = 0; kb < num_kb; ++kb) {
@@ -522,6 +528,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
         const int q = warp - EPI_WARP0;          // == warp % 4: the TMEM lane quarter this warp may read
         uint32_t tile_i = 0;
         bool ok = true;
+        if (p.pdl_roles) asm volatile("griddepcontrol.wait;" ::: "memory");          // token factors; nothing is stored before this
         for (int i = blockIdx.x; i < num_items && ok; i += gridDim.x, ++tile_i) {
             const bool both = p.wide != 0;
             const int buf = both ? 0 : (tile_i & 1);
@@ -743,6 +750,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const QmmParams p
 // operands, whose 3 extra mantissa bits keep the dequantised weights 8x closer to the f32 oracle than
 // bf16 weights would be; the epilogue multiplies the accumulator by 2^e again.
 __global__ void __launch_bounds__(256) rows_to_f16_kernel(const __nv_bfloat16 *x, __half *y, float *row_scale, int rows, int K) {
+    asm volatile("griddepcontrol.launch_dependents;");      // the product kernel may start on the weights meanwhile
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -852,20 +860,28 @@ template <int BITS>
 cudaError_t launch_bits(cudaStream_t st, const CUtensorMap &tmap, const QmmParams &p, int grid) {
     constexpr size_t smem = qmm_smem_bytes<BITS>();
     static_assert(smem <= 227 * 1024, "shared memory per CTA");
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute la[1];
+    la[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    la[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = la;
+    cfg.numAttrs = 1;
     if (p.ksplit > 1) {
         auto kern = qmm_tcgen05_kernel<BITS, true>;
         static PerDeviceAttr attr;
         cudaError_t e = attr.set(kern, smem);
         if (e != cudaSuccess) return e;
-        kern<<<grid, NUM_THREADS, smem, st>>>(tmap, p);
-        return cudaGetLastError();
+        return cudaLaunchKernelEx(&cfg, kern, tmap, p);
     }
     auto kern = qmm_tcgen05_kernel<BITS, false>;
     static PerDeviceAttr attr;
     cudaError_t e = attr.set(kern, smem);
     if (e != cudaSuccess) return e;
-    kern<<<grid, NUM_THREADS, smem, st>>>(tmap, p);
-    return cudaGetLastError();
+    return cudaLaunchKernelEx(&cfg, kern, tmap, p);
 }
 
 cudaError_t launch_any(int bits, cudaStream_t st, const CUtensorMap &tmap, const QmmParams &p, int grid) {
@@ -940,6 +956,7 @@ void fill_common(QmmParams &p, Ctx *ctx, const void *w, const void *scales, cons
     p.ksplit = 1;
     p.kb_per = K / BK;
     p.partial = nullptr;
+    p.pdl_roles = 0;               // the dense launcher turns it on: a gather launch reads a work list the previous kernel built
     plan_smem(p, ctx, bits);
     p.hint_ns = static_cast<uint32_t>(ctx->qmm_wait_hint_ns);
     const uint32_t fmt = p.op_f16 ? 0u : 1u;           // both operands carry the same 16-bit format
@@ -968,6 +985,7 @@ cudaError_t stage_x(Ctx *ctx, cudaStream_t st, const void *x, int rows, int K, i
 
 // out[i] = sum over the K slices of partial[s][i], in slice order
 __global__ void __launch_bounds__(256) ksplit_sum_kernel(const float *partial, void *out, size_t mn, int S, int dt) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");       // launched while the product kernel runs
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < mn; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
         float pv[16];
 #pragma unroll
@@ -1013,6 +1031,7 @@ cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const v
     p.M = M;
     p.m_chunks = (M + TN - 1) / TN;
     p.n_tiles = (N + BMW - 1) / BMW;
+    p.pdl_roles = ctx->pdl_early_weights ? 1 : 0;
     const int sms = ctx->sm_count;
     {
         // Two token chunks per item: the dequantised W stage, which sets the pace of a k block, is built once per
@@ -1075,8 +1094,16 @@ cudaError_t launch_qmm_tcgen05(Ctx *ctx, cudaStream_t st, const void *w, const v
     const size_t mn = static_cast<size_t>(M) * N;
     size_t sgrid = (mn + 255) / 256;
     if (sgrid > static_cast<size_t>(sms) * 8) sgrid = static_cast<size_t>(sms) * 8;
-    ksplit_sum_kernel<<<static_cast<int>(sgrid), 256, 0, st>>>(p.partial, out, mn, p.ksplit, dt);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(sgrid));
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute la[1];
+    la[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    la[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = la;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, ksplit_sum_kernel, static_cast<const float *>(p.partial), out, mn, p.ksplit, dt);
 }
 
 // scratch bytes the gather work list needs for these sizes
