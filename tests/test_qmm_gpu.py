@@ -318,3 +318,27 @@ def test_small_m_default_route_is_within_tolerance(ctx):
     torch.cuda.synchronize()
     ref = oracle.qmm(w, s, b, x, m, n, k, 8, 64, rows=(512, 576))[:, 512:576]
     assert rel_err(got.float().cpu().numpy()[:, 512:576], ref) <= TOL["bf16"] and ctx.status_word() == 0
+
+
+def test_k_slices_replay_from_a_cuda_graph(ctx):
+    """A launch that cuts K into slices (product kernel + sum kernel, linked by programmatic dependent launch) captured
+    in a CUDA graph after one eager run: every replay gives the eager result."""
+    import torch
+    from metaltile_b200 import ops
+    m, n, k, bits, gs, dt = 48, 1024, 4096, 8, 64, "bf16"
+    w, s, b, x = dense_case(m, n, k, bits, gs, dt, seed=12)
+    dev = [to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt)]
+    eager = ops.qmm(*dev, bits, gs, ctx=ctx).clone()
+    torch.cuda.synchronize()
+    out = torch.zeros_like(eager)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            ops.qmm(*dev, bits, gs, out=out, ctx=ctx)
+    for _ in range(3):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, eager)
+    assert ctx.status_word() == 0
