@@ -482,9 +482,11 @@ int mtc_qmv(mtc_ctx *ctx, void *stream, const void *w, const void *scales, const
         // cores against the tensor-memory kernel with K cut into slices
         cudaError_t e3 = mtc::launch_qmm_tcgen05(ctx, static_cast<cudaStream_t>(stream), w, scales, biases, x, out, M, N, K, bits,
                                                  group_size, dtype, &why);
-        if (e3 != cudaSuccess)
+        if (e3 == cudaSuccess) return MTC_OK;
+        // a scratch block would have to grow during stream capture: the CUDA-core kernel needs none
+        if (e3 != cudaErrorStreamCaptureUnsupported)
             return fail(ctx, MTC_ERR_DISPATCH, "qmv (tcgen05 qmm) launch: " + (why.empty() ? std::string(cudaGetErrorString(e3)) : why));
-        return MTC_OK;
+        why.clear();
     }
     cudaError_t e = mtc::launch_qmv(ctx, static_cast<cudaStream_t>(stream), w, scales, biases, x, out, M, N, K, bits,
                                     group_size, dtype, &why);

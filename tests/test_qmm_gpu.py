@@ -342,3 +342,26 @@ def test_k_slices_replay_from_a_cuda_graph(ctx):
         torch.cuda.synchronize()
         assert torch.equal(out, eager)
     assert ctx.status_word() == 0
+
+
+def test_small_m_capture_without_a_first_run_falls_back_to_cuda_cores():
+    """M = 16, 8-bit captured on a fresh context: the tensor-memory route would have to grow a scratch block during
+    capture, so mtc_qmv takes the CUDA-core kernel for that call instead of failing; the replay matches the oracle."""
+    import torch
+    from metaltile_b200 import Context
+    from metaltile_b200.ops import _TORCH_DT
+    fresh = Context(0)
+    m, n, k, bits, gs, dt = 16, 1024, 2048, 8, 64, "bf16"
+    w, s, b, x = dense_case(m, n, k, bits, gs, dt, seed=13)
+    wd, sd, bd, xd = to_dev(w), to_dev(s, dt), to_dev(b, dt), to_dev(x, dt)
+    out = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            fresh.qmv(wd.data_ptr(), sd.data_ptr(), bd.data_ptr(), xd.data_ptr(), out.data_ptr(), m, n, k, bits, gs,
+                      _TORCH_DT[xd.dtype], stream=torch.cuda.current_stream().cuda_stream)
+    graph.replay()
+    torch.cuda.synchronize()
+    ref = oracle.qmm(w, s, b, x, m, n, k, bits, gs)
+    assert rel_err(out.float().cpu().numpy(), ref) <= TOL[dt] and fresh.status_word() == 0
