@@ -9,7 +9,10 @@
 // affine part is applied per group on the f32 accumulators,
 //   acc += scale * (sum_k (OFF + q) x  -  OFF * sum_k x) + bias * sum_k x,
 // where OFF (128 for bf16, 1024 for f16) is the exponent trick that turns `(word >> 4j) & 0x000F000F | magic`
-// into two ready-made 16-bit floats OFF + q without any conversion instruction.
+// into two ready-made 16-bit floats OFF + q without any conversion instruction (qmv_mma_kernel).  The ring kernel
+// (qmv_mma_ring_kernel) goes one step further, as the streaming decode kernel does: the codes are the A operand as they
+// sit in the words - a 16-bit float with exponent field 0 is linear in its low bits - so a segment needs 16 LOP3 and
+// 4 shifts instead of 32 + 12, no OFF correction, and the activations are staged pre-scaled (stage_x_ring).
 //
 // Mapping.  A warp owns 16 weight rows; lane = 4*g + t holds rows g and g+8.  Per 64-code segment a lane
 // loads 8 bytes of each of its two rows (words 2t, 2t+1 of the segment), i.e. every byte of the packed
@@ -302,20 +305,29 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
 // Activations of the ring kernel: only the M real tokens are staged, so M = 1 keeps 32768 k values resident and
 // every practical K is staged once per CTA.  16-byte unit of (segment s, token m, quad-lane t, half h):
 //   ((s*M + m)*4 + t)*2 + (h ^ (m & 1));  half h holds the fragments j = 2h, 2h+1 of stage_x_mma's order.
-__device__ __forceinline__ void stage_x_ring(const MmaArgs &a, uint4 *xb, int seg0, int nseg) {
+// The fragments of the odd MMAs of a segment (j = 1, 3: the nibbles at bits 4-7, which enter the product as 16 q) hold
+// x / 16; bf16 activations are staged times 2^64 (2^60) so that products with the codes - read in place as bf16
+// subnormals q * 2^-133 - stay normal numbers; both changes of exponent are exact (f16: unless |x| < 2^-10, where the
+// quotient is a subnormal f16: absolute error below 2^-25).  xsum[s * Mp + m] = sum of the 64 unscaled activations of
+// (segment s, token m) in f32; tokens M .. Mp - 1 (padding) get 0.
+template <bool BF16>
+__device__ __forceinline__ void stage_x_ring(const MmaArgs &a, uint4 *xb, float *xsum, int Mp, int seg0, int nseg) {
     // thread -> quad-lane t (2 bits), token m (mb bits), segment = pass * s_step + (thread >> (2 + mb)): no division
     const int mb = a.M <= 1 ? 0 : a.M <= 2 ? 1 : a.M <= 4 ? 2 : a.M <= 8 ? 3 : 4;
     const int t = threadIdx.x & 3, m = (threadIdx.x >> 2) & ((1 << mb) - 1), s_first = threadIdx.x >> (2 + mb),
               s_step = blockDim.x >> (2 + mb);
-    if (m >= a.M) return;
+    if (m >= Mp) return;
+    const bool real = m < a.M;                                   // a padding token only zeroes its sums
+    const unsigned quad = 0xFu << (threadIdx.x & 28);            // the four lanes of a quad share (m, s) and stay together
     constexpr int U = 4;
-    const uint16_t *xrow = static_cast<const uint16_t *>(a.x) + static_cast<size_t>(m) * a.K + static_cast<size_t>(seg0) * 64 + 16 * t;
+    const uint16_t *xrow = static_cast<const uint16_t *>(a.x) + static_cast<size_t>(real ? m : 0) * a.K + static_cast<size_t>(seg0) * 64 + 16 * t;
     for (int s0 = s_first; s0 < nseg; s0 += s_step * U) {
         uint4 v0[U], v1[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int s = s0 + u * s_step;
-            if (s < nseg) {
+            v0[u] = v1[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (s < nseg && real) {
                 const uint4 *p = reinterpret_cast<const uint4 *>(xrow + static_cast<size_t>(s) * 64);
                 v0[u] = __ldg(p);
                 v1[u] = __ldg(p + 1);
@@ -325,10 +337,41 @@ __device__ __forceinline__ void stage_x_ring(const MmaArgs &a, uint4 *xb, int se
         for (int u = 0; u < U; ++u) {
             const int s = s0 + u * s_step;
             if (s >= nseg) break;
-            const uint4 f01 = make_uint4(__byte_perm(v0[u].x, v0[u].z, 0x5410), __byte_perm(v1[u].x, v1[u].z, 0x5410),
-                                         __byte_perm(v0[u].x, v0[u].z, 0x7632), __byte_perm(v1[u].x, v1[u].z, 0x7632));
-            const uint4 f23 = make_uint4(__byte_perm(v0[u].y, v0[u].w, 0x5410), __byte_perm(v1[u].y, v1[u].w, 0x5410),
-                                         __byte_perm(v0[u].y, v0[u].w, 0x7632), __byte_perm(v1[u].y, v1[u].w, 0x7632));
+            const uint32_t raw[8] = {v0[u].x, v0[u].y, v0[u].z, v0[u].w, v1[u].x, v1[u].y, v1[u].z, v1[u].w};
+            float sum = 0.0f;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                if (BF16) {
+                    sum += __uint_as_float(raw[q] << 16) + __uint_as_float(raw[q] & 0xFFFF0000u);
+                } else {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&raw[q]));
+                    sum += f.x + f.y;
+                }
+            }
+            sum += __shfl_xor_sync(quad, sum, 1);
+            sum += __shfl_xor_sync(quad, sum, 2);
+            if (t == 0) xsum[s * Mp + m] = sum;
+            if (!real) continue;
+            uint4 f01 = make_uint4(__byte_perm(v0[u].x, v0[u].z, 0x5410), __byte_perm(v1[u].x, v1[u].z, 0x5410),
+                                   __byte_perm(v0[u].x, v0[u].z, 0x7632), __byte_perm(v1[u].x, v1[u].z, 0x7632));
+            uint4 f23 = make_uint4(__byte_perm(v0[u].y, v0[u].w, 0x5410), __byte_perm(v1[u].y, v1[u].w, 0x5410),
+                                   __byte_perm(v0[u].y, v0[u].w, 0x7632), __byte_perm(v1[u].y, v1[u].w, 0x7632));
+            if (BF16) {
+                asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(f01.x) : "r"(0x5F805F80u));      // 2^64
+                asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(f01.y) : "r"(0x5F805F80u));
+                asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(f23.x) : "r"(0x5F805F80u));
+                asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(f23.y) : "r"(0x5F805F80u));
+                asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(f01.z) : "r"(0x5D805D80u));      // 2^60
+                asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(f01.w) : "r"(0x5D805D80u));
+                asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(f23.z) : "r"(0x5D805D80u));
+                asm("mul.rn.bf16x2 %0, %0, %1;" : "+r"(f23.w) : "r"(0x5D805D80u));
+            } else {
+                const __half2 sixteenth = __float2half2_rn(0.0625f);
+                *reinterpret_cast<__half2 *>(&f01.z) = __hmul2(*reinterpret_cast<__half2 *>(&f01.z), sixteenth);
+                *reinterpret_cast<__half2 *>(&f01.w) = __hmul2(*reinterpret_cast<__half2 *>(&f01.w), sixteenth);
+                *reinterpret_cast<__half2 *>(&f23.z) = __hmul2(*reinterpret_cast<__half2 *>(&f23.z), sixteenth);
+                *reinterpret_cast<__half2 *>(&f23.w) = __hmul2(*reinterpret_cast<__half2 *>(&f23.w), sixteenth);
+            }
             const int i = (s * a.M + m) * 4 + t;
             xb[i * 2 + (m & 1)] = f01;
             xb[i * 2 + ((m & 1) ^ 1)] = f23;
@@ -340,8 +383,6 @@ template <int NT, bool BF16, bool kFull /* M == 8 * NT: every lane has a token, 
           int GSH /* log2(group / 64): 0, 1 or 2 - a run of 8 segments holds 8, 4 or 2 groups per row */>
 __global__ void __launch_bounds__(kRingWarps * 32, 1) qmv_mma_ring_kernel(const MmaArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_mma[];
-    constexpr float off = BF16 ? 128.0f : 1024.0f;
-    constexpr uint32_t magic = BF16 ? 0x43004300u : 0x64006400u;
     uint4 *xb = reinterpret_cast<uint4 *>(smem_mma);
     unsigned char *ring_all = smem_mma + kStageBytes;                                   // [warps][2][kRunBytes]
     float *red = reinterpret_cast<float *>(ring_all + kRingWarps * 2 * kRunBytes);      // [warps][32][NT*4]
@@ -453,26 +494,7 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) qmv_mma_ring_kernel(const 
             if (it == 0 || nblocks > 1) {                // one block holding all of K is kept across tiles
                 const int nsb = min(block_segs, a.nseg - kb * block_segs);
                 __syncthreads();
-                stage_x_ring(a, xb, kb * block_segs, nsb);
-                __syncthreads();
-                // per-segment sums of the activations, once per block instead of once per row tile: a product
-                // with an A operand of ones leaves them in the accumulator layout (tokens 2t, 2t+1 in every row)
-                constexpr uint32_t one2 = BF16 ? 0x3F803F80u : 0x3C003C00u;
-                const uint32_t ones[4] = {one2, one2, one2, one2};
-                for (int sl = warp; sl < nsb; sl += kRingWarps) {
-                    uint4 bf[2][NT];
-                    load_frags(sl, bf);
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) {
-                        float sum[4];
-                        mma16816<BF16, true>(sum, ones, bf[0][nt].x, bf[0][nt].y);
-                        mma16816<BF16, false>(sum, ones, bf[0][nt].z, bf[0][nt].w);
-                        mma16816<BF16, false>(sum, ones, bf[1][nt].x, bf[1][nt].y);
-                        mma16816<BF16, false>(sum, ones, bf[1][nt].z, bf[1][nt].w);
-                        if (g == 0 && nt * 8 + 2 * t < Mp)
-                            *reinterpret_cast<float2 *>(xsum + sl * Mp + nt * 8 + 2 * t) = make_float2(sum[0], sum[1]);
-                    }
-                }
+                stage_x_ring<BF16>(a, xb, xsum, Mp, kb * block_segs, nsb);     // fragments and per-segment sums, once per block
                 __syncthreads();
             }
             if (!active) continue;
@@ -504,10 +526,14 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) qmv_mma_ring_kernel(const 
                         xs[nt][0] = v.x;
                         xs[nt][1] = v.y;
                     }
+                    // the codes are the A operand as they sit in the words: a 16-bit float with exponent field 0 is linear
+                    // in its low bits, so `word & 0x000F000F` is two operands q * c and `word & 0x00F000F0` two operands
+                    // 16 q * c (met by x / 16); one shift by 8 gives the other four nibbles
+                    const uint32_t wl[2][4] = {{cl.x, ch.x, cl.y, ch.y}, {cl.x >> 8, ch.x >> 8, cl.y >> 8, ch.y >> 8}};
 #define MTC_STEP(J, ZERO)                                                                                 \
     {                                                                                                     \
-        const uint32_t af[4] = {code_pair<J>(cl.x, magic), code_pair<J>(ch.x, magic), code_pair<J>(cl.y, magic), \
-                                code_pair<J>(ch.y, magic)};                                               \
+        constexpr uint32_t msk = ((J) & 1) ? 0x00F000F0u : 0x000F000Fu;                                   \
+        const uint32_t af[4] = {wl[(J) >> 1][0] & msk, wl[(J) >> 1][1] & msk, wl[(J) >> 1][2] & msk, wl[(J) >> 1][3] & msk}; \
         _Pragma("unroll") for (int nt = 0; nt < NT; ++nt) {                                               \
             const uint4 f = bf[(J) >> 1][nt];                                                             \
             mma16816<BF16, ZERO>(d[nt], af, ((J) & 1) ? f.z : f.x, ((J) & 1) ? f.w : f.y);                \
@@ -533,7 +559,11 @@ __global__ void __launch_bounds__(kRingWarps * 32, 1) qmv_mma_ring_kernel(const 
                         o_lo = (gi & 1) ? __high2float(h2) : __low2float(h2);
                         o_hi = (gi & 1) ? __high2float(h3) : __low2float(h3);
                     }
-                    const float b_lo = fmaf(-off, s_lo, o_lo), b_hi = fmaf(-off, s_hi, o_hi);
+                    // c * 2^(pre-scale) leaves with the scale: f16 codes are q * 2^-24; bf16 codes q * 2^-133 against x * 2^64
+                    constexpr float post = BF16 ? 5.9029581035870565e20f /* 2^69 */ : 16777216.0f /* 2^24 */;
+                    s_lo *= post;
+                    s_hi *= post;
+                    const float b_lo = o_lo, b_hi = o_hi;
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
                         acc[nt][0] = fmaf(s_lo, d[nt][0], fmaf(b_lo, xs[nt][0], acc[nt][0]));
