@@ -368,3 +368,26 @@ def test_rms_norm_qmv_typed(ctx, n, k, gs, dt):
     ref = oracle.rms_norm_qmv(w, s, b, x.reshape(-1), nw.reshape(-1), eps, n, k, 4, gs)
     assert ctx.status_word() == 0
     assert rel_err(got.float().cpu().numpy(), ref) <= TOL[dt]
+
+
+@pytest.mark.parametrize("m", [2, 5, 16])
+def test_small_m_tensor_core_path_special_activations(ctx, m):
+    """The ring kernel stages bf16 activations times 2^64 (and x / 16 for the nibbles at bits 4-7): zeros of both signs,
+    bf16 subnormals, tiny and large magnitudes must come through exactly."""
+    import torch
+    from metaltile_b200 import ops
+    n, k = 96, 4096
+    assert ctx.qmm_route(m, n, k, 4, 64, "bf16") == "qmv_mma_sync"
+    w, s, b, x = dense_case(m, n, k, 4, 64, "bf16", seed=14)
+    special = np.array([0x0000, 0x8000, 0x0001, 0x8001, 0x007F, 0x0080, 0x8080, 0x0100, 0x1F80, 0x5D80, 0xDD80, 0x3F80], dtype=np.uint32)
+    bits = (special[np.arange(m * k) % len(special)] << 16).astype(np.uint32).reshape(m, k)
+    x = bits.view(np.float32).copy()
+    x[:, 5::11] = oracle.round_through(np.random.default_rng(15).standard_normal(x[:, 5::11].shape).astype(np.float32), oracle.BF16)
+    ref = oracle.qmm(w, s, b, x, m, n, k, 4, 64)
+    xd = torch.from_numpy((np.ascontiguousarray(x).view(np.uint32) >> 16).astype(np.int16)).cuda().view(torch.bfloat16)
+    got = ops.qmv(to_dev(w), to_dev(s, "bf16"), to_dev(b, "bf16"), xd, 4, 64, ctx=ctx)
+    torch.cuda.synchronize()
+    got = got.float().cpu().numpy()
+    assert ctx.status_word() == 0 and np.all(np.isfinite(got))
+    assert rel_err(got, ref) <= TOL["bf16"]
+    assert np.mean(got == oracle.round_through(ref, oracle.BF16)) > 0.98
