@@ -12,7 +12,7 @@
 // into two ready-made 16-bit floats OFF + q without any conversion instruction (qmv_mma_kernel).  The ring kernel
 // (qmv_mma_ring_kernel) goes one step further, as the streaming decode kernel does: the codes are the A operand as they
 // sit in the words - a 16-bit float with exponent field 0 is linear in its low bits - so a segment needs 16 LOP3 and
-// 4 shifts instead of 32 + 12, no OFF correction, and the activations are staged pre-scaled (stage_x_ring).
+// 4 shifts instead of 16 + 12, no OFF correction, and the activations are staged pre-scaled (stage_x_ring).
 //
 // Mapping.  A warp owns 16 weight rows; lane = 4*g + t holds rows g and g+8.  Per 64-code segment a lane
 // loads 8 bytes of each of its two rows (words 2t, 2t+1 of the segment), i.e. every byte of the packed
