@@ -157,7 +157,7 @@ def spot_check(layers, xs, tiles, out_local, out_full, M, world, phase_cols):
     return ok
 
 
-def p2p_trial(ctx, dev, rank, world):
+def p2p_trial(ctx, dev, rank, world, stream_opt=1):
     """One small projection gathered through peer stores + barrier, compared with NCCL; every rank must agree."""
     import torch
     import torch.distributed as dist
@@ -177,7 +177,13 @@ def p2p_trial(ctx, dev, rank, world):
         for _ in range(2):
             peer.qmv_into(w, sc, bi, x, BITS, GROUP, rank * nl * 2, st)
             peer.barrier(st)
-        loc = ops.qmv(w, sc, bi, x, BITS, GROUP, ctx=ctx)
+        # the reference projection on the same kernel as the peer path (a single small projection would otherwise take
+        # the CUDA-core kernel, whose results differ in the last bit of some outputs)
+        ctx.set_option("qmv_stream", 2)
+        try:
+            loc = ops.qmv(w, sc, bi, x, BITS, GROUP, ctx=ctx)
+        finally:
+            ctx.set_option("qmv_stream", stream_opt)
         ref = torch.empty((world, nl), dtype=torch.bfloat16, device=dev)
         dist.all_gather_into_tensor(ref, loc)
         torch.cuda.synchronize()
@@ -299,7 +305,8 @@ def main():
     local_all = torch.empty(args.layers * M * cols_per_layer, dtype=torch.bfloat16, device=dev)
     p2p = gather and args.collective in ("p2p", "auto") and M == 1
     if p2p and args.collective == "auto":
-        p2p = p2p_trial(ctx, dev, rank, world)
+        p2p = p2p_trial(ctx, dev, rank, world,
+                        next((int(o.split("=")[1]) for o in args.option if o.startswith("qmv_stream=")), 1))
     config_collective = "p2p" if p2p else "nccl"
     peer = None
     if p2p:
@@ -455,6 +462,8 @@ def main():
         # the blocks the kernels' own stores assembled must equal an NCCL all-gather of the same projections
         dist.barrier()
         bad = 0
+        stream_opt = next((int(o.split("=")[1]) for o in args.option if o.startswith("qmv_stream=")), 1)
+        ctx.set_option("qmv_stream", 2)     # the reference shards on the kernel the peer path runs, whatever their size
         for li in (0, args.layers - 1):
             for ph in range(4):
                 c, col = phase_cols[ph], 0
@@ -466,6 +475,7 @@ def main():
                 ref = torch.empty((world * M, c), dtype=torch.bfloat16, device=dev)
                 dist.all_gather_into_tensor(ref, loc)
                 bad += int(not torch.equal(ref, out_full[li][ph]))
+        ctx.set_option("qmv_stream", stream_opt)
         torch.cuda.synchronize()
         print(f"[rank {rank}] p2p gather vs NCCL all-gather: {'identical' if bad == 0 else str(bad) + ' blocks differ'}; "
               f"status word {ctx.status_word():#x}", file=sys.stderr, flush=True)
